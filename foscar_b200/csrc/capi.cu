@@ -1,0 +1,131 @@
+// Host side of the C ABI for the decode path: argument checks, launch configuration, the
+// split planners (pure host arithmetic) and small queries.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "decode.cuh"
+
+using namespace fq;
+
+extern "C" const char* fq_version(void) { return "foscar_b200 0.1.0 (sm_100a)"; }
+
+extern "C" const char* fq_error_string(int code) {
+  switch (code) {
+    case 0: return "success";
+    case FQ_ERR_BAD_ARG: return "bad argument";
+    case FQ_ERR_UNSUPPORTED: return "unsupported configuration";
+    case FQ_ERR_TOO_LARGE: return "problem too large for one launch";
+    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown";
+  }
+}
+
+extern "C" int64_t fq_workspace_bytes(int32_t max_splits, int32_t batch, int32_t num_qo_heads,
+                                      int32_t head_dim) {
+  if (max_splits < 1 || batch < 1 || num_qo_heads < 1 || head_dim < 1) return FQ_ERR_BAD_ARG;
+  return 4ll * max_splits * batch * num_qo_heads * (head_dim + 2);
+}
+
+// Cost of running `base` units cut into s pieces each on `sms` CTAs (microseconds). Constants
+// are per 128-token tile of this library's kernel; the form (waves x (tiles + per-piece) +
+// merge) is the one the reference's planner uses (src/foscar/_sm100/scheduler.py:101-127).
+static double split_cost(long long base, int tiles, int s, int bits, int sms) {
+  const double t_tile = bits == 2 ? 0.085 : 0.13;  // us per 128-token tile per CTA
+  const double t_piece = 2.5, t_merge = 3.0;
+  const double waves = std::ceil(static_cast<double>(base) * s / sms);
+  return waves * (t_tile * std::ceil(static_cast<double>(tiles) / s) + t_piece) +
+         (s > 1 ? t_merge : 0.0);
+}
+
+extern "C" int fq_plan_splits(int32_t batch, int32_t num_kv_heads, int32_t head_tiles,
+                              int32_t max_kv_len, int32_t bits, int32_t head_dim,
+                              int32_t sm_count) {
+  (void)head_dim;
+  if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || sm_count < 1) return FQ_ERR_BAD_ARG;
+  if (bits != 2 && bits != 4) return FQ_ERR_BAD_ARG;
+  const long long base = static_cast<long long>(batch) * num_kv_heads * head_tiles;
+  const int tiles = std::max(1, (max_kv_len + TILE - 1) / TILE);
+  int best = 1;
+  double best_cost = split_cost(base, tiles, 1, bits, sm_count);
+  for (int s = 2; s <= 64; ++s) {
+    if (tiles / s < 4) break;  // at least 512 tokens per piece
+    const double c = split_cost(base, tiles, s, bits, sm_count);
+    if (c < best_cost - 1e-9) { best = s; best_cost = c; }
+  }
+  return best;
+}
+
+// Words an explicit list needs for `units` units on `num_ctas` CTAs (a cut adds one piece).
+static long long worklist_words(long long units, int num_ctas) {
+  const long long starts = (static_cast<long long>(num_ctas) + 1 + 7) / 8 * 8;
+  return WORK_WORDS + starts + WORK_WORDS * (units + num_ctas);
+}
+
+// Balanced plan: the units (request, KV head, head tile) are laid end to end, each weighing its
+// tile count plus a fixed per-piece overhead, and the line is cut into `num_ctas` equal
+// segments; a CTA's segment becomes its pieces, in line order. List layout (int32 words):
+// header {pieces, units, ctas, rows' word offset, 0...}, cta_start[ctas + 1] padded to 8 words,
+// then one row of 8 words per piece.
+extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t num_kv_heads,
+                                int32_t head_tiles, int32_t num_ctas, int32_t max_splits,
+                                int32_t* worklist, int32_t max_words, int32_t* split_counts) {
+  if (!seq_lens || !worklist || !split_counts) return FQ_ERR_BAD_ARG;
+  if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || num_ctas < 1 || max_splits < 1)
+    return FQ_ERR_BAD_ARG;
+  constexpr long long OVH = 8;  // per-piece overhead in tile units
+  const int upr = num_kv_heads * head_tiles;
+  const long long units = static_cast<long long>(batch) * upr;
+  if (worklist_words(units, num_ctas) > max_words) return FQ_ERR_TOO_LARGE;
+  auto tiles_of = [&](int b) -> long long {
+    return seq_lens[b] > 0 ? (static_cast<long long>(seq_lens[b]) + TILE - 1) / TILE : 0;
+  };
+  long long total = 0;
+  for (int b = 0; b < batch; ++b) total += (tiles_of(b) + OVH) * upr;
+  const long long seg = std::max<long long>(1, (total + num_ctas - 1) / num_ctas);
+  const int starts_words = (num_ctas + 1 + 7) / 8 * 8;
+  int32_t* cta_start = worklist + WORK_WORDS;
+  int32_t* rows = worklist + WORK_WORDS + starts_words;
+  std::memset(worklist, 0, sizeof(int32_t) * (WORK_WORDS + starts_words));
+  long long pos = 0;
+  int pieces_total = 0, next_cta = 0;
+  for (long long u = 0; u < units; ++u) {
+    const int b = static_cast<int>(u / upr), kvh = static_cast<int>(u % upr) / head_tiles,
+              ht = static_cast<int>(u % upr) % head_tiles;
+    const int tiles = static_cast<int>(tiles_of(b));
+    // tile t of this unit sits at line position start + t; a piece ends where its CTA's
+    // segment ends
+    const long long start = pos + OVH;
+    const int first_row = pieces_total;
+    int t0 = 0, pieces = 0;
+    do {
+      const int cta = static_cast<int>(std::min<long long>((start + t0) / seg, num_ctas - 1));
+      int t1 = tiles;
+      if (cta < num_ctas - 1 && start + tiles > (cta + 1) * seg)
+        t1 = static_cast<int>((cta + 1) * seg - start);
+      while (next_cta <= cta) cta_start[next_cta++] = pieces_total;
+      int32_t* row = rows + static_cast<long long>(WORK_WORDS) * pieces_total;
+      row[0] = b; row[1] = kvh; row[2] = ht; row[3] = t0; row[4] = t1; row[5] = pieces;
+      row[6] = 0; row[7] = 0;
+      ++pieces_total;
+      ++pieces;
+      t0 = t1;
+    } while (t0 < tiles);
+    if (pieces > max_splits) return FQ_ERR_TOO_LARGE;
+    if (pieces == 1) rows[static_cast<long long>(WORK_WORDS) * first_row + 5] = -1;
+    split_counts[u] = pieces;
+    pos += OVH + tiles;
+  }
+  while (next_cta <= num_ctas) cta_start[next_cta++] = pieces_total;
+  worklist[0] = pieces_total;
+  worklist[1] = static_cast<int32_t>(units);
+  worklist[2] = num_ctas;
+  worklist[3] = WORK_WORDS + starts_words;
+  return pieces_total;
+}
+
+extern "C" int64_t fq_worklist_words(int32_t batch, int32_t num_kv_heads, int32_t head_tiles,
+                                     int32_t num_ctas) {
+  if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || num_ctas < 1) return FQ_ERR_BAD_ARG;
+  return worklist_words(static_cast<long long>(batch) * num_kv_heads * head_tiles, num_ctas);
+}

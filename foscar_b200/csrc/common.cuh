@@ -1,0 +1,266 @@
+// Shared device helpers: pool-format arithmetic and sm_100a PTX wrappers (mbarrier, bulk async
+// copies, tcgen05 tensor-memory and MMA instructions). Every wait is bounded by a cycle budget:
+// when it runs out the waiter raises the CTA's abort flag and the caller's status word and
+// falls through, so a protocol error ends the kernel instead of hanging the GPU.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include "../../include/foscar_b200.h"
+
+namespace fq {
+
+constexpr int PAGE = FQ_PAGE_SIZE;
+
+// ---------------------------------------------------------------------------------------------
+// Pool format
+// ---------------------------------------------------------------------------------------------
+
+// Exponent bin of a page maximum (f32 bit pattern): lp = floor(log2(448/x)) = 135 - bin.
+__host__ __device__ inline uint32_t vmax_bucket(uint32_t bits) {
+  uint32_t m = bits & 0x7FFFFFFFu;
+  if (m > 0x7F800000u) m = 0x7F800000u;
+  return (m + 0x1FFFFFu) >> 23;
+}
+
+// Bit offset, inside a token row, of channel c: word c/W, field 2*(w%(W/2)) + w/(W/2).
+template <int BITS>
+__host__ __device__ inline int code_bit_offset(int c) {
+  constexpr int W = 32 / BITS;
+  const int within = c % W;
+  const int field = 2 * (within % (W / 2)) + within / (W / 2);
+  return (c / W) * 32 + BITS * field;
+}
+
+// The order in which byte-expansion of a packed row yields channels. A 32-bit word w expands to
+// BITS*... output words ((w >> (BITS*k)) & mask); byte j of output word k is field 4j+k (INT2)
+// or 2j+k (INT4). Position p of the expanded row therefore holds this channel.
+template <int BITS>
+__host__ __device__ inline int channel_of_expanded_pos(int p) {
+  if (BITS == 4) return p;
+  const int wi = p >> 4, k = (p >> 2) & 3, j = p & 3;
+  return 16 * wi + 2 * j + (k >> 1) + 8 * (k & 1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// PTX: shared addresses, mbarrier
+// ---------------------------------------------------------------------------------------------
+
+__device__ inline uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ inline void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ inline void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ inline void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ inline bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Cycle budget of one wait: about a second at B200 clocks.
+constexpr long long WAIT_BUDGET_CYCLES = 2000000000LL;
+
+// Wait for a barrier phase, bounded. `abort_flag` is a CTA-shared word: once any waiter has
+// given up every later wait returns at once, so the CTA drains in bounded time.
+__device__ inline void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                 int* status) {
+  if (mbar_try(bar, parity)) return;
+  const long long t0 = clock64();
+  int spins = 0;
+  while (!mbar_try(bar, parity)) {
+    if ((++spins & 31) == 0) {
+      if (*abort_flag) return;
+      if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
+        *abort_flag = 1;
+        if (status) atomicOr(status, FQ_STATUS_TIMEOUT);
+        return;
+      }
+    }
+  }
+}
+
+// Bounded wait that ignores the abort flag: used once, at exit, to let a CTA's own bulk copies
+// land before its shared memory is released.
+__device__ inline void mbar_wait_drain(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
+  while (!mbar_try(bar, parity)) {
+    if (clock64() - t0 > WAIT_BUDGET_CYCLES / 16) return;
+  }
+}
+
+__device__ inline void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+// Make generic-proxy shared-memory writes visible to the async proxy (TMA, tcgen05.mma).
+__device__ inline void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ inline void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// PTX: bulk async copy global -> shared, completing on an mbarrier
+// ---------------------------------------------------------------------------------------------
+
+__device__ inline void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// PTX: tcgen05 (tensor memory + 5th-generation tensor cores)
+// ---------------------------------------------------------------------------------------------
+
+// One full warp allocates `cols` (power of two >= 32) tensor-memory columns; the base address
+// lands in shared memory at `dst`.
+__device__ inline void tmem_alloc(uint32_t dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst),
+               "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ inline void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+__device__ inline void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ inline void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// Arrive on an mbarrier when every tcgen05 operation this thread issued so far has completed.
+__device__ inline void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+
+// Shared-memory matrix descriptor. `layout`: 0 none, 2 = 128-byte swizzle, 4 = 64B, 6 = 32B.
+__device__ inline uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                          uint32_t layout) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= 1ull << 46;  // descriptor version of sm_100
+  d |= static_cast<uint64_t>(layout & 7) << 61;
+  return d;
+}
+
+// Instruction descriptor of kind::f8f6f4 with E4M3 operands and an f32 accumulator.
+__host__ __device__ constexpr uint32_t make_idesc_e4m3(int m, int n, int a_mn_major,
+                                                       int b_mn_major) {
+  return (1u << 4)                                 // accumulator f32
+         | (0u << 7) | (0u << 10)                  // A, B = E4M3
+         | (static_cast<uint32_t>(a_mn_major) << 15) |
+         (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ inline void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ inline void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Tensor-memory loads/stores, shape 32x32b: lane i of the warp addresses TMEM lane
+// (taddr.lane + i) and N consecutive 32-bit columns.
+__device__ inline void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ inline void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+                 "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ inline void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ inline void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ inline void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(
+                   taddr),
+               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+               "r"(r[7])
+               : "memory");
+}
+__device__ inline void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Small numeric helpers
+// ---------------------------------------------------------------------------------------------
+
+// Two f32 -> packed E4M3 pair (RN, saturating): `lo` in the low byte, `hi` in the high byte.
+__device__ inline uint32_t f32x2_to_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// Packed E4M3 pair -> two f32 (low byte first).
+__device__ inline float2 e4m3x2_to_f32x2(uint32_t v) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(v)));
+  __half2 h = *reinterpret_cast<__half2*>(&h2);
+  return __half22float2(h);
+}
+__device__ inline float e4m3_to_f32(uint32_t byte) { return e4m3x2_to_f32x2(byte & 0xFF).x; }
+
+__device__ inline float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+}  // namespace fq

@@ -1,0 +1,751 @@
+// Paged GQA decode attention over packed INT2/INT4 KV, sm_100a.
+//
+// What it computes follows the reference decode's semantics (src/foscar/wrapper.py:1153-1171;
+// fold algebra src/foscar/_sm100/int_fold_decode.py:5-22, 378-434): codes are never
+// dequantized. For token t and query head h
+//     score = s_k[t] * (q_h . c_k[t]) + z_k[t] * sum(q_h)          (times sm_scale)
+//     out_h = ( sum_t w[t,h] c_v[t]  +  sum_t p~[t,h] z_v[t] ) / sum_t p[t,h]
+// with w = p * s_v * 2^lp stored as two E4M3 planes (hi + lo/16) and p~ = w / (s_v 2^lp).
+// The structure is this library's own:
+//
+//   warp 16      producer: per 128-token tile, bulk async copies (TMA engine) of the two pages'
+//                K codes, V codes and scale records into a deep shared-memory ring.
+//   warps 8-11   K expanders: thread t unpacks token t's codes to exact E4M3 bytes (code * 2^-9)
+//                and stores them straight into TENSOR MEMORY as the MMA's A operand (no
+//                shared-memory round trip for K).
+//   warps 12-15  V expanders: same unpack, written to a 128-byte-swizzled shared-memory stage.
+//   warp 17      MMA issuer (one thread): S[128 tok x 16] = C_K . Q^T  (A from tensor memory),
+//                O^T[128 ch x 16] = C_V^T . [P_hi | P_lo]  (A MN-major from shared memory).
+//   warps 0-3, 4-7  two consumer groups taking alternate tiles, each with its own running
+//                (m, l, O): thread t folds the scales into S row t, joins the group's column
+//                max, writes its P row; then thread d accumulates channel d of the tile's O.
+//                The two groups are merged once per work item.
+//
+// Every role walks the same list of work items, so the pipeline never drains between items.
+// Byte-expansion yields channels in a fixed permuted order; Q is loaded in that order and O is
+// stored through it, so no per-element fix-up exists anywhere.
+#include "decode.cuh"
+
+namespace fq {
+
+namespace {
+
+// barrier words: the ring's 2*ns first, then the fixed ones
+struct Bars {
+  uint32_t base;
+  int ns;
+  __device__ uint32_t at(int i) const { return base + 8u * i; }
+  __device__ uint32_t ring_full(int s) const { return at(s); }
+  __device__ uint32_t ring_empty(int s) const { return at(ns + s); }
+  __device__ uint32_t kop_full(int s) const { return at(2 * ns + s); }
+  __device__ uint32_t kop_empty(int s) const { return at(2 * ns + 2 + s); }
+  __device__ uint32_t vop_full(int s) const { return at(2 * ns + 4 + s); }
+  __device__ uint32_t vop_empty(int s) const { return at(2 * ns + 6 + s); }
+  __device__ uint32_t s_full(int wg, int s) const { return at(2 * ns + 8 + 2 * wg + s); }
+  __device__ uint32_t s_empty(int wg, int s) const { return at(2 * ns + 12 + 2 * wg + s); }
+  __device__ uint32_t p_full(int wg, int s) const { return at(2 * ns + 16 + 2 * wg + s); }
+  __device__ uint32_t p_empty(int wg, int s) const { return at(2 * ns + 20 + 2 * wg + s); }
+  __device__ uint32_t o_full(int wg, int s) const { return at(2 * ns + 24 + 2 * wg + s); }
+  __device__ uint32_t o_empty(int wg, int s) const { return at(2 * ns + 28 + 2 * wg + s); }
+  __device__ uint32_t q_full(int s) const { return at(2 * ns + 32 + s); }
+  __device__ uint32_t q_empty(int s) const { return at(2 * ns + 34 + s); }
+  __device__ int count() const { return 2 * ns + 36; }
+};
+
+// Tensor-memory column plan (f32 columns): K operand stages, then S and O buffers of 16.
+template <int D>
+struct TmemPlan {
+  static constexpr int KOP_COLS = D / 4;
+  static constexpr int KOP = 0;
+  static constexpr int S = K_STAGES * KOP_COLS;  // 4 buffers: [wg][2]
+  static constexpr int O = S + 4 * 16;           // 4 buffers: [wg][2]
+  static constexpr int USED = O + 4 * 16;
+  static constexpr int ALLOC = USED <= 128 ? 128 : (USED <= 256 ? 256 : 512);
+};
+
+// order-preserving float <-> int key for integer warp reductions
+__device__ inline int float_key(float x) {
+  const int b = __float_as_int(x);
+  return b ^ ((b >> 31) & 0x7FFFFFFF);
+}
+__device__ inline float key_float(int k) {
+  return __int_as_float(k ^ ((k >> 31) & 0x7FFFFFFF));
+}
+
+// Unpack this thread's token row (RB bytes at `src`) into exact operand bytes, one per code, in
+// expansion order: out[(32/BITS/4) * wi + k] = (w[wi] >> (BITS * k)) & mask.
+template <int BITS, int D>
+__device__ inline void expand_row(uint32_t src, uint32_t (&out)[D / 4]) {
+  constexpr int WORDS = D * BITS / 32;
+  constexpr uint32_t MASK = BITS == 2 ? 0x03030303u : 0x0F0F0F0Fu;
+  constexpr int PER = 8 / BITS;  // output words per input word
+#pragma unroll
+  for (int v = 0; v < WORDS / 4; ++v) {
+    uint32_t w[4];
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                 : "r"(src + 16 * v));
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int k = 0; k < PER; ++k) out[PER * (4 * v + i) + k] = (w[i] >> (BITS * k)) & MASK;
+  }
+}
+
+
+// Consumer role: one of two 128-thread groups; group `wg` takes the tiles whose running index
+// has parity `wg` and keeps its own (m, l, c, O), merged with the other group per work item.
+template <int BITS, int D, int GP>
+__device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* smem,
+                                              uint32_t smem0, uint32_t tmem, const Bars& bars,
+                                              volatile int* abort_flag, const ItemRange items) {
+  using SP = SmemPlan<BITS, D>;
+  using TP = TmemPlan<D>;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wg = warp >> 2, wq = warp & 3;
+  const int t = threadIdx.x & 127;  // token row in softmax, channel position in accumulation
+  const int NS = P.ring_stages;
+  int* status = P.a.status;
+  const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+  const uint32_t ring0 = smem0 + SP::RING_OFF;
+  float* red_max = reinterpret_cast<float*>(smem + SP::RED_OFF);          // [wg][buf][warp][8]
+  float* red_sum = reinterpret_cast<float*>(smem + SP::RED_OFF + 1024);   // [wg][warp][16]
+  constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+
+  // pool-wide P-scale exponent from the count table: lp = 135 - max(top nonzero bin, 27)
+  int lp;
+  {
+    int top = 0;
+    if (P.p.v_max_hist != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int bin = lane * 8 + i;
+        if (__ldg(P.p.v_max_hist + bin) != 0u) top = bin;
+      }
+    }
+    top = __reduce_max_sync(0xFFFFFFFFu, top);
+    lp = 135 - max(top, 27);
+  }
+  const float p2lp = exp2f(static_cast<float>(lp));
+  const float o_mul = exp2f(static_cast<float>(9 - lp));
+
+  int it = 0, ci = 0;
+  for (int wi = items.begin; wi < items.end; wi += items.step, ++ci) {
+    const WorkItem w = decode_item(P, wi);
+    float m[GP], l[GP], c[GP], oacc[GP], corr_pend[GP], qsum[GP], qs[GP];
+#pragma unroll
+    for (int h = 0; h < GP; ++h) {
+      m[h] = -INFINITY; l[h] = 0.f; c[h] = 0.f; oacc[h] = 0.f; corr_pend[h] = 1.f;
+      const int hl = w.ht * 8 + h;
+      float sum = 0.f, scale = 0.f;
+      if (hl < P.heads_per_kv && w.t1 > w.t0) {
+        const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
+        const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
+        const uint32_t qw = __ldg(reinterpret_cast<const uint32_t*>(
+            static_cast<const uint8_t*>(P.a.q) + row * D + 4 * lane));
+        const float2 a = e4m3x2_to_f32x2(qw & 0xFFFF), b2 = e4m3x2_to_f32x2(qw >> 16);
+        sum = (a.x + a.y) + (b2.x + b2.y);
+        scale = P.a.sm_scale * LOG2E;
+        if (P.a.q_descale != nullptr)
+          scale *= __ldg(P.a.q_descale + w.b * P.a.q_descale_stride_b +
+                         head * P.a.q_descale_stride_h);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+      qsum[h] = sum;
+      qs[h] = scale;
+    }
+    bool pending = false;
+    int pend_buf = 0, pend_ph = 0;
+
+    auto accumulate = [&]() {
+      mbar_wait(bars.o_full(wg, pend_buf), pend_ph, abort_flag, status);
+      tc_fence_after();
+      uint32_t r[16];
+      tmem_ld16(tmem + lane_base + TP::O + (2 * wg + pend_buf) * 16, r);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars.o_empty(wg, pend_buf));
+#pragma unroll
+      for (int h = 0; h < GP; ++h)
+        oacc[h] = oacc[h] * corr_pend[h] +
+                  (__uint_as_float(r[h]) + __uint_as_float(r[8 + h]) * 0.0625f);
+    };
+
+    for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
+      if ((it & 1) != wg) continue;
+      const int n = it >> 1, buf = n & 1, ph = (n >> 1) & 1;
+      const int s = it % NS;
+      // raw scores of token row t
+      mbar_wait(bars.s_full(wg, buf), ph, abort_flag, status);
+      tc_fence_after();
+      uint32_t raw[GP];
+      if constexpr (GP == 4) tmem_ld4(tmem + lane_base + TP::S + (2 * wg + buf) * 16, raw);
+      else tmem_ld8(tmem + lane_base + TP::S + (2 * wg + buf) * 16, raw);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars.s_empty(wg, buf));
+      // this token's records
+      mbar_wait(bars.ring_full(s), (it / NS) & 1, abort_flag, status);
+      float sk, zk, sv, zv;
+      asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                   : "=f"(sk), "=f"(zk), "=f"(sv), "=f"(zv)
+                   : "r"(ring0 + s * SP::STAGE + SP::S_OFF + t * 16));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars.ring_empty(s));
+      const bool valid = tt * TILE + t < w.len;
+      const float a_k = sk * 512.f;
+      float x[GP];
+      float* wmax = red_max + ((wg * 2 + buf) * 4 + wq) * 8;
+#pragma unroll
+      for (int h = 0; h < GP; ++h) {
+        x[h] = valid ? qs[h] * fmaf(a_k, __uint_as_float(raw[h]), zk * qsum[h]) : -INFINITY;
+        const int key = __reduce_max_sync(0xFFFFFFFFu, float_key(x[h]));
+        if (lane == 0) wmax[h] = key_float(key);
+      }
+      named_barrier(1 + wg, 128);
+      const float wsc = sv * p2lp;
+      const float inv = valid ? __fdividef(1.f, wsc) : 0.f;
+      float hi_f[GP], lo_f[GP], e[GP], corr[GP];
+      const float* gmax = red_max + (wg * 2 + buf) * 4 * 8;
+#pragma unroll
+      for (int h = 0; h < GP; ++h) {
+        const float tm = fmaxf(fmaxf(gmax[h], gmax[8 + h]), fmaxf(gmax[16 + h], gmax[24 + h]));
+        const float mn = fmaxf(m[h], tm);
+        corr[h] = m[h] == -INFINITY ? 0.f : fast_exp2(m[h] - mn);
+        m[h] = mn;
+        e[h] = valid ? fast_exp2(x[h] - mn) : 0.f;
+      }
+      uint32_t pw[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int h = 0; h < GP; h += 2) {
+        const float w0 = valid ? e[h] * wsc : 0.f, w1 = valid ? e[h + 1] * wsc : 0.f;
+        const uint32_t hi2 = f32x2_to_e4m3x2(w0, w1);
+        const float2 hf = e4m3x2_to_f32x2(hi2);
+        const uint32_t lo2 = f32x2_to_e4m3x2((w0 - hf.x) * 16.f, (w1 - hf.y) * 16.f);
+        const float2 lf = e4m3x2_to_f32x2(lo2);
+        hi_f[h] = hf.x; hi_f[h + 1] = hf.y;
+        lo_f[h] = lf.x; lo_f[h + 1] = lf.y;
+        pw[h >> 2] |= hi2 << (16 * ((h >> 1) & 1));
+        pw[2 + (h >> 2)] |= lo2 << (16 * ((h >> 1) & 1));
+      }
+#pragma unroll
+      for (int h = 0; h < GP; ++h) {
+        const float wq_ = hi_f[h] + lo_f[h] * 0.0625f;
+        const float pq = wq_ > 0.f ? wq_ * inv : e[h];
+        l[h] = l[h] * corr[h] + e[h];
+        c[h] = c[h] * corr[h] + (valid ? pq * zv : 0.f);
+      }
+      // the P row: bytes [hi_0..hi_7 | lo_0..lo_7]
+      mbar_wait(bars.p_empty(wg, buf), ph ^ 1, abort_flag, status);
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
+                       smem0 + SP::P_OFF + (2 * wg + buf) * SP::P_BYTES + t * 16),
+                   "r"(pw[0]), "r"(pw[1]), "r"(pw[2]), "r"(pw[3])
+                   : "memory");
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars.p_full(wg, buf));
+      // the previous tile's O, now that its MMA has had a tile's time to finish
+      if (pending) accumulate();
+#pragma unroll
+      for (int h = 0; h < GP; ++h) corr_pend[h] = corr[h];
+      pending = true; pend_buf = buf; pend_ph = ph;
+    }
+    if (pending) accumulate();
+
+    // ---- item epilogue: group sums, then the two groups' states merged by group 0
+    float* rs = red_sum + (wg * 4 + wq) * 16;
+#pragma unroll
+    for (int h = 0; h < GP; ++h) {
+      float ls = l[h], cs = c[h];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        ls += __shfl_xor_sync(0xFFFFFFFFu, ls, o);
+        cs += __shfl_xor_sync(0xFFFFFFFFu, cs, o);
+      }
+      if (lane == 0) { rs[h] = ls; rs[8 + h] = cs; }
+    }
+    named_barrier(1 + wg, 128);
+    const float* gs = red_sum + wg * 4 * 16;
+#pragma unroll
+    for (int h = 0; h < GP; ++h) {
+      l[h] = (gs[h] + gs[16 + h]) + (gs[32 + h] + gs[48 + h]);
+      c[h] = (gs[8 + h] + gs[24 + h]) + (gs[40 + h] + gs[56 + h]);
+    }
+    float* xo = reinterpret_cast<float*>(smem + SP::XCHG_OFF + (ci & 1) * SP::XCHG_BYTES);
+    float* xmeta = xo + TILE * 8;
+    if (wg == 1) {
+#pragma unroll
+      for (int h = 0; h < GP; ++h) xo[t * 8 + h] = oacc[h];
+      if (t == 0) {
+#pragma unroll
+        for (int h = 0; h < GP; ++h) { xmeta[h] = m[h]; xmeta[8 + h] = l[h]; xmeta[16 + h] = c[h]; }
+      }
+    }
+    named_barrier(3, 256);
+    if (wg == 0 && w.slot != -2) {
+      const int ch = channel_of_expanded_pos<BITS>(t);
+#pragma unroll
+      for (int h = 0; h < GP; ++h) {
+        const int hl = w.ht * 8 + h;
+        if (hl >= P.heads_per_kv) continue;
+        const float m1 = xmeta[h], l1 = xmeta[8 + h], c1 = xmeta[16 + h], o1 = xo[t * 8 + h];
+        const float M = fmaxf(m[h], m1);
+        const float f0 = m[h] == -INFINITY ? 0.f : exp2f(m[h] - M);
+        const float f1 = m1 == -INFINITY ? 0.f : exp2f(m1 - M);
+        const float L = l[h] * f0 + l1 * f1;
+        const float C = c[h] * f0 + c1 * f1;
+        const float O = (oacc[h] * f0 + o1 * f1) * o_mul + C;
+        const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
+        const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
+        if (w.slot < 0) {
+          const float val = L > 0.f ? O / L * P.a.o_scale : 0.f;
+          const long long idx = row * D + ch;
+          if (P.a.out_dtype == 0) static_cast<__nv_bfloat16*>(P.a.out)[idx] = __float2bfloat16_rn(val);
+          else if (P.a.out_dtype == 1) static_cast<__half*>(P.a.out)[idx] = __float2half_rn(val);
+          else static_cast<float*>(P.a.out)[idx] = val;
+          if (t == 0 && P.a.lse != nullptr)
+            P.a.lse[row] = L > 0.f ? (M + log2f(L)) * LN2 : -INFINITY;
+        } else {
+          const long long prow =
+              static_cast<long long>(w.slot) * P.a.batch * P.a.num_qo_heads + row;
+          P.a.o_partial[prow * D + ch] = O;
+          if (t == 0) { P.a.l_partial[prow] = L; P.a.m_partial[prow] = M; }
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+template <int BITS, int D, int GP>
+__global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeParams P) {
+  static_assert(D == 128, "this build tiles head_dim 128");
+  using SP = SmemPlan<BITS, D>;
+  using TP = TmemPlan<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* const smem = smem_raw + (smem0 - smem_u32(smem_raw));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int NS = P.ring_stages;
+  Bars bars{smem0 + SP::BAR_OFF, NS};
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SP::BAR_OFF + 1004);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SP::BAR_OFF + 1000);
+  int* status = P.a.status;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(bars.ring_full(s), 1);
+      mbar_init(bars.ring_empty(s), 12);  // 4 K-expander + 4 V-expander + 4 consumer warps
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bars.kop_full(s), 4);
+      mbar_init(bars.kop_empty(s), 1);
+      mbar_init(bars.vop_full(s), 4);
+      mbar_init(bars.vop_empty(s), 1);
+      mbar_init(bars.q_full(s), 4);
+      mbar_init(bars.q_empty(s), 1);
+      for (int wg = 0; wg < 2; ++wg) {
+        mbar_init(bars.s_full(wg, s), 1);
+        mbar_init(bars.s_empty(wg, s), 4);
+        mbar_init(bars.p_full(wg, s), 4);
+        mbar_init(bars.p_empty(wg, s), 1);
+        mbar_init(bars.o_full(wg, s), 1);
+        mbar_init(bars.o_empty(wg, s), 4);
+      }
+    }
+    fence_barrier_init();
+  }
+  if (warp == 17) tmem_alloc(smem_u32(tmem_slot), TP::ALLOC);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  const ItemRange items = item_range(P);
+  const uint32_t ring0 = smem0 + SP::RING_OFF;
+
+  if (warp == 16) {
+    // ------------------------------------------------------------------ producer
+    int it = 0;
+    for (int wi = items.begin; wi < items.end; wi += items.step) {
+      const WorkItem w = decode_item(P, wi);
+      const int npages = (w.len + PAGE - 1) / PAGE;
+      for (int t = w.t0; t < w.t1; ++t, ++it) {
+        const int s = it % NS;
+        mbar_wait(bars.ring_empty(s), ((it / NS) & 1) ^ 1, abort_flag, status);
+        if (lane == 0) {
+          int ids[2];
+          uint32_t bytes = 0;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int pg = 2 * t + j;
+            int id = -1;
+            if (pg < npages) {
+              const long long e = static_cast<long long>(w.table_off) + pg;
+              if (e >= 0 && e < P.a.table_len) id = __ldg(P.a.page_table + e);
+              if (id < 0 || id >= P.p.num_pages) {
+                id = -1;
+                if (status) atomicOr(status, FQ_STATUS_BAD_PAGE);
+              }
+            }
+            ids[j] = id;
+            if (id >= 0) bytes += 2 * SP::CODE_PAGE + SP::SCALE_PAGE;
+          }
+          const uint32_t full = bars.ring_full(s);
+          mbar_expect_tx(full, bytes);
+          const uint32_t dst = ring0 + s * SP::STAGE;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            if (ids[j] < 0) continue;
+            const long long blk = static_cast<long long>(ids[j]) * P.p.num_kv_heads + w.kvh;
+            bulk_g2s(dst + SP::K_OFF + j * SP::CODE_PAGE, P.p.k_codes + blk * SP::CODE_PAGE,
+                     SP::CODE_PAGE, full);
+            bulk_g2s(dst + SP::V_OFF + j * SP::CODE_PAGE, P.p.v_codes + blk * SP::CODE_PAGE,
+                     SP::CODE_PAGE, full);
+            bulk_g2s(dst + SP::S_OFF + j * SP::SCALE_PAGE,
+                     static_cast<const uint8_t*>(P.p.scales) + blk * SP::SCALE_PAGE,
+                     SP::SCALE_PAGE, full);
+          }
+        }
+        __syncwarp();
+      }
+    }
+    // drain: every copy this warp issued has landed once its stage's consumers released it
+    // or, for the last NS tiles, once the stage reports full.
+    for (int back = 0; back < NS && back < it; ++back) {
+      const int j = it - 1 - back;
+      mbar_wait_drain(bars.ring_full(j % NS), (j / NS) & 1);
+    }
+  } else if (warp == 17) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = make_idesc_e4m3(128, 16, 0, 0);
+      constexpr uint32_t IDESC_PV = make_idesc_e4m3(128, 16, 1, 1);
+      auto issue_pv = [&](int j) {
+        const int wg = j & 1, n = j >> 1, buf = n & 1, ph = (n >> 1) & 1;
+        const int vs = j % V_STAGES, vph = (j / V_STAGES) & 1;
+        mbar_wait(bars.vop_full(vs), vph, abort_flag, status);
+        mbar_wait(bars.p_full(wg, buf), ph, abort_flag, status);
+        mbar_wait(bars.o_empty(wg, buf), ph ^ 1, abort_flag, status);
+        tc_fence_after();
+        const uint32_t va = smem0 + SP::VOP_OFF + vs * SP::VOP_STAGE;
+        const uint32_t pa = smem0 + SP::P_OFF + (2 * wg + buf) * SP::P_BYTES;
+        const uint32_t od = tmem + TP::O + (2 * wg + buf) * 16;
+#pragma unroll
+        for (int k = 0; k < TILE / 32; ++k) {
+          const uint64_t ad = make_smem_desc(va + k * 32 * D, 16, 1024, 2);
+          const uint64_t bd = make_smem_desc(pa + k * 32 * 16, 128, 128, 0);
+          umma_ss(od, ad, bd, IDESC_PV, k > 0);
+        }
+        tc_commit(bars.o_full(wg, buf));
+        tc_commit(bars.vop_empty(vs));
+        tc_commit(bars.p_empty(wg, buf));
+      };
+      int it = 0, qi = 0;
+      for (int wi = items.begin; wi < items.end; wi += items.step) {
+        const WorkItem w = decode_item(P, wi);
+        if (w.t1 <= w.t0) continue;
+        const int qb = qi & 1;
+        mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status);
+        const uint32_t qa = smem0 + SP::Q_OFF + qb * SP::Q_BYTES;
+        for (int t = w.t0; t < w.t1; ++t, ++it) {
+          const int wg = it & 1, n = it >> 1, buf = n & 1, ph = (n >> 1) & 1;
+          const int ks = it % K_STAGES, kph = (it / K_STAGES) & 1;
+          mbar_wait(bars.kop_full(ks), kph, abort_flag, status);
+          mbar_wait(bars.s_empty(wg, buf), ph ^ 1, abort_flag, status);
+          tc_fence_after();
+          const uint32_t sd = tmem + TP::S + (2 * wg + buf) * 16;
+          const uint32_t ka = tmem + TP::KOP + ks * TP::KOP_COLS;
+#pragma unroll
+          for (int k = 0; k < D / 32; ++k) {
+            const uint64_t bd = make_smem_desc(qa + k * 32, 16, 1024, 2);
+            umma_ts(sd, ka + k * 8, bd, IDESC_S, k > 0);
+          }
+          tc_commit(bars.s_full(wg, buf));
+          tc_commit(bars.kop_empty(ks));
+          if (t == w.t1 - 1) tc_commit(bars.q_empty(qb));
+          if (it > 0) issue_pv(it - 1);
+        }
+        ++qi;
+      }
+      if (it > 0) issue_pv(it - 1);
+      // wait for the last MMAs before tensor memory is released
+      if (it > 0) {
+        const int j = it - 1, wg = j & 1, n = j >> 1;
+        mbar_wait(bars.o_full(wg, n & 1), (n >> 1) & 1, abort_flag, status);
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 8 && warp < 12) {
+    // ------------------------------------------------------------------ K expanders (+ Q)
+    const int t = threadIdx.x - 256;  // token row of the tile, = tensor-memory lane
+    const uint32_t lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;
+    int it = 0, qi = 0;
+    for (int wi = items.begin; wi < items.end; wi += items.step) {
+      const WorkItem w = decode_item(P, wi);
+      if (w.t1 <= w.t0) continue;
+      {  // this item's query rows, in expansion order, as the S MMA's B operand
+        const int qb = qi & 1;
+        mbar_wait(bars.q_empty(qb), ((qi >> 1) & 1) ^ 1, abort_flag, status);
+        const int r = t >> 3, c = t & 7;  // row (head), 16-byte chunk
+        uint4 v = make_uint4(0, 0, 0, 0);
+        const int hl = w.ht * 8 + r;  // head inside the KV head's group
+        if (r < 8 && hl < P.heads_per_kv) {
+          const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
+          const uint4 in = __ldg(reinterpret_cast<const uint4*>(
+              static_cast<const uint8_t*>(P.a.q) +
+              (static_cast<long long>(w.b) * P.a.num_qo_heads + head) * D + 16 * c));
+          if (BITS == 2) {
+            v.x = __byte_perm(in.x, in.y, 0x6420);
+            v.y = __byte_perm(in.z, in.w, 0x6420);
+            v.z = __byte_perm(in.x, in.y, 0x7531);
+            v.w = __byte_perm(in.z, in.w, 0x7531);
+          } else {
+            v = in;
+          }
+        }
+        *reinterpret_cast<uint4*>(smem + SP::Q_OFF + qb * SP::Q_BYTES + r * 128 +
+                                  ((c ^ (r & 7)) << 4)) = v;
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars.q_full(qb));
+        ++qi;
+      }
+      for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
+        const int s = it % NS, ks = it % K_STAGES;
+        mbar_wait(bars.ring_full(s), (it / NS) & 1, abort_flag, status);
+        uint32_t op[D / 4];
+        expand_row<BITS, D>(ring0 + s * SP::STAGE + SP::K_OFF + t * SP::RB, op);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars.ring_empty(s));
+        mbar_wait(bars.kop_empty(ks), ((it / K_STAGES) & 1) ^ 1, abort_flag, status);
+        tc_fence_after();
+        const uint32_t dst = tmem + lane_base + TP::KOP + ks * TP::KOP_COLS;
+#pragma unroll
+        for (int v = 0; v < D / 32; ++v) tmem_st8(dst + 8 * v, op + 8 * v);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars.kop_full(ks));
+      }
+    }
+  } else if (warp >= 12 && warp < 16) {
+    // ------------------------------------------------------------------ V expanders
+    const int t = threadIdx.x - 384;
+    int it = 0;
+    for (int wi = items.begin; wi < items.end; wi += items.step) {
+      const WorkItem w = decode_item(P, wi);
+      for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
+        const int s = it % NS, vs = it % V_STAGES;
+        mbar_wait(bars.ring_full(s), (it / NS) & 1, abort_flag, status);
+        uint32_t op[D / 4];
+        expand_row<BITS, D>(ring0 + s * SP::STAGE + SP::V_OFF + t * SP::RB, op);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars.ring_empty(s));
+        mbar_wait(bars.vop_empty(vs), ((it / V_STAGES) & 1) ^ 1, abort_flag, status);
+        const uint32_t row = smem0 + SP::VOP_OFF + vs * SP::VOP_STAGE + t * D;
+#pragma unroll
+        for (int c = 0; c < D / 16; ++c) {
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row + ((c ^ (t & 7)) << 4)),
+                       "r"(op[4 * c]), "r"(op[4 * c + 1]), "r"(op[4 * c + 2]), "r"(op[4 * c + 3])
+                       : "memory");
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars.vop_full(vs));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    consumer_role<BITS, D, GP>(P, smem, smem0, tmem, bars, abort_flag, items);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 17) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TP::ALLOC);
+  }
+}
+
+// Tensor-core self test (see foscar_b200.h): one tile of both contractions on given operands.
+__global__ void __launch_bounds__(128, 1)
+umma_selftest_kernel(int mode, const uint8_t* k_bytes, const uint8_t* q_bytes,
+                     const uint8_t* v_bytes, const uint8_t* p_bytes, float* s_out, float* o_out,
+                     int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* const smem = smem_raw + (smem0 - smem_u32(smem_raw));
+  constexpr int KOFF = 0, VOFF = 16384, QOFF = 32768, POFF = 34816, MISC = 36864;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + MISC + 16);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + MISC + 8);
+  const uint32_t bar = smem0 + MISC;
+  if (t == 0) {
+    *abort_flag = 0;
+    mbar_init(bar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) tmem_alloc(smem_u32(tmem_slot), 128);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t lane_base = static_cast<uint32_t>(32 * warp) << 16;
+  // operands: K row t (128 bytes), V row t, P row t, Q chunk
+  uint32_t kr[32];
+  for (int i = 0; i < 32; ++i) kr[i] = reinterpret_cast<const uint32_t*>(k_bytes + t * 128)[i];
+  if (mode == 0) {
+    for (int v = 0; v < 4; ++v) tmem_st8(tmem + lane_base + 8 * v, kr + 8 * v);
+    tmem_st_wait();
+  } else {
+    for (int c = 0; c < 8; ++c)
+      *reinterpret_cast<uint4*>(smem + KOFF + t * 128 + ((c ^ (t & 7)) << 4)) =
+          make_uint4(kr[4 * c], kr[4 * c + 1], kr[4 * c + 2], kr[4 * c + 3]);
+  }
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<uint4*>(smem + VOFF + t * 128 + ((c ^ (t & 7)) << 4)) =
+        reinterpret_cast<const uint4*>(v_bytes + t * 128)[c];
+  *reinterpret_cast<uint4*>(smem + POFF + t * 16) = reinterpret_cast<const uint4*>(p_bytes)[t];
+  {
+    const int r = t >> 3, c = t & 7;
+    *reinterpret_cast<uint4*>(smem + QOFF + r * 128 + ((c ^ (r & 7)) << 4)) =
+        reinterpret_cast<const uint4*>(q_bytes + r * 128)[c];
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  if (t == 0) {
+    tc_fence_after();
+    constexpr uint32_t IDESC_S = make_idesc_e4m3(128, 16, 0, 0);
+    constexpr uint32_t IDESC_PV = make_idesc_e4m3(128, 16, 1, 1);
+    for (int k = 0; k < 4; ++k) {
+      const uint64_t bd = make_smem_desc(smem0 + QOFF + k * 32, 16, 1024, 2);
+      if (mode == 0) {
+        umma_ts(tmem + 32, tmem + k * 8, bd, IDESC_S, k > 0);
+      } else {
+        const uint64_t ad = make_smem_desc(smem0 + KOFF + k * 32, 16, 1024, 2);
+        umma_ss(tmem + 32, ad, bd, IDESC_S, k > 0);
+      }
+    }
+    for (int k = 0; k < 4; ++k) {
+      const uint64_t ad = make_smem_desc(smem0 + VOFF + k * 4096, 16, 1024, 2);
+      const uint64_t bd = make_smem_desc(smem0 + POFF + k * 512, 128, 128, 0);
+      umma_ss(tmem + 48, ad, bd, IDESC_PV, k > 0);
+    }
+    tc_commit(bar);
+  }
+  mbar_wait(bar, 0, abort_flag, status);
+  tc_fence_after();
+  uint32_t r16[16];
+  tmem_ld16(tmem + lane_base + 32, r16);
+  tmem_ld_wait();
+  for (int i = 0; i < 16; ++i) s_out[t * 16 + i] = __uint_as_float(r16[i]);
+  tmem_ld16(tmem + lane_base + 48, r16);
+  tmem_ld_wait();
+  for (int i = 0; i < 16; ++i) o_out[t * 16 + i] = __uint_as_float(r16[i]);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 128);
+  }
+}
+
+}  // namespace fq
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+#include <algorithm>
+
+namespace fq {
+
+static int device_sm_count() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 148;
+  return sms > 0 ? sms : 148;
+}
+
+template <int BITS, int D, int GP>
+static int launch_decode(DecodeParams& P, cudaStream_t stream) {
+  using SP = SmemPlan<BITS, D>;
+  int stages = SP::max_ring_stages();
+  if (stages > 20) stages = 20;
+  if (stages < 2) return FQ_ERR_UNSUPPORTED;
+  P.ring_stages = stages;
+  const int smem = SP::RING_OFF + stages * SP::STAGE + 1024;
+  static bool configured[64] = {};  // per (BITS, D, GP) instantiation and device
+  auto kernel = decode_kernel<BITS, D, GP>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_LIMIT);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  int ctas = P.a.max_ctas > 0 ? P.a.max_ctas : device_sm_count();
+  int grid = P.a.worklist ? ctas : std::min(ctas, P.num_items);
+  if (grid < 1) grid = 1;
+  kernel<<<grid, DECODE_THREADS, smem, stream>>>(P);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace fq
+
+
+using namespace fq;
+
+extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void* stream) {
+  if (!pools || !args) return FQ_ERR_BAD_ARG;
+  if (!pools->k_codes || !pools->v_codes || !pools->scales) return FQ_ERR_BAD_ARG;
+  if (pools->k_groups != 1 || pools->scale_bf16) return FQ_ERR_UNSUPPORTED;
+  if (pools->head_dim != 128) return FQ_ERR_UNSUPPORTED;
+  if (pools->bits != 2 && pools->bits != 4) return FQ_ERR_UNSUPPORTED;
+  const fq_decode_args& a = *args;
+  if (a.batch <= 0 || a.num_qo_heads <= 0 || a.num_qo_heads % pools->num_kv_heads) return FQ_ERR_BAD_ARG;
+  if (!a.seq_lens || !a.page_table || !a.table_offsets || !a.q || !a.out) return FQ_ERR_BAD_ARG;
+  if (a.out_dtype < 0 || a.out_dtype > 2) return FQ_ERR_BAD_ARG;
+  DecodeParams P{};
+  P.p = *pools;
+  P.a = a;
+  P.heads_per_kv = a.num_qo_heads / pools->num_kv_heads;
+  P.head_tiles = (P.heads_per_kv + 7) / 8;
+  const long long units = static_cast<long long>(a.batch) * pools->num_kv_heads * P.head_tiles;
+  if (a.worklist) {
+    if (a.num_work <= 0 || a.max_splits < 1) return FQ_ERR_BAD_ARG;
+    if (!a.o_partial || !a.l_partial || !a.m_partial) return FQ_ERR_BAD_ARG;
+    P.num_items = a.num_work;  // capacity; the live row count is read from the list's header
+  } else {
+    if (a.kv_splits < 1) return FQ_ERR_BAD_ARG;
+    if (a.kv_splits > 1 && (!a.o_partial || !a.l_partial || !a.m_partial ||
+                            a.kv_splits > a.max_splits))
+      return FQ_ERR_BAD_ARG;
+    if (units * a.kv_splits > 0x7FFFFFFFLL) return FQ_ERR_TOO_LARGE;
+    P.num_items = static_cast<int>(units * a.kv_splits);
+  }
+  const int gp = std::min(P.heads_per_kv, 8) <= 4 ? 4 : 8;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pools->bits == 2) return gp == 4 ? launch_decode<2, 128, 4>(P, s) : launch_decode<2, 128, 8>(P, s);
+  return gp == 4 ? launch_decode<4, 128, 4>(P, s) : launch_decode<4, 128, 8>(P, s);
+}
+
+extern "C" int fq_umma_selftest(int32_t mode, const uint8_t* k_bytes, const uint8_t* q_bytes,
+                                const uint8_t* v_bytes, const uint8_t* p_bytes, float* s_out,
+                                float* o_out, int32_t* status, void* stream) {
+  if (!k_bytes || !q_bytes || !v_bytes || !p_bytes || !s_out || !o_out) return FQ_ERR_BAD_ARG;
+  const int smem = 36864 + 64 + 1024;
+  cudaError_t e = cudaFuncSetAttribute(umma_selftest_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  umma_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+      mode, k_bytes, q_bytes, v_bytes, p_bytes, s_out, o_out, status);
+  return static_cast<int>(cudaGetLastError());
+}

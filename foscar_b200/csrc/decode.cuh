@@ -1,0 +1,114 @@
+// Decode kernel parameters, work items and shared-memory plan (shared by decode.cu and the
+// host-side launcher/planner in capi.cu).
+#pragma once
+#include "common.cuh"
+
+namespace fq {
+
+constexpr int TILE = 128;            // tokens per sequence tile: two pages
+constexpr int WORK_WORDS = 8;        // int32 words per explicit work-list row
+constexpr int DECODE_THREADS = 576;  // 18 warps, see decode.cu
+constexpr int K_STAGES = 2;          // K operand stages in tensor memory
+constexpr int V_STAGES = 2;          // V operand stages in shared memory
+constexpr int SMEM_LIMIT = 232448;   // 227 KiB opt-in limit per CTA on sm_100
+
+struct DecodeParams {
+  fq_pools p;
+  fq_decode_args a;
+  int heads_per_kv;  // GQA ratio
+  int head_tiles;    // ceil(ratio / 8)
+  int num_items;     // implicit: B*HKV*head_tiles*kv_splits; explicit: row capacity
+  int ring_stages;
+};
+
+struct WorkItem {
+  int b, kvh, ht, t0, t1, slot, len, table_off;
+};
+
+// Shared-memory plan for one (BITS, D) build. All offsets from a 1024-byte aligned base.
+template <int BITS, int D>
+struct SmemPlan {
+  static constexpr int RB = D * BITS / 8;              // code row bytes
+  static constexpr int CODE_PAGE = PAGE * RB;          // one page of K (or V) codes, one head
+  static constexpr int SCALE_PAGE = PAGE * 16;         // f32 (s_k,z_k,s_v,z_v) records
+  static constexpr int K_OFF = 0;
+  static constexpr int V_OFF = 2 * CODE_PAGE;
+  static constexpr int S_OFF = 4 * CODE_PAGE;
+  static constexpr int STAGE = 4 * CODE_PAGE + 2 * SCALE_PAGE;
+  static constexpr int VOP_STAGE = TILE * D;           // expanded V operand, one tile
+  static constexpr int Q_BYTES = 16 * D;               // 16 MMA rows of D bytes
+  static constexpr int P_BYTES = TILE * 16;            // 16 bytes (8 hi + 8 lo) per token
+  static constexpr int VOP_OFF = 0;
+  static constexpr int Q_OFF = VOP_OFF + V_STAGES * VOP_STAGE;
+  static constexpr int P_OFF = Q_OFF + 2 * Q_BYTES;
+  static constexpr int XCHG_BYTES = TILE * 8 * 4 + 128;   // one WG's accumulators + (m,l,c)
+  static constexpr int XCHG_OFF = P_OFF + 4 * P_BYTES;
+  static constexpr int RED_OFF = XCHG_OFF + 2 * XCHG_BYTES;  // cross-warp reduction scratch
+  static constexpr int RED_BYTES = 2048;
+  static constexpr int BAR_OFF = RED_OFF + RED_BYTES;
+  static constexpr int BAR_BYTES = 1024;
+  static constexpr int RING_OFF = (BAR_OFF + BAR_BYTES + 1023) / 1024 * 1024;
+  static constexpr int max_ring_stages() {
+    return (SMEM_LIMIT - 1024 /*alignment slack*/ - RING_OFF) / STAGE;
+  }
+};
+
+// The items a launch runs, decoded the same way by every role of every CTA.
+__device__ inline WorkItem decode_item(const DecodeParams& P, int i) {
+  WorkItem w;
+  const fq_decode_args& a = P.a;
+  if (a.worklist != nullptr) {
+    const int* rows = a.worklist + __ldg(a.worklist + 3);  // header word 3: rows' word offset
+    const int4 r0 = __ldg(reinterpret_cast<const int4*>(rows) + 2 * i);
+    const int4 r1 = __ldg(reinterpret_cast<const int4*>(rows) + 2 * i + 1);
+    w.b = r0.x; w.kvh = r0.y; w.ht = r0.z; w.t0 = r0.w; w.t1 = r1.x; w.slot = r1.y;
+    const bool ok = w.b >= 0 && w.b < a.batch && w.kvh >= 0 && w.kvh < P.p.num_kv_heads &&
+                    w.ht >= 0 && w.ht < P.head_tiles && w.slot < a.max_splits;
+    if (!ok) { w.b = 0; w.kvh = 0; w.ht = 0; w.t0 = w.t1 = 0; w.slot = -2; }
+  } else {
+    const int S = a.kv_splits;
+    w.slot = S > 1 ? i % S : -1;
+    int rest = i / S;
+    w.ht = rest % P.head_tiles; rest /= P.head_tiles;
+    w.kvh = rest % P.p.num_kv_heads;
+    w.b = rest / P.p.num_kv_heads;
+    w.t0 = 0; w.t1 = 0x7FFFFFFF;
+  }
+  int len = __ldg(a.seq_lens + w.b);
+  if (len < 0) len = 0;
+  w.len = len;
+  const int tiles = (len + TILE - 1) / TILE;
+  if (a.worklist == nullptr) {
+    const int S = a.kv_splits;
+    const int per = (tiles + S - 1) / S;
+    const int s = S > 1 ? w.slot : 0;
+    w.t0 = min(s * per, tiles);
+    w.t1 = min(w.t0 + per, tiles);
+  } else {
+    w.t0 = max(0, min(w.t0, tiles));
+    w.t1 = max(w.t0, min(w.t1, tiles));
+  }
+  w.table_off = __ldg(a.table_offsets + w.b);
+  return w;
+}
+
+// The items one CTA runs: [begin, end) in steps of `step`. Implicit plans stride the grid over
+// the item space. An explicit list carries a header {pieces, units, ctas, rows' word offset},
+// then cta_start[ctas + 1], then the rows; CTA c runs rows [cta_start[c], cta_start[c+1]).
+// The header is read on the device, so a captured launch follows a list rewritten between
+// replays.
+struct ItemRange {
+  int begin, end, step;
+};
+__device__ inline ItemRange item_range(const DecodeParams& P) {
+  if (P.a.worklist == nullptr)
+    return ItemRange{static_cast<int>(blockIdx.x), P.num_items, static_cast<int>(gridDim.x)};
+  const int pieces = min(__ldg(P.a.worklist), P.num_items);
+  const int ctas = __ldg(P.a.worklist + 2);
+  if (static_cast<int>(blockIdx.x) >= ctas) return ItemRange{0, 0, 1};
+  const int b = __ldg(P.a.worklist + WORK_WORDS + blockIdx.x);
+  const int e = __ldg(P.a.worklist + WORK_WORDS + blockIdx.x + 1);
+  return ItemRange{max(0, min(b, pieces)), max(0, min(e, pieces)), 1};
+}
+
+}  // namespace fq

@@ -1,0 +1,399 @@
+// Cache writer: quantizes bf16 K/V rows (or lays out engine-quantized rows) into the packed
+// INT2/INT4 pools with their per-token scale records, and keeps the per-page V-scale maxima
+// and their exponent count table.
+//
+// Result contract (what a launch leaves in the pools) follows the reference writer,
+// src/foscar/_append_core.py:18-22 (runs), :73-109 (tail clear, page maxima), :533-587
+// (quantizer arithmetic), :589-628 (records); code placement src/foscar/_sm100/code_layout.py.
+//
+// Structure is this library's own. Two stream-ordered launches:
+//   1. page_start_kernel: every token at in-page position 0 begins a new use of its page: the
+//      page's scale records are zeroed and its maximum cell is cleared (count moved out).
+//   2. append_kernel: one warp per (token, KV head) quantizes, packs, stores the row, the
+//      record, and raises the page maximum with atomicMax, moving the count between bins.
+// Zero-then-overwrite leaves exactly the bytes "clear every position no token of the launch
+// writes" leaves, and needs no scan of the slot map. HBM-bound: 2*D*2 bytes read per (token,
+// head), coalesced 16-byte-per-lane-group loads.
+#include "common.cuh"
+
+namespace fq {
+
+constexpr float S_CLAMP = 1.0e-8f;
+constexpr float ENVELOPE = 18446744073709551616.0f;       // 2^64
+constexpr float DIVIDEND_FLOOR = 8.673617379884035e-19f;  // 2^-60
+
+struct WriterArgs {
+  fq_pools p;
+  const void* k;
+  const void* v;
+  long long k_stride, v_stride;  // token strides in elements
+  const float* k_scale;
+  const float* k_zero;
+  const float* v_scale;
+  const float* v_zero;
+  const long long* slots;
+  int num_tokens;
+  int k_clip, v_clip;
+  int* status;
+};
+
+__device__ inline float warp_group_min(float x, int lanes) {
+  for (int o = lanes >> 1; o > 0; o >>= 1) x = fminf(x, __shfl_xor_sync(0xFFFFFFFFu, x, o));
+  return x;
+}
+__device__ inline float warp_group_max(float x, int lanes) {
+  for (int o = lanes >> 1; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xFFFFFFFFu, x, o));
+  return x;
+}
+
+// Bytes of one (page, head) scale block and where a token's records sit in it.
+__device__ inline long long scale_block_bytes(const fq_pools& p) {
+  const int esz = p.scale_bf16 ? 2 : 4;
+  const int elems = p.k_groups == 1 ? 4 * PAGE : 2 * p.k_groups * PAGE + 2 * PAGE;
+  return static_cast<long long>(elems) * esz;
+}
+
+// Move one cell's count in the table when the cell went from `old` to `now`.
+__device__ inline void settle_count(uint32_t* hist, uint32_t old, uint32_t now) {
+  const bool c_old = (old & 0x7FFFFFFFu) != 0, c_new = (now & 0x7FFFFFFFu) != 0;
+  const uint32_t b_old = vmax_bucket(old), b_new = vmax_bucket(now);
+  if (c_old && c_new && b_old == b_new) return;
+  if (c_new) atomicAdd(hist + b_new, 1u);
+  if (c_old) atomicAdd(hist + b_old, 0xFFFFFFFFu);
+}
+
+// -------------------------------------------------------------------------------------------
+// 1. page starts
+// -------------------------------------------------------------------------------------------
+__global__ void page_start_kernel(WriterArgs a) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int hkv = a.p.num_kv_heads;
+  if (warp >= a.num_tokens * hkv) return;
+  const int token = warp / hkv, head = warp % hkv;
+  const long long slot = a.slots[token];
+  if (slot < 0 || (slot & (PAGE - 1)) != 0) return;
+  const long long page = slot >> 6;
+  if (page >= a.p.num_pages) return;  // reported by append_kernel
+  const long long bb = scale_block_bytes(a.p);
+  uint4* block = reinterpret_cast<uint4*>(static_cast<char*>(a.p.scales) +
+                                          (page * hkv + head) * bb);
+  for (int i = lane; i < bb / 16; i += 32) block[i] = make_uint4(0, 0, 0, 0);
+  if (lane == 0 && a.p.v_page_max != nullptr) {
+    const uint32_t old = atomicExch(a.p.v_page_max + page * hkv + head, 0u);
+    if ((old & 0x7FFFFFFFu) != 0) atomicAdd(a.p.v_max_hist + vmax_bucket(old), 0xFFFFFFFFu);
+  }
+}
+
+// -------------------------------------------------------------------------------------------
+// 2. rows
+// -------------------------------------------------------------------------------------------
+
+// Per-row clip threshold: the element at `index` of the row's |x| sorted ascending, found by a
+// radix select over the 15 value bits of a bf16 magnitude (bits 30..16 of the f32 pattern).
+template <int CH>
+__device__ inline float clip_threshold(const float (&x)[CH], int index) {
+  uint32_t prefix = 0;
+  int rank = index;
+  for (int bit = 30; bit >= 16; --bit) {
+    const uint32_t decided = 0x80000000u - (1u << bit);  // bits 30..bit
+    int count = 0;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const uint32_t mag = __float_as_uint(x[i]) & 0x7FFFFFFFu;
+      count += ((mag & decided) == prefix) ? 1 : 0;
+    }
+    for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xFFFFFFFFu, count, o);
+    if (rank >= count) {
+      rank -= count;
+      prefix |= 1u << bit;
+    }
+  }
+  return __uint_as_float(prefix);
+}
+
+// Quantize CH values held by this lane against the group's (s, z); returns them as a partial
+// 32-bit code word contribution (this lane's fields of word `c0 / W`).
+template <int BITS, int CH>
+__device__ inline uint32_t quantize_fields(const float (&x)[CH], float s, float z, int c0,
+                                           bool inside) {
+  constexpr int QMAX = (1 << BITS) - 1;
+  uint32_t word = 0;
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    float xv = x[i];
+    if (!inside) xv = fminf(fmaxf(xv, -ENVELOPE), ENVELOPE);
+    const float dividend = fmaxf(__fsub_rn(xv, z), DIVIDEND_FLOOR);
+    int q = __float2int_rn(__fdiv_rn(dividend, s));
+    q = min(q, QMAX);
+    word |= static_cast<uint32_t>(q) << (code_bit_offset<BITS>(c0 + i) & 31);
+  }
+  return word;
+}
+
+template <int BITS, int D, bool PREQ>
+__global__ void __launch_bounds__(256) append_kernel(WriterArgs a) {
+  constexpr int CH = D / 32;        // channels per lane
+  constexpr int W = 32 / BITS;      // codes per word
+  constexpr int LPW = W / CH;       // lanes sharing one code word (>= 1)
+  constexpr int RB = D * BITS / 8;  // row bytes
+  constexpr int QMAX = (1 << BITS) - 1;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int hkv = a.p.num_kv_heads;
+  if (warp >= a.num_tokens * hkv) return;
+  const int token = warp / hkv, head = warp % hkv;
+  const long long slot = a.slots[token];
+  if (slot < 0) return;
+  const long long page = slot >> 6;
+  const int pos = static_cast<int>(slot & (PAGE - 1));
+  if (page >= a.p.num_pages) {
+    if (lane == 0 && a.status) atomicOr(a.status, FQ_STATUS_BAD_SLOT);
+    return;
+  }
+  const int kg = a.p.k_groups;
+  const int c0 = lane * CH;
+  float sk, zk, sv, zv;
+  uint32_t kw, vw;
+
+  if (!PREQ) {
+    float xk[CH], xv[CH];
+    const __nv_bfloat16* kr = static_cast<const __nv_bfloat16*>(a.k) +
+                              token * a.k_stride + static_cast<long long>(head) * D + c0;
+    const __nv_bfloat16* vr = static_cast<const __nv_bfloat16*>(a.v) +
+                              token * a.v_stride + static_cast<long long>(head) * D + c0;
+    if constexpr (CH == 8) {
+      const uint4 uk = __ldg(reinterpret_cast<const uint4*>(kr));
+      const uint4 uv = __ldg(reinterpret_cast<const uint4*>(vr));
+      const uint32_t wk[4] = {uk.x, uk.y, uk.z, uk.w}, wv[4] = {uv.x, uv.y, uv.z, uv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        xk[2 * i] = __uint_as_float(wk[i] << 16);
+        xk[2 * i + 1] = __uint_as_float(wk[i] & 0xFFFF0000u);
+        xv[2 * i] = __uint_as_float(wv[i] << 16);
+        xv[2 * i + 1] = __uint_as_float(wv[i] & 0xFFFF0000u);
+      }
+    } else if constexpr (CH == 4) {
+      const uint2 uk = __ldg(reinterpret_cast<const uint2*>(kr));
+      const uint2 uv = __ldg(reinterpret_cast<const uint2*>(vr));
+      xk[0] = __uint_as_float(uk.x << 16); xk[1] = __uint_as_float(uk.x & 0xFFFF0000u);
+      xk[2] = __uint_as_float(uk.y << 16); xk[3] = __uint_as_float(uk.y & 0xFFFF0000u);
+      xv[0] = __uint_as_float(uv.x << 16); xv[1] = __uint_as_float(uv.x & 0xFFFF0000u);
+      xv[2] = __uint_as_float(uv.y << 16); xv[3] = __uint_as_float(uv.y & 0xFFFF0000u);
+    } else {
+      const uint32_t uk = __ldg(reinterpret_cast<const uint32_t*>(kr));
+      const uint32_t uv = __ldg(reinterpret_cast<const uint32_t*>(vr));
+      xk[0] = __uint_as_float(uk << 16); xk[1] = __uint_as_float(uk & 0xFFFF0000u);
+      xv[0] = __uint_as_float(uv << 16); xv[1] = __uint_as_float(uv & 0xFFFF0000u);
+    }
+    if (a.k_clip >= 0) {
+      const float t = clip_threshold<CH>(xk, a.k_clip);
+#pragma unroll
+      for (int i = 0; i < CH; ++i) xk[i] = fminf(fmaxf(xk[i], -t), t);
+    }
+    if (a.v_clip >= 0) {
+      const float t = clip_threshold<CH>(xv, a.v_clip);
+#pragma unroll
+      for (int i = 0; i < CH; ++i) xv[i] = fminf(fmaxf(xv[i], -t), t);
+    }
+    float kmn = xk[0], kmx = xk[0], vmn = xv[0], vmx = xv[0];
+#pragma unroll
+    for (int i = 1; i < CH; ++i) {
+      kmn = fminf(kmn, xk[i]); kmx = fmaxf(kmx, xk[i]);
+      vmn = fminf(vmn, xv[i]); vmx = fmaxf(vmx, xv[i]);
+    }
+    const int klanes = 32 / kg;  // lanes of one K group
+    kmn = warp_group_min(kmn, klanes); kmx = warp_group_max(kmx, klanes);
+    vmn = warp_group_min(vmn, 32); vmx = warp_group_max(vmx, 32);
+    const bool k_in = kmx <= ENVELOPE && kmn >= -ENVELOPE;
+    const bool v_in = vmx <= ENVELOPE && vmn >= -ENVELOPE;
+    zk = fminf(fmaxf(kmn, -ENVELOPE), ENVELOPE);
+    zv = fminf(fmaxf(vmn, -ENVELOPE), ENVELOPE);
+    const float ktop = fminf(fmaxf(kmx, -ENVELOPE), ENVELOPE);
+    const float vtop = fminf(fmaxf(vmx, -ENVELOPE), ENVELOPE);
+    sk = __fdiv_rn(fmaxf(__fsub_rn(ktop, zk), S_CLAMP), static_cast<float>(QMAX));
+    sv = __fdiv_rn(fmaxf(__fsub_rn(vtop, zv), S_CLAMP), static_cast<float>(QMAX));
+    kw = quantize_fields<BITS, CH>(xk, sk, zk, c0, k_in);
+    vw = quantize_fields<BITS, CH>(xv, sv, zv, c0, v_in);
+  } else {
+    // engine-quantized: one code per byte, masked to the stored width; records saturated
+    const uint8_t* kc = static_cast<const uint8_t*>(a.k) +
+                        (static_cast<long long>(token) * hkv + head) * D + c0;
+    const uint8_t* vc = static_cast<const uint8_t*>(a.v) +
+                        (static_cast<long long>(token) * hkv + head) * D + c0;
+    kw = vw = 0;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int sh = code_bit_offset<BITS>(c0 + i) & 31;
+      kw |= static_cast<uint32_t>(__ldg(kc + i) & QMAX) << sh;
+      vw |= static_cast<uint32_t>(__ldg(vc + i) & QMAX) << sh;
+    }
+    const float s_lo = __fdiv_rn(S_CLAMP, static_cast<float>(QMAX));
+    const float s_hi = __fdiv_rn(2.0f * ENVELOPE, static_cast<float>(QMAX));
+    const long long row = static_cast<long long>(token) * hkv + head;
+    const int grp = lane / (32 / kg);
+    sk = fminf(fmaxf(__ldg(a.k_scale + row * kg + grp), s_lo), s_hi);
+    zk = fminf(fmaxf(__ldg(a.k_zero + row * kg + grp), -ENVELOPE), ENVELOPE);
+    sv = fminf(fmaxf(__ldg(a.v_scale + row), s_lo), s_hi);
+    zv = fminf(fmaxf(__ldg(a.v_zero + row), -ENVELOPE), ENVELOPE);
+  }
+
+  // assemble code words across the lanes that share one, then one lane per word stores it
+#pragma unroll
+  for (int o = 1; o < LPW; o <<= 1) {
+    kw |= __shfl_xor_sync(0xFFFFFFFFu, kw, o);
+    vw |= __shfl_xor_sync(0xFFFFFFFFu, vw, o);
+  }
+  const long long row_index = (page * hkv + head) * PAGE + pos;
+  if (lane % LPW == 0) {
+    const int word = c0 / W;
+    reinterpret_cast<uint32_t*>(a.p.k_codes + row_index * RB)[word] = kw;
+    reinterpret_cast<uint32_t*>(a.p.v_codes + row_index * RB)[word] = vw;
+  }
+
+  // scale records, rounded to the pool dtype; the K groups' (s, z) sit with their first lanes
+  const float sk1 = __shfl_sync(0xFFFFFFFFu, sk, (32 / kg) * 1 % 32);
+  const float zk1 = __shfl_sync(0xFFFFFFFFu, zk, (32 / kg) * 1 % 32);
+  const float sk2 = __shfl_sync(0xFFFFFFFFu, sk, (32 / kg) * 2 % 32);
+  const float zk2 = __shfl_sync(0xFFFFFFFFu, zk, (32 / kg) * 2 % 32);
+  const float sk3 = __shfl_sync(0xFFFFFFFFu, sk, (32 / kg) * 3 % 32);
+  const float zk3 = __shfl_sync(0xFFFFFFFFu, zk, (32 / kg) * 3 % 32);
+  if (lane == 0) {
+    char* block = static_cast<char*>(a.p.scales) + (page * hkv + head) * scale_block_bytes(a.p);
+    uint32_t sv_bits;
+    if (!a.p.scale_bf16) {
+      // f32 pool: whole-head K only
+      reinterpret_cast<float4*>(block)[pos] = make_float4(sk, zk, sv, zv);
+      sv_bits = __float_as_uint(sv);
+    } else {
+      auto pack = [](float s, float z) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(s, z);
+        return *reinterpret_cast<const uint32_t*>(&h);
+      };
+      const uint32_t vrec = pack(sv, zv);
+      sv_bits = vrec << 16;
+      if (kg == 1) {
+        reinterpret_cast<uint2*>(block)[pos] = make_uint2(pack(sk, zk), vrec);
+      } else {
+        uint32_t* kring = reinterpret_cast<uint32_t*>(block) + kg * pos;
+        kring[0] = pack(sk, zk);
+        kring[1] = pack(sk1, zk1);
+        if (kg == 4) {
+          kring[2] = pack(sk2, zk2);
+          kring[3] = pack(sk3, zk3);
+        }
+        reinterpret_cast<uint32_t*>(block + 2 * kg * PAGE * 2)[pos] = vrec;
+      }
+    }
+    if (a.p.v_page_max != nullptr) {
+      uint32_t* cell = a.p.v_page_max + page * hkv + head;
+      const uint32_t seen = *reinterpret_cast<volatile uint32_t*>(cell);
+      if (sv_bits > seen) {
+        const uint32_t old = atomicMax(cell, sv_bits);
+        if (old < sv_bits) settle_count(a.p.v_max_hist, old, sv_bits);
+      }
+    }
+  }
+}
+
+// -------------------------------------------------------------------------------------------
+// recount
+// -------------------------------------------------------------------------------------------
+__global__ void recount_kernel(uint32_t* cells, long long n, uint32_t* hist) {
+  __shared__ uint32_t local[FQ_VMAX_BINS];
+  for (int i = threadIdx.x; i < FQ_VMAX_BINS; i += blockDim.x) local[i] = 0;
+  __syncthreads();
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint32_t v = cells[i] & 0x7FFFFFFFu;
+    cells[i] = v;
+    if (v != 0) atomicAdd(&local[vmax_bucket(v)], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < FQ_VMAX_BINS; i += blockDim.x)
+    if (local[i]) atomicAdd(hist + i, local[i]);
+}
+
+template <bool PREQ>
+static int launch_append(const WriterArgs& a, cudaStream_t stream) {
+  const long long warps = static_cast<long long>(a.num_tokens) * a.p.num_kv_heads;
+  if (warps == 0) return 0;
+  const int threads = 256;
+  const long long blocks = (warps * 32 + threads - 1) / threads;
+  if (blocks > 0x7FFFFFFFLL) return FQ_ERR_TOO_LARGE;
+  page_start_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(a);
+#define FQ_LAUNCH(B, DD)                                                                  \
+  if (a.p.bits == B && a.p.head_dim == DD) {                                              \
+    append_kernel<B, DD, PREQ><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(a); \
+    return static_cast<int>(cudaGetLastError());                                          \
+  }
+  FQ_LAUNCH(2, 64) FQ_LAUNCH(2, 128) FQ_LAUNCH(2, 256)
+  FQ_LAUNCH(4, 64) FQ_LAUNCH(4, 128) FQ_LAUNCH(4, 256)
+#undef FQ_LAUNCH
+  return FQ_ERR_UNSUPPORTED;
+}
+
+static int check_pools(const fq_pools* p) {
+  if (!p || !p->k_codes || !p->v_codes || !p->scales) return FQ_ERR_BAD_ARG;
+  if (p->bits != 2 && p->bits != 4) return FQ_ERR_UNSUPPORTED;
+  if (p->head_dim != 64 && p->head_dim != 128 && p->head_dim != 256) return FQ_ERR_UNSUPPORTED;
+  if (p->k_groups != 1 && p->k_groups != 2 && p->k_groups != 4) return FQ_ERR_UNSUPPORTED;
+  if (p->head_dim / p->k_groups < 64) return FQ_ERR_UNSUPPORTED;
+  if (p->k_groups > 1 && !p->scale_bf16) return FQ_ERR_UNSUPPORTED;
+  if (p->num_kv_heads <= 0 || p->num_pages <= 0) return FQ_ERR_BAD_ARG;
+  if ((p->v_page_max == nullptr) != (p->v_max_hist == nullptr)) return FQ_ERR_BAD_ARG;
+  return 0;
+}
+
+}  // namespace fq
+
+extern "C" int fq_append(const fq_pools* pools, const void* k, const void* v,
+                         int64_t k_token_stride, int64_t v_token_stride,
+                         const int64_t* slot_mapping, int32_t num_tokens, int32_t k_clip,
+                         int32_t v_clip, int32_t* status, void* stream) {
+  if (int e = fq::check_pools(pools)) return e;
+  if (num_tokens < 0 || (num_tokens > 0 && (!k || !v || !slot_mapping))) return FQ_ERR_BAD_ARG;
+  if (k_clip >= pools->head_dim || v_clip >= pools->head_dim) return FQ_ERR_BAD_ARG;
+  fq::WriterArgs a{};
+  a.p = *pools;
+  a.k = k; a.v = v;
+  a.k_stride = k_token_stride; a.v_stride = v_token_stride;
+  a.slots = reinterpret_cast<const long long*>(slot_mapping);
+  a.num_tokens = num_tokens;
+  a.k_clip = k_clip < 0 ? -1 : k_clip;
+  a.v_clip = v_clip < 0 ? -1 : v_clip;
+  a.status = status;
+  return fq::launch_append<false>(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fq_append_quantized(const fq_pools* pools, const uint8_t* k_codes,
+                                   const float* k_scale, const float* k_zero,
+                                   const uint8_t* v_codes, const float* v_scale,
+                                   const float* v_zero, const int64_t* slot_mapping,
+                                   int32_t num_tokens, int32_t* status, void* stream) {
+  if (int e = fq::check_pools(pools)) return e;
+  if (num_tokens < 0 || (num_tokens > 0 && (!k_codes || !v_codes || !k_scale || !k_zero ||
+                                            !v_scale || !v_zero || !slot_mapping)))
+    return FQ_ERR_BAD_ARG;
+  fq::WriterArgs a{};
+  a.p = *pools;
+  a.k = k_codes; a.v = v_codes;
+  a.k_scale = k_scale; a.k_zero = k_zero; a.v_scale = v_scale; a.v_zero = v_zero;
+  a.slots = reinterpret_cast<const long long*>(slot_mapping);
+  a.num_tokens = num_tokens;
+  a.k_clip = a.v_clip = -1;
+  a.status = status;
+  return fq::launch_append<true>(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fq_recount_vmax(const fq_pools* pools, void* stream) {
+  if (int e = fq::check_pools(pools)) return e;
+  if (!pools->v_page_max) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err = cudaMemsetAsync(pools->v_max_hist, 0, FQ_VMAX_BINS * sizeof(uint32_t), s);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  const long long n = static_cast<long long>(pools->num_pages) * pools->num_kv_heads;
+  const int blocks = static_cast<int>(n / 1024 + 1 < 592 ? n / 1024 + 1 : 592);
+  fq::recount_kernel<<<blocks, 256, 0, s>>>(pools->v_page_max, n, pools->v_max_hist);
+  return static_cast<int>(cudaGetLastError());
+}

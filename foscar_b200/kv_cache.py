@@ -1,0 +1,417 @@
+"""`QuantKVLayout` and `QuantKVCache`: one layer's quantized KV-cache layout and pools.
+
+Host-side mirror of the reference's cache objects (src/foscar/kv_cache.py:258-877): the same
+names, fields, argument meaning, pool geometry (byte-identical, region-major) and refusals.
+Every operation on the pools launches a kernel of the C-ABI library on the current stream;
+nothing here computes on the host.
+"""
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+from typing import Optional
+
+import torch
+
+from . import _lib, device as _dev
+from .pool_format import (HEAD_DIMS, PAGE_SIZE, QUANT_BITS, VMAX_BINS, envelope_refusal,
+                          normalize_pair, scale_block_sections)
+
+#: Most tokens one `append` takes (32-bit token counters, with slack).
+MAX_APPEND_TOKENS = 2**31 - 512
+#: Most requests one `dequantize` takes.
+MAX_DEQUANT_REQUESTS = 2**31 - 512
+SCALE_DTYPES = (torch.float32, torch.bfloat16)
+V_PAGE_MAX_DTYPE = torch.uint32
+READER = "IntDecodeSm100"
+
+
+def clip_index(ratio, head_dim: int) -> int:
+    """Order-statistic index of `append`'s per-row clip, -1 for none: a ratio r in (0, 1] clamps a
+    row to +-(its |x| sorted ascending)[min(int(r*D), D-1)] (src/foscar/kv_cache.py:104-118)."""
+    if ratio is None:
+        return -1
+    if isinstance(ratio, bool) or not isinstance(ratio, (int, float)) or not 0.0 < ratio <= 1.0:
+        raise ValueError(f"a clip ratio is a number in (0, 1], or None for no clip; got {ratio!r}")
+    return min(int(ratio * head_dim), head_dim - 1)
+
+
+def _positive_int(name, value):
+    if isinstance(value, bool) or not isinstance(value, int) or value <= 0:
+        raise ValueError(f"{name} must be a positive int; got {value!r}")
+
+
+def _resolve(arch, bits, head_dim, num_kv_heads, k_quant, v_quant, scale_dtype):
+    """Every field of a layout, validated (src/foscar/kv_cache.py:136-225)."""
+    if arch != "sm100":
+        raise ValueError(f"arch must be 'sm100'; got {arch!r}")
+    if isinstance(bits, bool) or not isinstance(bits, int) or bits not in QUANT_BITS:
+        raise ValueError(f"bits must be one of {QUANT_BITS}; got {bits!r}")
+    _positive_int("head_dim", head_dim)
+    _positive_int("num_kv_heads", num_kv_heads)
+    if head_dim not in HEAD_DIMS:
+        raise ValueError(f"head_dim {head_dim} is not accepted on {arch}; the decode accepts "
+                         f"{list(HEAD_DIMS)} there")
+    k_quant = normalize_pair(k_quant, head_dim, "k_quant")
+    v_quant = normalize_pair(v_quant, head_dim, "v_quant")
+    k_sub_token = k_quant[0] == "token" and k_quant[1] < head_dim
+    if scale_dtype is None:
+        scale_dtype = torch.bfloat16 if k_sub_token else torch.float32
+    if scale_dtype not in SCALE_DTYPES:
+        raise ValueError(f"scale_dtype must be one of {SCALE_DTYPES}; got {scale_dtype!r}")
+    why = envelope_refusal(k_quant, v_quant, head_dim)
+    if why is not None:
+        raise ValueError(f"k_quant={k_quant} v_quant={v_quant} is outside the decode's "
+                         f"envelope: {why}")
+    if k_sub_token and scale_dtype != torch.bfloat16:
+        raise ValueError(f"k_quant={k_quant} needs a bfloat16 scale pool on Blackwell; got "
+                         f"{scale_dtype}")
+    return dict(arch=arch, bits=bits, head_dim=head_dim, num_kv_heads=num_kv_heads,
+                k_quant=k_quant, v_quant=v_quant, scale_dtype=scale_dtype, reader=READER,
+                code_pool_order=None, k_pool_permuted=True, v_pool_permuted=True)
+
+
+@dataclasses.dataclass(frozen=True)
+class QuantKVLayout:
+    """One layer's cache layout: stored width, head dimension, KV heads, K and V granularity,
+    scale dtype, and the pool orders the decode reads. Build it with `QuantKVLayout.create`;
+    a hand-built instance whose fields disagree with what `create` resolves is refused."""
+    arch: str
+    bits: int
+    head_dim: int
+    num_kv_heads: int
+    k_quant: tuple
+    v_quant: tuple
+    scale_dtype: torch.dtype
+    reader: str
+    code_pool_order: Optional[str]
+    k_pool_permuted: Optional[bool]
+    v_pool_permuted: Optional[bool]
+
+    def __post_init__(self):
+        want = _resolve(self.arch, self.bits, self.head_dim, self.num_kv_heads, self.k_quant,
+                        self.v_quant, self.scale_dtype)
+        mine = {f.name: getattr(self, f.name) for f in dataclasses.fields(self)}
+        if mine != want:
+            diff = {k: (mine[k], want[k]) for k in want if mine[k] != want[k]}
+            raise ValueError(f"a QuantKVLayout is built by QuantKVLayout.create(); these fields "
+                             f"disagree with what the reader resolves: {diff}")
+
+    @classmethod
+    def create(cls, *, bits, head_dim, num_kv_heads, k_quant=None, v_quant=None,
+               scale_dtype=None, device=None) -> "QuantKVLayout":
+        """The production layout for `device` (default: the current CUDA device)."""
+        return cls._create(_dev.require_arch(device), bits=bits, head_dim=head_dim,
+                           num_kv_heads=num_kv_heads, k_quant=k_quant, v_quant=v_quant,
+                           scale_dtype=scale_dtype)
+
+    @classmethod
+    def _create(cls, arch, *, bits, head_dim, num_kv_heads, k_quant=None, v_quant=None,
+                scale_dtype=None, kernel_kwargs=None) -> "QuantKVLayout":
+        """`create()` for a named architecture; needs no GPU."""
+        if kernel_kwargs:
+            raise TypeError("kernel_kwargs is retired: this library has one build per layout")
+        return cls(**_resolve(arch, bits, head_dim, num_kv_heads, k_quant, v_quant, scale_dtype))
+
+    # -- geometry ---------------------------------------------------------------------------
+    def _sections(self) -> dict:
+        return scale_block_sections(self.k_quant, self.v_quant, self.head_dim)
+
+    def _blocks(self) -> dict:
+        sec = self._sections()
+        row = (PAGE_SIZE, self.head_dim * self.bits // 8)
+        return {"k_codes": row, "v_codes": row,
+                "scales": (PAGE_SIZE, 4) if sec["legacy"] else (sec["block_tot"],),
+                "v_page_max": () if self.has_v_page_max else None}
+
+    @property
+    def has_v_page_max(self) -> bool:
+        """Whether the cache keeps `v_page_max` and `v_max_hist`: token-wise V."""
+        return self.v_quant[0] == "token"
+
+    @property
+    def is_token_wise(self) -> bool:
+        return self.k_quant[0] == "token" and self.v_quant[0] == "token"
+
+    def pool_dtypes(self) -> dict:
+        return {"k_codes": torch.uint8, "v_codes": torch.uint8, "scales": self.scale_dtype,
+                "v_page_max": V_PAGE_MAX_DTYPE if self.has_v_page_max else None}
+
+    def pool_shapes(self, num_pages: int) -> dict:
+        _positive_int("num_pages", num_pages)
+        return {name: None if block is None else (num_pages, self.num_kv_heads, *block)
+                for name, block in self._blocks().items()}
+
+    def _page_bytes(self) -> dict:
+        sizes, dtypes = {}, self.pool_dtypes()
+        for name, block in self._blocks().items():
+            if block is None:
+                continue
+            n = self.num_kv_heads
+            for extent in block:
+                n *= extent
+            sizes[name] = n * dtypes[name].itemsize
+        return sizes
+
+    def bytes_per_page(self) -> int:
+        """Bytes one page takes across K, V, scales and page maxima, all KV heads."""
+        return sum(self._page_bytes().values())
+
+    # -- caches -----------------------------------------------------------------------------
+    def allocate(self, num_pages: int, *, device=None) -> "QuantKVCache":
+        """A fresh `num_pages`-page cache on `device`, laid out and initialised as `bind` does."""
+        _positive_int("num_pages", num_pages)
+        index = _dev.cuda_index(device)
+        buffer = torch.empty(num_pages * self.bytes_per_page(), dtype=torch.uint8,
+                             device=torch.device("cuda", index))
+        return self.bind(buffer, num_pages)
+
+    def bind(self, buffer: torch.Tensor, num_pages: int) -> "QuantKVCache":
+        """A cache over an engine-owned uint8 buffer, region-major `[K | V | scales | page
+        maxima]`; zeroes only the page maxima (src/foscar/kv_cache.py:405-455)."""
+        _positive_int("num_pages", num_pages)
+        if not isinstance(buffer, torch.Tensor):
+            raise TypeError(f"bind() takes a torch.Tensor; got {type(buffer).__name__}")
+        if buffer.dtype != torch.uint8:
+            raise ValueError(f"bind() takes a uint8 buffer; got {buffer.dtype}")
+        if not buffer.is_contiguous():
+            raise ValueError("bind() takes a C-contiguous buffer")
+        need = num_pages * self.bytes_per_page()
+        if buffer.numel() < need:
+            raise ValueError(f"a {num_pages}-page cache of this layout needs {need} bytes; the "
+                             f"buffer holds {buffer.numel()}")
+        if buffer.data_ptr() % 16:
+            raise ValueError("bind() takes a buffer whose start is 16-byte aligned")
+        _require_device(self, buffer.device)
+        flat = buffer.view(-1)
+        shapes, dtypes = self.pool_shapes(num_pages), self.pool_dtypes()
+        pools, start = {}, 0
+        for name, per_page in self._page_bytes().items():
+            region = flat[start:start + num_pages * per_page]
+            if name == "v_page_max":
+                region.zero_()
+            if dtypes[name] != torch.uint8:
+                region = region.view(dtypes[name])
+            pools[name] = region.view(shapes[name])
+            start += num_pages * per_page
+        v_page_max, v_max_hist = pools.get("v_page_max"), None
+        if v_page_max is not None:
+            v_max_hist = torch.zeros(VMAX_BINS, dtype=torch.int32,
+                                     device=buffer.device).view(V_PAGE_MAX_DTYPE)
+        return QuantKVCache._build(self, pools["k_codes"], pools["v_codes"], pools["scales"],
+                                   v_page_max, v_max_hist)
+
+
+def _require_device(layout, device):
+    arch = _dev.require_arch(device)
+    if arch != layout.arch:
+        raise ValueError(f"this layout was resolved for {layout.arch}, and {device} is {arch}; "
+                         f"create the layout for the device the cache lives on")
+
+
+class QuantKVCache:
+    """One layer's pools in global memory: `k_codes`, `v_codes`, `scales`, and with token-wise V
+    `v_page_max` (uint32 [NP, HKV]) and `v_max_hist` (uint32 [256]). Built only by
+    `QuantKVLayout.allocate` / `bind`. The pools are views into the engine's buffer.
+
+    Engine contracts (src/foscar/kv_cache.py:492-510): every use of a page begins with a write at
+    position 0; no decode of a layer runs concurrently with an append to it; after a raw copy
+    into the buffer call `recount_v_max()`; bind once per buffer.
+
+    Device-side faults set bits of `status` (int32 [1] on the device) instead of trapping;
+    `last_status()` reads it (it waits for the device)."""
+
+    __slots__ = ("layout", "num_pages", "device", "k_codes", "v_codes", "scales", "v_page_max",
+                 "v_max_hist", "status", "_c_pools")
+
+    def __init__(self, *args, **kwargs):
+        raise TypeError("a QuantKVCache is built by QuantKVLayout.allocate() or "
+                        "QuantKVLayout.bind()")
+
+    @classmethod
+    def _build(cls, layout, k_codes, v_codes, scales, v_page_max, v_max_hist) -> "QuantKVCache":
+        self = object.__new__(cls)
+        self.layout = layout
+        self.num_pages = int(k_codes.shape[0])
+        self.device = k_codes.device
+        self.k_codes, self.v_codes, self.scales = k_codes, v_codes, scales
+        self.v_page_max, self.v_max_hist = v_page_max, v_max_hist
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        k_groups = (layout.head_dim // layout.k_quant[1]) if layout.k_quant[0] == "token" else 1
+        self._c_pools = _lib.Pools(
+            bits=layout.bits, head_dim=layout.head_dim, num_kv_heads=layout.num_kv_heads,
+            k_groups=k_groups, scale_bf16=int(layout.scale_dtype == torch.bfloat16),
+            num_pages=self.num_pages, k_codes=k_codes.data_ptr(), v_codes=v_codes.data_ptr(),
+            scales=scales.data_ptr(),
+            v_page_max=None if v_page_max is None else v_page_max.data_ptr(),
+            v_max_hist=None if v_max_hist is None else v_max_hist.data_ptr())
+        return self
+
+    def last_status(self) -> int:
+        """The device status word (0 = no fault). Waits for the device."""
+        return int(self.status.item())
+
+    def _refuse_channel_wise(self, method):
+        lay = self.layout
+        if not lay.is_token_wise:
+            raise NotImplementedError(
+                f"{method}() writes token-wise layouts only; k_quant={lay.k_quant} "
+                f"v_quant={lay.v_quant} has a channel-wise tensor")
+
+    def _check_slots(self, slot_mapping, num_tokens):
+        if (not isinstance(slot_mapping, torch.Tensor) or slot_mapping.dtype != torch.int64
+                or tuple(slot_mapping.shape) != (num_tokens,)
+                or not slot_mapping.is_contiguous()):
+            raise ValueError(f"slot_mapping must be a contiguous int64 [{num_tokens}] tensor")
+        if slot_mapping.device != self.device:
+            raise ValueError(f"slot_mapping is on {slot_mapping.device}; the cache is on "
+                             f"{self.device}")
+
+    def recount_v_max(self) -> None:
+        """Clear every page maximum's sign bit and rebuild `v_max_hist` from the cells, on the
+        current stream; no host wait, capturable (src/foscar/kv_cache.py:595-616)."""
+        if self.v_page_max is None:
+            return
+        with _dev.on_device(self.device):
+            _lib.check(_lib.load().fq_recount_vmax(ctypes.byref(self._c_pools),
+                                                   _dev.current_stream_ptr(self.device)),
+                       "recount_v_max")
+
+    def append(self, k: torch.Tensor, v: torch.Tensor, slot_mapping: torch.Tensor, *,
+               k_clip=None, v_clip=None) -> None:
+        """Quantize and write tokens: k, v bfloat16 [T, HKV, D] (head dimension contiguous, free
+        token stride, 16-byte aligned rows); slot_mapping int64 [T], token t to page slot // 64,
+        position slot % 64; a negative slot is skipped (src/foscar/kv_cache.py:618-687). A slot at
+        or past num_pages * 64 is skipped and sets a status bit (the reference traps)."""
+        lay = self.layout
+        self._refuse_channel_wise("append")
+        shape = (lay.num_kv_heads, lay.head_dim)
+        for name, x in (("k", k), ("v", v)):
+            if not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or x.dim() != 3 \
+                    or tuple(x.shape[1:]) != shape:
+                raise ValueError(f"{name} must be a bfloat16 [T, {shape[0]}, {shape[1]}] tensor; "
+                                 f"got {getattr(x, 'dtype', None)} "
+                                 f"{tuple(getattr(x, 'shape', ()))}")
+            if x.device != self.device:
+                raise ValueError(f"{name} is on {x.device}; the cache is on {self.device}")
+            if x.stride(2) != 1 or x.stride(1) != lay.head_dim:
+                raise ValueError(f"{name} must have a contiguous [num_kv_heads, head_dim] row "
+                                 f"per token (strides (*, {lay.head_dim}, 1)); got "
+                                 f"{tuple(x.stride())}")
+            if x.data_ptr() % 16 or (x.stride(0) * x.element_size()) % 16:
+                raise ValueError(f"every token row of {name} must start 16-byte aligned")
+        if k.shape[0] != v.shape[0]:
+            raise ValueError(f"k has {k.shape[0]} tokens and v has {v.shape[0]}")
+        if k.shape[0] > MAX_APPEND_TOKENS:
+            raise ValueError(f"one append takes at most {MAX_APPEND_TOKENS} tokens; got "
+                             f"{k.shape[0]}: split it into several appends")
+        self._check_slots(slot_mapping, k.shape[0])
+        kc, vc = clip_index(k_clip, lay.head_dim), clip_index(v_clip, lay.head_dim)
+        if k.shape[0] == 0:
+            return
+        with _dev.on_device(self.device):
+            _lib.check(_lib.load().fq_append(
+                ctypes.byref(self._c_pools), k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0),
+                slot_mapping.data_ptr(), k.shape[0], kc, vc, self.status.data_ptr(),
+                _dev.current_stream_ptr(self.device)), "append")
+
+    def append_quantized(self, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero,
+                         slot_mapping) -> None:
+        """Layout-only write of engine-quantized tokens (src/foscar/kv_cache.py:689-767): codes
+        uint8 [T, HKV, D] one value per byte; f32 scales and zero points [T, HKV] ([T, HKV, g] for
+        K over head_dim // g); records saturated to the quantizing writer's ranges."""
+        lay = self.layout
+        self._refuse_channel_wise("append_quantized")
+        H, D = lay.num_kv_heads, lay.head_dim
+        T = k_codes.shape[0] if isinstance(k_codes, torch.Tensor) and k_codes.dim() else None
+        groups = D // lay.k_quant[1]
+        k_group = (T, H, groups) if groups > 1 else (T, H)
+        for name, x, dtype, shape in (("k_codes", k_codes, torch.uint8, (T, H, D)),
+                                      ("k_scale", k_scale, torch.float32, k_group),
+                                      ("k_zero", k_zero, torch.float32, k_group),
+                                      ("v_codes", v_codes, torch.uint8, (T, H, D)),
+                                      ("v_scale", v_scale, torch.float32, (T, H)),
+                                      ("v_zero", v_zero, torch.float32, (T, H))):
+            if not isinstance(x, torch.Tensor) or x.dtype != dtype or tuple(x.shape) != shape:
+                want = ["T" if e is None else e for e in shape]
+                raise ValueError(f"{name} must be a {dtype} {want} tensor; got "
+                                 f"{getattr(x, 'dtype', None)} {tuple(getattr(x, 'shape', ()))}")
+            if not x.is_contiguous():
+                raise ValueError(f"{name} must be C-contiguous")
+            if x.device != self.device:
+                raise ValueError(f"{name} is on {x.device}; the cache is on {self.device}")
+            if dtype == torch.uint8 and x.data_ptr() % 16:
+                raise ValueError(f"{name} must start 16-byte aligned")
+        if T > MAX_APPEND_TOKENS:
+            raise ValueError(f"one append takes at most {MAX_APPEND_TOKENS} tokens; got {T}: "
+                             f"split it into several appends")
+        self._check_slots(slot_mapping, T)
+        if T == 0:
+            return
+        with _dev.on_device(self.device):
+            _lib.check(_lib.load().fq_append_quantized(
+                ctypes.byref(self._c_pools), k_codes.data_ptr(), k_scale.data_ptr(),
+                k_zero.data_ptr(), v_codes.data_ptr(), v_scale.data_ptr(), v_zero.data_ptr(),
+                slot_mapping.data_ptr(), T, self.status.data_ptr(),
+                _dev.current_stream_ptr(self.device)), "append_quantized")
+
+    def dequantize(self, k_out, v_out, page_indptr, page_indices, seq_lens, out_indptr) -> None:
+        """Read K and V of a batch back into bf16 rows: `k_out[out_indptr[b] + t] =
+        bf16(fma(s_k, q, z_k))` for t < seq_lens[b], V likewise
+        (src/foscar/kv_cache.py:792-877). No host wait, no allocation, capturable. Out-of-range
+        page ids, rows or lengths are skipped and set a status bit (the reference traps)."""
+        lay = self.layout
+        if not lay.is_token_wise:
+            raise NotImplementedError(
+                f"dequantize() reads token-wise layouts only, the layouts append() writes; "
+                f"k_quant={lay.k_quant} v_quant={lay.v_quant} has a channel-wise tensor")
+        H, D = lay.num_kv_heads, lay.head_dim
+        for name, x in (("k_out", k_out), ("v_out", v_out)):
+            if not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or x.dim() != 3 \
+                    or tuple(x.shape[1:]) != (H, D):
+                raise ValueError(f"{name} must be a bfloat16 [N, {H}, {D}] tensor; got "
+                                 f"{getattr(x, 'dtype', None)} "
+                                 f"{tuple(getattr(x, 'shape', ()))}")
+            if x.device != self.device:
+                raise ValueError(f"{name} is on {x.device}; the cache is on {self.device}")
+            if x.stride(2) != 1 or x.stride(1) != D or (x.shape[0] > 1 and x.stride(0) < H * D):
+                raise ValueError(f"{name} must hold each token's [num_kv_heads, head_dim] row "
+                                 f"contiguously, rows not overlapping (strides (>= {H * D}, "
+                                 f"{D}, 1)); got {tuple(x.stride())}")
+            if x.data_ptr() % 16 or (x.stride(0) * x.element_size()) % 16:
+                raise ValueError(f"every token row of {name} must start 16-byte aligned")
+        if k_out.shape[0] != v_out.shape[0]:
+            raise ValueError(f"k_out has {k_out.shape[0]} rows and v_out has {v_out.shape[0]}")
+        index = {"page_indptr": (page_indptr, (torch.int32,)),
+                 "page_indices": (page_indices, (torch.int32,)),
+                 "seq_lens": (seq_lens, (torch.int32,)),
+                 "out_indptr": (out_indptr, (torch.int32, torch.int64))}
+        for name, (x, dtypes) in index.items():
+            if not isinstance(x, torch.Tensor) or x.dtype not in dtypes or x.dim() != 1 \
+                    or not x.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous one-dimensional "
+                                 f"{' or '.join(str(d) for d in dtypes)} tensor; got "
+                                 f"{getattr(x, 'dtype', None)} {tuple(getattr(x, 'shape', ()))}")
+            if x.device != self.device:
+                raise ValueError(f"{name} is on {x.device}; the cache is on {self.device}")
+        batch = seq_lens.shape[0]
+        if page_indptr.shape[0] != batch + 1 or out_indptr.shape[0] != batch:
+            raise ValueError(f"seq_lens has {batch} requests, so page_indptr must have "
+                             f"{batch + 1} entries and out_indptr {batch}; got "
+                             f"{page_indptr.shape[0]} and {out_indptr.shape[0]}")
+        if batch > MAX_DEQUANT_REQUESTS:
+            raise ValueError(f"one dequantize takes at most {MAX_DEQUANT_REQUESTS} requests; got "
+                             f"{batch}: split it into several calls")
+        if page_indices.shape[0] * H > 2**31 - 1:
+            raise ValueError(f"one dequantize launches a CTA per page entry and KV head, at most "
+                             f"2^31 - 1; got {page_indices.shape[0]} entries and {H} KV heads: "
+                             f"split it into several calls")
+        if batch == 0:
+            return
+        with _dev.on_device(self.device):
+            _lib.check(_lib.load().fq_dequantize(
+                ctypes.byref(self._c_pools), k_out.data_ptr(), v_out.data_ptr(), k_out.stride(0),
+                v_out.stride(0), k_out.shape[0], page_indptr.data_ptr(), page_indices.data_ptr(),
+                page_indices.shape[0], seq_lens.data_ptr(), out_indptr.data_ptr(),
+                int(out_indptr.dtype == torch.int64), batch, self.status.data_ptr(),
+                _dev.current_stream_ptr(self.device)), "dequantize")

@@ -1,0 +1,175 @@
+/* C ABI of libfoscar_b200: paged GQA decode attention over packed INT2/INT4 KV caches on
+ * B200 (sm_100a). Plain pointers and sizes only; every launch is asynchronous on the given
+ * CUDA stream (a cudaStream_t passed as void*). Return value: 0 on success, a negative
+ * FQ_ERR_* for a refused argument, or a positive cudaError_t from the launch.
+ *
+ * The reference has no C ABI: its device entry points are TVM-FFI callables compiled from
+ * CuTe-DSL. Each entry point below names the reference call it stands in for.
+ *
+ * Device-side faults never trap: a kernel that meets an out-of-range slot, page id, output row
+ * or length, or a wait that ran out, skips the access and ORs a FQ_STATUS_* bit into the
+ * caller's int32 status word (may be NULL).
+ */
+#ifndef FOSCAR_B200_H
+#define FOSCAR_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FQ_PAGE_SIZE 64
+#define FQ_VMAX_BINS 256
+
+/* host-side refusals */
+#define FQ_ERR_BAD_ARG (-1)
+#define FQ_ERR_UNSUPPORTED (-2)
+#define FQ_ERR_TOO_LARGE (-3)
+
+/* device status bits */
+#define FQ_STATUS_BAD_SLOT 0x1      /* append: slot >= num_pages * 64 (skipped) */
+#define FQ_STATUS_BAD_PAGE 0x2      /* dequantize/decode: page id outside the pool (skipped) */
+#define FQ_STATUS_BAD_ROW 0x4       /* dequantize: output row outside k_out/v_out (skipped) */
+#define FQ_STATUS_BAD_LENGTH 0x8    /* negative length, or longer than the request's pages */
+#define FQ_STATUS_TIMEOUT 0x10      /* a bounded device wait ran out; output is invalid */
+
+/* One layer's pools (reference: QuantKVCache, src/foscar/kv_cache.py:477-533).
+ * k_codes, v_codes: uint8 [num_pages, num_kv_heads, 64, head_dim*bits/8].
+ * scales: [num_pages, num_kv_heads, 64, 4] (s_k,z_k,s_v,z_v) when k_groups == 1, else the
+ *   sectioned block [num_pages, num_kv_heads, 2*k_groups*64 + 128]; f32 or bf16.
+ * v_page_max: uint32 [num_pages, num_kv_heads]; v_max_hist: uint32 [256]. */
+typedef struct fq_pools {
+  int32_t bits;          /* 2 or 4 */
+  int32_t head_dim;      /* 64, 128 or 256 */
+  int32_t num_kv_heads;
+  int32_t k_groups;      /* head_dim / K token-wise group: 1, 2 or 4 */
+  int32_t scale_bf16;    /* 0: f32 records, 1: bf16 records */
+  int32_t num_pages;
+  uint8_t* k_codes;
+  uint8_t* v_codes;
+  void* scales;
+  uint32_t* v_page_max;
+  uint32_t* v_max_hist;
+} fq_pools;
+
+const char* fq_version(void);
+const char* fq_error_string(int code);
+
+/* Quantize bf16 K,V [T, HKV, D] (token strides in elements) and write them at slot_mapping
+ * (int64 [T]; negative = skipped). k_clip/v_clip: order-statistic index of the per-row clip,
+ * -1 for none. Stands in for QuantKVCache.append -> launch_writer
+ * (src/foscar/kv_cache.py:618-687, src/foscar/_append_core.py:1320-1332). */
+int fq_append(const fq_pools* pools, const void* k, const void* v, int64_t k_token_stride,
+              int64_t v_token_stride, const int64_t* slot_mapping, int32_t num_tokens,
+              int32_t k_clip, int32_t v_clip, int32_t* status, void* stream);
+
+/* Layout-only write of engine-quantized tokens: codes uint8 [T, HKV, D] one value per byte,
+ * f32 scales/zeros [T, HKV(, k_groups)]. Stands in for QuantKVCache.append_quantized
+ * (src/foscar/kv_cache.py:689-767). */
+int fq_append_quantized(const fq_pools* pools, const uint8_t* k_codes, const float* k_scale,
+                        const float* k_zero, const uint8_t* v_codes, const float* v_scale,
+                        const float* v_zero, const int64_t* slot_mapping, int32_t num_tokens,
+                        int32_t* status, void* stream);
+
+/* Read K,V of a batch back into bf16 rows [N, HKV, D]: out[out_indptr[b]+t] =
+ * bf16(fma(s, q, z)) for t < seq_lens[b]. Stands in for QuantKVCache.dequantize
+ * (src/foscar/kv_cache.py:792-877). out_indptr is int32 or int64 (out_indptr_64). */
+int fq_dequantize(const fq_pools* pools, void* k_out, void* v_out, int64_t k_row_stride,
+                  int64_t v_row_stride, int64_t num_out_rows, const int32_t* page_indptr,
+                  const int32_t* page_indices, int32_t num_entries, const int32_t* seq_lens,
+                  const void* out_indptr, int32_t out_indptr_64, int32_t batch,
+                  int32_t* status, void* stream);
+
+/* Clear the sign bit of every v_page_max cell and rebuild v_max_hist from the cells. Stands
+ * in for QuantKVCache.recount_v_max (src/foscar/kv_cache.py:595-616). */
+int fq_recount_vmax(const fq_pools* pools, void* stream);
+
+/* One decode step. Stands in for launch_fold / launch_fold_graph
+ * (src/foscar/_sm100/fold_runtime.py:680-779).
+ * A work item is (request, KV head, head tile, chunk of 128-token tiles). With worklist ==
+ * NULL the items are implicit: every request is cut into `kv_splits` contiguous chunks by the
+ * kernel from seq_lens. Otherwise worklist is the int32 list fq_plan_worklist writes: a header
+ * {pieces, units, ctas, rows' word offset, 0...}, cta_start[ctas + 1] (padded to 8 words), then
+ * one row per piece
+ *   {request, kv_head, head_tile, tile_begin, tile_end, partial_slot, 0, 0}
+ * with partial_slot -1 = write the final output. CTA c runs rows [cta_start[c], cta_start[c+1]).
+ * The header is read on the device, so a captured launch follows a list rewritten between
+ * replays; launch with max_ctas = the plan's ctas.
+ * Items with a partial slot write unnormalised f32 o_partial [max_splits, B, HQ, D] and
+ * l_partial / m_partial [max_splits, B, HQ] (m in the log2 domain); fq_merge combines them. */
+typedef struct fq_decode_args {
+  int32_t batch;
+  int32_t num_qo_heads;
+  int32_t out_dtype;            /* 0 bf16, 1 f16, 2 f32 */
+  int32_t kv_splits;            /* implicit mode: chunks per request, >= 1 */
+  int32_t max_splits;           /* leading extent of the partial buffers */
+  int32_t num_work;             /* explicit mode: most rows the list may hold */
+  int32_t max_ctas;             /* grid cap; 0 = one CTA per SM */
+  int32_t reserved;
+  float sm_scale;
+  float o_scale;
+  const int32_t* worklist;      /* NULL = implicit mode */
+  const int32_t* seq_lens;      /* int32 [B] */
+  const int32_t* page_table;    /* int32 flat page ids */
+  const int32_t* table_offsets; /* int32 [B]: first entry of request b in page_table */
+  int64_t table_len;            /* entries in page_table (bounds check) */
+  const void* q;                /* fp8 e4m3 [B, HQ, D] */
+  const float* q_descale;       /* NULL or f32, element (b,h) at b*stride_b + h*stride_h */
+  int64_t q_descale_stride_b;
+  int64_t q_descale_stride_h;
+  void* out;                    /* [B, HQ, D] in out_dtype */
+  float* lse;                   /* NULL or f32 [B, HQ], natural log */
+  float* o_partial;
+  float* l_partial;
+  float* m_partial;
+  int32_t* status;
+} fq_decode_args;
+
+int fq_decode(const fq_pools* pools, const fq_decode_args* args, void* stream);
+
+/* Merge split partials in fixed slot order. split_counts NULL: every row combines slots
+ * [0, kv_splits). Otherwise split_counts is int32 [B * HKV * head_tiles], the piece count of
+ * each unit (request, KV head, tile of eight query heads): a unit with one piece wrote its final
+ * output itself and is left alone. Stands in for launch_reduction
+ * (src/foscar/_sm100/gqa_decode.py:377-456). */
+int fq_merge(const float* o_partial, const float* l_partial, const float* m_partial,
+             const int32_t* split_counts, int32_t kv_splits, int32_t max_splits, int32_t batch,
+             int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim, float o_scale,
+             void* out, int32_t out_dtype, float* lse, void* stream);
+
+/* Merge attention states from several sequence shards: out = sum_r exp(lse_r - L) o_r,
+ * L = logsumexp_r lse_r, o f32 [R, B, HQ, D], lse f32 [R, B, HQ] (natural log). The reference
+ * has no counterpart (single-GPU library); this is the local half of the cross-GPU
+ * sequence split. */
+int fq_merge_states(const float* o_shards, const float* lse_shards, int32_t num_shards,
+                    int32_t batch, int32_t num_qo_heads, int32_t head_dim, void* out,
+                    int32_t out_dtype, float* lse, void* stream);
+
+/* Host-only planning. fq_plan_splits: uniform split count for the longest request (closed-form
+ * cost model; stands in for plan_splits_sm100, src/foscar/_sm100/scheduler.py:129-160).
+ * fq_plan_worklist: balanced pieces from host seq_lens: writes the list (at most max_words int32
+ * words; fq_worklist_words gives the size that always suffices) and the piece count of each
+ * unit into split_counts [B * HKV * head_tiles]; returns the number of pieces, or a negative
+ * FQ_ERR_* (FQ_ERR_TOO_LARGE when a unit would need more than max_splits pieces). */
+int fq_plan_splits(int32_t batch, int32_t num_kv_heads, int32_t head_tiles, int32_t max_kv_len,
+                   int32_t bits, int32_t head_dim, int32_t sm_count);
+int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t num_kv_heads,
+                     int32_t head_tiles, int32_t num_ctas, int32_t max_splits,
+                     int32_t* worklist, int32_t max_words, int32_t* split_counts);
+int64_t fq_worklist_words(int32_t batch, int32_t num_kv_heads, int32_t head_tiles,
+                          int32_t num_ctas);
+int64_t fq_workspace_bytes(int32_t max_splits, int32_t batch, int32_t num_qo_heads,
+                           int32_t head_dim);
+
+/* Tensor-core self test: runs one 128-token tile of both contractions on known operands and
+ * writes the raw accumulators (f32 [128][16] each) for the host to compare. mode 0: K operand
+ * from tensor memory; mode 1: K operand from shared memory. */
+int fq_umma_selftest(int32_t mode, const uint8_t* k_bytes, const uint8_t* q_bytes,
+                     const uint8_t* v_bytes, const uint8_t* p_bytes, float* s_out, float* o_out,
+                     int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FOSCAR_B200_H */

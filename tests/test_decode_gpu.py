@@ -1,0 +1,128 @@
+"""Decode output through the public API against the fp32 oracle (dequantize + softmax on CPU).
+
+Tolerance (bf16 output vs the fp32 oracle over the read-back values): max-abs <= 2e-2 and
+mean-abs <= 2e-3; LSE within 5e-2 absolute."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import PAGE, cpu_twin, make_kv, make_q, oracle_outputs, paged_batch
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, MEAN_ABS, LSE_ABS = 2e-2, 2e-3, 5e-2
+
+
+def _run_case(bits, d, hq, hkv, seq, *, kv_splits=None, host_lens=True, outliers=False,
+              q_scale=1.0, lse=True, q_descale=False, out_dtype=torch.bfloat16, seed=0,
+              reduction="auto", max_kv_len=None):
+    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
+    batch = len(seq)
+    indptr, indices, slots, npages = paged_batch(seq, seed=seed)
+    k, v = make_kv(len(slots), hkv, d, seed=seed, outliers=outliers)
+    layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device="cuda")
+    cache = layout.allocate(npages + 1)
+    cache.append(k, v, torch.from_numpy(slots).cuda())
+    q = make_q(batch, hq, d, seed=seed + 1, scale=q_scale)
+    sm_scale = d ** -0.5 / q_scale
+    w = PagedDecodeWrapper(torch.empty(64 << 20, dtype=torch.uint8, device="cuda"))
+    lens = torch.tensor(seq, dtype=torch.int32)
+    w.plan(torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda(),
+           lens if host_lens else lens.cuda(), hq, layout, sm_scale=sm_scale,
+           kv_splits=kv_splits, o_data_type=out_dtype, reduction=reduction,
+           max_kv_len=max_kv_len)
+    out = torch.full((batch, hq, d), float("nan"), dtype=out_dtype, device="cuda")
+    lse_t = torch.full((batch, hq), float("nan"), device="cuda") if lse else None
+    qd = None
+    if q_descale:
+        qd = (torch.rand(batch, hq, generator=torch.Generator().manual_seed(7)) + 0.5).cuda()
+    w.run(q, cache, out=out, lse=lse_t, q_descale=qd)
+    torch.cuda.synchronize()
+    assert w.last_status() == 0, w.last_status()
+    pools = cpu_twin(cache, k, v, slots)
+    want, lse_want = oracle_outputs(pools, q.cpu(), indptr, indices, seq, sm_scale,
+                                    None if qd is None else qd.cpu())
+    err = (out.float().cpu() - want).abs()
+    assert torch.isfinite(out.float()).all()
+    assert err.max().item() <= MAX_ABS, f"max-abs {err.max().item():.3e}"
+    assert err.mean().item() <= MEAN_ABS, f"mean-abs {err.mean().item():.3e}"
+    if lse:
+        assert (lse_t.cpu() - lse_want).abs().max().item() <= LSE_ABS
+    return w, out, err
+
+
+def test_config1_cpu_reference_case():
+    """INT4, B=2, 32/8 heads, D=128, two full pages per request."""
+    _run_case(4, 128, 32, 8, [128, 128])
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (16, 2), (8, 8), (24, 2)])
+def test_ragged_batch(bits, hq, hkv):
+    _run_case(bits, 128, hq, hkv, [1, 63, 64, 65, 129, 1000, 4097], seed=bits)
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+@pytest.mark.parametrize("kv_splits", [1, 4, 7, None])
+def test_uniform_and_planned_splits(bits, kv_splits):
+    w, _, _ = _run_case(bits, 128, 32, 8, [4096, 700], kv_splits=kv_splits, host_lens=False,
+                        max_kv_len=4096 if kv_splits is None else None)
+    assert w.kv_splits >= 1
+
+
+def test_balanced_plan_splits_long_request():
+    w, _, _ = _run_case(2, 128, 32, 8, [20000, 130], seed=3)
+    assert w.kv_splits > 1 and w.reduction == "kernel"
+
+
+def test_outlier_keys_fp8_query_scale():
+    """K with per-channel log-normal magnitudes, q = e4m3(8 q) with sm_scale / 8."""
+    _run_case(2, 128, 32, 8, [3000, 5000], outliers=True, q_scale=8.0, seed=5)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+def test_output_dtypes_and_descale(out_dtype):
+    _run_case(4, 128, 16, 4, [300, 900], out_dtype=out_dtype, q_descale=True)
+
+
+def test_reduction_none_forces_one_piece():
+    w, _, _ = _run_case(2, 128, 32, 8, [9000], reduction="none")
+    assert w.kv_splits == 1 and w.reduction == "none"
+
+
+def test_run_is_deterministic():
+    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
+    seq = [5000, 333, 8000]
+    indptr, indices, slots, npages = paged_batch(seq, seed=9)
+    k, v = make_kv(len(slots), 8, 128, seed=9)
+    layout = QuantKVLayout.create(bits=2, head_dim=128, num_kv_heads=8, device="cuda")
+    cache = layout.allocate(npages)
+    cache.append(k, v, torch.from_numpy(slots).cuda())
+    q = make_q(3, 32, 128)
+    w = PagedDecodeWrapper(torch.empty(64 << 20, dtype=torch.uint8, device="cuda"))
+    w.plan(torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda(),
+           torch.tensor(seq, dtype=torch.int32), 32, layout)
+    outs = []
+    for _ in range(3):
+        out = torch.empty(3, 32, 128, dtype=torch.bfloat16, device="cuda")
+        w.run(q, cache, out=out)
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
+def test_bad_page_id_sets_status_without_fault():
+    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
+    layout = QuantKVLayout.create(bits=2, head_dim=128, num_kv_heads=2, device="cuda")
+    cache = layout.allocate(4)
+    k, v = make_kv(256, 2, 128)
+    cache.append(k, v, torch.arange(256, device="cuda"))
+    w = PagedDecodeWrapper(torch.empty(1 << 20, dtype=torch.uint8, device="cuda"))
+    w.plan(torch.tensor([0, 4], dtype=torch.int32), torch.tensor([0, 99, 2, -5], dtype=torch.int32),
+           torch.tensor([256], dtype=torch.int32), 8, layout)
+    out = torch.empty(1, 8, 128, dtype=torch.bfloat16, device="cuda")
+    w.run(make_q(1, 8, 128), cache, out=out)
+    torch.cuda.synchronize()
+    assert w.last_status() & 0x2
