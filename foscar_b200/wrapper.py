@@ -151,6 +151,9 @@ class PagedDecodeWrapper:
         self._float_workspace_buffer = float_workspace_buffer
         self.device = float_workspace_buffer.device
         self._status = None
+        #: kernels this wrapper has launched (decode and merge), for benchmark accounting
+        self.launches = 0
+        self._decode_done_event = None
         self._invalidate_plan()
 
     def _invalidate_plan(self):
@@ -447,7 +450,11 @@ class PagedDecodeWrapper:
         args.status = self._status_ptr()
         _lib.check(lib.fq_decode(ctypes.byref(cache._c_pools), ctypes.byref(args), stream),
                    "decode")
+        self.launches += 1
+        if self._decode_done_event is not None:
+            self._decode_done_event.record()       # lets a benchmark time the decode kernel alone
         if self._merge:
+            self.launches += 1
             counts = None if self._split_counts is None else self._split_counts.data_ptr()
             _lib.check(lib.fq_merge(
                 self._o_partial.data_ptr(), self._l_partial.data_ptr(),

@@ -261,8 +261,10 @@ def _fma_f32(s, q, z):
     return (s.double() * q.double() + z.double()).float()
 
 
-def ref_dequantize(pools: CpuPools, page_indptr, page_indices, seq_lens):
-    """Per request, (k_hat, v_hat) bf16 [len, HKV, D] = bf16_rne(fma(s, q, z))."""
+def ref_dequantize(pools: CpuPools, page_indptr, page_indices, seq_lens, rounded=True):
+    """Per request, (k_hat, v_hat) [len, HKV, D] = bf16_rne(fma(s, q, z)), the cache's read-back.
+    `rounded=False` keeps the f32 fma result: the "fp32 dequantize" the decode's tolerance is
+    stated against (the decode never rounds a K or V value to bf16)."""
     out = []
     krec, vrec = pools._k_records().float(), pools._v_records().float()
     for b, n in enumerate(np.asarray(seq_lens)):
@@ -276,8 +278,10 @@ def ref_dequantize(pools: CpuPools, page_indptr, page_indices, seq_lens):
         ks = kr[..., 0].repeat_interleave(pools.d // pools.k_groups, dim=-1)
         kz = kr[..., 1].repeat_interleave(pools.d // pools.k_groups, dim=-1)
         vr = vrec[pg, :, pos]
-        k_hat = _fma_f32(ks, kq, kz).to(torch.bfloat16)
-        v_hat = _fma_f32(vr[..., 0:1], vq, vr[..., 1:2]).to(torch.bfloat16)
+        k_hat = _fma_f32(ks, kq, kz)
+        v_hat = _fma_f32(vr[..., 0:1], vq, vr[..., 1:2])
+        if rounded:
+            k_hat, v_hat = k_hat.to(torch.bfloat16), v_hat.to(torch.bfloat16)
         out.append((k_hat, v_hat))
     return out
 

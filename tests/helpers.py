@@ -41,9 +41,10 @@ def paged_batch(seq_lens, seed=0, shuffle=True):
 
 
 def oracle_outputs(pools: CpuPools, q_fp8_cpu, indptr, indices, seq_lens, sm_scale,
-                   q_descale=None):
-    """fp32 attention over the oracle's read-back: (out [B,HQ,D], lse [B,HQ])."""
-    kv = ref_dequantize(pools, indptr, indices, seq_lens)
+                   q_descale=None, rounded=False):
+    """fp32 softmax attention over the oracle's fp32 dequantized values (or, with `rounded`,
+    over the bf16 read-back rows): (out [B,HQ,D], lse [B,HQ])."""
+    kv = ref_dequantize(pools, indptr, indices, seq_lens, rounded=rounded)
     outs, lses = [], []
     for b in range(len(seq_lens)):
         o, l = ref_attention(q_fp8_cpu[b].float(), kv[b][0], kv[b][1], sm_scale,

@@ -1,7 +1,10 @@
-"""Decode output through the public API against the fp32 oracle (dequantize + softmax on CPU).
+"""Decode output through the public API against the fp32 oracle (fp32 dequantize + fp32 softmax
+on CPU).
 
-Tolerance (bf16 output vs the fp32 oracle over the read-back values): max-abs <= 2e-2 and
-mean-abs <= 2e-3; LSE within 5e-2 absolute."""
+Tolerance (bf16 output vs the oracle): max-abs <= 2e-2 and mean-abs <= 2e-3; LSE within 5e-2
+absolute. A second check scores the output against the cache's own bf16 read-back the way the
+reference's GPU test does (global relative L2 < 6e-3, tests/test_cache_gpu.py:22-27) on N(0,1)
+inputs, where the read-back's bf16 rounding does not dominate."""
 import math
 
 import numpy as np
@@ -50,6 +53,11 @@ def _run_case(bits, d, hq, hkv, seq, *, kv_splits=None, host_lens=True, outliers
     assert err.mean().item() <= MEAN_ABS, f"mean-abs {err.mean().item():.3e}"
     if lse:
         assert (lse_t.cpu() - lse_want).abs().max().item() <= LSE_ABS
+    if not outliers:
+        back, _ = oracle_outputs(pools, q.cpu(), indptr, indices, seq, sm_scale,
+                                 None if qd is None else qd.cpu(), rounded=True)
+        rel = ((out.float().cpu() - back).norm() / back.norm()).item()
+        assert rel < 6e-3, f"rel-L2 vs read-back {rel:.3e}"
     return w, out, err
 
 

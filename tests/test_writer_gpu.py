@@ -51,6 +51,7 @@ def test_decode_step_appends_and_page_reuse(bits):
     reused from position 0: tail clear, page maxima and count table follow the oracle."""
     hkv, d, npages = 2, 128, 6
     cache = _layout(bits, d, hkv).allocate(npages)
+    cache.k_codes.zero_(); cache.v_codes.zero_()
     cache.scales.view(torch.uint8).fill_(0xFF)
     pools = CpuPools(npages, hkv, d, bits)
     pools.scales.view(torch.uint8).fill_(0xFF)
@@ -94,6 +95,7 @@ def test_bf16_pool_and_grouped_k(bits):
     k, v = make_kv(len(slots), hkv, d, seed=9)
     for kw in (dict(scale_dtype=torch.bfloat16), dict(k_quant=("token", 64))):
         cache = _layout(bits, d, hkv, **kw).allocate(npages)
+        cache.k_codes.zero_(); cache.v_codes.zero_(); cache.scales.zero_()
         cache.append(k, v, torch.from_numpy(slots).cuda())
         pools = cpu_twin(cache, k, v, slots)
         assert_pools_equal(cache, pools)
@@ -111,6 +113,7 @@ def test_append_quantized_matches_oracle(bits):
     ks[0, 0] = float("nan"); vz[1, 1] = 1e30
     kc = kc | 0xF0                                  # high bits are ignored
     cache = _layout(bits, d, hkv).allocate(npages)
+    cache.k_codes.zero_(); cache.v_codes.zero_(); cache.scales.zero_()
     cache.append_quantized(kc.cuda(), ks.cuda(), kz.cuda(), vc.cuda(), vs.cuda(), vz.cuda(),
                            torch.from_numpy(slots).cuda())
     pools = CpuPools(npages, hkv, d, bits)
@@ -126,6 +129,7 @@ def test_clipped_append(clip):
     indptr, indices, slots, npages = paged_batch(seq, seed=1)
     k, v = make_kv(len(slots), hkv, d, seed=4, outliers=True)
     cache = _layout(bits, d, hkv).allocate(npages)
+    cache.k_codes.zero_(); cache.v_codes.zero_(); cache.scales.zero_()
     cache.append(k, v, torch.from_numpy(slots).cuda(), k_clip=clip[0], v_clip=clip[1])
     pools = CpuPools(npages, hkv, d, bits)
     ref_append(pools, k.cpu(), v.cpu(), slots, clip_index(clip[0], d), clip_index(clip[1], d))
