@@ -64,7 +64,8 @@ _lib = None
 
 
 def library_path() -> str:
-    return _build.LIB_PATH
+    """The library to load: the in-tree build, or FOSCAR_B200_LIB (a diagnostic build)."""
+    return os.environ.get("FOSCAR_B200_LIB") or _build.LIB_PATH
 
 
 def load():

@@ -78,9 +78,11 @@ constexpr long long WAIT_BUDGET_CYCLES = 2000000000LL;
 
 // Wait for a barrier phase, bounded. `abort_flag` is a CTA-shared word: once any waiter has
 // given up every later wait returns at once, so the CTA drains in bounded time.
-__device__ inline void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                 int* status) {
-  if (mbar_try(bar, parity)) return;
+// `site` names the call site for the optional wait profile (see FQ_WAIT_PROFILE): the cycles
+// lane 0 of each warp spent blocked are summed per site in the words after the abort flag.
+constexpr int WAIT_SITES = 24;
+static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity,
+                                            volatile int* abort_flag, int* status) {
   const long long t0 = clock64();
   int spins = 0;
   while (!mbar_try(bar, parity)) {
@@ -94,6 +96,23 @@ __device__ inline void mbar_wait(uint32_t bar, uint32_t parity, volatile int* ab
     }
   }
 }
+#ifndef FQ_WAIT_PROFILE
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity,
+                                          volatile int* abort_flag, int* status, int = -1,
+                                          int* = nullptr) {
+  if (!mbar_try(bar, parity)) mbar_wait_slow(bar, parity, abort_flag, status);
+}
+#else
+// Diagnostic build: the cycles each thread spends inside a wait are summed per call site in
+// a thread-local array (constant indices, so it stays in registers).
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity,
+                                          volatile int* abort_flag, int* status, int site = -1,
+                                          int* wprof = nullptr) {
+  const long long t0 = clock64();
+  if (!mbar_try(bar, parity)) mbar_wait_slow(bar, parity, abort_flag, status);
+  if (wprof != nullptr && site >= 0) wprof[site] += static_cast<int>(clock64() - t0);
+}
+#endif
 
 // Bounded wait that ignores the abort flag: used once, at exit, to let a CTA's own bulk copies
 // land before its shared memory is released.
@@ -176,6 +195,36 @@ __host__ __device__ constexpr uint32_t make_idesc_e4m3(int m, int n, int a_mn_ma
          | (static_cast<uint32_t>(a_mn_major) << 15) |
          (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// Descriptor halves: the low word carries the start address (and the leading byte offset), the
+// high word is constant per operand kind, so an issue loop only adds to the low word.
+__device__ inline uint32_t smem_desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+  return ((addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t sbo_bytes, uint32_t layout) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | ((layout & 7u) << 29);
+}
+// Lean issue forms: constant high words, instruction descriptor and accumulate flag.
+template <uint32_t A_HI, uint32_t B_HI, uint32_t IDESC, bool ACC>
+__device__ inline void umma_ss_c(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "n"(A_HI), "n"(B_HI), "n"(IDESC), "n"(ACC ? 1 : 0)
+      : "memory");
+}
+template <uint32_t B_HI, uint32_t IDESC, bool ACC>
+__device__ inline void umma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "n"(B_HI), "n"(IDESC), "n"(ACC ? 1 : 0)
+      : "memory");
 }
 
 // D[tmem] (+)= A[smem] * B[smem]

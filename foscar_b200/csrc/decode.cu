@@ -28,6 +28,11 @@
 
 namespace fq {
 
+#ifdef FQ_WAIT_PROFILE
+// Diagnostic build only: per-CTA cycles (/16) each role spent blocked at each wait site.
+__device__ int* g_wait_profile = nullptr;
+#endif
+
 namespace {
 
 // barrier words: the ring's 2*ns first, then the fixed ones
@@ -50,6 +55,15 @@ struct Bars {
   __device__ uint32_t q_full(int s) const { return at(2 * ns + 32 + s); }
   __device__ uint32_t q_empty(int s) const { return at(2 * ns + 34 + s); }
   __device__ int count() const { return 2 * ns + 36; }
+};
+
+// Position in the code ring: stage and phase, advanced without a division.
+struct RingPos {
+  int s = 0;
+  uint32_t ph = 0;
+  __device__ __forceinline__ void next(int ns) {
+    if (++s == ns) { s = 0; ph ^= 1u; }
+  }
 };
 
 // Tensor-memory column plan (f32 columns): K operand stages, then S and O buffers of 16.
@@ -98,7 +112,8 @@ __device__ inline void expand_row(uint32_t src, uint32_t (&out)[D / 4]) {
 template <int BITS, int D, int GP>
 __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* smem,
                                               uint32_t smem0, uint32_t tmem, const Bars& bars,
-                                              volatile int* abort_flag, const ItemRange items) {
+                                              volatile int* abort_flag, const ItemRange items,
+                                              int* wprof) {
   using SP = SmemPlan<BITS, D>;
   using TP = TmemPlan<D>;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -130,6 +145,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
   const float o_mul = exp2f(static_cast<float>(9 - lp));
 
   int it = 0, ci = 0;
+  RingPos rp;
   for (int wi = items.begin; wi < items.end; wi += items.step, ++ci) {
     const WorkItem w = decode_item(P, wi);
     float m[GP], l[GP], c[GP], oacc[GP], corr_pend[GP], qsum[GP], qs[GP];
@@ -159,7 +175,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
     int pend_buf = 0, pend_ph = 0;
 
     auto accumulate = [&]() {
-      mbar_wait(bars.o_full(wg, pend_buf), pend_ph, abort_flag, status);
+      mbar_wait(bars.o_full(wg, pend_buf), pend_ph, abort_flag, status, 15, wprof);
       tc_fence_after();
       uint32_t r[16];
       tmem_ld16(tmem + lane_base + TP::O + (2 * wg + pend_buf) * 16, r);
@@ -174,11 +190,13 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
     };
 
     for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
+      const int s = rp.s;
+      const uint32_t rph = rp.ph;
+      rp.next(NS);
       if ((it & 1) != wg) continue;
       const int n = it >> 1, buf = n & 1, ph = (n >> 1) & 1;
-      const int s = it % NS;
       // raw scores of token row t
-      mbar_wait(bars.s_full(wg, buf), ph, abort_flag, status);
+      mbar_wait(bars.s_full(wg, buf), ph, abort_flag, status, 12, wprof);
       tc_fence_after();
       uint32_t raw[GP];
       if constexpr (GP == 4) tmem_ld4(tmem + lane_base + TP::S + (2 * wg + buf) * 16, raw);
@@ -188,7 +206,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
       __syncwarp();
       if (lane == 0) mbar_arrive(bars.s_empty(wg, buf));
       // this token's records
-      mbar_wait(bars.ring_full(s), (it / NS) & 1, abort_flag, status);
+      mbar_wait(bars.ring_full(s), rph, abort_flag, status, 13, wprof);
       float sk, zk, sv, zv;
       asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
                    : "=f"(sk), "=f"(zk), "=f"(sv), "=f"(zv)
@@ -239,7 +257,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
         c[h] = c[h] * corr[h] + (valid ? pq * zv : 0.f);
       }
       // the P row: bytes [hi_0..hi_7 | lo_0..lo_7]
-      mbar_wait(bars.p_empty(wg, buf), ph ^ 1, abort_flag, status);
+      mbar_wait(bars.p_empty(wg, buf), ph ^ 1, abort_flag, status, 14, wprof);
       asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
                        smem0 + SP::P_OFF + (2 * wg + buf) * SP::P_BYTES + t * 16),
                    "r"(pw[0]), "r"(pw[1]), "r"(pw[2]), "r"(pw[3])
@@ -332,9 +350,13 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int NS = P.ring_stages;
   Bars bars{smem0 + SP::BAR_OFF, NS};
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SP::BAR_OFF + 1004);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SP::BAR_OFF + 1000);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SP::BAR_OFF + 1024);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SP::BAR_OFF + 1016);
   int* status = P.a.status;
+#ifdef FQ_WAIT_PROFILE
+  const long long kernel_t0 = clock64();
+  if (threadIdx.x < WAIT_SITES) const_cast<int*>(abort_flag)[1 + threadIdx.x] = 0;
+#endif
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -368,116 +390,137 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
 
   const ItemRange items = item_range(P);
   const uint32_t ring0 = smem0 + SP::RING_OFF;
+  int wprof[WAIT_SITES] = {};   // used by the diagnostic build only
 
   if (warp == 16) {
     // ------------------------------------------------------------------ producer
+    // Page ids are fetched 32 at a time, one per lane, a chunk ahead of the tiles that use them,
+    // so the table's load latency is paid once per 16 tiles and overlapped with their copies.
     int it = 0;
+    RingPos rp;
     for (int wi = items.begin; wi < items.end; wi += items.step) {
       const WorkItem w = decode_item(P, wi);
       const int npages = (w.len + PAGE - 1) / PAGE;
-      for (int t = w.t0; t < w.t1; ++t, ++it) {
-        const int s = it % NS;
-        mbar_wait(bars.ring_empty(s), ((it / NS) & 1) ^ 1, abort_flag, status);
-        if (lane == 0) {
-          int ids[2];
-          uint32_t bytes = 0;
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const int pg = 2 * t + j;
-            int id = -1;
-            if (pg < npages) {
-              const long long e = static_cast<long long>(w.table_off) + pg;
-              if (e >= 0 && e < P.a.table_len) id = __ldg(P.a.page_table + e);
-              if (id < 0 || id >= P.p.num_pages) {
-                id = -1;
-                if (status) atomicOr(status, FQ_STATUS_BAD_PAGE);
-              }
-            }
-            ids[j] = id;
-            if (id >= 0) bytes += 2 * SP::CODE_PAGE + SP::SCALE_PAGE;
-          }
-          const uint32_t full = bars.ring_full(s);
-          mbar_expect_tx(full, bytes);
-          const uint32_t dst = ring0 + s * SP::STAGE;
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            if (ids[j] < 0) continue;
-            const long long blk = static_cast<long long>(ids[j]) * P.p.num_kv_heads + w.kvh;
-            bulk_g2s(dst + SP::K_OFF + j * SP::CODE_PAGE, P.p.k_codes + blk * SP::CODE_PAGE,
-                     SP::CODE_PAGE, full);
-            bulk_g2s(dst + SP::V_OFF + j * SP::CODE_PAGE, P.p.v_codes + blk * SP::CODE_PAGE,
-                     SP::CODE_PAGE, full);
-            bulk_g2s(dst + SP::S_OFF + j * SP::SCALE_PAGE,
-                     static_cast<const uint8_t*>(P.p.scales) + blk * SP::SCALE_PAGE,
-                     SP::SCALE_PAGE, full);
+      const int pend = min(2 * w.t1, npages);
+      auto fetch = [&](int pg0) {
+        const int pg = pg0 + lane;
+        int id = -1;
+        if (pg < pend) {
+          const long long e = static_cast<long long>(w.table_off) + pg;
+          if (e >= 0 && e < P.a.table_len) id = __ldg(P.a.page_table + e);
+          if (id < 0 || id >= P.p.num_pages) {
+            id = -1;
+            if (status) atomicOr(status, FQ_STATUS_BAD_PAGE);
           }
         }
-        __syncwarp();
+        return id;
+      };
+      int cur = fetch(2 * w.t0);
+      for (int base = 2 * w.t0; base < 2 * w.t1; base += 32) {
+        const int nxt = base + 32 < 2 * w.t1 ? fetch(base + 32) : -1;
+        for (int k = 0; k < 16 && base + 2 * k < 2 * w.t1; ++k, ++it) {
+          const int id0 = __shfl_sync(0xFFFFFFFFu, cur, 2 * k);
+          const int id1 = __shfl_sync(0xFFFFFFFFu, cur, 2 * k + 1);
+          const int s = rp.s;
+          mbar_wait(bars.ring_empty(s), rp.ph ^ 1u, abort_flag, status, 0, wprof);
+          rp.next(NS);
+          if (lane == 0) {
+            const int ids[2] = {id0, id1};
+            uint32_t bytes = 0;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              if (ids[j] >= 0) bytes += 2 * SP::CODE_PAGE + SP::SCALE_PAGE;
+            const uint32_t full = bars.ring_full(s);
+            mbar_expect_tx(full, bytes);
+            const uint32_t dst = ring0 + s * SP::STAGE;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              if (ids[j] < 0) continue;
+              const long long blk = static_cast<long long>(ids[j]) * P.p.num_kv_heads + w.kvh;
+              bulk_g2s(dst + SP::K_OFF + j * SP::CODE_PAGE, P.p.k_codes + blk * SP::CODE_PAGE,
+                       SP::CODE_PAGE, full);
+              bulk_g2s(dst + SP::V_OFF + j * SP::CODE_PAGE, P.p.v_codes + blk * SP::CODE_PAGE,
+                       SP::CODE_PAGE, full);
+              bulk_g2s(dst + SP::S_OFF + j * SP::SCALE_PAGE,
+                       static_cast<const uint8_t*>(P.p.scales) + blk * SP::SCALE_PAGE,
+                       SP::SCALE_PAGE, full);
+            }
+          }
+          __syncwarp();
+        }
+        cur = nxt;
       }
     }
     // drain: every copy this warp issued has landed once its stage's consumers released it
     // or, for the last NS tiles, once the stage reports full.
     for (int back = 0; back < NS && back < it; ++back) {
-      const int j = it - 1 - back;
-      mbar_wait_drain(bars.ring_full(j % NS), (j / NS) & 1);
+      if (--rp.s < 0) { rp.s = NS - 1; rp.ph ^= 1u; }
+      mbar_wait_drain(bars.ring_full(rp.s), rp.ph);
     }
   } else if (warp == 17) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ S issuer
+    // One thread issues S = C_K . Q^T for every tile. The loop is kept to a few dozen scalar
+    // instructions per tile: descriptor high words, the instruction descriptor and the
+    // accumulate flags are immediates, and every buffer index is a bit of the tile counter.
     if (lane == 0) {
       constexpr uint32_t IDESC_S = make_idesc_e4m3(128, 16, 0, 0);
-      constexpr uint32_t IDESC_PV = make_idesc_e4m3(128, 16, 1, 1);
-      auto issue_pv = [&](int j) {
-        const int wg = j & 1, n = j >> 1, buf = n & 1, ph = (n >> 1) & 1;
-        const int vs = j % V_STAGES, vph = (j / V_STAGES) & 1;
-        mbar_wait(bars.vop_full(vs), vph, abort_flag, status);
-        mbar_wait(bars.p_full(wg, buf), ph, abort_flag, status);
-        mbar_wait(bars.o_empty(wg, buf), ph ^ 1, abort_flag, status);
-        tc_fence_after();
-        const uint32_t va = smem0 + SP::VOP_OFF + vs * SP::VOP_STAGE;
-        const uint32_t pa = smem0 + SP::P_OFF + (2 * wg + buf) * SP::P_BYTES;
-        const uint32_t od = tmem + TP::O + (2 * wg + buf) * 16;
-#pragma unroll
-        for (int k = 0; k < TILE / 32; ++k) {
-          const uint64_t ad = make_smem_desc(va + k * 32 * D, 16, 1024, 2);
-          const uint64_t bd = make_smem_desc(pa + k * 32 * 16, 128, 128, 0);
-          umma_ss(od, ad, bd, IDESC_PV, k > 0);
-        }
-        tc_commit(bars.o_full(wg, buf));
-        tc_commit(bars.vop_empty(vs));
-        tc_commit(bars.p_empty(wg, buf));
-      };
+      constexpr uint32_t Q_HI = smem_desc_hi(1024, 2);
       int it = 0, qi = 0;
       for (int wi = items.begin; wi < items.end; wi += items.step) {
         const WorkItem w = decode_item(P, wi);
         if (w.t1 <= w.t0) continue;
         const int qb = qi & 1;
-        mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status);
-        const uint32_t qa = smem0 + SP::Q_OFF + qb * SP::Q_BYTES;
+        mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status, 1, wprof);
+        const uint32_t q_lo = smem_desc_lo(smem0 + SP::Q_OFF + qb * SP::Q_BYTES, 16);
         for (int t = w.t0; t < w.t1; ++t, ++it) {
-          const int wg = it & 1, n = it >> 1, buf = n & 1, ph = (n >> 1) & 1;
-          const int ks = it % K_STAGES, kph = (it / K_STAGES) & 1;
-          mbar_wait(bars.kop_full(ks), kph, abort_flag, status);
-          mbar_wait(bars.s_empty(wg, buf), ph ^ 1, abort_flag, status);
+          const int wg = it & 1, buf = (it >> 1) & 1, ks = it & 1;
+          const uint32_t ph = (it >> 2) & 1, kph = (it >> 1) & 1;
+          mbar_wait(bars.kop_full(ks), kph, abort_flag, status, 2, wprof);
+          mbar_wait(bars.s_empty(wg, buf), ph ^ 1u, abort_flag, status, 3, wprof);
           tc_fence_after();
           const uint32_t sd = tmem + TP::S + (2 * wg + buf) * 16;
           const uint32_t ka = tmem + TP::KOP + ks * TP::KOP_COLS;
+          umma_ts_c<Q_HI, IDESC_S, false>(sd, ka, q_lo);
 #pragma unroll
-          for (int k = 0; k < D / 32; ++k) {
-            const uint64_t bd = make_smem_desc(qa + k * 32, 16, 1024, 2);
-            umma_ts(sd, ka + k * 8, bd, IDESC_S, k > 0);
-          }
+          for (int k = 1; k < D / 32; ++k)
+            umma_ts_c<Q_HI, IDESC_S, true>(sd, ka + 8 * k, q_lo + 2 * k);
           tc_commit(bars.s_full(wg, buf));
           tc_commit(bars.kop_empty(ks));
           if (t == w.t1 - 1) tc_commit(bars.q_empty(qb));
-          if (it > 0) issue_pv(it - 1);
         }
         ++qi;
       }
-      if (it > 0) issue_pv(it - 1);
-      // wait for the last MMAs before tensor memory is released
-      if (it > 0) {
-        const int j = it - 1, wg = j & 1, n = j >> 1;
-        mbar_wait(bars.o_full(wg, n & 1), (n >> 1) & 1, abort_flag, status);
+    }
+    __syncwarp();
+  } else if (warp == 18) {
+    // ------------------------------------------------------------------ PV issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC_PV = make_idesc_e4m3(128, 16, 1, 1);
+      constexpr uint32_t V_HI = smem_desc_hi(1024, 2), P_HI = smem_desc_hi(128, 0);
+      const uint32_t v_lo0 = smem_desc_lo(smem0 + SP::VOP_OFF, 16);
+      const uint32_t p_lo0 = smem_desc_lo(smem0 + SP::P_OFF, 128);
+      int it = 0;
+      for (int wi = items.begin; wi < items.end; wi += items.step) {
+        const WorkItem w = decode_item(P, wi);
+        for (int t = w.t0; t < w.t1; ++t, ++it) {
+          const int wg = it & 1, buf = (it >> 1) & 1, vs = it & 1;
+          const uint32_t ph = (it >> 2) & 1, vph = (it >> 1) & 1;
+          mbar_wait(bars.vop_full(vs), vph, abort_flag, status, 4, wprof);
+          mbar_wait(bars.p_full(wg, buf), ph, abort_flag, status, 5, wprof);
+          mbar_wait(bars.o_empty(wg, buf), ph ^ 1u, abort_flag, status, 6, wprof);
+          tc_fence_after();
+          const uint32_t v_lo = v_lo0 + vs * (SP::VOP_STAGE >> 4);
+          const uint32_t p_lo = p_lo0 + (2 * wg + buf) * (SP::P_BYTES >> 4);
+          const uint32_t od = tmem + TP::O + (2 * wg + buf) * 16;
+          umma_ss_c<V_HI, P_HI, IDESC_PV, false>(od, v_lo, p_lo);
+#pragma unroll
+          for (int k = 1; k < TILE / 32; ++k)
+            umma_ss_c<V_HI, P_HI, IDESC_PV, true>(od, v_lo + k * (32 * D >> 4),
+                                                  p_lo + k * (32 * 16 >> 4));
+          tc_commit(bars.o_full(wg, buf));
+          tc_commit(bars.vop_empty(vs));
+          tc_commit(bars.p_empty(wg, buf));
+        }
       }
     }
     __syncwarp();
@@ -486,12 +529,13 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     const int t = threadIdx.x - 256;  // token row of the tile, = tensor-memory lane
     const uint32_t lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;
     int it = 0, qi = 0;
+    RingPos rp;
     for (int wi = items.begin; wi < items.end; wi += items.step) {
       const WorkItem w = decode_item(P, wi);
       if (w.t1 <= w.t0) continue;
       {  // this item's query rows, in expansion order, as the S MMA's B operand
         const int qb = qi & 1;
-        mbar_wait(bars.q_empty(qb), ((qi >> 1) & 1) ^ 1, abort_flag, status);
+        mbar_wait(bars.q_empty(qb), ((qi >> 1) & 1) ^ 1, abort_flag, status, 7, wprof);
         const int r = t >> 3, c = t & 7;  // row (head), 16-byte chunk
         uint4 v = make_uint4(0, 0, 0, 0);
         const int hl = w.ht * 8 + r;  // head inside the KV head's group
@@ -517,13 +561,14 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         ++qi;
       }
       for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
-        const int s = it % NS, ks = it % K_STAGES;
-        mbar_wait(bars.ring_full(s), (it / NS) & 1, abort_flag, status);
+        const int s = rp.s, ks = it & 1;
+        mbar_wait(bars.ring_full(s), rp.ph, abort_flag, status, 8, wprof);
+        rp.next(NS);
         uint32_t op[D / 4];
         expand_row<BITS, D>(ring0 + s * SP::STAGE + SP::K_OFF + t * SP::RB, op);
         __syncwarp();
         if (lane == 0) mbar_arrive(bars.ring_empty(s));
-        mbar_wait(bars.kop_empty(ks), ((it / K_STAGES) & 1) ^ 1, abort_flag, status);
+        mbar_wait(bars.kop_empty(ks), ((it >> 1) & 1) ^ 1, abort_flag, status, 9, wprof);
         tc_fence_after();
         const uint32_t dst = tmem + lane_base + TP::KOP + ks * TP::KOP_COLS;
 #pragma unroll
@@ -538,16 +583,18 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     // ------------------------------------------------------------------ V expanders
     const int t = threadIdx.x - 384;
     int it = 0;
+    RingPos rp;
     for (int wi = items.begin; wi < items.end; wi += items.step) {
       const WorkItem w = decode_item(P, wi);
       for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
-        const int s = it % NS, vs = it % V_STAGES;
-        mbar_wait(bars.ring_full(s), (it / NS) & 1, abort_flag, status);
+        const int s = rp.s, vs = it & 1;
+        mbar_wait(bars.ring_full(s), rp.ph, abort_flag, status, 10, wprof);
+        rp.next(NS);
         uint32_t op[D / 4];
         expand_row<BITS, D>(ring0 + s * SP::STAGE + SP::V_OFF + t * SP::RB, op);
         __syncwarp();
         if (lane == 0) mbar_arrive(bars.ring_empty(s));
-        mbar_wait(bars.vop_empty(vs), ((it / V_STAGES) & 1) ^ 1, abort_flag, status);
+        mbar_wait(bars.vop_empty(vs), ((it >> 1) & 1) ^ 1, abort_flag, status, 11, wprof);
         const uint32_t row = smem0 + SP::VOP_OFF + vs * SP::VOP_STAGE + t * D;
 #pragma unroll
         for (int c = 0; c < D / 16; ++c) {
@@ -562,7 +609,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     }
   } else {
     // ------------------------------------------------------------------ consumers
-    consumer_role<BITS, D, GP>(P, smem, smem0, tmem, bars, abort_flag, items);
+    consumer_role<BITS, D, GP>(P, smem, smem0, tmem, bars, abort_flag, items, wprof);
   }
 
   tc_fence_before();
@@ -571,6 +618,19 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     tc_fence_after();
     tmem_dealloc(tmem, TP::ALLOC);
   }
+#ifdef FQ_WAIT_PROFILE
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < WAIT_SITES; ++i)
+      if (wprof[i]) atomicAdd(const_cast<int*>(abort_flag) + 1 + i, wprof[i] >> 4);
+  }
+  __syncthreads();
+  if (g_wait_profile != nullptr && threadIdx.x < WAIT_SITES) {
+    int v = const_cast<int*>(abort_flag)[1 + threadIdx.x];
+    if (threadIdx.x == WAIT_SITES - 1) v = static_cast<int>((clock64() - kernel_t0) >> 4);
+    g_wait_profile[blockIdx.x * WAIT_SITES + threadIdx.x] = v;
+  }
+#endif
 }
 
 // Tensor-core self test (see foscar_b200.h): one tile of both contractions on given operands.
@@ -736,6 +796,12 @@ extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void
   if (pools->bits == 2) return gp == 4 ? launch_decode<2, 128, 4>(P, s) : launch_decode<2, 128, 8>(P, s);
   return gp == 4 ? launch_decode<4, 128, 4>(P, s) : launch_decode<4, 128, 8>(P, s);
 }
+
+#ifdef FQ_WAIT_PROFILE
+extern "C" int fq_debug_set_wait_profile(void* buffer) {
+  return static_cast<int>(cudaMemcpyToSymbol(fq::g_wait_profile, &buffer, sizeof(buffer)));
+}
+#endif
 
 extern "C" int fq_umma_selftest(int32_t mode, const uint8_t* k_bytes, const uint8_t* q_bytes,
                                 const uint8_t* v_bytes, const uint8_t* p_bytes, float* s_out,

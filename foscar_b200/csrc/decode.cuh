@@ -7,7 +7,7 @@ namespace fq {
 
 constexpr int TILE = 128;            // tokens per sequence tile: two pages
 constexpr int WORK_WORDS = 8;        // int32 words per explicit work-list row
-constexpr int DECODE_THREADS = 576;  // 18 warps, see decode.cu
+constexpr int DECODE_THREADS = 608;  // 19 warps, see decode.cu
 constexpr int K_STAGES = 2;          // K operand stages in tensor memory
 constexpr int V_STAGES = 2;          // V operand stages in shared memory
 constexpr int SMEM_LIMIT = 232448;   // 227 KiB opt-in limit per CTA on sm_100
@@ -46,7 +46,7 @@ struct SmemPlan {
   static constexpr int RED_OFF = XCHG_OFF + 2 * XCHG_BYTES;  // cross-warp reduction scratch
   static constexpr int RED_BYTES = 2048;
   static constexpr int BAR_OFF = RED_OFF + RED_BYTES;
-  static constexpr int BAR_BYTES = 1024;
+  static constexpr int BAR_BYTES = 2048;   // barriers, then flags and diagnostics
   static constexpr int RING_OFF = (BAR_OFF + BAR_BYTES + 1023) / 1024 * 1024;
   static constexpr int max_ring_stages() {
     return (SMEM_LIMIT - 1024 /*alignment slack*/ - RING_OFF) / STAGE;
