@@ -424,26 +424,29 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           const int s = rp.s;
           mbar_wait(bars.ring_empty(s), rp.ph ^ 1u, abort_flag, status, 0, wprof);
           rp.next(NS);
+          const uint32_t full = bars.ring_full(s);
           if (lane == 0) {
-            const int ids[2] = {id0, id1};
-            uint32_t bytes = 0;
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-              if (ids[j] >= 0) bytes += 2 * SP::CODE_PAGE + SP::SCALE_PAGE;
-            const uint32_t full = bars.ring_full(s);
-            mbar_expect_tx(full, bytes);
-            const uint32_t dst = ring0 + s * SP::STAGE;
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              if (ids[j] < 0) continue;
-              const long long blk = static_cast<long long>(ids[j]) * P.p.num_kv_heads + w.kvh;
-              bulk_g2s(dst + SP::K_OFF + j * SP::CODE_PAGE, P.p.k_codes + blk * SP::CODE_PAGE,
-                       SP::CODE_PAGE, full);
-              bulk_g2s(dst + SP::V_OFF + j * SP::CODE_PAGE, P.p.v_codes + blk * SP::CODE_PAGE,
-                       SP::CODE_PAGE, full);
-              bulk_g2s(dst + SP::S_OFF + j * SP::SCALE_PAGE,
-                       static_cast<const uint8_t*>(P.p.scales) + blk * SP::SCALE_PAGE,
-                       SP::SCALE_PAGE, full);
+            const uint32_t per_page = 2 * SP::CODE_PAGE + SP::SCALE_PAGE;
+            mbar_expect_tx(full, (id0 >= 0 ? per_page : 0u) + (id1 >= 0 ? per_page : 0u));
+          }
+          __syncwarp();
+          // six copies per tile, one per lane: (page 0|1) x (K codes, V codes, scale records)
+          if (lane < 6) {
+            const int j = lane >= 3 ? 1 : 0, kind = lane - 3 * j;
+            const int id = j ? id1 : id0;
+            if (id >= 0) {
+              const long long blk = static_cast<long long>(id) * P.p.num_kv_heads + w.kvh;
+              const uint32_t dst = ring0 + s * SP::STAGE;
+              if (kind == 0)
+                bulk_g2s(dst + SP::K_OFF + j * SP::CODE_PAGE, P.p.k_codes + blk * SP::CODE_PAGE,
+                         SP::CODE_PAGE, full);
+              else if (kind == 1)
+                bulk_g2s(dst + SP::V_OFF + j * SP::CODE_PAGE, P.p.v_codes + blk * SP::CODE_PAGE,
+                         SP::CODE_PAGE, full);
+              else
+                bulk_g2s(dst + SP::S_OFF + j * SP::SCALE_PAGE,
+                         static_cast<const uint8_t*>(P.p.scales) + blk * SP::SCALE_PAGE,
+                         SP::SCALE_PAGE, full);
             }
           }
           __syncwarp();

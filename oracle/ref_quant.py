@@ -207,6 +207,8 @@ def _write_tokens(pools: CpuPools, slots, k_codes, k_s, k_z, v_codes, v_s, v_z):
     if (slots[valid] >= pools.num_pages * PAGE).any():
         raise IndexError("slot outside the cache")
     idx = np.nonzero(valid)[0]
+    if len(idx) == 0:
+        return
     page, pos = slots[idx] // PAGE, slots[idx] % PAGE
     kq = pack_rows(k_codes[idx], pools.bits)
     vq = pack_rows(v_codes[idx], pools.bits)

@@ -1,0 +1,101 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header declares, and
+its host-only planners keep their invariants (every tile covered exactly once, balanced CTAs).
+No compute entry point is called here."""
+import os
+import re
+
+import numpy as np
+import pytest
+
+from foscar_b200 import _build, _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "foscar_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fq_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_builds_loads_and_exports_the_header():
+    path = _build.build()
+    assert os.path.exists(path)
+    lib = _lib.load()
+    names = _declared_functions()
+    assert "fq_decode" in names and "fq_append" in names and len(names) >= 14
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert sorted(_lib.EXPORTS) == names
+    assert lib.fq_version().decode().startswith("foscar_b200")
+    assert lib.fq_error_string(-2).decode() == "unsupported configuration"
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setenv("FOSCAR_B200_LIB", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.load()
+
+
+def _plan(lens, hkv, ht, ctas, cap=64):
+    lib = _lib.load()
+    lens = np.asarray(lens, dtype=np.int32)
+    words = int(lib.fq_worklist_words(len(lens), hkv, ht, ctas))
+    work = np.zeros(words, dtype=np.int32)
+    counts = np.zeros(len(lens) * hkv * ht, dtype=np.int32)
+    n = lib.fq_plan_worklist(lens.ctypes.data, len(lens), hkv, ht, ctas, cap, work.ctypes.data,
+                             words, counts.ctypes.data)
+    return n, work, counts
+
+
+@pytest.mark.parametrize("lens,hkv,ht,ctas", [
+    ([128, 128], 8, 1, 148), ([1, 63, 64, 65, 5000, 131072], 8, 1, 148), ([100352], 8, 1, 148),
+    (list(range(1, 300, 7)), 2, 2, 148), ([0, 5, 0], 1, 1, 4), ([70000] * 3, 1, 1, 7),
+])
+def test_worklist_covers_every_tile_once(lens, hkv, ht, ctas):
+    n, work, counts = _plan(lens, hkv, ht, ctas)
+    assert n > 0 and work[0] == n and work[1] == len(lens) * hkv * ht and work[2] == ctas
+    starts = work[8:8 + ctas + 1]
+    assert starts[0] == 0 and starts[-1] == n and np.all(np.diff(starts) >= 0)
+    rows = work[work[3]:work[3] + 8 * n].reshape(n, 8)
+    tiles = {b: -(-l // 128) if l > 0 else 0 for b, l in enumerate(lens)}
+    seen = {}
+    for b, kvh, t, t0, t1, slot, _, _ in rows:
+        assert 0 <= b < len(lens) and 0 <= kvh < hkv and 0 <= t < ht and 0 <= t0 <= t1
+        seen.setdefault((b, kvh, t), []).append((t0, t1, slot))
+    assert len(seen) == len(lens) * hkv * ht
+    for (b, kvh, t), pieces in seen.items():
+        pieces.sort()
+        assert pieces[0][0] == 0 and pieces[-1][1] == tiles[b]
+        for (a0, a1, _), (b0, _, _) in zip(pieces, pieces[1:]):
+            assert a1 == b0 and a1 > a0
+        k = counts[(b * hkv + kvh) * ht + t]
+        assert k == len(pieces)
+        assert [p[2] for p in pieces] == ([-1] if k == 1 else list(range(k)))
+    load = np.array([(rows[starts[c]:starts[c + 1], 4] - rows[starts[c]:starts[c + 1], 3]).sum()
+                     for c in range(ctas)])
+    total = load.sum()
+    if total > 50 * ctas:
+        assert load.max() <= total / ctas * 1.15 + 8
+
+
+def test_worklist_respects_the_split_cap_and_buffer():
+    n, _, _ = _plan([131072], 1, 1, 148, cap=4)
+    assert n == _lib.ERR_TOO_LARGE
+    lib = _lib.load()
+    lens = np.array([100], dtype=np.int32)
+    small = np.zeros(16, dtype=np.int32)
+    counts = np.zeros(8, dtype=np.int32)
+    assert lib.fq_plan_worklist(lens.ctypes.data, 1, 8, 1, 148, 64, small.ctypes.data, 16,
+                                counts.ctypes.data) == _lib.ERR_TOO_LARGE
+
+
+def test_uniform_planner_behaviour():
+    lib = _lib.load()
+    assert lib.fq_plan_splits(64, 8, 1, 16384, 2, 128, 148) == 1      # enough units: no split
+    s1 = lib.fq_plan_splits(1, 8, 1, 100352, 2, 128, 148)
+    assert 8 <= s1 <= 64                                               # one long request: split
+    assert lib.fq_plan_splits(1, 8, 1, 256, 2, 128, 148) == 1          # too short to split
+    assert lib.fq_plan_splits(0, 8, 1, 256, 2, 128, 148) == _lib.ERR_BAD_ARG
+    assert lib.fq_workspace_bytes(4, 2, 32, 128) == 4 * 4 * 2 * 32 * 130
