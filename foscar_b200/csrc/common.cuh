@@ -146,6 +146,16 @@ __device__ inline void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, u
       : "memory");
 }
 
+// 16-byte asynchronous copy global -> shared issued by a thread (LSU path, bypassing L1), and the
+// arrive that fires on an mbarrier once all of this thread's earlier copies have landed. The
+// barrier's expected count must include these arrivals (".noinc").
+__device__ inline void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ inline void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // PTX: tcgen05 (tensor memory + 5th-generation tensor cores)
 // ---------------------------------------------------------------------------------------------

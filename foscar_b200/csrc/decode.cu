@@ -26,6 +26,19 @@
 // stored through it, so no per-element fix-up exists anywhere.
 #include "decode.cuh"
 
+#ifdef FQ_WAIT_PROFILE
+#define FQ_STAMP_BEGIN() long long stamp_t = clock64()
+#define FQ_STAMP(site)                                            \
+  do {                                                            \
+    const long long now_ = clock64();                             \
+    wprof[site] += static_cast<int>(now_ - stamp_t);              \
+    stamp_t = now_;                                               \
+  } while (0)
+#else
+#define FQ_STAMP_BEGIN() ((void)0)
+#define FQ_STAMP(site) ((void)0)
+#endif
+
 namespace fq {
 
 #ifdef FQ_WAIT_PROFILE
@@ -197,6 +210,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
       const int n = it >> 1, buf = n & 1, ph = (n >> 1) & 1;
       // raw scores of token row t
       mbar_wait(bars.s_full(wg, buf), ph, abort_flag, status, 12, wprof);
+      FQ_STAMP_BEGIN();
       tc_fence_after();
       uint32_t raw[GP];
       if constexpr (GP == 4) tmem_ld4(tmem + lane_base + TP::S + (2 * wg + buf) * 16, raw);
@@ -205,6 +219,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars.s_empty(wg, buf));
+      FQ_STAMP(17);
       // this token's records
       mbar_wait(bars.ring_full(s), rph, abort_flag, status, 13, wprof);
       float sk, zk, sv, zv;
@@ -213,6 +228,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
                    : "r"(ring0 + s * SP::STAGE + SP::S_OFF + t * 16));
       __syncwarp();
       if (lane == 0) mbar_arrive(bars.ring_empty(s));
+      FQ_STAMP(18);
       const bool valid = tt * TILE + t < w.len;
       const float a_k = sk * 512.f;
       float x[GP];
@@ -224,6 +240,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
         if (lane == 0) wmax[h] = key_float(key);
       }
       named_barrier(1 + wg, 128);
+      FQ_STAMP(19);
       const float wsc = sv * p2lp;
       const float inv = valid ? __fdividef(1.f, wsc) : 0.f;
       float hi_f[GP], lo_f[GP], e[GP], corr[GP];
@@ -256,6 +273,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
         l[h] = l[h] * corr[h] + e[h];
         c[h] = c[h] * corr[h] + (valid ? pq * zv : 0.f);
       }
+      FQ_STAMP(20);
       // the P row: bytes [hi_0..hi_7 | lo_0..lo_7]
       mbar_wait(bars.p_empty(wg, buf), ph ^ 1, abort_flag, status, 14, wprof);
       asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
@@ -265,8 +283,10 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars.p_full(wg, buf));
+      FQ_STAMP(21);
       // the previous tile's O, now that its MMA has had a tile's time to finish
       if (pending) accumulate();
+      FQ_STAMP(22);
 #pragma unroll
       for (int h = 0; h < GP; ++h) corr_pend[h] = corr[h];
       pending = true; pend_buf = buf; pend_ph = ph;
@@ -361,7 +381,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < NS; ++s) {
-      mbar_init(bars.ring_full(s), 1);
+      mbar_init(bars.ring_full(s), 33);   // the TMA expect-tx arrive + 32 cp.async arrivals
       mbar_init(bars.ring_empty(s), 12);  // 4 K-expander + 4 V-expander + 4 consumer warps
     }
     for (int s = 0; s < 2; ++s) {
@@ -425,30 +445,35 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           mbar_wait(bars.ring_empty(s), rp.ph ^ 1u, abort_flag, status, 0, wprof);
           rp.next(NS);
           const uint32_t full = bars.ring_full(s);
-          if (lane == 0) {
-            const uint32_t per_page = 2 * SP::CODE_PAGE + SP::SCALE_PAGE;
-            mbar_expect_tx(full, (id0 >= 0 ? per_page : 0u) + (id1 >= 0 ? per_page : 0u));
-          }
+          const uint32_t dst = ring0 + s * SP::STAGE;
+          const long long blk0 = static_cast<long long>(id0) * P.p.num_kv_heads + w.kvh;
+          const long long blk1 = static_cast<long long>(id1) * P.p.num_kv_heads + w.kvh;
+          // V code pages ride the TMA engine (one bulk copy per page, ~110 cycles of engine time
+          // each whatever the size); K code pages and scale records go as 16-byte asynchronous
+          // copies issued by all 32 lanes, so neither path is the per-tile limit.
+          if (lane == 0)
+            mbar_expect_tx(full, (id0 >= 0 ? SP::CODE_PAGE : 0) + (id1 >= 0 ? SP::CODE_PAGE : 0));
           __syncwarp();
-          // six copies per tile, one per lane: (page 0|1) x (K codes, V codes, scale records)
-          if (lane < 6) {
-            const int j = lane >= 3 ? 1 : 0, kind = lane - 3 * j;
-            const int id = j ? id1 : id0;
-            if (id >= 0) {
-              const long long blk = static_cast<long long>(id) * P.p.num_kv_heads + w.kvh;
-              const uint32_t dst = ring0 + s * SP::STAGE;
-              if (kind == 0)
-                bulk_g2s(dst + SP::K_OFF + j * SP::CODE_PAGE, P.p.k_codes + blk * SP::CODE_PAGE,
-                         SP::CODE_PAGE, full);
-              else if (kind == 1)
-                bulk_g2s(dst + SP::V_OFF + j * SP::CODE_PAGE, P.p.v_codes + blk * SP::CODE_PAGE,
-                         SP::CODE_PAGE, full);
-              else
-                bulk_g2s(dst + SP::S_OFF + j * SP::SCALE_PAGE,
-                         static_cast<const uint8_t*>(P.p.scales) + blk * SP::SCALE_PAGE,
-                         SP::SCALE_PAGE, full);
-            }
+          if (lane < 2) {
+            const int id = lane ? id1 : id0;
+            if (id >= 0)
+              bulk_g2s(dst + SP::V_OFF + lane * SP::CODE_PAGE,
+                       P.p.v_codes + (lane ? blk1 : blk0) * SP::CODE_PAGE, SP::CODE_PAGE, full);
           }
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            if ((j ? id1 : id0) < 0) continue;
+            const long long blk = j ? blk1 : blk0;
+            const uint8_t* ks = P.p.k_codes + blk * SP::CODE_PAGE;
+            const uint8_t* ss = static_cast<const uint8_t*>(P.p.scales) + blk * SP::SCALE_PAGE;
+#pragma unroll
+            for (int c = 0; c < SP::CODE_PAGE / 16; c += 32)
+              cp_async16(dst + SP::K_OFF + j * SP::CODE_PAGE + 16 * (c + lane), ks + 16 * (c + lane));
+#pragma unroll
+            for (int c = 0; c < SP::SCALE_PAGE / 16; c += 32)
+              cp_async16(dst + SP::S_OFF + j * SP::SCALE_PAGE + 16 * (c + lane), ss + 16 * (c + lane));
+          }
+          cp_async_arrive(full);
           __syncwarp();
         }
         cur = nxt;
