@@ -73,6 +73,20 @@ __device__ inline bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same with a suspend-time hint (ns): the waiting thread sleeps in hardware until the phase
+// completes or the hint elapses, instead of re-polling the shared-memory pipe.
+__device__ inline bool mbar_try_sleep(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(100000u)
+      : "memory");
+  return ok != 0;
+}
+
 // Cycle budget of one wait: about a second at B200 clocks.
 constexpr long long WAIT_BUDGET_CYCLES = 2000000000LL;
 
@@ -80,19 +94,16 @@ constexpr long long WAIT_BUDGET_CYCLES = 2000000000LL;
 // given up every later wait returns at once, so the CTA drains in bounded time.
 // `site` names the call site for the optional wait profile (see FQ_WAIT_PROFILE): the cycles
 // lane 0 of each warp spent blocked are summed per site in the words after the abort flag.
-constexpr int WAIT_SITES = 24;
+constexpr int WAIT_SITES = 32;
 static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity,
                                             volatile int* abort_flag, int* status) {
   const long long t0 = clock64();
-  int spins = 0;
-  while (!mbar_try(bar, parity)) {
-    if ((++spins & 31) == 0) {
-      if (*abort_flag) return;
-      if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
-        *abort_flag = 1;
-        if (status) atomicOr(status, FQ_STATUS_TIMEOUT);
-        return;
-      }
+  while (!mbar_try_sleep(bar, parity)) {
+    if (*abort_flag) return;
+    if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
+      *abort_flag = 1;
+      if (status) atomicOr(status, FQ_STATUS_TIMEOUT);
+      return;
     }
   }
 }

@@ -4,23 +4,30 @@
 // fold algebra src/foscar/_sm100/int_fold_decode.py:5-22, 378-434): codes are never
 // dequantized. For token t and query head h
 //     score = s_k[t] * (q_h . c_k[t]) + z_k[t] * sum(q_h)          (times sm_scale)
-//     out_h = ( sum_t w[t,h] c_v[t]  +  sum_t p~[t,h] z_v[t] ) / sum_t p[t,h]
-// with w = p * s_v * 2^lp stored as two E4M3 planes (hi + lo/16) and p~ = w / (s_v 2^lp).
-// The structure is this library's own:
+//     out_h = ( sum_t w[t,h] c_v[t]  +  sum_t p[t,h] z_v[t] ) / sum_t p[t,h]
+// with w = p * s_v * 2^lp stored as two E4M3 planes (hi + lo/16).
+// The structure is this library's own. One persistent CTA per SM, 28 warps, 128-token tiles:
 //
-//   warp 16      producer: per 128-token tile, bulk async copies (TMA engine) of the two pages'
-//                K codes, V codes and scale records into a deep shared-memory ring.
-//   warps 8-11   K expanders: thread t unpacks token t's codes to exact E4M3 bytes (code * 2^-9)
-//                and stores them straight into TENSOR MEMORY as the MMA's A operand (no
-//                shared-memory round trip for K).
-//   warps 12-15  V expanders: same unpack, written to a 128-byte-swizzled shared-memory stage.
-//   warp 17      MMA issuer (one thread): S[128 tok x 16] = C_K . Q^T  (A from tensor memory),
-//                O^T[128 ch x 16] = C_V^T . [P_hi | P_lo]  (A MN-major from shared memory).
-//   warps 0-3, 4-7  two consumer groups taking alternate tiles, each with its own running
-//                (m, l, O): thread t folds the scales into S row t, joins the group's column
-//                max, writes its P row; then thread d accumulates channel d of the tile's O.
-//                The two groups are merged once per work item.
+//   warps 24, 27  producers on alternate tiles: page ids fetched 32 at a time a chunk ahead; a
+//                 tile's two pages (K codes, V codes, scale records) as 16-byte cp.async copies
+//                 from all lanes into a deep shared-memory ring, completion on an mbarrier.
+//   warps 16-19   K expanders: thread t unpacks token t's K row to exact E4M3 bytes (code * 2^-9)
+//                 and stores it straight into TENSOR MEMORY as the S MMA's A operand (no
+//                 shared-memory round trip for K).
+//   warps 20-23   V expanders: same unpack into a 128-byte-swizzled shared-memory stage, as late
+//                 as the PV MMA allows (the packed codes wait in the ring, 4x smaller).
+//   warp 25       S issuer (one thread):  S[128 tok x 16] = C_K . Q^T   (A from tensor memory)
+//   warp 26       PV issuer (one thread): O^T[128 ch x 16] = C_V^T . [P_hi | P_lo]
+//   warps 0-15    four consumer groups, tile i -> group i % 4, each with its own running
+//                 (m, l, c, O): thread t folds the scales into S row t, joins the group's column
+//                 max, writes its P row; one tile later thread d accumulates channel d of the
+//                 tile's O. The groups are merged once per work item.
 //
+// Why four consumer groups: a group's per-tile work is a chain of dependent latencies
+// (tensor-memory loads, shared-memory round trips, mbarrier waits) of roughly 1800 cycles, while
+// a tile must retire every ~470 cycles to stream INT2 codes at 6 TB/s; the groups overlap those
+// chains. A tile's K and V operands stay live from expansion to the end of its MMA (a chain of
+// ~2500 cycles through the softmax), hence four operand stages each.
 // Every role walks the same list of work items, so the pipeline never drains between items.
 // Byte-expansion yields channels in a fixed permuted order; Q is loaded in that order and O is
 // stored through it, so no per-element fix-up exists anywhere.
@@ -52,22 +59,23 @@ namespace {
 struct Bars {
   uint32_t base;
   int ns;
+  static constexpr int G = CONSUMER_GROUPS;
   __device__ uint32_t at(int i) const { return base + 8u * i; }
   __device__ uint32_t ring_full(int s) const { return at(s); }
   __device__ uint32_t ring_empty(int s) const { return at(ns + s); }
   __device__ uint32_t kop_full(int s) const { return at(2 * ns + s); }
-  __device__ uint32_t kop_empty(int s) const { return at(2 * ns + 2 + s); }
-  __device__ uint32_t vop_full(int s) const { return at(2 * ns + 4 + s); }
-  __device__ uint32_t vop_empty(int s) const { return at(2 * ns + 6 + s); }
-  __device__ uint32_t s_full(int wg, int s) const { return at(2 * ns + 8 + 2 * wg + s); }
-  __device__ uint32_t s_empty(int wg, int s) const { return at(2 * ns + 12 + 2 * wg + s); }
-  __device__ uint32_t p_full(int wg, int s) const { return at(2 * ns + 16 + 2 * wg + s); }
-  __device__ uint32_t p_empty(int wg, int s) const { return at(2 * ns + 20 + 2 * wg + s); }
-  __device__ uint32_t o_full(int wg, int s) const { return at(2 * ns + 24 + 2 * wg + s); }
-  __device__ uint32_t o_empty(int wg, int s) const { return at(2 * ns + 28 + 2 * wg + s); }
-  __device__ uint32_t q_full(int s) const { return at(2 * ns + 32 + s); }
-  __device__ uint32_t q_empty(int s) const { return at(2 * ns + 34 + s); }
-  __device__ int count() const { return 2 * ns + 36; }
+  __device__ uint32_t kop_empty(int s) const { return at(2 * ns + 4 + s); }
+  __device__ uint32_t vop_full(int s) const { return at(2 * ns + 8 + s); }
+  __device__ uint32_t vop_empty(int s) const { return at(2 * ns + 12 + s); }
+  __device__ uint32_t q_full(int s) const { return at(2 * ns + 16 + s); }
+  __device__ uint32_t q_empty(int s) const { return at(2 * ns + 18 + s); }
+  __device__ uint32_t s_full(int wg, int s) const { return at(2 * ns + 20 + 2 * wg + s); }
+  __device__ uint32_t s_empty(int wg, int s) const { return at(2 * ns + 20 + 2 * G + 2 * wg + s); }
+  __device__ uint32_t p_full(int wg, int s) const { return at(2 * ns + 20 + 4 * G + 2 * wg + s); }
+  __device__ uint32_t p_empty(int wg, int s) const { return at(2 * ns + 20 + 6 * G + 2 * wg + s); }
+  __device__ uint32_t o_full(int wg, int s) const { return at(2 * ns + 20 + 8 * G + 2 * wg + s); }
+  __device__ uint32_t o_empty(int wg, int s) const { return at(2 * ns + 20 + 10 * G + 2 * wg + s); }
+  // 2*ns + 20 + 12*G words of 8 bytes: 68 + 2*ns <= 108 at ns <= 20 (864 of 1016 bytes)
 };
 
 // Position in the code ring: stage and phase, advanced without a division.
@@ -79,49 +87,63 @@ struct RingPos {
   }
 };
 
-// Tensor-memory column plan (f32 columns): K operand stages, then S and O buffers of 16.
+// Tensor-memory column plan (f32 columns): K operand stages, then S and O buffers of 16 columns,
+// two per consumer group.
 template <int D>
 struct TmemPlan {
   static constexpr int KOP_COLS = D / 4;
   static constexpr int KOP = 0;
-  static constexpr int S = K_STAGES * KOP_COLS;  // 4 buffers: [wg][2]
-  static constexpr int O = S + 4 * 16;           // 4 buffers: [wg][2]
-  static constexpr int USED = O + 4 * 16;
+  static constexpr int S = K_STAGES * KOP_COLS;
+  static constexpr int O = S + 2 * CONSUMER_GROUPS * 16;
+  static constexpr int USED = O + 2 * CONSUMER_GROUPS * 16;
   static constexpr int ALLOC = USED <= 128 ? 128 : (USED <= 256 ? 256 : 512);
+  static_assert(USED <= 512, "tensor memory plan exceeds 512 columns");
 };
 
-// order-preserving float <-> int key for integer warp reductions
-__device__ inline int float_key(float x) {
-  const int b = __float_as_int(x);
-  return b ^ ((b >> 31) & 0x7FFFFFFF);
+__device__ inline float warp_max_f32(float x) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
+  return r;
 }
-__device__ inline float key_float(int k) {
-  return __int_as_float(k ^ ((k >> 31) & 0x7FFFFFFF));
+__device__ inline __half2 h2_exp2(__half2 x) {
+  uint32_t r, a = *reinterpret_cast<uint32_t*>(&x);
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(r) : "r"(a));
+  return *reinterpret_cast<__half2*>(&r);
+}
+__device__ inline uint32_t f16x2_to_e4m3x2(__half2 x) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(r) : "r"(*reinterpret_cast<uint32_t*>(&x)));
+  return r;
+}
+__device__ inline __half2 e4m3x2_to_f16x2(uint32_t v) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(static_cast<uint16_t>(v)));
+  return *reinterpret_cast<__half2*>(&r);
 }
 
-// Unpack this thread's token row (RB bytes at `src`) into exact operand bytes, one per code, in
-// expansion order: out[(32/BITS/4) * wi + k] = (w[wi] >> (BITS * k)) & mask.
+// Load this thread's token row (RB bytes at `src`) as packed words.
 template <int BITS, int D>
-__device__ inline void expand_row(uint32_t src, uint32_t (&out)[D / 4]) {
-  constexpr int WORDS = D * BITS / 32;
+__device__ inline void load_row(uint32_t src, uint32_t (&w)[D * BITS / 32]) {
+#pragma unroll
+  for (int v = 0; v < D * BITS / 128; ++v)
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(w[4 * v]), "=r"(w[4 * v + 1]), "=r"(w[4 * v + 2]), "=r"(w[4 * v + 3])
+                 : "r"(src + 16 * v));
+}
+// Unpack packed words into exact operand bytes, one per code, in expansion order:
+// out[(8/BITS) * wi + k] = (w[wi] >> (BITS * k)) & mask.
+template <int BITS, int D>
+__device__ inline void expand_words(const uint32_t (&w)[D * BITS / 32], uint32_t (&out)[D / 4]) {
   constexpr uint32_t MASK = BITS == 2 ? 0x03030303u : 0x0F0F0F0Fu;
   constexpr int PER = 8 / BITS;  // output words per input word
 #pragma unroll
-  for (int v = 0; v < WORDS / 4; ++v) {
-    uint32_t w[4];
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-                 : "r"(src + 16 * v));
+  for (int i = 0; i < D * BITS / 32; ++i)
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int k = 0; k < PER; ++k) out[PER * (4 * v + i) + k] = (w[i] >> (BITS * k)) & MASK;
-  }
+    for (int k = 0; k < PER; ++k) out[PER * i + k] = (w[i] >> (BITS * k)) & MASK;
 }
 
-
-// Consumer role: one of two 128-thread groups; group `wg` takes the tiles whose running index
-// has parity `wg` and keeps its own (m, l, c, O), merged with the other group per work item.
+// Consumer role: one of four 128-thread groups; group `wg` takes the tiles whose running index
+// is `wg` modulo 4 and keeps its own (m, l, c, O), merged with the other groups per work item.
 template <int BITS, int D, int GP>
 __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* smem,
                                               uint32_t smem0, uint32_t tmem, const Bars& bars,
@@ -129,6 +151,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
                                               int* wprof) {
   using SP = SmemPlan<BITS, D>;
   using TP = TmemPlan<D>;
+  constexpr int G = CONSUMER_GROUPS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wg = warp >> 2, wq = warp & 3;
   const int t = threadIdx.x & 127;  // token row in softmax, channel position in accumulation
@@ -157,9 +180,9 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
   const float p2lp = exp2f(static_cast<float>(lp));
   const float o_mul = exp2f(static_cast<float>(9 - lp));
 
-  int it = 0, ci = 0;
+  int it = 0;
   RingPos rp;
-  for (int wi = items.begin; wi < items.end; wi += items.step, ++ci) {
+  for (int wi = items.begin; wi < items.end; wi += items.step) {
     const WorkItem w = decode_item(P, wi);
     float m[GP], l[GP], c[GP], oacc[GP], corr_pend[GP], qsum[GP], qs[GP];
 #pragma unroll
@@ -198,16 +221,16 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
       if (lane == 0) mbar_arrive(bars.o_empty(wg, pend_buf));
 #pragma unroll
       for (int h = 0; h < GP; ++h)
-        oacc[h] = oacc[h] * corr_pend[h] +
-                  (__uint_as_float(r[h]) + __uint_as_float(r[8 + h]) * 0.0625f);
+        oacc[h] = fmaf(oacc[h], corr_pend[h],
+                       fmaf(__uint_as_float(r[8 + h]), 0.0625f, __uint_as_float(r[h])));
     };
 
     for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
       const int s = rp.s;
       const uint32_t rph = rp.ph;
       rp.next(NS);
-      if ((it & 1) != wg) continue;
-      const int n = it >> 1, buf = n & 1, ph = (n >> 1) & 1;
+      if ((it & (G - 1)) != wg) continue;
+      const int n = it / G, buf = n & 1, ph = (n >> 1) & 1;
       // raw scores of token row t
       mbar_wait(bars.s_full(wg, buf), ph, abort_flag, status, 12, wprof);
       FQ_STAMP_BEGIN();
@@ -229,49 +252,76 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
       __syncwarp();
       if (lane == 0) mbar_arrive(bars.ring_empty(s));
       FQ_STAMP(18);
-      const bool valid = tt * TILE + t < w.len;
+      // Only a request's last tile has positions past its length: their scores become -inf and
+      // their records are neutralised, so stale shared memory can never reach the output.
+      const bool valid = (tt + 1) * TILE <= w.len || tt * TILE + t < w.len;
       const float a_k = sk * 512.f;
+      float wsc = sv * p2lp;
+      if (!valid) { wsc = 0.f; zv = 0.f; }
       float x[GP];
       float* wmax = red_max + ((wg * 2 + buf) * 4 + wq) * 8;
 #pragma unroll
       for (int h = 0; h < GP; ++h) {
-        x[h] = valid ? qs[h] * fmaf(a_k, __uint_as_float(raw[h]), zk * qsum[h]) : -INFINITY;
-        const int key = __reduce_max_sync(0xFFFFFFFFu, float_key(x[h]));
-        if (lane == 0) wmax[h] = key_float(key);
+        const float xv = qs[h] * fmaf(a_k, __uint_as_float(raw[h]), zk * qsum[h]);
+        x[h] = valid ? xv : -INFINITY;
+        const float wm = warp_max_f32(x[h]);
+        if (lane == 0) wmax[h] = wm;
       }
       named_barrier(1 + wg, 128);
       FQ_STAMP(19);
-      const float wsc = sv * p2lp;
-      const float inv = valid ? __fdividef(1.f, wsc) : 0.f;
-      float hi_f[GP], lo_f[GP], e[GP], corr[GP];
-      const float* gmax = red_max + (wg * 2 + buf) * 4 * 8;
+      // the group's tile maximum: four warps' values, read as 16-byte vectors
+      float tm[GP];
+      {
+        const uint32_t g0 = smem0 + SP::RED_OFF + (wg * 2 + buf) * 4 * 8 * 4;
+#pragma unroll
+        for (int v4 = 0; v4 < GP / 4; ++v4) {
+          float a4[4][4];
+#pragma unroll
+          for (int wv = 0; wv < 4; ++wv)
+            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                         : "=f"(a4[wv][0]), "=f"(a4[wv][1]), "=f"(a4[wv][2]), "=f"(a4[wv][3])
+                         : "r"(g0 + wv * 32 + v4 * 16));
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            tm[4 * v4 + i] = fmaxf(fmaxf(a4[0][i], a4[1][i]), fmaxf(a4[2][i], a4[3][i]));
+        }
+      }
+      // the running maximum rarely moves after the first tiles: the rescale is a uniform branch
+      float corr[GP];
+      bool moved = false;
 #pragma unroll
       for (int h = 0; h < GP; ++h) {
-        const float tm = fmaxf(fmaxf(gmax[h], gmax[8 + h]), fmaxf(gmax[16 + h], gmax[24 + h]));
-        const float mn = fmaxf(m[h], tm);
-        corr[h] = m[h] == -INFINITY ? 0.f : fast_exp2(m[h] - mn);
-        m[h] = mn;
-        e[h] = valid ? fast_exp2(x[h] - mn) : 0.f;
+        tm[h] = fmaxf(m[h], tm[h]);
+        moved |= tm[h] != m[h];
+        corr[h] = 1.f;
       }
+      if (moved) {
+#pragma unroll
+        for (int h = 0; h < GP; ++h) {
+          corr[h] = m[h] == -INFINITY ? 0.f : fast_exp2(m[h] - tm[h]);
+          l[h] *= corr[h];
+          c[h] *= corr[h];
+          m[h] = tm[h];
+        }
+      }
+      // two heads per instruction in f16x2: p = 2^(x-m), w = p * s_v 2^lp, E4M3 hi + lo/16
       uint32_t pw[4] = {0u, 0u, 0u, 0u};
+      const __half2 wsc2 = __float2half2_rn(wsc);
 #pragma unroll
       for (int h = 0; h < GP; h += 2) {
-        const float w0 = valid ? e[h] * wsc : 0.f, w1 = valid ? e[h + 1] * wsc : 0.f;
-        const uint32_t hi2 = f32x2_to_e4m3x2(w0, w1);
-        const float2 hf = e4m3x2_to_f32x2(hi2);
-        const uint32_t lo2 = f32x2_to_e4m3x2((w0 - hf.x) * 16.f, (w1 - hf.y) * 16.f);
-        const float2 lf = e4m3x2_to_f32x2(lo2);
-        hi_f[h] = hf.x; hi_f[h + 1] = hf.y;
-        lo_f[h] = lf.x; lo_f[h + 1] = lf.y;
+        const __half2 d2 = __floats2half2_rn(x[h] - m[h], x[h + 1] - m[h + 1]);
+        const __half2 e2 = h2_exp2(d2);
+        const float2 ef = __half22float2(e2);
+        l[h] += ef.x;
+        l[h + 1] += ef.y;
+        c[h] = fmaf(ef.x, zv, c[h]);
+        c[h + 1] = fmaf(ef.y, zv, c[h + 1]);
+        const __half2 w2 = __hmul2(e2, wsc2);
+        const uint32_t hi2 = f16x2_to_e4m3x2(w2);
+        const __half2 r2 = __hmul2(__hsub2(w2, e4m3x2_to_f16x2(hi2)), __float2half2_rn(16.f));
+        const uint32_t lo2 = f16x2_to_e4m3x2(r2);
         pw[h >> 2] |= hi2 << (16 * ((h >> 1) & 1));
         pw[2 + (h >> 2)] |= lo2 << (16 * ((h >> 1) & 1));
-      }
-#pragma unroll
-      for (int h = 0; h < GP; ++h) {
-        const float wq_ = hi_f[h] + lo_f[h] * 0.0625f;
-        const float pq = wq_ > 0.f ? wq_ * inv : e[h];
-        l[h] = l[h] * corr[h] + e[h];
-        c[h] = c[h] * corr[h] + (valid ? pq * zv : 0.f);
       }
       FQ_STAMP(20);
       // the P row: bytes [hi_0..hi_7 | lo_0..lo_7]
@@ -293,7 +343,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
     }
     if (pending) accumulate();
 
-    // ---- item epilogue: group sums, then the two groups' states merged by group 0
+    // ---- item epilogue: group sums, then the groups' states merged by group 0
     float* rs = red_sum + (wg * 4 + wq) * 16;
 #pragma unroll
     for (int h = 0; h < GP; ++h) {
@@ -312,9 +362,9 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
       l[h] = (gs[h] + gs[16 + h]) + (gs[32 + h] + gs[48 + h]);
       c[h] = (gs[8 + h] + gs[24 + h]) + (gs[40 + h] + gs[56 + h]);
     }
-    float* xo = reinterpret_cast<float*>(smem + SP::XCHG_OFF + (ci & 1) * SP::XCHG_BYTES);
-    float* xmeta = xo + TILE * 8;
-    if (wg == 1) {
+    if (wg > 0) {
+      float* xo = reinterpret_cast<float*>(smem + SP::XCHG_OFF + (wg - 1) * SP::XCHG_BYTES);
+      float* xmeta = xo + TILE * 8;
 #pragma unroll
       for (int h = 0; h < GP; ++h) xo[t * 8 + h] = oacc[h];
       if (t == 0) {
@@ -322,20 +372,30 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
         for (int h = 0; h < GP; ++h) { xmeta[h] = m[h]; xmeta[8 + h] = l[h]; xmeta[16 + h] = c[h]; }
       }
     }
-    named_barrier(3, 256);
+    named_barrier(1 + G, 128 * G);
     if (wg == 0 && w.slot != -2) {
       const int ch = channel_of_expanded_pos<BITS>(t);
 #pragma unroll
       for (int h = 0; h < GP; ++h) {
         const int hl = w.ht * 8 + h;
         if (hl >= P.heads_per_kv) continue;
-        const float m1 = xmeta[h], l1 = xmeta[8 + h], c1 = xmeta[16 + h], o1 = xo[t * 8 + h];
-        const float M = fmaxf(m[h], m1);
-        const float f0 = m[h] == -INFINITY ? 0.f : exp2f(m[h] - M);
-        const float f1 = m1 == -INFINITY ? 0.f : exp2f(m1 - M);
-        const float L = l[h] * f0 + l1 * f1;
-        const float C = c[h] * f0 + c1 * f1;
-        const float O = (oacc[h] * f0 + o1 * f1) * o_mul + C;
+        // fixed merge order: group 0, then 1, 2, 3
+        float M = m[h], L = l[h], C = c[h], O = oacc[h];
+#pragma unroll
+        for (int g = 1; g < G; ++g) {
+          const float* xo = reinterpret_cast<const float*>(smem + SP::XCHG_OFF +
+                                                           (g - 1) * SP::XCHG_BYTES);
+          const float* xmeta = xo + TILE * 8;
+          const float m1 = xmeta[h], l1 = xmeta[8 + h], c1 = xmeta[16 + h], o1 = xo[t * 8 + h];
+          const float Mn = fmaxf(M, m1);
+          const float f0 = M == -INFINITY ? 0.f : exp2f(M - Mn);
+          const float f1 = m1 == -INFINITY ? 0.f : exp2f(m1 - Mn);
+          L = L * f0 + l1 * f1;
+          C = C * f0 + c1 * f1;
+          O = O * f0 + o1 * f1;
+          M = Mn;
+        }
+        O = O * o_mul + C;
         const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
         const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
         if (w.slot < 0) {
@@ -354,6 +414,8 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
         }
       }
     }
+    // the exchange buffers are reused by the next item
+    named_barrier(1 + G, 128 * G);
   }
 }
 
@@ -364,6 +426,9 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   static_assert(D == 128, "this build tiles head_dim 128");
   using SP = SmemPlan<BITS, D>;
   using TP = TmemPlan<D>;
+  constexpr int G = CONSUMER_GROUPS;
+  constexpr int W_EXPAND = 4 * G, W_PRODUCER = W_EXPAND + 4 * EXPAND_GROUPS,
+                W_S = W_PRODUCER + 1, W_PV = W_PRODUCER + 2, W_PRODUCER2 = W_PRODUCER + 3;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* const smem = smem_raw + (smem0 - smem_u32(smem_raw));
@@ -381,17 +446,20 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < NS; ++s) {
-      mbar_init(bars.ring_full(s), 33);   // the TMA expect-tx arrive + 32 cp.async arrivals
+      mbar_init(bars.ring_full(s), 32);   // one cp.async arrival per producer lane
       mbar_init(bars.ring_empty(s), 12);  // 4 K-expander + 4 V-expander + 4 consumer warps
     }
-    for (int s = 0; s < 2; ++s) {
+    static_assert(K_STAGES == 4 && V_STAGES == 4, "barrier plan holds four operand stages");
+    for (int s = 0; s < 4; ++s) {
       mbar_init(bars.kop_full(s), 4);
       mbar_init(bars.kop_empty(s), 1);
       mbar_init(bars.vop_full(s), 4);
       mbar_init(bars.vop_empty(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(bars.q_full(s), 4);
       mbar_init(bars.q_empty(s), 1);
-      for (int wg = 0; wg < 2; ++wg) {
+      for (int wg = 0; wg < G; ++wg) {
         mbar_init(bars.s_full(wg, s), 1);
         mbar_init(bars.s_empty(wg, s), 4);
         mbar_init(bars.p_full(wg, s), 4);
@@ -402,7 +470,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     }
     fence_barrier_init();
   }
-  if (warp == 17) tmem_alloc(smem_u32(tmem_slot), TP::ALLOC);
+  if (warp == W_S) tmem_alloc(smem_u32(tmem_slot), TP::ALLOC);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -412,10 +480,14 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   const uint32_t ring0 = smem0 + SP::RING_OFF;
   int wprof[WAIT_SITES] = {};   // used by the diagnostic build only
 
-  if (warp == 16) {
-    // ------------------------------------------------------------------ producer
-    // Page ids are fetched 32 at a time, one per lane, a chunk ahead of the tiles that use them,
-    // so the table's load latency is paid once per 16 tiles and overlapped with their copies.
+  if (warp == W_PRODUCER || warp == W_PRODUCER2) {
+    // ------------------------------------------------------------------ producers
+    // Two warps take alternate tiles. A tile's two pages (K codes, V codes, scale records of
+    // one KV head) arrive as 16-byte cp.async copies issued by all 32 lanes: measured on B200,
+    // a cp.async.bulk costs its issuing warp ~200 cycles whatever its size, so six 1-2 KB bulk
+    // copies per tile cap the ring near 2.5 TB/s, while 20 cp.async per lane cost ~370 cycles.
+    // Page ids are fetched 32 at a time, one per lane, a chunk ahead of the tiles that use them.
+    const int pi = warp == W_PRODUCER ? 0 : 1;
     int it = 0;
     RingPos rp;
     for (int wi = items.begin; wi < items.end; wi += items.step) {
@@ -439,57 +511,53 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       for (int base = 2 * w.t0; base < 2 * w.t1; base += 32) {
         const int nxt = base + 32 < 2 * w.t1 ? fetch(base + 32) : -1;
         for (int k = 0; k < 16 && base + 2 * k < 2 * w.t1; ++k, ++it) {
+          const int s = rp.s;
+          const uint32_t eph = rp.ph ^ 1u;
+          rp.next(NS);
+          if ((it & 1) != pi) continue;
+          FQ_STAMP_BEGIN();
           const int id0 = __shfl_sync(0xFFFFFFFFu, cur, 2 * k);
           const int id1 = __shfl_sync(0xFFFFFFFFu, cur, 2 * k + 1);
-          const int s = rp.s;
-          mbar_wait(bars.ring_empty(s), rp.ph ^ 1u, abort_flag, status, 0, wprof);
-          rp.next(NS);
+          mbar_wait(bars.ring_empty(s), eph, abort_flag, status, 0, wprof);
+          FQ_STAMP(24);
           const uint32_t full = bars.ring_full(s);
-          const uint32_t dst = ring0 + s * SP::STAGE;
-          const long long blk0 = static_cast<long long>(id0) * P.p.num_kv_heads + w.kvh;
-          const long long blk1 = static_cast<long long>(id1) * P.p.num_kv_heads + w.kvh;
-          // V code pages ride the TMA engine (one bulk copy per page, ~110 cycles of engine time
-          // each whatever the size); K code pages and scale records go as 16-byte asynchronous
-          // copies issued by all 32 lanes, so neither path is the per-tile limit.
-          if (lane == 0)
-            mbar_expect_tx(full, (id0 >= 0 ? SP::CODE_PAGE : 0) + (id1 >= 0 ? SP::CODE_PAGE : 0));
-          __syncwarp();
-          if (lane < 2) {
-            const int id = lane ? id1 : id0;
-            if (id >= 0)
-              bulk_g2s(dst + SP::V_OFF + lane * SP::CODE_PAGE,
-                       P.p.v_codes + (lane ? blk1 : blk0) * SP::CODE_PAGE, SP::CODE_PAGE, full);
-          }
+          const uint32_t dst = ring0 + s * SP::STAGE + 16 * lane;
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            if ((j ? id1 : id0) < 0) continue;
-            const long long blk = j ? blk1 : blk0;
-            const uint8_t* ks = P.p.k_codes + blk * SP::CODE_PAGE;
-            const uint8_t* ss = static_cast<const uint8_t*>(P.p.scales) + blk * SP::SCALE_PAGE;
+            const int id = j ? id1 : id0;
+            if (id < 0) continue;
+            const long long blk = static_cast<long long>(id) * P.p.num_kv_heads + w.kvh;
+            const uint8_t* ks = P.p.k_codes + blk * SP::CODE_PAGE + 16 * lane;
+            const uint8_t* vs = P.p.v_codes + blk * SP::CODE_PAGE + 16 * lane;
+            const uint8_t* ss = static_cast<const uint8_t*>(P.p.scales) + blk * SP::SCALE_PAGE +
+                                16 * lane;
 #pragma unroll
-            for (int c = 0; c < SP::CODE_PAGE / 16; c += 32)
-              cp_async16(dst + SP::K_OFF + j * SP::CODE_PAGE + 16 * (c + lane), ks + 16 * (c + lane));
+            for (int c = 0; c < SP::CODE_PAGE; c += 512)
+              cp_async16(dst + SP::K_OFF + j * SP::CODE_PAGE + c, ks + c);
 #pragma unroll
-            for (int c = 0; c < SP::SCALE_PAGE / 16; c += 32)
-              cp_async16(dst + SP::S_OFF + j * SP::SCALE_PAGE + 16 * (c + lane), ss + 16 * (c + lane));
+            for (int c = 0; c < SP::SCALE_PAGE; c += 512)
+              cp_async16(dst + SP::S_OFF + j * SP::SCALE_PAGE + c, ss + c);
+#pragma unroll
+            for (int c = 0; c < SP::CODE_PAGE; c += 512)
+              cp_async16(dst + SP::V_OFF + j * SP::CODE_PAGE + c, vs + c);
           }
+          FQ_STAMP(26);
           cp_async_arrive(full);
-          __syncwarp();
+          FQ_STAMP(27);
         }
         cur = nxt;
       }
     }
-    // drain: every copy this warp issued has landed once its stage's consumers released it
-    // or, for the last NS tiles, once the stage reports full.
+    // drain: every copy this warp issued has landed once its stage reports full
     for (int back = 0; back < NS && back < it; ++back) {
       if (--rp.s < 0) { rp.s = NS - 1; rp.ph ^= 1u; }
       mbar_wait_drain(bars.ring_full(rp.s), rp.ph);
     }
-  } else if (warp == 17) {
+  } else if (warp == W_S) {
     // ------------------------------------------------------------------ S issuer
     // One thread issues S = C_K . Q^T for every tile. The loop is kept to a few dozen scalar
     // instructions per tile: descriptor high words, the instruction descriptor and the
-    // accumulate flags are immediates, and every buffer index is a bit of the tile counter.
+    // accumulate flags are immediates, and every buffer index is a bit field of the counter.
     if (lane == 0) {
       constexpr uint32_t IDESC_S = make_idesc_e4m3(128, 16, 0, 0);
       constexpr uint32_t Q_HI = smem_desc_hi(1024, 2);
@@ -501,8 +569,8 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status, 1, wprof);
         const uint32_t q_lo = smem_desc_lo(smem0 + SP::Q_OFF + qb * SP::Q_BYTES, 16);
         for (int t = w.t0; t < w.t1; ++t, ++it) {
-          const int wg = it & 1, buf = (it >> 1) & 1, ks = it & 1;
-          const uint32_t ph = (it >> 2) & 1, kph = (it >> 1) & 1;
+          const int wg = it & (G - 1), n = it / G, buf = n & 1, ks = it & (K_STAGES - 1);
+          const uint32_t ph = (n >> 1) & 1, kph = (it / K_STAGES) & 1;
           mbar_wait(bars.kop_full(ks), kph, abort_flag, status, 2, wprof);
           mbar_wait(bars.s_empty(wg, buf), ph ^ 1u, abort_flag, status, 3, wprof);
           tc_fence_after();
@@ -520,7 +588,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       }
     }
     __syncwarp();
-  } else if (warp == 18) {
+  } else if (warp == W_PV) {
     // ------------------------------------------------------------------ PV issuer
     if (lane == 0) {
       constexpr uint32_t IDESC_PV = make_idesc_e4m3(128, 16, 1, 1);
@@ -531,8 +599,8 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       for (int wi = items.begin; wi < items.end; wi += items.step) {
         const WorkItem w = decode_item(P, wi);
         for (int t = w.t0; t < w.t1; ++t, ++it) {
-          const int wg = it & 1, buf = (it >> 1) & 1, vs = it & 1;
-          const uint32_t ph = (it >> 2) & 1, vph = (it >> 1) & 1;
+          const int wg = it & (G - 1), n = it / G, buf = n & 1, vs = it & (V_STAGES - 1);
+          const uint32_t ph = (n >> 1) & 1, vph = (it / V_STAGES) & 1;
           mbar_wait(bars.vop_full(vs), vph, abort_flag, status, 4, wprof);
           mbar_wait(bars.p_full(wg, buf), ph, abort_flag, status, 5, wprof);
           mbar_wait(bars.o_empty(wg, buf), ph ^ 1u, abort_flag, status, 6, wprof);
@@ -552,9 +620,9 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       }
     }
     __syncwarp();
-  } else if (warp >= 8 && warp < 12) {
+  } else if (warp >= W_EXPAND && warp < W_EXPAND + 4) {
     // ------------------------------------------------------------------ K expanders (+ Q)
-    const int t = threadIdx.x - 256;  // token row of the tile, = tensor-memory lane
+    const int t = threadIdx.x - 32 * W_EXPAND;  // token row of the tile = tensor-memory lane
     const uint32_t lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;
     int it = 0, qi = 0;
     RingPos rp;
@@ -589,14 +657,16 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         ++qi;
       }
       for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
-        const int s = rp.s, ks = it & 1;
+        const int s = rp.s, ks = it & (K_STAGES - 1);
+        const uint32_t kph = (it / K_STAGES) & 1;
         mbar_wait(bars.ring_full(s), rp.ph, abort_flag, status, 8, wprof);
         rp.next(NS);
-        uint32_t op[D / 4];
-        expand_row<BITS, D>(ring0 + s * SP::STAGE + SP::K_OFF + t * SP::RB, op);
+        uint32_t wk[D * BITS / 32], op[D / 4];
+        load_row<BITS, D>(ring0 + s * SP::STAGE + SP::K_OFF + t * SP::RB, wk);
+        expand_words<BITS, D>(wk, op);
         __syncwarp();
         if (lane == 0) mbar_arrive(bars.ring_empty(s));
-        mbar_wait(bars.kop_empty(ks), ((it >> 1) & 1) ^ 1, abort_flag, status, 9, wprof);
+        mbar_wait(bars.kop_empty(ks), kph ^ 1u, abort_flag, status, 9, wprof);
         tc_fence_after();
         const uint32_t dst = tmem + lane_base + TP::KOP + ks * TP::KOP_COLS;
 #pragma unroll
@@ -607,22 +677,26 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         if (lane == 0) mbar_arrive(bars.kop_full(ks));
       }
     }
-  } else if (warp >= 12 && warp < 16) {
+  } else if (warp >= W_EXPAND + 4 && warp < W_PRODUCER) {
     // ------------------------------------------------------------------ V expanders
-    const int t = threadIdx.x - 384;
+    // They run as late as the PV MMA allows: the packed codes wait in the ring (4 KB a tile),
+    // not as expanded operands (16 KB a tile).
+    const int t = threadIdx.x - 32 * (W_EXPAND + 4);
     int it = 0;
     RingPos rp;
     for (int wi = items.begin; wi < items.end; wi += items.step) {
       const WorkItem w = decode_item(P, wi);
       for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
-        const int s = rp.s, vs = it & 1;
+        const int s = rp.s, vs = it & (V_STAGES - 1);
+        const uint32_t vph = (it / V_STAGES) & 1;
+        mbar_wait(bars.vop_empty(vs), vph ^ 1u, abort_flag, status, 11, wprof);
         mbar_wait(bars.ring_full(s), rp.ph, abort_flag, status, 10, wprof);
         rp.next(NS);
-        uint32_t op[D / 4];
-        expand_row<BITS, D>(ring0 + s * SP::STAGE + SP::V_OFF + t * SP::RB, op);
+        uint32_t wv[D * BITS / 32], op[D / 4];
+        load_row<BITS, D>(ring0 + s * SP::STAGE + SP::V_OFF + t * SP::RB, wv);
+        expand_words<BITS, D>(wv, op);
         __syncwarp();
         if (lane == 0) mbar_arrive(bars.ring_empty(s));
-        mbar_wait(bars.vop_empty(vs), ((it >> 1) & 1) ^ 1, abort_flag, status, 11, wprof);
         const uint32_t row = smem0 + SP::VOP_OFF + vs * SP::VOP_STAGE + t * D;
 #pragma unroll
         for (int c = 0; c < D / 16; ++c) {
@@ -635,14 +709,14 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         if (lane == 0) mbar_arrive(bars.vop_full(vs));
       }
     }
-  } else {
+  } else if (warp < W_EXPAND) {
     // ------------------------------------------------------------------ consumers
     consumer_role<BITS, D, GP>(P, smem, smem0, tmem, bars, abort_flag, items, wprof);
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 17) {
+  if (warp == W_S) {
     tc_fence_after();
     tmem_dealloc(tmem, TP::ALLOC);
   }
@@ -655,7 +729,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   __syncthreads();
   if (g_wait_profile != nullptr && threadIdx.x < WAIT_SITES) {
     int v = const_cast<int*>(abort_flag)[1 + threadIdx.x];
-    if (threadIdx.x == WAIT_SITES - 1) v = static_cast<int>((clock64() - kernel_t0) >> 4);
+    if (threadIdx.x == 23) v = static_cast<int>((clock64() - kernel_t0) >> 4);
     g_wait_profile[blockIdx.x * WAIT_SITES + threadIdx.x] = v;
   }
 #endif

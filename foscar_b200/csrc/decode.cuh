@@ -7,9 +7,11 @@ namespace fq {
 
 constexpr int TILE = 128;            // tokens per sequence tile: two pages
 constexpr int WORK_WORDS = 8;        // int32 words per explicit work-list row
-constexpr int DECODE_THREADS = 608;  // 19 warps, see decode.cu
-constexpr int K_STAGES = 2;          // K operand stages in tensor memory
-constexpr int V_STAGES = 2;          // V operand stages in shared memory
+constexpr int CONSUMER_GROUPS = 4;   // 128-thread softmax/accumulate groups, tile i -> group i % 4
+constexpr int EXPAND_GROUPS = 2;     // 128-thread unpack groups: one for K, one for V
+constexpr int DECODE_THREADS = 896;  // 28 warps, see decode.cu
+constexpr int K_STAGES = 4;          // K operand stages in tensor memory
+constexpr int V_STAGES = 4;          // V operand stages in shared memory
 constexpr int SMEM_LIMIT = 232448;   // 227 KiB opt-in limit per CTA on sm_100
 
 struct DecodeParams {
@@ -41,9 +43,9 @@ struct SmemPlan {
   static constexpr int VOP_OFF = 0;
   static constexpr int Q_OFF = VOP_OFF + V_STAGES * VOP_STAGE;
   static constexpr int P_OFF = Q_OFF + 2 * Q_BYTES;
-  static constexpr int XCHG_BYTES = TILE * 8 * 4 + 128;   // one WG's accumulators + (m,l,c)
-  static constexpr int XCHG_OFF = P_OFF + 4 * P_BYTES;
-  static constexpr int RED_OFF = XCHG_OFF + 2 * XCHG_BYTES;  // cross-warp reduction scratch
+  static constexpr int XCHG_BYTES = TILE * 8 * 4 + 128;   // one group's accumulators + (m,l,c)
+  static constexpr int XCHG_OFF = P_OFF + 2 * CONSUMER_GROUPS * P_BYTES;
+  static constexpr int RED_OFF = XCHG_OFF + (CONSUMER_GROUPS - 1) * XCHG_BYTES;  // reductions
   static constexpr int RED_BYTES = 2048;
   static constexpr int BAR_OFF = RED_OFF + RED_BYTES;
   static constexpr int BAR_BYTES = 2048;   // barriers, then flags and diagnostics
