@@ -63,19 +63,25 @@ struct Bars {
   __device__ uint32_t at(int i) const { return base + 8u * i; }
   __device__ uint32_t ring_full(int s) const { return at(s); }
   __device__ uint32_t ring_empty(int s) const { return at(ns + s); }
-  __device__ uint32_t kop_full(int s) const { return at(2 * ns + s); }
-  __device__ uint32_t kop_empty(int s) const { return at(2 * ns + 4 + s); }
-  __device__ uint32_t vop_full(int s) const { return at(2 * ns + 8 + s); }
-  __device__ uint32_t vop_empty(int s) const { return at(2 * ns + 12 + s); }
-  __device__ uint32_t q_full(int s) const { return at(2 * ns + 16 + s); }
-  __device__ uint32_t q_empty(int s) const { return at(2 * ns + 18 + s); }
-  __device__ uint32_t s_full(int wg, int s) const { return at(2 * ns + 20 + 2 * wg + s); }
-  __device__ uint32_t s_empty(int wg, int s) const { return at(2 * ns + 20 + 2 * G + 2 * wg + s); }
-  __device__ uint32_t p_full(int wg, int s) const { return at(2 * ns + 20 + 4 * G + 2 * wg + s); }
-  __device__ uint32_t p_empty(int wg, int s) const { return at(2 * ns + 20 + 6 * G + 2 * wg + s); }
-  __device__ uint32_t o_full(int wg, int s) const { return at(2 * ns + 20 + 8 * G + 2 * wg + s); }
-  __device__ uint32_t o_empty(int wg, int s) const { return at(2 * ns + 20 + 10 * G + 2 * wg + s); }
-  // 2*ns + 20 + 12*G words of 8 bytes: 68 + 2*ns <= 108 at ns <= 20 (864 of 1016 bytes)
+  __device__ uint32_t q_full(int s) const { return at(2 * ns + s); }
+  __device__ uint32_t q_empty(int s) const { return at(2 * ns + 2 + s); }
+  // One barrier per tile slot (tile index modulo 8) and event, so that each MMA issuer makes
+  // ONE wait and ONE commit per tile (a successful wait costs its thread ~100 cycles, which at
+  // four MMAs of ~70 cycles each is what decides whether a tile retires in time):
+  //   s_ready : K operand of the tile is in tensor memory (4 K-expander warps) and the tile's S
+  //             buffer has been read by its consumer group (4 warps; pre-armed once)
+  //   s_done  : the tile's S MMA is complete (commit): its consumers read S, and the K expander
+  //             may reuse the operand stage four tiles later
+  //   pv_ready: V operand of the tile is in shared memory (4 V-expander warps) and its P rows are
+  //             written (4 consumer warps; the same group has by then read the O buffer's
+  //             previous contents)
+  //   pv_done : the tile's PV MMA is complete (commit): its consumers read O, the V expander may
+  //             reuse the stage four tiles later, and the P buffer is free
+  __device__ uint32_t s_ready(int slot) const { return at(2 * ns + 4 + slot); }
+  __device__ uint32_t s_done(int slot) const { return at(2 * ns + 12 + slot); }
+  __device__ uint32_t pv_ready(int slot) const { return at(2 * ns + 20 + slot); }
+  __device__ uint32_t pv_done(int slot) const { return at(2 * ns + 28 + slot); }
+  // 2*ns + 36 words of 8 bytes
 };
 
 // Position in the code ring: stage and phase, advanced without a division.
@@ -180,6 +186,11 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
   const float p2lp = exp2f(static_cast<float>(lp));
   const float o_mul = exp2f(static_cast<float>(9 - lp));
 
+  // this group's two S buffers start out free
+  if (lane == 0) {
+    mbar_arrive(bars.s_ready(wg));
+    mbar_arrive(bars.s_ready(wg + G));
+  }
   int it = 0;
   RingPos rp;
   for (int wi = items.begin; wi < items.end; wi += items.step) {
@@ -208,17 +219,15 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
       qs[h] = scale;
     }
     bool pending = false;
-    int pend_buf = 0, pend_ph = 0;
+    int pend_it = 0;
 
     auto accumulate = [&]() {
-      mbar_wait(bars.o_full(wg, pend_buf), pend_ph, abort_flag, status, 15, wprof);
+      mbar_wait(bars.pv_done(pend_it & 7), (pend_it >> 3) & 1, abort_flag, status, 15, wprof);
       tc_fence_after();
       uint32_t r[16];
-      tmem_ld16(tmem + lane_base + TP::O + (2 * wg + pend_buf) * 16, r);
+      tmem_ld16(tmem + lane_base + TP::O + (pend_it & 7) * 16, r);
       tmem_ld_wait();
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bars.o_empty(wg, pend_buf));
 #pragma unroll
       for (int h = 0; h < GP; ++h)
         oacc[h] = fmaf(oacc[h], corr_pend[h],
@@ -230,18 +239,18 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
       const uint32_t rph = rp.ph;
       rp.next(NS);
       if ((it & (G - 1)) != wg) continue;
-      const int n = it / G, buf = n & 1, ph = (n >> 1) & 1;
+      const int slot = it & 7, buf = (it / G) & 1;
       // raw scores of token row t
-      mbar_wait(bars.s_full(wg, buf), ph, abort_flag, status, 12, wprof);
+      mbar_wait(bars.s_done(slot), (it >> 3) & 1, abort_flag, status, 12, wprof);
       FQ_STAMP_BEGIN();
       tc_fence_after();
       uint32_t raw[GP];
-      if constexpr (GP == 4) tmem_ld4(tmem + lane_base + TP::S + (2 * wg + buf) * 16, raw);
-      else tmem_ld8(tmem + lane_base + TP::S + (2 * wg + buf) * 16, raw);
+      if constexpr (GP == 4) tmem_ld4(tmem + lane_base + TP::S + slot * 16, raw);
+      else tmem_ld8(tmem + lane_base + TP::S + slot * 16, raw);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars.s_empty(wg, buf));
+      if (lane == 0) mbar_arrive(bars.s_ready(slot));   // free for the tile eight ahead
       FQ_STAMP(17);
       // this token's records
       mbar_wait(bars.ring_full(s), rph, abort_flag, status, 13, wprof);
@@ -324,22 +333,22 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
         pw[2 + (h >> 2)] |= lo2 << (16 * ((h >> 1) & 1));
       }
       FQ_STAMP(20);
-      // the P row: bytes [hi_0..hi_7 | lo_0..lo_7]
-      mbar_wait(bars.p_empty(wg, buf), ph ^ 1, abort_flag, status, 14, wprof);
+      // the P row: bytes [hi_0..hi_7 | lo_0..lo_7]. The buffer is free: this group accumulated
+      // the tile that last used it (two of its own tiles ago), which waited for that PV MMA.
       asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
-                       smem0 + SP::P_OFF + (2 * wg + buf) * SP::P_BYTES + t * 16),
+                       smem0 + SP::P_OFF + slot * SP::P_BYTES + t * 16),
                    "r"(pw[0]), "r"(pw[1]), "r"(pw[2]), "r"(pw[3])
                    : "memory");
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars.p_full(wg, buf));
+      if (lane == 0) mbar_arrive(bars.pv_ready(slot));
       FQ_STAMP(21);
       // the previous tile's O, now that its MMA has had a tile's time to finish
       if (pending) accumulate();
       FQ_STAMP(22);
 #pragma unroll
       for (int h = 0; h < GP; ++h) corr_pend[h] = corr[h];
-      pending = true; pend_buf = buf; pend_ph = ph;
+      pending = true; pend_it = it;
     }
     if (pending) accumulate();
 
@@ -449,24 +458,17 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       mbar_init(bars.ring_full(s), 32);   // one cp.async arrival per producer lane
       mbar_init(bars.ring_empty(s), 12);  // 4 K-expander + 4 V-expander + 4 consumer warps
     }
-    static_assert(K_STAGES == 4 && V_STAGES == 4, "barrier plan holds four operand stages");
-    for (int s = 0; s < 4; ++s) {
-      mbar_init(bars.kop_full(s), 4);
-      mbar_init(bars.kop_empty(s), 1);
-      mbar_init(bars.vop_full(s), 4);
-      mbar_init(bars.vop_empty(s), 1);
+    static_assert(K_STAGES == 4 && V_STAGES == 4 && CONSUMER_GROUPS == 4,
+                  "the barrier plan assumes four operand stages and eight tile slots");
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(bars.s_ready(s), 8);
+      mbar_init(bars.s_done(s), 1);
+      mbar_init(bars.pv_ready(s), 8);
+      mbar_init(bars.pv_done(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bars.q_full(s), 4);
       mbar_init(bars.q_empty(s), 1);
-      for (int wg = 0; wg < G; ++wg) {
-        mbar_init(bars.s_full(wg, s), 1);
-        mbar_init(bars.s_empty(wg, s), 4);
-        mbar_init(bars.p_full(wg, s), 4);
-        mbar_init(bars.p_empty(wg, s), 1);
-        mbar_init(bars.o_full(wg, s), 1);
-        mbar_init(bars.o_empty(wg, s), 4);
-      }
     }
     fence_barrier_init();
   }
@@ -569,19 +571,16 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status, 1, wprof);
         const uint32_t q_lo = smem_desc_lo(smem0 + SP::Q_OFF + qb * SP::Q_BYTES, 16);
         for (int t = w.t0; t < w.t1; ++t, ++it) {
-          const int wg = it & (G - 1), n = it / G, buf = n & 1, ks = it & (K_STAGES - 1);
-          const uint32_t ph = (n >> 1) & 1, kph = (it / K_STAGES) & 1;
-          mbar_wait(bars.kop_full(ks), kph, abort_flag, status, 2, wprof);
-          mbar_wait(bars.s_empty(wg, buf), ph ^ 1u, abort_flag, status, 3, wprof);
+          const int slot = it & 7, ks = it & (K_STAGES - 1);
+          mbar_wait(bars.s_ready(slot), (it >> 3) & 1, abort_flag, status, 2, wprof);
           tc_fence_after();
-          const uint32_t sd = tmem + TP::S + (2 * wg + buf) * 16;
+          const uint32_t sd = tmem + TP::S + slot * 16;
           const uint32_t ka = tmem + TP::KOP + ks * TP::KOP_COLS;
           umma_ts_c<Q_HI, IDESC_S, false>(sd, ka, q_lo);
 #pragma unroll
           for (int k = 1; k < D / 32; ++k)
             umma_ts_c<Q_HI, IDESC_S, true>(sd, ka + 8 * k, q_lo + 2 * k);
-          tc_commit(bars.s_full(wg, buf));
-          tc_commit(bars.kop_empty(ks));
+          tc_commit(bars.s_done(slot));
           if (t == w.t1 - 1) tc_commit(bars.q_empty(qb));
         }
         ++qi;
@@ -599,37 +598,33 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       for (int wi = items.begin; wi < items.end; wi += items.step) {
         const WorkItem w = decode_item(P, wi);
         for (int t = w.t0; t < w.t1; ++t, ++it) {
-          const int wg = it & (G - 1), n = it / G, buf = n & 1, vs = it & (V_STAGES - 1);
-          const uint32_t ph = (n >> 1) & 1, vph = (it / V_STAGES) & 1;
-          mbar_wait(bars.vop_full(vs), vph, abort_flag, status, 4, wprof);
-          mbar_wait(bars.p_full(wg, buf), ph, abort_flag, status, 5, wprof);
-          mbar_wait(bars.o_empty(wg, buf), ph ^ 1u, abort_flag, status, 6, wprof);
+          const int slot = it & 7, vs = it & (V_STAGES - 1);
+          mbar_wait(bars.pv_ready(slot), (it >> 3) & 1, abort_flag, status, 4, wprof);
           tc_fence_after();
           const uint32_t v_lo = v_lo0 + vs * (SP::VOP_STAGE >> 4);
-          const uint32_t p_lo = p_lo0 + (2 * wg + buf) * (SP::P_BYTES >> 4);
-          const uint32_t od = tmem + TP::O + (2 * wg + buf) * 16;
+          const uint32_t p_lo = p_lo0 + slot * (SP::P_BYTES >> 4);
+          const uint32_t od = tmem + TP::O + slot * 16;
           umma_ss_c<V_HI, P_HI, IDESC_PV, false>(od, v_lo, p_lo);
 #pragma unroll
           for (int k = 1; k < TILE / 32; ++k)
             umma_ss_c<V_HI, P_HI, IDESC_PV, true>(od, v_lo + k * (32 * D >> 4),
                                                   p_lo + k * (32 * 16 >> 4));
-          tc_commit(bars.o_full(wg, buf));
-          tc_commit(bars.vop_empty(vs));
-          tc_commit(bars.p_empty(wg, buf));
+          tc_commit(bars.pv_done(slot));
         }
       }
     }
     __syncwarp();
   } else if (warp >= W_EXPAND && warp < W_EXPAND + 4) {
     // ------------------------------------------------------------------ K expanders (+ Q)
-    const int t = threadIdx.x - 32 * W_EXPAND;  // token row of the tile = tensor-memory lane
+    constexpr int eg = 0;
+    const int t = threadIdx.x - 32 * W_EXPAND;  // token row = tensor-memory lane
     const uint32_t lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;
     int it = 0, qi = 0;
     RingPos rp;
     for (int wi = items.begin; wi < items.end; wi += items.step) {
       const WorkItem w = decode_item(P, wi);
       if (w.t1 <= w.t0) continue;
-      {  // this item's query rows, in expansion order, as the S MMA's B operand
+      if (eg == 0) {  // this item's query rows, in expansion order, as the S MMA's B operand
         const int qb = qi & 1;
         mbar_wait(bars.q_empty(qb), ((qi >> 1) & 1) ^ 1, abort_flag, status, 7, wprof);
         const int r = t >> 3, c = t & 7;  // row (head), 16-byte chunk
@@ -654,19 +649,22 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars.q_full(qb));
-        ++qi;
       }
+      ++qi;
       for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
         const int s = rp.s, ks = it & (K_STAGES - 1);
-        const uint32_t kph = (it / K_STAGES) & 1;
-        mbar_wait(bars.ring_full(s), rp.ph, abort_flag, status, 8, wprof);
+        const uint32_t rph = rp.ph;
         rp.next(NS);
+        mbar_wait(bars.ring_full(s), rph, abort_flag, status, 8, wprof);
         uint32_t wk[D * BITS / 32], op[D / 4];
         load_row<BITS, D>(ring0 + s * SP::STAGE + SP::K_OFF + t * SP::RB, wk);
         expand_words<BITS, D>(wk, op);
         __syncwarp();
         if (lane == 0) mbar_arrive(bars.ring_empty(s));
-        mbar_wait(bars.kop_empty(ks), kph ^ 1u, abort_flag, status, 9, wprof);
+        // the stage was last read by the S MMA four tiles ago
+        if (it >= K_STAGES)
+          mbar_wait(bars.s_done((it - K_STAGES) & 7), ((it - K_STAGES) >> 3) & 1, abort_flag,
+                    status, 9, wprof);
         tc_fence_after();
         const uint32_t dst = tmem + lane_base + TP::KOP + ks * TP::KOP_COLS;
 #pragma unroll
@@ -674,7 +672,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bars.kop_full(ks));
+        if (lane == 0) mbar_arrive(bars.s_ready(it & 7));
       }
     }
   } else if (warp >= W_EXPAND + 4 && warp < W_PRODUCER) {
@@ -688,8 +686,10 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       const WorkItem w = decode_item(P, wi);
       for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
         const int s = rp.s, vs = it & (V_STAGES - 1);
-        const uint32_t vph = (it / V_STAGES) & 1;
-        mbar_wait(bars.vop_empty(vs), vph ^ 1u, abort_flag, status, 11, wprof);
+        // the stage was last read by the PV MMA four tiles ago
+        if (it >= V_STAGES)
+          mbar_wait(bars.pv_done((it - V_STAGES) & 7), ((it - V_STAGES) >> 3) & 1, abort_flag,
+                    status, 11, wprof);
         mbar_wait(bars.ring_full(s), rp.ph, abort_flag, status, 10, wprof);
         rp.next(NS);
         uint32_t wv[D * BITS / 32], op[D / 4];
@@ -706,7 +706,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         }
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bars.vop_full(vs));
+        if (lane == 0) mbar_arrive(bars.pv_ready(it & 7));
       }
     }
   } else if (warp < W_EXPAND) {
@@ -825,6 +825,7 @@ umma_selftest_kernel(int mode, const uint8_t* k_bytes, const uint8_t* q_bytes,
 // host side
 // ---------------------------------------------------------------------------------------------
 #include <algorithm>
+#include <cstdlib>
 
 namespace fq {
 
@@ -840,6 +841,10 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   using SP = SmemPlan<BITS, D>;
   int stages = SP::max_ring_stages();
   if (stages > 20) stages = 20;
+  if (const char* env = getenv("FOSCAR_B200_RING_STAGES")) {   // tuning knob for experiments
+    const int want = atoi(env);
+    if (want >= 2 && want < stages) stages = want;
+  }
   if (stages < 2) return FQ_ERR_UNSUPPORTED;
   P.ring_stages = stages;
   const int smem = SP::RING_OFF + stages * SP::STAGE + 1024;
