@@ -11,6 +11,8 @@ import os
 from . import _build
 
 ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_TOO_LARGE = -1, -2, -3
+ERR_SCRATCH_TOO_SMALL = -4
+STATIC_SCRATCH_BYTES = 8 << 20
 STATUS_BITS = {0x1: "slot outside the cache", 0x2: "page id outside the pool",
                0x4: "output row outside the buffer", 0x8: "bad sequence length",
                0x10: "device wait timed out"}
@@ -49,6 +51,7 @@ _PROTOTYPES = {
                                 _I32, _I32, _P, _P]),
     "fq_recount_vmax": (C.c_int, [C.POINTER(Pools), _P]),
     "fq_decode": (C.c_int, [C.POINTER(Pools), C.POINTER(DecodeArgs), _P]),
+    "fq_decode_split_static": (C.c_int, [C.POINTER(Pools), C.POINTER(DecodeArgs), _P]),
     "fq_merge": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _F32, _P, _I32,
                            _P, _P]),
     "fq_merge_states": (C.c_int, [_P, _P, _I32, _I32, _I32, _I32, _P, _I32, _P, _P]),
@@ -96,7 +99,7 @@ def check(code: int, what: str) -> None:
     text = load().fq_error_string(code).decode()
     if code == ERR_UNSUPPORTED:
         raise NotImplementedError(f"{what}: {text}")
-    if code in (ERR_BAD_ARG, ERR_TOO_LARGE):
+    if code in (ERR_BAD_ARG, ERR_TOO_LARGE, ERR_SCRATCH_TOO_SMALL):
         raise ValueError(f"{what}: {text}")
     raise RuntimeError(f"{what}: CUDA error {code}: {text}")
 

@@ -17,6 +17,9 @@ extern "C" const char* fq_error_string(int code) {
     case FQ_ERR_BAD_ARG: return "bad argument";
     case FQ_ERR_UNSUPPORTED: return "unsupported configuration";
     case FQ_ERR_TOO_LARGE: return "problem too large for one launch";
+    case FQ_ERR_SCRATCH_TOO_SMALL:
+      return "the split partials exceed the library's built-in scratch buffer "
+             "(kv_splits * batch * num_qo_heads * (head_dim + 2) * 4 > FQ_STATIC_SCRATCH_BYTES)";
     default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown";
   }
 }

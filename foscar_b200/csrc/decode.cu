@@ -904,6 +904,49 @@ extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void
   return gp == 4 ? launch_decode<4, 128, 4>(P, s) : launch_decode<4, 128, 8>(P, s);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Split decode for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------------------------
+namespace fq {
+// Scratch for the split partials (o, l, m) of fq_decode_split_static. It lives in the library
+// image: every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) float g_static_partials[FQ_STATIC_SCRATCH_BYTES / 4];
+}  // namespace fq
+
+extern "C" int fq_decode_split_static(const fq_pools* pools, const fq_decode_args* args,
+                                      void* stream) {
+  if (!pools || !args) return FQ_ERR_BAD_ARG;
+  if (args->worklist != nullptr || args->kv_splits < 1) return FQ_ERR_BAD_ARG;
+  if (args->batch <= 0 || args->num_qo_heads <= 0) return FQ_ERR_BAD_ARG;
+  const long long rows = static_cast<long long>(args->kv_splits) * args->batch * args->num_qo_heads;
+  const long long need = rows * (pools->head_dim + 2) * 4;
+  if (need > static_cast<long long>(FQ_STATIC_SCRATCH_BYTES)) return FQ_ERR_SCRATCH_TOO_SMALL;
+  // In host code the array's name is only a handle: the device address is asked for once per
+  // device, with that device current, and cached.
+  static float* base_of_device[64] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return FQ_ERR_UNSUPPORTED;
+  if (base_of_device[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, fq::g_static_partials);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (p == nullptr) return FQ_ERR_UNSUPPORTED;
+    base_of_device[dev] = static_cast<float*>(p);
+  }
+  fq_decode_args a = *args;
+  a.max_splits = a.kv_splits;
+  a.o_partial = base_of_device[dev];
+  a.l_partial = a.o_partial + rows * pools->head_dim;
+  a.m_partial = a.l_partial + rows;
+  const int rc = fq_decode(pools, &a, stream);
+  if (rc != 0 || a.kv_splits == 1) return rc;
+  return fq_merge(a.o_partial, a.l_partial, a.m_partial, nullptr, a.kv_splits, a.kv_splits,
+                  a.batch, a.num_qo_heads, pools->num_kv_heads, pools->head_dim, a.o_scale, a.out,
+                  a.out_dtype, a.lse, stream);
+}
+
 #ifdef FQ_WAIT_PROFILE
 extern "C" int fq_debug_set_wait_profile(void* buffer) {
   return static_cast<int>(cudaMemcpyToSymbol(fq::g_wait_profile, &buffer, sizeof(buffer)));

@@ -26,6 +26,7 @@ extern "C" {
 #define FQ_ERR_BAD_ARG (-1)
 #define FQ_ERR_UNSUPPORTED (-2)
 #define FQ_ERR_TOO_LARGE (-3)
+#define FQ_ERR_SCRATCH_TOO_SMALL (-4) /* fq_decode_split_static: needs more than its static scratch */
 
 /* device status bits */
 #define FQ_STATUS_BAD_SLOT 0x1      /* append: slot >= num_pages * 64 (skipped) */
@@ -127,6 +128,26 @@ typedef struct fq_decode_args {
 } fq_decode_args;
 
 int fq_decode(const fq_pools* pools, const fq_decode_args* args, void* stream);
+
+/* Split decode plus merge for callers that cannot allocate device memory. It has no counterpart
+ * in the reference, whose wrapper always takes the partial buffers from a caller-allocated
+ * workspace. Some hosts of this library have no workspace to give: a plugin running inside an
+ * engine that owns the CUDA allocator and forbids cudaMalloc from extensions, or a call site
+ * inside a region where allocation is illegal (a stream capture, a real-time loop). For them the
+ * unnormalised partials (o, l, m) of a uniform split (worklist == NULL, kv_splits >= 1) go into a
+ * buffer of FQ_STATIC_SCRATCH_BYTES that is part of the library image itself, so every GPU that
+ * loads the library carries those bytes until the process exits. The caller passes inputs and
+ * outputs exactly as to fq_decode; o_partial/l_partial/m_partial/max_splits are ignored.
+ *   - Limit: kv_splits * batch * num_qo_heads * (head_dim + 2) * 4 bytes must fit the buffer,
+ *     else FQ_ERR_SCRATCH_TOO_SMALL is returned and nothing is launched.
+ *   - The first call on each device looks the buffer's device address up; make that first call
+ *     (with the device current) before any stream capture.
+ *   - Calls no cudaMalloc, cudaFree or allocating library routine.
+ *   - All calls share the one buffer, which keeps the previous call's partials. Nothing needs
+ *     clearing (each call writes every slot it later reads), but two calls that overlap on the GPU
+ *     (different streams, or graphs replayed concurrently) race on it: order them. */
+#define FQ_STATIC_SCRATCH_BYTES (8u << 20)
+int fq_decode_split_static(const fq_pools* pools, const fq_decode_args* args, void* stream);
 
 /* Merge split partials in fixed slot order. split_counts NULL: every row combines slots
  * [0, kv_splits). Otherwise split_counts is int32 [B * HKV * head_tiles], the piece count of
