@@ -89,9 +89,17 @@ class ClockSampler:
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            t0 = time.time()            # nvidia-smi needs ~0.1-1 s before its first line
+            while not self.samples and time.time() - t0 < 5.0:
+                time.sleep(0.02)
+            self.primed = len(self.samples)
         except Exception:
             self.proc = None
         return self
+
+    def under_load(self):
+        """Samples taken since the sampler was primed (the idle first lines are dropped)."""
+        return len(self.samples) - getattr(self, "primed", 0)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -108,7 +116,7 @@ class ClockSampler:
     def summary(self):
         sm, mx, reasons = [], 0, set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.samples:
+        for line in self.samples[getattr(self, "primed", 0):]:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -121,7 +129,9 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm),
+                "window": "timed region, continued with untimed repeats of the same step until "
+                          "nvidia-smi (100 ms period) has sampled it 4 times"}
 
 
 def build_gpu_case(cfg, device, seed):
@@ -296,10 +306,15 @@ def main():
             ends[i].record()
         t_all1.record()
         barrier()
-        if args.steps < 20:
-            time.sleep(0.3)     # let the sampler see at least a few lines on short runs
-    w._decode_done_event = None
-    launches = w.launches - launches0
+        w._decode_done_event = None
+        launches = w.launches - launches0
+        # A timed region of a few milliseconds falls between two nvidia-smi samples: keep the
+        # same step running, untimed, until the sampler has seen the GPU under this load.
+        t_load = time.time()
+        while clocks.proc is not None and clocks.under_load() < 4 and time.time() - t_load < 3.0:
+            for _ in range(200):
+                w.run(q, cache, out=out)
+            torch.cuda.synchronize(device)
     total_ms = t_all0.elapsed_time(t_all1)
     decode_ms = float(np.mean([s.elapsed_time(m) for s, m in zip(starts, mids)]))
     step_ms = total_ms / args.steps

@@ -46,6 +46,13 @@
 #define FQ_STAMP(site) ((void)0)
 #endif
 
+// Diagnostic builds only: a bit mask of roles whose arithmetic is skipped while every barrier
+// arrival stays (1 consumers, 2 K expanders, 4 V expanders, 8 producers' copies). The output is
+// then meaningless; the launch time and instruction count show what each role costs.
+#ifndef FQ_STUB_ROLES
+#define FQ_STUB_ROLES 0
+#endif
+
 namespace fq {
 
 #ifdef FQ_WAIT_PROFILE
@@ -263,6 +270,12 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
       FQ_STAMP(18);
       // Only a request's last tile has positions past its length: their scores become -inf and
       // their records are neutralised, so stale shared memory can never reach the output.
+#if FQ_STUB_ROLES & 1
+      uint32_t pw[4] = {__float_as_uint(sk + zk) & 1u, raw[0] & 1u, __float_as_uint(sv + zv) & 1u, 0u};
+      float corr[GP];
+#pragma unroll
+      for (int h = 0; h < GP; ++h) corr[h] = 1.f;
+#else
       const bool valid = (tt + 1) * TILE <= w.len || tt * TILE + t < w.len;
       const float a_k = sk * 512.f;
       float wsc = sv * p2lp;
@@ -332,6 +345,7 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
         pw[h >> 2] |= hi2 << (16 * ((h >> 1) & 1));
         pw[2 + (h >> 2)] |= lo2 << (16 * ((h >> 1) & 1));
       }
+#endif
       FQ_STAMP(20);
       // the P row: bytes [hi_0..hi_7 | lo_0..lo_7]. The buffer is free: this group accumulated
       // the tile that last used it (two of its own tiles ago), which waited for that PV MMA.
@@ -527,7 +541,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
             const int id = j ? id1 : id0;
-            if (id < 0) continue;
+            if (id < 0 || (FQ_STUB_ROLES & 8)) continue;
             const long long blk = static_cast<long long>(id) * P.p.num_kv_heads + w.kvh;
             const uint8_t* ks = P.p.k_codes + blk * SP::CODE_PAGE + 16 * lane;
             const uint8_t* vs = P.p.v_codes + blk * SP::CODE_PAGE + 16 * lane;
@@ -657,8 +671,13 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         rp.next(NS);
         mbar_wait(bars.ring_full(s), rph, abort_flag, status, 8, wprof);
         uint32_t wk[D * BITS / 32], op[D / 4];
+#if FQ_STUB_ROLES & 2
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i) op[i] = it;
+#else
         load_row<BITS, D>(ring0 + s * SP::STAGE + SP::K_OFF + t * SP::RB, wk);
         expand_words<BITS, D>(wk, op);
+#endif
         __syncwarp();
         if (lane == 0) mbar_arrive(bars.ring_empty(s));
         // the stage was last read by the S MMA four tiles ago
@@ -693,8 +712,13 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         mbar_wait(bars.ring_full(s), rp.ph, abort_flag, status, 10, wprof);
         rp.next(NS);
         uint32_t wv[D * BITS / 32], op[D / 4];
+#if FQ_STUB_ROLES & 4
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i) op[i] = it;
+#else
         load_row<BITS, D>(ring0 + s * SP::STAGE + SP::V_OFF + t * SP::RB, wv);
         expand_words<BITS, D>(wv, op);
+#endif
         __syncwarp();
         if (lane == 0) mbar_arrive(bars.ring_empty(s));
         const uint32_t row = smem0 + SP::VOP_OFF + vs * SP::VOP_STAGE + t * D;
