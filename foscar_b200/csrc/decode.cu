@@ -6,29 +6,31 @@
 //     score = s_k[t] * (q_h . c_k[t]) + z_k[t] * sum(q_h)          (times sm_scale)
 //     out_h = ( sum_t w[t,h] c_v[t]  +  sum_t p[t,h] z_v[t] ) / sum_t p[t,h]
 // with w = p * s_v * 2^lp stored as two E4M3 planes (hi + lo/16).
-// The structure is this library's own. One persistent CTA per SM, 28 warps, 128-token tiles:
+// The structure is this library's own. One persistent CTA per SM, 20 warps, 128-token tiles:
 //
-//   warps 24, 27  producers on alternate tiles: page ids fetched 32 at a time a chunk ahead; a
+//   warps 16, 19  producers on alternate tiles: page ids fetched 32 at a time a chunk ahead; a
 //                 tile's two pages (K codes, V codes, scale records) as 16-byte cp.async copies
-//                 from all lanes into a deep shared-memory ring, completion on an mbarrier.
-//   warps 16-19   K expanders: thread t unpacks token t's K row to exact E4M3 bytes (code * 2^-9)
-//                 and stores it straight into TENSOR MEMORY as the S MMA's A operand (no
-//                 shared-memory round trip for K).
-//   warps 20-23   V expanders: same unpack into a 128-byte-swizzled shared-memory stage, as late
-//                 as the PV MMA allows (the packed codes wait in the ring, 4x smaller).
-//   warp 25       S issuer (one thread):  S[128 tok x 16] = C_K . Q^T   (A from tensor memory)
-//   warp 26       PV issuer (one thread): O^T[128 ch x 16] = C_V^T . [P_hi | P_lo]
-//   warps 0-15    four consumer groups, tile i -> group i % 4, each with its own running
-//                 (m, l, c, O): thread t folds the scales into S row t, joins the group's column
-//                 max, writes its P row; one tile later thread d accumulates channel d of the
-//                 tile's O. The groups are merged once per work item.
+//                 from all lanes into a deep shared-memory ring, completion on an mbarrier. The
+//                 first producer also stages each work item's query rows.
+//   warps 0-15    four worker groups, tile i -> group i % 4. A group carries its tile through
+//                 every stage: thread t unpacks token t's K row to exact E4M3 bytes
+//                 (code * 2^-9) straight into TENSOR MEMORY as the S MMA's A operand, unpacks its
+//                 V row into the group's 128-byte-swizzled shared-memory stage, folds the scales
+//                 into S row t, joins the group's column max, writes its P row; one tile later
+//                 thread d adds channel d of the tile's O to the group's accumulators. Each
+//                 group keeps its own running (m, l, c, O); they are merged once per work item.
+//   warp 17       S issuer (one thread):  S[128 tok x 16] = C_K . Q^T   (A from tensor memory)
+//   warp 18       PV issuer (one thread): O^T[128 ch x 16] = C_V^T . [P_hi | P_lo]
 //
-// Why four consumer groups: a group's per-tile work is a chain of dependent latencies
-// (tensor-memory loads, shared-memory round trips, mbarrier waits) of roughly 1800 cycles, while
-// a tile must retire every ~470 cycles to stream INT2 codes at 6 TB/s; the groups overlap those
-// chains. A tile's K and V operands stay live from expansion to the end of its MMA (a chain of
-// ~2500 cycles through the softmax), hence four operand stages each.
-// Every role walks the same list of work items, so the pipeline never drains between items.
+// Why one group per tile rather than a role per stage: the kernel is bound by instruction issue
+// and by hand-off latency, not by arithmetic. With separate unpack and softmax roles every tile
+// crossed seven mbarrier hand-offs per warp and 28 warps walked the tile list; measured with all
+// arithmetic removed, that skeleton alone took 70% of the launch time. Here a tile costs each of
+// its four warps three waits (codes landed, S done, previous PV done) and three arrivals, the
+// group's K stage, S, V stage, P rows and O need no barrier of their own (the group itself was
+// their last reader), and a group's chain of dependent latencies (~1500-2000 cycles a tile)
+// overlaps with the other three groups'.
+// Every role walks the same list of work items, so the pipeline never drains inside an item.
 // Byte-expansion yields channels in a fixed permuted order; Q is loaded in that order and O is
 // stored through it, so no per-element fix-up exists anywhere.
 #include "decode.cuh"
@@ -66,29 +68,25 @@ namespace {
 struct Bars {
   uint32_t base;
   int ns;
-  static constexpr int G = CONSUMER_GROUPS;
+  static constexpr int G = WORKER_GROUPS;
   __device__ uint32_t at(int i) const { return base + 8u * i; }
   __device__ uint32_t ring_full(int s) const { return at(s); }
   __device__ uint32_t ring_empty(int s) const { return at(ns + s); }
   __device__ uint32_t q_full(int s) const { return at(2 * ns + s); }
   __device__ uint32_t q_empty(int s) const { return at(2 * ns + 2 + s); }
-  // One barrier per tile slot (tile index modulo 8) and event, so that each MMA issuer makes
-  // ONE wait and ONE commit per tile (a successful wait costs its thread ~100 cycles, which at
-  // four MMAs of ~70 cycles each is what decides whether a tile retires in time):
-  //   s_ready : K operand of the tile is in tensor memory (4 K-expander warps) and the tile's S
-  //             buffer has been read by its consumer group (4 warps; pre-armed once)
-  //   s_done  : the tile's S MMA is complete (commit): its consumers read S, and the K expander
-  //             may reuse the operand stage four tiles later
-  //   pv_ready: V operand of the tile is in shared memory (4 V-expander warps) and its P rows are
-  //             written (4 consumer warps; the same group has by then read the O buffer's
-  //             previous contents)
-  //   pv_done : the tile's PV MMA is complete (commit): its consumers read O, the V expander may
-  //             reuse the stage four tiles later, and the P buffer is free
-  __device__ uint32_t s_ready(int slot) const { return at(2 * ns + 4 + slot); }
-  __device__ uint32_t s_done(int slot) const { return at(2 * ns + 12 + slot); }
-  __device__ uint32_t pv_ready(int slot) const { return at(2 * ns + 20 + slot); }
-  __device__ uint32_t pv_done(int slot) const { return at(2 * ns + 28 + slot); }
-  // 2*ns + 36 words of 8 bytes
+  // One barrier per worker group and event; a group's n-th tile uses phase n & 1:
+  //   k_ready : the tile's K operand is in tensor memory (the group's 4 warps); the group has by
+  //             then read the S of its previous tile
+  //   s_done  : the tile's S MMA is complete (commit)
+  //   pv_ready: the tile's V operand and P rows are in shared memory (4 warps); the group has by
+  //             then read the O of its previous tile
+  //   pv_done : the tile's PV MMA is complete (commit): O can be read, and the group's V stage
+  //             and P rows are free
+  __device__ uint32_t k_ready(int g) const { return at(2 * ns + 4 + g); }
+  __device__ uint32_t s_done(int g) const { return at(2 * ns + 4 + G + g); }
+  __device__ uint32_t pv_ready(int g) const { return at(2 * ns + 4 + 2 * G + g); }
+  __device__ uint32_t pv_done(int g) const { return at(2 * ns + 4 + 3 * G + g); }
+  // 2*ns + 4 + 4*G words of 8 bytes
 };
 
 // Position in the code ring: stage and phase, advanced without a division.
@@ -98,17 +96,21 @@ struct RingPos {
   __device__ __forceinline__ void next(int ns) {
     if (++s == ns) { s = 0; ph ^= 1u; }
   }
+  __device__ __forceinline__ void advance(int k, int ns) {  // k <= ns
+    s += k;
+    if (s >= ns) { s -= ns; ph ^= 1u; }
+  }
 };
 
-// Tensor-memory column plan (f32 columns): K operand stages, then S and O buffers of 16 columns,
-// two per consumer group.
+// Tensor-memory column plan (f32 columns): per worker group one K operand stage, one S and one
+// O buffer of 16 columns.
 template <int D>
 struct TmemPlan {
   static constexpr int KOP_COLS = D / 4;
   static constexpr int KOP = 0;
-  static constexpr int S = K_STAGES * KOP_COLS;
-  static constexpr int O = S + 2 * CONSUMER_GROUPS * 16;
-  static constexpr int USED = O + 2 * CONSUMER_GROUPS * 16;
+  static constexpr int S = WORKER_GROUPS * KOP_COLS;
+  static constexpr int O = S + WORKER_GROUPS * 16;
+  static constexpr int USED = O + WORKER_GROUPS * 16;
   static constexpr int ALLOC = USED <= 128 ? 128 : (USED <= 256 ? 256 : 512);
   static_assert(USED <= 512, "tensor memory plan exceeds 512 columns");
 };
@@ -155,23 +157,31 @@ __device__ inline void expand_words(const uint32_t (&w)[D * BITS / 32], uint32_t
     for (int k = 0; k < PER; ++k) out[PER * i + k] = (w[i] >> (BITS * k)) & MASK;
 }
 
-// Consumer role: one of four 128-thread groups; group `wg` takes the tiles whose running index
-// is `wg` modulo 4 and keeps its own (m, l, c, O), merged with the other groups per work item.
+// Worker role: one of four 128-thread groups. Group `wg` takes the tiles whose running index is
+// `wg` modulo 4 and carries each of them through every stage itself: unpack K into tensor memory,
+// unpack V into shared memory, fold the scales into the raw scores, softmax, write the P rows,
+// and (one of its own tiles later) add the tile's O to its accumulators. The group keeps its own
+// running (m, l, c, O); the four groups are merged once per work item.
 template <int BITS, int D, int GP>
-__device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* smem,
-                                              uint32_t smem0, uint32_t tmem, const Bars& bars,
-                                              volatile int* abort_flag, const ItemRange items,
-                                              int* wprof) {
+__device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem, uint32_t smem0,
+                                            uint32_t tmem, const Bars& bars,
+                                            volatile int* abort_flag, const ItemRange items,
+                                            int* wprof) {
   using SP = SmemPlan<BITS, D>;
   using TP = TmemPlan<D>;
-  constexpr int G = CONSUMER_GROUPS;
+  constexpr int G = WORKER_GROUPS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wg = warp >> 2, wq = warp & 3;
-  const int t = threadIdx.x & 127;  // token row in softmax, channel position in accumulation
+  const int t = threadIdx.x & 127;  // token row while unpacking and in softmax, channel in O
   const int NS = P.ring_stages;
   int* status = P.a.status;
   const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
   const uint32_t ring0 = smem0 + SP::RING_OFF;
+  const uint32_t k_dst = tmem + lane_base + TP::KOP + wg * TP::KOP_COLS;
+  const uint32_t s_src = tmem + lane_base + TP::S + wg * 16;
+  const uint32_t o_src = tmem + lane_base + TP::O + wg * 16;
+  const uint32_t v_row = smem0 + SP::VOP_OFF + wg * SP::VOP_STAGE + t * D;
+  const uint32_t p_row = smem0 + SP::P_OFF + wg * SP::P_BYTES + t * 16;
   float* red_max = reinterpret_cast<float*>(smem + SP::RED_OFF);          // [wg][buf][warp][8]
   float* red_sum = reinterpret_cast<float*>(smem + SP::RED_OFF + 1024);   // [wg][warp][16]
   constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
@@ -193,22 +203,21 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
   const float p2lp = exp2f(static_cast<float>(lp));
   const float o_mul = exp2f(static_cast<float>(9 - lp));
 
-  // this group's two S buffers start out free
-  if (lane == 0) {
-    mbar_arrive(bars.s_ready(wg));
-    mbar_arrive(bars.s_ready(wg + G));
-  }
-  int it = 0;
-  RingPos rp;
+  int it0 = 0;      // running index of the current item's first tile (every role counts alike)
+  int mine = wg;    // running index of this group's next tile
+  int n = 0;        // tiles this group has taken: the phase of its barriers
+  RingPos rp;       // ring position of tile `mine`
+  rp.advance(wg, NS);
   for (int wi = items.begin; wi < items.end; wi += items.step) {
     const WorkItem w = decode_item(P, wi);
+    const int nt = max(w.t1 - w.t0, 0);
     float m[GP], l[GP], c[GP], oacc[GP], corr_pend[GP], qsum[GP], qs[GP];
 #pragma unroll
     for (int h = 0; h < GP; ++h) {
       m[h] = -INFINITY; l[h] = 0.f; c[h] = 0.f; oacc[h] = 0.f; corr_pend[h] = 1.f;
       const int hl = w.ht * 8 + h;
       float sum = 0.f, scale = 0.f;
-      if (hl < P.heads_per_kv && w.t1 > w.t0) {
+      if (hl < P.heads_per_kv && nt > 0) {
         const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
         const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
         const uint32_t qw = __ldg(reinterpret_cast<const uint32_t*>(
@@ -226,13 +235,14 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
       qs[h] = scale;
     }
     bool pending = false;
-    int pend_it = 0;
 
+    // Add the group's previous tile's O (its PV MMA has had most of a tile's time to finish).
+    // The wait also frees the group's V stage and P rows for the tile in hand.
     auto accumulate = [&]() {
-      mbar_wait(bars.pv_done(pend_it & 7), (pend_it >> 3) & 1, abort_flag, status, 15, wprof);
+      mbar_wait(bars.pv_done(wg), (n - 1) & 1, abort_flag, status, 15, wprof);
       tc_fence_after();
       uint32_t r[16];
-      tmem_ld16(tmem + lane_base + TP::O + (pend_it & 7) * 16, r);
+      tmem_ld16(o_src, r);
       tmem_ld_wait();
       tc_fence_before();
 #pragma unroll
@@ -241,45 +251,81 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
                        fmaf(__uint_as_float(r[8 + h]), 0.0625f, __uint_as_float(r[h])));
     };
 
-    for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
-      const int s = rp.s;
-      const uint32_t rph = rp.ph;
-      rp.next(NS);
-      if ((it & (G - 1)) != wg) continue;
-      const int slot = it & 7, buf = (it / G) & 1;
-      // raw scores of token row t
-      mbar_wait(bars.s_done(slot), (it >> 3) & 1, abort_flag, status, 12, wprof);
+    for (; mine < it0 + nt; mine += G, rp.advance(G, NS), ++n) {
+      const int tt = w.t0 + (mine - it0);
+      const uint32_t stage = ring0 + rp.s * SP::STAGE;
+      mbar_wait(bars.ring_full(rp.s), rp.ph, abort_flag, status, 8, wprof);
       FQ_STAMP_BEGIN();
-      tc_fence_after();
-      uint32_t raw[GP];
-      if constexpr (GP == 4) tmem_ld4(tmem + lane_base + TP::S + slot * 16, raw);
-      else tmem_ld8(tmem + lane_base + TP::S + slot * 16, raw);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bars.s_ready(slot));   // free for the tile eight ahead
+      // ---- K row -> tensor memory (the S MMA's A operand). The stage is free: this group read
+      // the S of its previous tile, so that tile's MMA, the stage's last reader, is complete.
+      {
+        uint32_t wk[D * BITS / 32], op[D / 4];
+#if FQ_STUB_ROLES & 2
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i) op[i] = n;
+#else
+        load_row<BITS, D>(stage + SP::K_OFF + t * SP::RB, wk);
+        expand_words<BITS, D>(wk, op);
+#endif
+        tc_fence_after();
+#pragma unroll
+        for (int v = 0; v < D / 32; ++v) tmem_st8(k_dst + 8 * v, op + 8 * v);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars.k_ready(wg));
+      }
       FQ_STAMP(17);
-      // this token's records
-      mbar_wait(bars.ring_full(s), rph, abort_flag, status, 13, wprof);
+      if (pending) accumulate();
+      FQ_STAMP(18);
+      // ---- V row -> the group's 128-byte-swizzled shared-memory stage (the PV MMA's A operand)
+      {
+        uint32_t wv[D * BITS / 32], op[D / 4];
+#if FQ_STUB_ROLES & 4
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i) op[i] = n;
+#else
+        load_row<BITS, D>(stage + SP::V_OFF + t * SP::RB, wv);
+        expand_words<BITS, D>(wv, op);
+#endif
+#pragma unroll
+        for (int cc = 0; cc < D / 16; ++cc) {
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(v_row + ((cc ^ (t & 7)) << 4)),
+                       "r"(op[4 * cc]), "r"(op[4 * cc + 1]), "r"(op[4 * cc + 2]),
+                       "r"(op[4 * cc + 3])
+                       : "memory");
+        }
+      }
+      // this token's records; then the ring stage goes back to the producers
       float sk, zk, sv, zv;
       asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
                    : "=f"(sk), "=f"(zk), "=f"(sv), "=f"(zv)
-                   : "r"(ring0 + s * SP::STAGE + SP::S_OFF + t * 16));
+                   : "r"(stage + SP::S_OFF + t * 16));
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars.ring_empty(s));
-      FQ_STAMP(18);
-      // Only a request's last tile has positions past its length: their scores become -inf and
-      // their records are neutralised, so stale shared memory can never reach the output.
+      if (lane == 0) mbar_arrive(bars.ring_empty(rp.s));
+      FQ_STAMP(19);
+      // ---- raw scores of token row t
+      mbar_wait(bars.s_done(wg), n & 1, abort_flag, status, 12, wprof);
+      tc_fence_after();
+      uint32_t raw[GP];
+      if constexpr (GP == 4) tmem_ld4(s_src, raw);
+      else tmem_ld8(s_src, raw);
+      tmem_ld_wait();
+      tc_fence_before();
+      FQ_STAMP(20);
 #if FQ_STUB_ROLES & 1
       uint32_t pw[4] = {__float_as_uint(sk + zk) & 1u, raw[0] & 1u, __float_as_uint(sv + zv) & 1u, 0u};
       float corr[GP];
 #pragma unroll
       for (int h = 0; h < GP; ++h) corr[h] = 1.f;
 #else
+      // Only a request's last tile has positions past its length: their scores become -inf and
+      // their records are neutralised, so stale shared memory can never reach the output.
       const bool valid = (tt + 1) * TILE <= w.len || tt * TILE + t < w.len;
       const float a_k = sk * 512.f;
       float wsc = sv * p2lp;
       if (!valid) { wsc = 0.f; zv = 0.f; }
+      const int buf = n & 1;
       float x[GP];
       float* wmax = red_max + ((wg * 2 + buf) * 4 + wq) * 8;
 #pragma unroll
@@ -290,7 +336,6 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
         if (lane == 0) wmax[h] = wm;
       }
       named_barrier(1 + wg, 128);
-      FQ_STAMP(19);
       // the group's tile maximum: four warps' values, read as 16-byte vectors
       float tm[GP];
       {
@@ -346,24 +391,21 @@ __device__ __forceinline__ void consumer_role(const DecodeParams& P, uint8_t* sm
         pw[2 + (h >> 2)] |= lo2 << (16 * ((h >> 1) & 1));
       }
 #endif
-      FQ_STAMP(20);
-      // the P row: bytes [hi_0..hi_7 | lo_0..lo_7]. The buffer is free: this group accumulated
-      // the tile that last used it (two of its own tiles ago), which waited for that PV MMA.
-      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
-                       smem0 + SP::P_OFF + slot * SP::P_BYTES + t * 16),
-                   "r"(pw[0]), "r"(pw[1]), "r"(pw[2]), "r"(pw[3])
+      FQ_STAMP(21);
+      // the P row: bytes [hi_0..hi_7 | lo_0..lo_7]; with the V rows above it completes the PV
+      // MMA's operands
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_row), "r"(pw[0]), "r"(pw[1]),
+                   "r"(pw[2]), "r"(pw[3])
                    : "memory");
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars.pv_ready(slot));
-      FQ_STAMP(21);
-      // the previous tile's O, now that its MMA has had a tile's time to finish
-      if (pending) accumulate();
+      if (lane == 0) mbar_arrive(bars.pv_ready(wg));
       FQ_STAMP(22);
 #pragma unroll
       for (int h = 0; h < GP; ++h) corr_pend[h] = corr[h];
-      pending = true; pend_it = it;
+      pending = true;
     }
+    it0 += nt;
     if (pending) accumulate();
 
     // ---- item epilogue: group sums, then the groups' states merged by group 0
@@ -449,9 +491,10 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   static_assert(D == 128, "this build tiles head_dim 128");
   using SP = SmemPlan<BITS, D>;
   using TP = TmemPlan<D>;
-  constexpr int G = CONSUMER_GROUPS;
-  constexpr int W_EXPAND = 4 * G, W_PRODUCER = W_EXPAND + 4 * EXPAND_GROUPS,
-                W_S = W_PRODUCER + 1, W_PV = W_PRODUCER + 2, W_PRODUCER2 = W_PRODUCER + 3;
+  constexpr int G = WORKER_GROUPS;
+  constexpr int W_PRODUCER = 4 * G, W_S = W_PRODUCER + 1, W_PV = W_PRODUCER + 2,
+                W_PRODUCER2 = W_PRODUCER + 3;
+  static_assert(DECODE_THREADS == 32 * (W_PRODUCER2 + 1), "warp roles and block size disagree");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* const smem = smem_raw + (smem0 - smem_u32(smem_raw));
@@ -469,19 +512,17 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < NS; ++s) {
-      mbar_init(bars.ring_full(s), 32);   // one cp.async arrival per producer lane
-      mbar_init(bars.ring_empty(s), 12);  // 4 K-expander + 4 V-expander + 4 consumer warps
+      mbar_init(bars.ring_full(s), 32);  // one cp.async arrival per producer lane
+      mbar_init(bars.ring_empty(s), 4);  // the four warps of the group that took the tile
     }
-    static_assert(K_STAGES == 4 && V_STAGES == 4 && CONSUMER_GROUPS == 4,
-                  "the barrier plan assumes four operand stages and eight tile slots");
-    for (int s = 0; s < 8; ++s) {
-      mbar_init(bars.s_ready(s), 8);
-      mbar_init(bars.s_done(s), 1);
-      mbar_init(bars.pv_ready(s), 8);
-      mbar_init(bars.pv_done(s), 1);
+    for (int g = 0; g < G; ++g) {
+      mbar_init(bars.k_ready(g), 4);
+      mbar_init(bars.s_done(g), 1);
+      mbar_init(bars.pv_ready(g), 4);
+      mbar_init(bars.pv_done(g), 1);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(bars.q_full(s), 4);
+      mbar_init(bars.q_full(s), 1);
       mbar_init(bars.q_empty(s), 1);
     }
     fence_barrier_init();
@@ -503,11 +544,45 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     // a cp.async.bulk costs its issuing warp ~200 cycles whatever its size, so six 1-2 KB bulk
     // copies per tile cap the ring near 2.5 TB/s, while 20 cp.async per lane cost ~370 cycles.
     // Page ids are fetched 32 at a time, one per lane, a chunk ahead of the tiles that use them.
+    // The first producer also stages each item's query rows, in expansion order, as the S MMA's
+    // B operand; it runs a ring's depth ahead of the MMAs, which hides the load.
     const int pi = warp == W_PRODUCER ? 0 : 1;
-    int it = 0;
+    int it = 0, qi = 0;
     RingPos rp;
     for (int wi = items.begin; wi < items.end; wi += items.step) {
       const WorkItem w = decode_item(P, wi);
+      if (w.t1 <= w.t0) continue;
+      if (pi == 0) {
+        const int qb = qi & 1;
+        mbar_wait(bars.q_empty(qb), ((qi >> 1) & 1) ^ 1, abort_flag, status, 7, wprof);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int chunk = lane + 32 * j;      // 16 rows of eight 16-byte chunks
+          const int r = chunk >> 3, cc = chunk & 7;
+          uint4 v = make_uint4(0, 0, 0, 0);
+          const int hl = w.ht * 8 + r;  // head inside the KV head's group
+          if (r < 8 && hl < P.heads_per_kv) {
+            const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
+            const uint4 in = __ldg(reinterpret_cast<const uint4*>(
+                static_cast<const uint8_t*>(P.a.q) +
+                (static_cast<long long>(w.b) * P.a.num_qo_heads + head) * D + 16 * cc));
+            if (BITS == 2) {
+              v.x = __byte_perm(in.x, in.y, 0x6420);
+              v.y = __byte_perm(in.z, in.w, 0x6420);
+              v.z = __byte_perm(in.x, in.y, 0x7531);
+              v.w = __byte_perm(in.z, in.w, 0x7531);
+            } else {
+              v = in;
+            }
+          }
+          *reinterpret_cast<uint4*>(smem + SP::Q_OFF + qb * SP::Q_BYTES + r * 128 +
+                                    ((cc ^ (r & 7)) << 4)) = v;
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars.q_full(qb));
+      }
+      ++qi;
       const int npages = (w.len + PAGE - 1) / PAGE;
       const int pend = min(2 * w.t1, npages);
       auto fetch = [&](int pg0) {
@@ -531,11 +606,9 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           const uint32_t eph = rp.ph ^ 1u;
           rp.next(NS);
           if ((it & 1) != pi) continue;
-          FQ_STAMP_BEGIN();
           const int id0 = __shfl_sync(0xFFFFFFFFu, cur, 2 * k);
           const int id1 = __shfl_sync(0xFFFFFFFFu, cur, 2 * k + 1);
           mbar_wait(bars.ring_empty(s), eph, abort_flag, status, 0, wprof);
-          FQ_STAMP(24);
           const uint32_t full = bars.ring_full(s);
           const uint32_t dst = ring0 + s * SP::STAGE + 16 * lane;
 #pragma unroll
@@ -551,15 +624,13 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
             for (int c = 0; c < SP::CODE_PAGE; c += 512)
               cp_async16(dst + SP::K_OFF + j * SP::CODE_PAGE + c, ks + c);
 #pragma unroll
-            for (int c = 0; c < SP::SCALE_PAGE; c += 512)
-              cp_async16(dst + SP::S_OFF + j * SP::SCALE_PAGE + c, ss + c);
-#pragma unroll
             for (int c = 0; c < SP::CODE_PAGE; c += 512)
               cp_async16(dst + SP::V_OFF + j * SP::CODE_PAGE + c, vs + c);
+#pragma unroll
+            for (int c = 0; c < SP::SCALE_PAGE; c += 512)
+              cp_async16(dst + SP::S_OFF + j * SP::SCALE_PAGE + c, ss + c);
           }
-          FQ_STAMP(26);
           cp_async_arrive(full);
-          FQ_STAMP(27);
         }
         cur = nxt;
       }
@@ -571,9 +642,9 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     }
   } else if (warp == W_S) {
     // ------------------------------------------------------------------ S issuer
-    // One thread issues S = C_K . Q^T for every tile. The loop is kept to a few dozen scalar
-    // instructions per tile: descriptor high words, the instruction descriptor and the
-    // accumulate flags are immediates, and every buffer index is a bit field of the counter.
+    // One thread issues S = C_K . Q^T for every tile, in tile order. The loop is kept to a few
+    // dozen scalar instructions per tile: descriptor high words, the instruction descriptor and
+    // the accumulate flags are immediates, and every buffer index is a bit field of the counter.
     if (lane == 0) {
       constexpr uint32_t IDESC_S = make_idesc_e4m3(128, 16, 0, 0);
       constexpr uint32_t Q_HI = smem_desc_hi(1024, 2);
@@ -585,16 +656,16 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status, 1, wprof);
         const uint32_t q_lo = smem_desc_lo(smem0 + SP::Q_OFF + qb * SP::Q_BYTES, 16);
         for (int t = w.t0; t < w.t1; ++t, ++it) {
-          const int slot = it & 7, ks = it & (K_STAGES - 1);
-          mbar_wait(bars.s_ready(slot), (it >> 3) & 1, abort_flag, status, 2, wprof);
+          const int g = it & (G - 1);
+          mbar_wait(bars.k_ready(g), (it / G) & 1, abort_flag, status, 2, wprof);
           tc_fence_after();
-          const uint32_t sd = tmem + TP::S + slot * 16;
-          const uint32_t ka = tmem + TP::KOP + ks * TP::KOP_COLS;
+          const uint32_t sd = tmem + TP::S + g * 16;
+          const uint32_t ka = tmem + TP::KOP + g * TP::KOP_COLS;
           umma_ts_c<Q_HI, IDESC_S, false>(sd, ka, q_lo);
 #pragma unroll
           for (int k = 1; k < D / 32; ++k)
             umma_ts_c<Q_HI, IDESC_S, true>(sd, ka + 8 * k, q_lo + 2 * k);
-          tc_commit(bars.s_done(slot));
+          tc_commit(bars.s_done(g));
           if (t == w.t1 - 1) tc_commit(bars.q_empty(qb));
         }
         ++qi;
@@ -612,130 +683,25 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       for (int wi = items.begin; wi < items.end; wi += items.step) {
         const WorkItem w = decode_item(P, wi);
         for (int t = w.t0; t < w.t1; ++t, ++it) {
-          const int slot = it & 7, vs = it & (V_STAGES - 1);
-          mbar_wait(bars.pv_ready(slot), (it >> 3) & 1, abort_flag, status, 4, wprof);
+          const int g = it & (G - 1);
+          mbar_wait(bars.pv_ready(g), (it / G) & 1, abort_flag, status, 4, wprof);
           tc_fence_after();
-          const uint32_t v_lo = v_lo0 + vs * (SP::VOP_STAGE >> 4);
-          const uint32_t p_lo = p_lo0 + slot * (SP::P_BYTES >> 4);
-          const uint32_t od = tmem + TP::O + slot * 16;
+          const uint32_t v_lo = v_lo0 + g * (SP::VOP_STAGE >> 4);
+          const uint32_t p_lo = p_lo0 + g * (SP::P_BYTES >> 4);
+          const uint32_t od = tmem + TP::O + g * 16;
           umma_ss_c<V_HI, P_HI, IDESC_PV, false>(od, v_lo, p_lo);
 #pragma unroll
           for (int k = 1; k < TILE / 32; ++k)
             umma_ss_c<V_HI, P_HI, IDESC_PV, true>(od, v_lo + k * (32 * D >> 4),
                                                   p_lo + k * (32 * 16 >> 4));
-          tc_commit(bars.pv_done(slot));
+          tc_commit(bars.pv_done(g));
         }
       }
     }
     __syncwarp();
-  } else if (warp >= W_EXPAND && warp < W_EXPAND + 4) {
-    // ------------------------------------------------------------------ K expanders (+ Q)
-    constexpr int eg = 0;
-    const int t = threadIdx.x - 32 * W_EXPAND;  // token row = tensor-memory lane
-    const uint32_t lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;
-    int it = 0, qi = 0;
-    RingPos rp;
-    for (int wi = items.begin; wi < items.end; wi += items.step) {
-      const WorkItem w = decode_item(P, wi);
-      if (w.t1 <= w.t0) continue;
-      if (eg == 0) {  // this item's query rows, in expansion order, as the S MMA's B operand
-        const int qb = qi & 1;
-        mbar_wait(bars.q_empty(qb), ((qi >> 1) & 1) ^ 1, abort_flag, status, 7, wprof);
-        const int r = t >> 3, c = t & 7;  // row (head), 16-byte chunk
-        uint4 v = make_uint4(0, 0, 0, 0);
-        const int hl = w.ht * 8 + r;  // head inside the KV head's group
-        if (r < 8 && hl < P.heads_per_kv) {
-          const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
-          const uint4 in = __ldg(reinterpret_cast<const uint4*>(
-              static_cast<const uint8_t*>(P.a.q) +
-              (static_cast<long long>(w.b) * P.a.num_qo_heads + head) * D + 16 * c));
-          if (BITS == 2) {
-            v.x = __byte_perm(in.x, in.y, 0x6420);
-            v.y = __byte_perm(in.z, in.w, 0x6420);
-            v.z = __byte_perm(in.x, in.y, 0x7531);
-            v.w = __byte_perm(in.z, in.w, 0x7531);
-          } else {
-            v = in;
-          }
-        }
-        *reinterpret_cast<uint4*>(smem + SP::Q_OFF + qb * SP::Q_BYTES + r * 128 +
-                                  ((c ^ (r & 7)) << 4)) = v;
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars.q_full(qb));
-      }
-      ++qi;
-      for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
-        const int s = rp.s, ks = it & (K_STAGES - 1);
-        const uint32_t rph = rp.ph;
-        rp.next(NS);
-        mbar_wait(bars.ring_full(s), rph, abort_flag, status, 8, wprof);
-        uint32_t wk[D * BITS / 32], op[D / 4];
-#if FQ_STUB_ROLES & 2
-#pragma unroll
-        for (int i = 0; i < D / 4; ++i) op[i] = it;
-#else
-        load_row<BITS, D>(ring0 + s * SP::STAGE + SP::K_OFF + t * SP::RB, wk);
-        expand_words<BITS, D>(wk, op);
-#endif
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars.ring_empty(s));
-        // the stage was last read by the S MMA four tiles ago
-        if (it >= K_STAGES)
-          mbar_wait(bars.s_done((it - K_STAGES) & 7), ((it - K_STAGES) >> 3) & 1, abort_flag,
-                    status, 9, wprof);
-        tc_fence_after();
-        const uint32_t dst = tmem + lane_base + TP::KOP + ks * TP::KOP_COLS;
-#pragma unroll
-        for (int v = 0; v < D / 32; ++v) tmem_st8(dst + 8 * v, op + 8 * v);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars.s_ready(it & 7));
-      }
-    }
-  } else if (warp >= W_EXPAND + 4 && warp < W_PRODUCER) {
-    // ------------------------------------------------------------------ V expanders
-    // They run as late as the PV MMA allows: the packed codes wait in the ring (4 KB a tile),
-    // not as expanded operands (16 KB a tile).
-    const int t = threadIdx.x - 32 * (W_EXPAND + 4);
-    int it = 0;
-    RingPos rp;
-    for (int wi = items.begin; wi < items.end; wi += items.step) {
-      const WorkItem w = decode_item(P, wi);
-      for (int tt = w.t0; tt < w.t1; ++tt, ++it) {
-        const int s = rp.s, vs = it & (V_STAGES - 1);
-        // the stage was last read by the PV MMA four tiles ago
-        if (it >= V_STAGES)
-          mbar_wait(bars.pv_done((it - V_STAGES) & 7), ((it - V_STAGES) >> 3) & 1, abort_flag,
-                    status, 11, wprof);
-        mbar_wait(bars.ring_full(s), rp.ph, abort_flag, status, 10, wprof);
-        rp.next(NS);
-        uint32_t wv[D * BITS / 32], op[D / 4];
-#if FQ_STUB_ROLES & 4
-#pragma unroll
-        for (int i = 0; i < D / 4; ++i) op[i] = it;
-#else
-        load_row<BITS, D>(ring0 + s * SP::STAGE + SP::V_OFF + t * SP::RB, wv);
-        expand_words<BITS, D>(wv, op);
-#endif
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars.ring_empty(s));
-        const uint32_t row = smem0 + SP::VOP_OFF + vs * SP::VOP_STAGE + t * D;
-#pragma unroll
-        for (int c = 0; c < D / 16; ++c) {
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row + ((c ^ (t & 7)) << 4)),
-                       "r"(op[4 * c]), "r"(op[4 * c + 1]), "r"(op[4 * c + 2]), "r"(op[4 * c + 3])
-                       : "memory");
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars.pv_ready(it & 7));
-      }
-    }
-  } else if (warp < W_EXPAND) {
-    // ------------------------------------------------------------------ consumers
-    consumer_role<BITS, D, GP>(P, smem, smem0, tmem, bars, abort_flag, items, wprof);
+  } else {
+    // ------------------------------------------------------------------ workers
+    worker_role<BITS, D, GP>(P, smem, smem0, tmem, bars, abort_flag, items, wprof);
   }
 
   tc_fence_before();
@@ -867,9 +833,9 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   if (stages > 20) stages = 20;
   if (const char* env = getenv("FOSCAR_B200_RING_STAGES")) {   // tuning knob for experiments
     const int want = atoi(env);
-    if (want >= 2 && want < stages) stages = want;
+    if (want >= WORKER_GROUPS && want < stages) stages = want;
   }
-  if (stages < 2) return FQ_ERR_UNSUPPORTED;
+  if (stages < WORKER_GROUPS) return FQ_ERR_UNSUPPORTED;  // a group steps the ring by one lap at most
   P.ring_stages = stages;
   const int smem = SP::RING_OFF + stages * SP::STAGE + 1024;
   static bool configured[64] = {};  // per (BITS, D, GP) instantiation and device

@@ -7,11 +7,8 @@ namespace fq {
 
 constexpr int TILE = 128;            // tokens per sequence tile: two pages
 constexpr int WORK_WORDS = 8;        // int32 words per explicit work-list row
-constexpr int CONSUMER_GROUPS = 4;   // 128-thread softmax/accumulate groups, tile i -> group i % 4
-constexpr int EXPAND_GROUPS = 2;     // 128-thread unpack groups: one for K, one for V
-constexpr int DECODE_THREADS = 896;  // 28 warps, see decode.cu
-constexpr int K_STAGES = 4;          // K operand stages in tensor memory
-constexpr int V_STAGES = 4;          // V operand stages in shared memory
+constexpr int WORKER_GROUPS = 4;     // 128-thread groups, tile i -> group i % 4, see decode.cu
+constexpr int DECODE_THREADS = 640;  // 16 worker warps + 2 producers + 2 MMA issuers
 constexpr int SMEM_LIMIT = 232448;   // 227 KiB opt-in limit per CTA on sm_100
 
 struct DecodeParams {
@@ -41,11 +38,11 @@ struct SmemPlan {
   static constexpr int Q_BYTES = 16 * D;               // 16 MMA rows of D bytes
   static constexpr int P_BYTES = TILE * 16;            // 16 bytes (8 hi + 8 lo) per token
   static constexpr int VOP_OFF = 0;
-  static constexpr int Q_OFF = VOP_OFF + V_STAGES * VOP_STAGE;
+  static constexpr int Q_OFF = VOP_OFF + WORKER_GROUPS * VOP_STAGE;
   static constexpr int P_OFF = Q_OFF + 2 * Q_BYTES;
   static constexpr int XCHG_BYTES = TILE * 8 * 4 + 128;   // one group's accumulators + (m,l,c)
-  static constexpr int XCHG_OFF = P_OFF + 2 * CONSUMER_GROUPS * P_BYTES;
-  static constexpr int RED_OFF = XCHG_OFF + (CONSUMER_GROUPS - 1) * XCHG_BYTES;  // reductions
+  static constexpr int XCHG_OFF = P_OFF + WORKER_GROUPS * P_BYTES;
+  static constexpr int RED_OFF = XCHG_OFF + (WORKER_GROUPS - 1) * XCHG_BYTES;  // reductions
   static constexpr int RED_BYTES = 2048;
   static constexpr int BAR_OFF = RED_OFF + RED_BYTES;
   static constexpr int BAR_BYTES = 2048;   // barriers, then flags and diagnostics
