@@ -155,6 +155,19 @@ __device__ __forceinline__ void reg_dec() {
 __device__ inline void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+// Named barrier that also returns whether `pred` held for any of the arriving threads.
+__device__ inline bool named_barrier_or(int id, int threads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(threads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
+}
 
 // ---------------------------------------------------------------------------------------------
 // PTX: bulk async copy global -> shared, completing on an mbarrier

@@ -156,6 +156,30 @@ __device__ inline void expand_words(const uint32_t (&w)[D * BITS / 32], uint32_t
 #pragma unroll
     for (int k = 0; k < PER; ++k) out[PER * i + k] = (w[i] >> (BITS * k)) & MASK;
 }
+// The cheaper unpack for INT2 V rows: odd output words keep their codes two bits up, i.e. hold
+// 4 * code, which is still an exact E4M3 byte (values up to 15 * 2^-9 are linear in the byte).
+// Five instead of seven instructions per packed word; the channels at those positions
+// (expanded position p with (p >> 2) & 1) come out of the PV MMA four times too large and are
+// scaled back once per work item (v_position_scale).
+template <int BITS, int D>
+__device__ inline void expand_words_v(const uint32_t (&w)[D * BITS / 32], uint32_t (&out)[D / 4]) {
+  if constexpr (BITS == 2) {
+#pragma unroll
+    for (int i = 0; i < D * BITS / 32; ++i) {
+      const uint32_t hi = w[i] >> 4;
+      out[4 * i + 0] = w[i] & 0x03030303u;
+      out[4 * i + 1] = w[i] & 0x0C0C0C0Cu;
+      out[4 * i + 2] = hi & 0x03030303u;
+      out[4 * i + 3] = hi & 0x0C0C0C0Cu;
+    }
+  } else {
+    expand_words<BITS, D>(w, out);
+  }
+}
+template <int BITS>
+__device__ inline float v_position_scale(int pos) {
+  return BITS == 2 && ((pos >> 2) & 1) ? 0.25f : 1.f;
+}
 
 // Worker role: one of four 128-thread groups. Group `wg` takes the tiles whose running index is
 // `wg` modulo 4 and carries each of them through every stage itself: unpack K into tensor memory,
@@ -200,6 +224,9 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     top = __reduce_max_sync(0xFFFFFFFFu, top);
     lp = 135 - max(top, 27);
   }
+  // w = p * s_v * 2^lp must stay inside E4M3 with p up to 2^MAX_LAG (see the softmax below)
+  constexpr float MAX_LAG = 3.f;
+  lp -= static_cast<int>(MAX_LAG);
   const float p2lp = exp2f(static_cast<float>(lp));
   const float o_mul = exp2f(static_cast<float>(9 - lp));
 
@@ -211,10 +238,10 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   for (int wi = items.begin; wi < items.end; wi += items.step) {
     const WorkItem w = decode_item(P, wi);
     const int nt = max(w.t1 - w.t0, 0);
-    float m[GP], l[GP], c[GP], oacc[GP], corr_pend[GP], qsum[GP], qs[GP];
+    float m[GP], l[GP], c[GP], oacc[GP], qsum[GP], qs[GP];
 #pragma unroll
     for (int h = 0; h < GP; ++h) {
-      m[h] = -INFINITY; l[h] = 0.f; c[h] = 0.f; oacc[h] = 0.f; corr_pend[h] = 1.f;
+      m[h] = -INFINITY; l[h] = 0.f; c[h] = 0.f; oacc[h] = 0.f;
       const int hl = w.ht * 8 + h;
       float sum = 0.f, scale = 0.f;
       if (hl < P.heads_per_kv && nt > 0) {
@@ -247,8 +274,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       tc_fence_before();
 #pragma unroll
       for (int h = 0; h < GP; ++h)
-        oacc[h] = fmaf(oacc[h], corr_pend[h],
-                       fmaf(__uint_as_float(r[8 + h]), 0.0625f, __uint_as_float(r[h])));
+        oacc[h] += fmaf(__uint_as_float(r[8 + h]), 0.0625f, __uint_as_float(r[h]));
     };
 
     for (; mine < it0 + nt; mine += G, rp.advance(G, NS), ++n) {
@@ -286,7 +312,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         for (int i = 0; i < D / 4; ++i) op[i] = n;
 #else
         load_row<BITS, D>(stage + SP::V_OFF + t * SP::RB, wv);
-        expand_words<BITS, D>(wv, op);
+        expand_words_v<BITS, D>(wv, op);
 #endif
 #pragma unroll
         for (int cc = 0; cc < D / 16; ++cc) {
@@ -315,9 +341,6 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       FQ_STAMP(20);
 #if FQ_STUB_ROLES & 1
       uint32_t pw[4] = {__float_as_uint(sk + zk) & 1u, raw[0] & 1u, __float_as_uint(sv + zv) & 1u, 0u};
-      float corr[GP];
-#pragma unroll
-      for (int h = 0; h < GP; ++h) corr[h] = 1.f;
 #else
       // Only a request's last tile has positions past its length: their scores become -inf and
       // their records are neutralised, so stale shared memory can never reach the output.
@@ -325,50 +348,38 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       const float a_k = sk * 512.f;
       float wsc = sv * p2lp;
       if (!valid) { wsc = 0.f; zv = 0.f; }
-      const int buf = n & 1;
+      // Scores against the group's running reference m, which may lag the true maximum by up to
+      // MAX_LAG (p <= 2^MAX_LAG; the P scale leaves that headroom below the E4M3 range). Only
+      // when some score of the tile exceeds that does the group take the exact column maximum
+      // and rescale; the common tile costs one reducing barrier instead of an exchange through
+      // shared memory.
       float x[GP];
-      float* wmax = red_max + ((wg * 2 + buf) * 4 + wq) * 8;
+      float over = -INFINITY;
 #pragma unroll
       for (int h = 0; h < GP; ++h) {
         const float xv = qs[h] * fmaf(a_k, __uint_as_float(raw[h]), zk * qsum[h]);
         x[h] = valid ? xv : -INFINITY;
-        const float wm = warp_max_f32(x[h]);
-        if (lane == 0) wmax[h] = wm;
+        over = fmaxf(over, x[h] - m[h]);
       }
-      named_barrier(1 + wg, 128);
-      // the group's tile maximum: four warps' values, read as 16-byte vectors
-      float tm[GP];
-      {
-        const uint32_t g0 = smem0 + SP::RED_OFF + (wg * 2 + buf) * 4 * 8 * 4;
-#pragma unroll
-        for (int v4 = 0; v4 < GP / 4; ++v4) {
-          float a4[4][4];
-#pragma unroll
-          for (int wv = 0; wv < 4; ++wv)
-            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-                         : "=f"(a4[wv][0]), "=f"(a4[wv][1]), "=f"(a4[wv][2]), "=f"(a4[wv][3])
-                         : "r"(g0 + wv * 32 + v4 * 16));
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            tm[4 * v4 + i] = fmaxf(fmaxf(a4[0][i], a4[1][i]), fmaxf(a4[2][i], a4[3][i]));
-        }
-      }
-      // the running maximum rarely moves after the first tiles: the rescale is a uniform branch
-      float corr[GP];
-      bool moved = false;
-#pragma unroll
-      for (int h = 0; h < GP; ++h) {
-        tm[h] = fmaxf(m[h], tm[h]);
-        moved |= tm[h] != m[h];
-        corr[h] = 1.f;
-      }
-      if (moved) {
+      if (named_barrier_or(1 + wg, 128, over > MAX_LAG)) {
+        const int buf = n & 1;
+        float* wmax = red_max + ((wg * 2 + buf) * 4 + wq) * 8;
 #pragma unroll
         for (int h = 0; h < GP; ++h) {
-          corr[h] = m[h] == -INFINITY ? 0.f : fast_exp2(m[h] - tm[h]);
-          l[h] *= corr[h];
-          c[h] *= corr[h];
-          m[h] = tm[h];
+          const float wm = warp_max_f32(x[h]);
+          if (lane == 0) wmax[h] = wm;
+        }
+        named_barrier(1 + wg, 128);
+        const float* gm = red_max + (wg * 2 + buf) * 4 * 8;
+#pragma unroll
+        for (int h = 0; h < GP; ++h) {
+          const float tm =
+              fmaxf(m[h], fmaxf(fmaxf(gm[h], gm[8 + h]), fmaxf(gm[16 + h], gm[24 + h])));
+          const float corr = m[h] == -INFINITY ? 0.f : fast_exp2(m[h] - tm);
+          l[h] *= corr;
+          c[h] *= corr;
+          oacc[h] *= corr;   // holds every earlier tile's O (added above)
+          m[h] = tm;
         }
       }
       // two heads per instruction in f16x2: p = 2^(x-m), w = p * s_v 2^lp, E4M3 hi + lo/16
@@ -401,8 +412,6 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       __syncwarp();
       if (lane == 0) mbar_arrive(bars.pv_ready(wg));
       FQ_STAMP(22);
-#pragma unroll
-      for (int h = 0; h < GP; ++h) corr_pend[h] = corr[h];
       pending = true;
     }
     it0 += nt;
@@ -460,7 +469,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           O = O * f0 + o1 * f1;
           M = Mn;
         }
-        O = O * o_mul + C;
+        O = O * (o_mul * v_position_scale<BITS>(t)) + C;
         const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
         const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
         if (w.slot < 0) {
