@@ -97,6 +97,11 @@ constexpr long long WAIT_BUDGET_CYCLES = 2000000000LL;
 constexpr int WAIT_SITES = 32;
 static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity,
                                             volatile int* abort_flag, int* status) {
+  // mbarrier.try_wait suspends the thread in hardware for a bounded time by itself; a
+  // suspend-time hint on top of it compiles to a software loop of clock reads and nanosleeps
+  // whose instructions, over twenty waiting warps, took a third of the SM's issue slots. The
+  // abort flag and the clock are looked at once every 32 failed tries only.
+#ifdef FQ_WAIT_SLEEP_HINT
   const long long t0 = clock64();
   while (!mbar_try_sleep(bar, parity)) {
     if (*abort_flag) return;
@@ -106,6 +111,20 @@ static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity
       return;
     }
   }
+#else
+  long long t0 = 0;
+  for (uint32_t tries = 1; !mbar_try(bar, parity); ++tries) {
+    if ((tries & 31u) != 0) continue;
+    if (*abort_flag) return;
+    const long long now = clock64();
+    if (t0 == 0) t0 = now;
+    if (now - t0 > WAIT_BUDGET_CYCLES) {
+      *abort_flag = 1;
+      if (status) atomicOr(status, FQ_STATUS_TIMEOUT);
+      return;
+    }
+  }
+#endif
 }
 #ifndef FQ_WAIT_PROFILE
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity,

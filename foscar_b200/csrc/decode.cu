@@ -206,8 +206,11 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   const uint32_t o_src = tmem + lane_base + TP::O + wg * 16;
   const uint32_t v_row = smem0 + SP::VOP_OFF + wg * SP::VOP_STAGE + t * D;
   const uint32_t p_row = smem0 + SP::P_OFF + wg * SP::P_BYTES + t * 16;
-  float* red_max = reinterpret_cast<float*>(smem + SP::RED_OFF);          // [wg][buf][warp][8]
-  float* red_sum = reinterpret_cast<float*>(smem + SP::RED_OFF + 1024);   // [wg][warp][16]
+  float* red_max = reinterpret_cast<float*>(smem + SP::RED_OFF);              // [wg][buf][warp][8]
+  float* red_sum = reinterpret_cast<float*>(smem + SP::RED_OFF + 256 * G);    // [wg][warp][16]
+  // this warp's copy of the item's per-head constants: sm_scale*log2e*q_descale, and that times
+  // the sum of the head's query values
+  float* head_k = reinterpret_cast<float*>(smem + SP::RED_OFF + 512 * G) + warp * 16;
   constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 
   // pool-wide P-scale exponent from the count table: lp = 135 - max(top nonzero bin, 27)
@@ -238,7 +241,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   for (int wi = items.begin; wi < items.end; wi += items.step) {
     const WorkItem w = decode_item(P, wi);
     const int nt = max(w.t1 - w.t0, 0);
-    float m[GP], l[GP], c[GP], oacc[GP], qsum[GP], qs[GP];
+    float m[GP], l[GP], c[GP], oacc[GP];
+    __syncwarp();   // the warp's reads of the previous item's values are over
 #pragma unroll
     for (int h = 0; h < GP; ++h) {
       m[h] = -INFINITY; l[h] = 0.f; c[h] = 0.f; oacc[h] = 0.f;
@@ -258,9 +262,11 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
-      qsum[h] = sum;
-      qs[h] = scale;
+      // per-head constants of the item: read back from shared memory each tile instead of
+      // living in 16 registers of every thread
+      if (lane == 0) { head_k[h] = scale; head_k[8 + h] = scale * sum; }
     }
+    __syncwarp();
     bool pending = false;
 
     // Add the group's previous tile's O (its PV MMA has had most of a tile's time to finish).
@@ -293,10 +299,12 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         load_row<BITS, D>(stage + SP::K_OFF + t * SP::RB, wk);
         expand_words<BITS, D>(wk, op);
 #endif
+        FQ_STAMP(3);
         tc_fence_after();
 #pragma unroll
         for (int v = 0; v < D / 32; ++v) tmem_st8(k_dst + 8 * v, op + 8 * v);
         tmem_st_wait();
+        FQ_STAMP(5);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars.k_ready(wg));
@@ -314,6 +322,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         load_row<BITS, D>(stage + SP::V_OFF + t * SP::RB, wv);
         expand_words_v<BITS, D>(wv, op);
 #endif
+        FQ_STAMP(6);
 #pragma unroll
         for (int cc = 0; cc < D / 16; ++cc) {
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(v_row + ((cc ^ (t & 7)) << 4)),
@@ -322,6 +331,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
                        : "memory");
         }
       }
+      FQ_STAMP(9);
       // this token's records; then the ring stage goes back to the producers
       float sk, zk, sv, zv;
       asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
@@ -339,6 +349,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       tmem_ld_wait();
       tc_fence_before();
       FQ_STAMP(20);
+      FQ_STAMP(10);   // the cost of one stamp itself
 #if FQ_STUB_ROLES & 1
       uint32_t pw[4] = {__float_as_uint(sk + zk) & 1u, raw[0] & 1u, __float_as_uint(sv + zv) & 1u, 0u};
 #else
@@ -357,7 +368,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       float over = -INFINITY;
 #pragma unroll
       for (int h = 0; h < GP; ++h) {
-        const float xv = qs[h] * fmaf(a_k, __uint_as_float(raw[h]), zk * qsum[h]);
+        const float xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[h]), head_k[8 + h] * zk);
         x[h] = valid ? xv : -INFINITY;
         over = fmaxf(over, x[h] - m[h]);
       }
@@ -409,6 +420,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
                    "r"(pw[2]), "r"(pw[3])
                    : "memory");
       fence_proxy_async();
+      FQ_STAMP(11);
       __syncwarp();
       if (lane == 0) mbar_arrive(bars.pv_ready(wg));
       FQ_STAMP(22);
@@ -653,20 +665,20 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     // ------------------------------------------------------------------ S issuer
     // One thread issues S = C_K . Q^T for every tile, in tile order. The loop is kept to a few
     // dozen scalar instructions per tile: descriptor high words, the instruction descriptor and
-    // the accumulate flags are immediates, and every buffer index is a bit field of the counter.
+    // the accumulate flags are immediates, and the group index is a counter.
     if (lane == 0) {
       constexpr uint32_t IDESC_S = make_idesc_e4m3(128, 16, 0, 0);
       constexpr uint32_t Q_HI = smem_desc_hi(1024, 2);
-      int it = 0, qi = 0;
+      int qi = 0, g = 0;   // tiles go to the groups in turn
+      uint32_t gph = 0;    // phase of the groups' barriers: flips once per round of G tiles
       for (int wi = items.begin; wi < items.end; wi += items.step) {
         const WorkItem w = decode_item(P, wi);
         if (w.t1 <= w.t0) continue;
         const int qb = qi & 1;
         mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status, 1, wprof);
         const uint32_t q_lo = smem_desc_lo(smem0 + SP::Q_OFF + qb * SP::Q_BYTES, 16);
-        for (int t = w.t0; t < w.t1; ++t, ++it) {
-          const int g = it & (G - 1);
-          mbar_wait(bars.k_ready(g), (it / G) & 1, abort_flag, status, 2, wprof);
+        for (int t = w.t0; t < w.t1; ++t) {
+          mbar_wait(bars.k_ready(g), gph, abort_flag, status, 2, wprof);
           tc_fence_after();
           const uint32_t sd = tmem + TP::S + g * 16;
           const uint32_t ka = tmem + TP::KOP + g * TP::KOP_COLS;
@@ -676,6 +688,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
             umma_ts_c<Q_HI, IDESC_S, true>(sd, ka + 8 * k, q_lo + 2 * k);
           tc_commit(bars.s_done(g));
           if (t == w.t1 - 1) tc_commit(bars.q_empty(qb));
+          if (++g == G) { g = 0; gph ^= 1u; }
         }
         ++qi;
       }
@@ -688,12 +701,12 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       constexpr uint32_t V_HI = smem_desc_hi(1024, 2), P_HI = smem_desc_hi(128, 0);
       const uint32_t v_lo0 = smem_desc_lo(smem0 + SP::VOP_OFF, 16);
       const uint32_t p_lo0 = smem_desc_lo(smem0 + SP::P_OFF, 128);
-      int it = 0;
+      int g = 0;
+      uint32_t gph = 0;
       for (int wi = items.begin; wi < items.end; wi += items.step) {
         const WorkItem w = decode_item(P, wi);
-        for (int t = w.t0; t < w.t1; ++t, ++it) {
-          const int g = it & (G - 1);
-          mbar_wait(bars.pv_ready(g), (it / G) & 1, abort_flag, status, 4, wprof);
+        for (int t = w.t0; t < w.t1; ++t) {
+          mbar_wait(bars.pv_ready(g), gph, abort_flag, status, 4, wprof);
           tc_fence_after();
           const uint32_t v_lo = v_lo0 + g * (SP::VOP_STAGE >> 4);
           const uint32_t p_lo = p_lo0 + g * (SP::P_BYTES >> 4);
@@ -704,6 +717,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
             umma_ss_c<V_HI, P_HI, IDESC_PV, true>(od, v_lo + k * (32 * D >> 4),
                                                   p_lo + k * (32 * 16 >> 4));
           tc_commit(bars.pv_done(g));
+          if (++g == G) { g = 0; gph ^= 1u; }
         }
       }
     }

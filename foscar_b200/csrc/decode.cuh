@@ -7,8 +7,11 @@ namespace fq {
 
 constexpr int TILE = 128;            // tokens per sequence tile: two pages
 constexpr int WORK_WORDS = 8;        // int32 words per explicit work-list row
-constexpr int WORKER_GROUPS = 4;     // 128-thread groups, tile i -> group i % 4, see decode.cu
-constexpr int DECODE_THREADS = 640;  // 16 worker warps + 2 producers + 2 MMA issuers
+#ifndef FQ_WORKER_GROUPS
+#define FQ_WORKER_GROUPS 4
+#endif
+constexpr int WORKER_GROUPS = FQ_WORKER_GROUPS;  // 128-thread groups, tile i -> group i % G
+constexpr int DECODE_THREADS = 32 * (4 * WORKER_GROUPS + 4);  // + 2 producers + 2 MMA issuers
 constexpr int SMEM_LIMIT = 232448;   // 227 KiB opt-in limit per CTA on sm_100
 
 struct DecodeParams {
@@ -43,7 +46,8 @@ struct SmemPlan {
   static constexpr int XCHG_BYTES = TILE * 8 * 4 + 128;   // one group's accumulators + (m,l,c)
   static constexpr int XCHG_OFF = P_OFF + WORKER_GROUPS * P_BYTES;
   static constexpr int RED_OFF = XCHG_OFF + (WORKER_GROUPS - 1) * XCHG_BYTES;  // reductions
-  static constexpr int RED_BYTES = 2048;
+  // column maxima 256 B and sums 256 B per group, then 64 B of per-head constants per warp
+  static constexpr int RED_BYTES = (512 * WORKER_GROUPS + 64 * 4 * WORKER_GROUPS + 1023) / 1024 * 1024;
   static constexpr int BAR_OFF = RED_OFF + RED_BYTES;
   static constexpr int BAR_BYTES = 2048;   // barriers, then flags and diagnostics
   static constexpr int RING_OFF = (BAR_OFF + BAR_BYTES + 1023) / 1024 * 1024;
