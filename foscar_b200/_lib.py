@@ -37,7 +37,8 @@ class DecodeArgs(C.Structure):
                 ("q_descale", C.c_void_p), ("q_descale_stride_b", C.c_int64),
                 ("q_descale_stride_h", C.c_int64), ("out", C.c_void_p), ("lse", C.c_void_p),
                 ("o_partial", C.c_void_p), ("l_partial", C.c_void_p), ("m_partial", C.c_void_p),
-                ("status", C.c_void_p)]
+                ("status", C.c_void_p), ("unit_counters", C.c_void_p),
+                ("split_counts", C.c_void_p)]
 
 
 _P = C.c_void_p

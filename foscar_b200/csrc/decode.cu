@@ -49,7 +49,8 @@
 #endif
 
 // Diagnostic builds only: a bit mask of roles whose arithmetic is skipped while every barrier
-// arrival stays (1 consumers, 2 K expanders, 4 V expanders, 8 producers' copies). The output is
+// arrival stays (1 softmax, 2 K unpack, 4 V unpack, 8 producers' copies; 16 / 32: one S / PV MMA
+// per tile instead of four). The output is
 // then meaningless; the launch time and instruction count show what each role costs.
 #ifndef FQ_STUB_ROLES
 #define FQ_STUB_ROLES 0
@@ -211,6 +212,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   // this warp's copy of the item's per-head constants: sm_scale*log2e*q_descale, and that times
   // the sum of the head's query values
   float* head_k = reinterpret_cast<float*>(smem + SP::RED_OFF + 512 * G) + warp * 16;
+  // set per work item by group 0: pieces of the unit this CTA must merge (0: none)
+  volatile int* merge_flag = reinterpret_cast<volatile int*>(smem + SP::RED_OFF + 768 * G);
   constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 
   // pool-wide P-scale exponent from the count table: lp = 135 - max(top nonzero bin, 27)
@@ -459,6 +462,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       }
     }
     named_barrier(1 + G, 128 * G);
+    int k_merge = 0;
     if (wg == 0 && w.slot != -2) {
       const int ch = channel_of_expanded_pos<BITS>(t);
 #pragma unroll
@@ -499,9 +503,81 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           if (t == 0) { P.a.l_partial[prow] = L; P.a.m_partial[prow] = M; }
         }
       }
+      // ---- in-kernel merge, step 1: count this piece in; the piece that completes its unit
+      // makes the whole CTA merge the unit's partials after the barrier below
+      if (w.slot >= 0 && P.a.unit_counters != nullptr) {
+        __threadfence();
+        named_barrier(1 + wg, 128);
+        if (t == 0) {
+          const int unit = (w.b * P.p.num_kv_heads + w.kvh) * P.head_tiles + w.ht;
+          const int k = P.a.split_counts != nullptr ? __ldg(P.a.split_counts + unit)
+                                                    : P.a.kv_splits;
+          const int seen = atomicAdd(P.a.unit_counters + unit, 1);
+          if (seen == k - 1) {
+            P.a.unit_counters[unit] = 0;   // nobody touches it again before the next launch
+            k_merge = k;
+          }
+        }
+      }
     }
+    if (wg == 0 && t == 0) *merge_flag = k_merge;
     // the exchange buffers are reused by the next item
     named_barrier(1 + G, 128 * G);
+    // ---- in-kernel merge, step 2: every group takes its share of the unit's heads (the flag is
+    // next written after the next item's first all-group barrier, which this read precedes)
+    if (const int k = *merge_flag; k > 0) {
+      __threadfence();
+      const int ch = channel_of_expanded_pos<BITS>(t);
+      const long long rows = static_cast<long long>(P.a.batch) * P.a.num_qo_heads;
+      for (int h = wg; h < GP; h += G) {
+        const int hl = w.ht * 8 + h;
+        if (hl >= P.heads_per_kv) continue;
+        const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
+        const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
+        // same arithmetic and slot order as merge_kernel; up to eight pieces are fetched in one
+        // round trip (this runs at the very end of the CTA that completes the unit)
+        float M = -INFINITY, den = 0.f, acc = 0.f;
+        if (k <= 8) {
+          float ms[8], ls[8], os[8];
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            const bool on = s < k;
+            ms[s] = on ? __ldcg(P.a.m_partial + s * rows + row) : -INFINITY;
+            ls[s] = on ? __ldcg(P.a.l_partial + s * rows + row) : 0.f;
+            os[s] = on ? __ldcg(P.a.o_partial + (s * rows + row) * D + ch) : 0.f;
+          }
+#pragma unroll
+          for (int s = 0; s < 8; ++s) M = fmaxf(M, ms[s]);
+          if (M > -INFINITY) {
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+              if (s < k) {
+                const float wgt = exp2f(ms[s] - M);
+                den += wgt * ls[s];
+                acc += wgt * os[s];
+              }
+            }
+          }
+        } else {
+          for (int s = 0; s < k; ++s) M = fmaxf(M, __ldcg(P.a.m_partial + s * rows + row));
+          if (M > -INFINITY) {
+            for (int s = 0; s < k; ++s) {
+              const float wgt = exp2f(__ldcg(P.a.m_partial + s * rows + row) - M);
+              den += wgt * __ldcg(P.a.l_partial + s * rows + row);
+              acc += wgt * __ldcg(P.a.o_partial + (s * rows + row) * D + ch);
+            }
+          }
+        }
+        const bool live = den > 0.f;
+        const float val = live ? acc / den * P.a.o_scale : 0.f;
+        const long long idx = row * D + ch;
+        if (P.a.out_dtype == 0) static_cast<__nv_bfloat16*>(P.a.out)[idx] = __float2bfloat16_rn(val);
+        else if (P.a.out_dtype == 1) static_cast<__half*>(P.a.out)[idx] = __float2half_rn(val);
+        else static_cast<float*>(P.a.out)[idx] = val;
+        if (t == 0 && P.a.lse != nullptr)
+          P.a.lse[row] = live ? (M + log2f(den)) * LN2 : -INFINITY;
+      }
+    }
   }
 }
 
@@ -684,7 +760,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           const uint32_t ka = tmem + TP::KOP + g * TP::KOP_COLS;
           umma_ts_c<Q_HI, IDESC_S, false>(sd, ka, q_lo);
 #pragma unroll
-          for (int k = 1; k < D / 32; ++k)
+          for (int k = 1; k < ((FQ_STUB_ROLES & 16) ? 1 : D / 32); ++k)
             umma_ts_c<Q_HI, IDESC_S, true>(sd, ka + 8 * k, q_lo + 2 * k);
           tc_commit(bars.s_done(g));
           if (t == w.t1 - 1) tc_commit(bars.q_empty(qb));
@@ -713,7 +789,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           const uint32_t od = tmem + TP::O + g * 16;
           umma_ss_c<V_HI, P_HI, IDESC_PV, false>(od, v_lo, p_lo);
 #pragma unroll
-          for (int k = 1; k < TILE / 32; ++k)
+          for (int k = 1; k < ((FQ_STUB_ROLES & 32) ? 1 : TILE / 32); ++k)
             umma_ss_c<V_HI, P_HI, IDESC_PV, true>(od, v_lo + k * (32 * D >> 4),
                                                   p_lo + k * (32 * 16 >> 4));
           tc_commit(bars.pv_done(g));
@@ -949,6 +1025,8 @@ extern "C" int fq_decode_split_static(const fq_pools* pools, const fq_decode_arg
     base_of_device[dev] = static_cast<float*>(p);
   }
   fq_decode_args a = *args;
+  a.unit_counters = nullptr;  // partials are merged by fq_merge below
+  a.split_counts = nullptr;
   a.max_splits = a.kv_splits;
   a.o_partial = base_of_device[dev];
   a.l_partial = a.o_partial + rows * pools->head_dim;

@@ -145,6 +145,10 @@ class PagedDecodeWrapper:
             cls = _GraphDecodeWrapper
         return super().__new__(cls)
 
+    # Split units are merged inside the decode kernel by the piece that arrives last. False
+    # restores the separate merge launch (fq_merge) after every decode.
+    fused_merge = True
+
     def __init__(self, float_workspace_buffer: torch.Tensor, use_cuda_graph: bool = False):
         if not isinstance(float_workspace_buffer, torch.Tensor):
             raise TypeError("float_workspace_buffer must be a torch.Tensor")
@@ -172,6 +176,7 @@ class PagedDecodeWrapper:
         self._max_splits = 1
         self._worklist = None          # device int32 list, explicit plans only
         self._split_counts = None      # device int32 [units], explicit plans only
+        self._unit_counters = None     # device int32 [units]: in-kernel merge of split units
         self._work_rows = 0
         self._plan_ctas = 0
         self._merge = False
@@ -304,6 +309,20 @@ class PagedDecodeWrapper:
             self._o_partial, self._l_partial, self._m_partial = _carve_partials(
                 self._float_workspace_buffer, self._kv_splits, self._batch_size,
                 self._num_qo_heads, self._head_dim)
+            self._new_unit_counters()
+
+    def _new_unit_counters(self):
+        """Zeroed per-unit arrival counters: the decode kernel merges a split unit itself when
+        its last piece arrives (and sets the counter back), so no merge launch follows."""
+        if not self.fused_merge:
+            self._unit_counters = None
+            return
+        units = self._batch_size * self._num_kv_heads * _head_tiles(self._num_qo_heads,
+                                                                     self._num_kv_heads)
+        if self._unit_counters is None or self._unit_counters.numel() != units:
+            self._unit_counters = torch.zeros(units, dtype=torch.int32, device=self.device)
+        else:
+            self._unit_counters.zero_()
 
     def _plan_balanced(self, host_lens, non_blocking):
         lay, lib = self._layout, _lib.load()
@@ -333,6 +352,7 @@ class PagedDecodeWrapper:
             self._o_partial, self._l_partial, self._m_partial = _carve_partials(
                 self._float_workspace_buffer, most, self._batch_size, self._num_qo_heads,
                 self._head_dim)
+            self._new_unit_counters()
         else:
             # the kernel still wants valid partial pointers for an explicit list
             self._o_partial = self._l_partial = self._m_partial = None
@@ -448,12 +468,17 @@ class PagedDecodeWrapper:
             ws = self._float_workspace_buffer.data_ptr()
             args.o_partial = args.l_partial = args.m_partial = ws
         args.status = self._status_ptr()
+        fused = self._merge and self._unit_counters is not None
+        if fused:
+            args.unit_counters = self._unit_counters.data_ptr()
+            if self._split_counts is not None:
+                args.split_counts = self._split_counts.data_ptr()
         _lib.check(lib.fq_decode(ctypes.byref(cache._c_pools), ctypes.byref(args), stream),
                    "decode")
         self.launches += 1
         if self._decode_done_event is not None:
             self._decode_done_event.record()       # lets a benchmark time the decode kernel alone
-        if self._merge:
+        if self._merge and not fused:
             self.launches += 1
             counts = None if self._split_counts is None else self._split_counts.data_ptr()
             _lib.check(lib.fq_merge(
@@ -580,6 +605,7 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
         self._kv_splits = cap
         self._reduction = "kernel"
         self._merge = True
+        self._new_unit_counters()
         self._seqlens = seq_lens
         self._page_table = page_table.view(-1)
         self._table_offsets = (torch.arange(b, dtype=torch.int32, device=self.device)

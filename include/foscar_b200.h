@@ -125,6 +125,14 @@ typedef struct fq_decode_args {
   float* l_partial;
   float* m_partial;
   int32_t* status;
+  /* In-kernel merge of split units (optional). unit_counters: int32 [B * HKV * head_tiles],
+   * zero before the first launch; each piece of a unit bumps its counter after writing its
+   * partials, and the CTA that brings it to the unit's piece count merges the unit's partials
+   * in slot order (the arithmetic of fq_merge), writes out/lse and sets the counter back to 0,
+   * so no merge launch follows and the counters need no clearing between launches.
+   * split_counts: int32 per unit, pieces of each unit in an explicit list (NULL: kv_splits). */
+  int32_t* unit_counters;
+  const int32_t* split_counts;
 } fq_decode_args;
 
 int fq_decode(const fq_pools* pools, const fq_decode_args* args, void* stream);

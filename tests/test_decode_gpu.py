@@ -121,6 +121,41 @@ def test_run_is_deterministic():
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
+@pytest.mark.parametrize("kv_splits", [5, None])
+def test_in_kernel_merge_equals_merge_launch(kv_splits):
+    """Split units merged by their last piece inside the decode launch give the bytes the
+    separate merge launch gives (same arithmetic, same slot order), launch after launch: the
+    arrival counters reset themselves."""
+    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
+    seq = [7000, 150, 12000, 64]
+    indptr, indices, slots, npages = paged_batch(seq, seed=4)
+    k, v = make_kv(len(slots), 8, 128, seed=4)
+    layout = QuantKVLayout.create(bits=4, head_dim=128, num_kv_heads=8, device="cuda")
+    cache = layout.allocate(npages)
+    cache.append(k, v, torch.from_numpy(slots).cuda())
+    q = make_q(len(seq), 32, 128)
+    lens = torch.tensor(seq, dtype=torch.int32)
+    results = []
+    for fused in (False, True, True):
+        w = PagedDecodeWrapper(torch.empty(64 << 20, dtype=torch.uint8, device="cuda"))
+        w.fused_merge = fused
+        w.plan(torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda(),
+               lens.cuda() if kv_splits else lens, 32, layout, kv_splits=kv_splits)
+        assert w.kv_splits > 1
+        for _ in range(2):
+            out = torch.full((len(seq), 32, 128), float("nan"), dtype=torch.bfloat16,
+                             device="cuda")
+            lse = torch.full((len(seq), 32), float("nan"), device="cuda")
+            before = w.launches
+            w.run(q, cache, out=out, lse=lse)
+            assert w.launches - before == (1 if fused else 2)
+            results.append((out, lse))
+        torch.cuda.synchronize()
+        assert w.last_status() == 0
+    for out, lse in results[1:]:
+        assert torch.equal(out, results[0][0]) and torch.equal(lse, results[0][1])
+
+
 def test_bad_page_id_sets_status_without_fault():
     from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
     layout = QuantKVLayout.create(bits=2, head_dim=128, num_kv_heads=2, device="cuda")

@@ -276,7 +276,19 @@ def test_plan_and_run_wiring(recorder):
     assert w.kv_splits == 4 and w.reduction == "kernel"
     recorder.calls.clear()
     w.run(q, cache, out=out)
+    # split units are merged inside the decode launch by default ...
+    assert [c[0] for c in recorder.calls] == ["fq_decode"]
+    args = ctypes.cast(recorder.calls[0][1][1], ctypes.POINTER(_lib.DecodeArgs)).contents
+    assert args.unit_counters and not args.split_counts and args.kv_splits == 4
+    # ... and by a second launch when that is switched off
+    w.fused_merge = False
+    w.plan(indptr, indices, torch.tensor([256, 200], dtype=torch.int32), 32, lay, kv_splits=4)
+    recorder.calls.clear()
+    w.run(q, cache, out=out)
     assert [c[0] for c in recorder.calls] == ["fq_decode", "fq_merge"]
+    args = ctypes.cast(recorder.calls[0][1][1], ctypes.POINTER(_lib.DecodeArgs)).contents
+    assert not args.unit_counters
+    w.fused_merge = True
     w.plan(indptr, indices, torch.tensor([256, 200], dtype=torch.int32), 32, lay, kv_splits=1)
     assert w.kv_splits == 1 and w.reduction == "none"
 
