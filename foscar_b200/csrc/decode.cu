@@ -205,7 +205,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   const uint32_t k_dst = tmem + lane_base + TP::KOP + wg * TP::KOP_COLS;
   const uint32_t s_src = tmem + lane_base + TP::S + wg * 16;
   const uint32_t o_src = tmem + lane_base + TP::O + wg * 16;
-  const uint32_t v_row = smem0 + SP::VOP_OFF + wg * SP::VOP_STAGE + t * D;
+  const uint32_t v_row = smem0 + SP::VOP_OFF + wg * SP::VOP_STAGE + t * SP::ROW;
   const uint32_t p_row = smem0 + SP::P_OFF + wg * SP::P_BYTES + t * 16;
   float* red_max = reinterpret_cast<float*>(smem + SP::RED_OFF);              // [wg][buf][warp][8]
   float* red_sum = reinterpret_cast<float*>(smem + SP::RED_OFF + 256 * G);    // [wg][warp][16]
@@ -254,10 +254,12 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       if (hl < P.heads_per_kv && nt > 0) {
         const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
         const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
-        const uint32_t qw = __ldg(reinterpret_cast<const uint32_t*>(
-            static_cast<const uint8_t*>(P.a.q) + row * D + 4 * lane));
-        const float2 a = e4m3x2_to_f32x2(qw & 0xFFFF), b2 = e4m3x2_to_f32x2(qw >> 16);
-        sum = (a.x + a.y) + (b2.x + b2.y);
+        if (4 * lane < D) {
+          const uint32_t qw = __ldg(reinterpret_cast<const uint32_t*>(
+              static_cast<const uint8_t*>(P.a.q) + row * D + 4 * lane));
+          const float2 a = e4m3x2_to_f32x2(qw & 0xFFFF), b2 = e4m3x2_to_f32x2(qw >> 16);
+          sum = (a.x + a.y) + (b2.x + b2.y);
+        }
         scale = P.a.sm_scale * LOG2E;
         if (P.a.q_descale != nullptr)
           scale *= __ldg(P.a.q_descale + w.b * P.a.q_descale_stride_b +
@@ -465,6 +467,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     int k_merge = 0;
     if (wg == 0 && w.slot != -2) {
       const int ch = channel_of_expanded_pos<BITS>(t);
+      const bool on = t < D;   // head_dim 64: the upper half of the O rows is padding
 #pragma unroll
       for (int h = 0; h < GP; ++h) {
         const int hl = w.ht * 8 + h;
@@ -491,7 +494,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         if (w.slot < 0) {
           const float val = L > 0.f ? O / L * P.a.o_scale : 0.f;
           const long long idx = row * D + ch;
-          if (P.a.out_dtype == 0) static_cast<__nv_bfloat16*>(P.a.out)[idx] = __float2bfloat16_rn(val);
+          if (!on) {
+          } else if (P.a.out_dtype == 0) static_cast<__nv_bfloat16*>(P.a.out)[idx] = __float2bfloat16_rn(val);
           else if (P.a.out_dtype == 1) static_cast<__half*>(P.a.out)[idx] = __float2half_rn(val);
           else static_cast<float*>(P.a.out)[idx] = val;
           if (t == 0 && P.a.lse != nullptr)
@@ -499,7 +503,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         } else {
           const long long prow =
               static_cast<long long>(w.slot) * P.a.batch * P.a.num_qo_heads + row;
-          P.a.o_partial[prow * D + ch] = O;
+          if (on) P.a.o_partial[prow * D + ch] = O;
           if (t == 0) { P.a.l_partial[prow] = L; P.a.m_partial[prow] = M; }
         }
       }
@@ -525,7 +529,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     named_barrier(1 + G, 128 * G);
     // ---- in-kernel merge, step 2: every group takes its share of the unit's heads (the flag is
     // next written after the next item's first all-group barrier, which this read precedes)
-    if (const int k = *merge_flag; k > 0) {
+    if (const int k = *merge_flag; k > 0 && t < D) {
       __threadfence();
       const int ch = channel_of_expanded_pos<BITS>(t);
       const long long rows = static_cast<long long>(P.a.batch) * P.a.num_qo_heads;
@@ -585,7 +589,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 
 template <int BITS, int D, int GP>
 __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeParams P) {
-  static_assert(D == 128, "this build tiles head_dim 128");
+  static_assert(D == 64 || D == 128, "this build tiles head_dim 64 and 128");
   using SP = SmemPlan<BITS, D>;
   using TP = TmemPlan<D>;
   constexpr int G = WORKER_GROUPS;
@@ -658,7 +662,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           const int r = chunk >> 3, cc = chunk & 7;
           uint4 v = make_uint4(0, 0, 0, 0);
           const int hl = w.ht * 8 + r;  // head inside the KV head's group
-          if (r < 8 && hl < P.heads_per_kv) {
+          if (r < 8 && hl < P.heads_per_kv && 16 * cc < D) {
             const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
             const uint4 in = __ldg(reinterpret_cast<const uint4*>(
                 static_cast<const uint8_t*>(P.a.q) +
@@ -790,7 +794,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           umma_ss_c<V_HI, P_HI, IDESC_PV, false>(od, v_lo, p_lo);
 #pragma unroll
           for (int k = 1; k < ((FQ_STUB_ROLES & 32) ? 1 : TILE / 32); ++k)
-            umma_ss_c<V_HI, P_HI, IDESC_PV, true>(od, v_lo + k * (32 * D >> 4),
+            umma_ss_c<V_HI, P_HI, IDESC_PV, true>(od, v_lo + k * (32 * SP::ROW >> 4),
                                                   p_lo + k * (32 * 16 >> 4));
           tc_commit(bars.pv_done(g));
           if (++g == G) { g = 0; gph ^= 1u; }
@@ -963,7 +967,7 @@ extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void
   if (!pools || !args) return FQ_ERR_BAD_ARG;
   if (!pools->k_codes || !pools->v_codes || !pools->scales) return FQ_ERR_BAD_ARG;
   if (pools->k_groups != 1 || pools->scale_bf16) return FQ_ERR_UNSUPPORTED;
-  if (pools->head_dim != 128) return FQ_ERR_UNSUPPORTED;
+  if (pools->head_dim != 64 && pools->head_dim != 128) return FQ_ERR_UNSUPPORTED;
   if (pools->bits != 2 && pools->bits != 4) return FQ_ERR_UNSUPPORTED;
   const fq_decode_args& a = *args;
   if (a.batch <= 0 || a.num_qo_heads <= 0 || a.num_qo_heads % pools->num_kv_heads) return FQ_ERR_BAD_ARG;
@@ -989,6 +993,10 @@ extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void
   }
   const int gp = std::min(P.heads_per_kv, 8) <= 4 ? 4 : 8;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pools->head_dim == 64) {
+    if (pools->bits == 2) return gp == 4 ? launch_decode<2, 64, 4>(P, s) : launch_decode<2, 64, 8>(P, s);
+    return gp == 4 ? launch_decode<4, 64, 4>(P, s) : launch_decode<4, 64, 8>(P, s);
+  }
   if (pools->bits == 2) return gp == 4 ? launch_decode<2, 128, 4>(P, s) : launch_decode<2, 128, 8>(P, s);
   return gp == 4 ? launch_decode<4, 128, 4>(P, s) : launch_decode<4, 128, 8>(P, s);
 }

@@ -37,8 +37,11 @@ struct SmemPlan {
   static constexpr int V_OFF = 2 * CODE_PAGE;
   static constexpr int S_OFF = 4 * CODE_PAGE;
   static constexpr int STAGE = 4 * CODE_PAGE + 2 * SCALE_PAGE;
-  static constexpr int VOP_STAGE = TILE * D;           // expanded V operand, one tile
-  static constexpr int Q_BYTES = 16 * D;               // 16 MMA rows of D bytes
+  // Operand rows keep a 128-byte pitch (the swizzle atom) whatever D <= 128: head_dim 64 uses
+  // the first half of each row.
+  static constexpr int ROW = 128;
+  static constexpr int VOP_STAGE = TILE * ROW;         // expanded V operand, one tile
+  static constexpr int Q_BYTES = 16 * ROW;             // 16 MMA rows
   static constexpr int P_BYTES = TILE * 16;            // 16 bytes (8 hi + 8 lo) per token
   static constexpr int VOP_OFF = 0;
   static constexpr int Q_OFF = VOP_OFF + WORKER_GROUPS * VOP_STAGE;

@@ -73,6 +73,18 @@ def test_ragged_batch(bits, hq, hkv):
 
 
 @pytest.mark.parametrize("bits", [2, 4])
+@pytest.mark.parametrize("hq,hkv", [(64, 8), (8, 2), (4, 4)])
+def test_head_dim_64(bits, hq, hkv):
+    """head_dim 64 (operand rows half used): ragged batch, planned splits."""
+    _run_case(bits, 64, hq, hkv, [1, 64, 130, 2000, 9000], seed=3 + bits)
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+def test_head_dim_64_uniform_splits(bits):
+    _run_case(bits, 64, 64, 8, [5000, 257], kv_splits=3, host_lens=False)
+
+
+@pytest.mark.parametrize("bits", [2, 4])
 @pytest.mark.parametrize("kv_splits", [1, 4, 7, None])
 def test_uniform_and_planned_splits(bits, kv_splits):
     w, _, _ = _run_case(bits, 128, 32, 8, [4096, 700], kv_splits=kv_splits, host_lens=False,
