@@ -41,6 +41,10 @@ WORKLOADS = {
                    outliers=True, identity=False, q_scale=8.0),
     "c3-b64": dict(bits=2, batch=64, hq=32, hkv=8, d=128, seq=(100352, 100352), dist="uniform",
                    outliers=True, identity=False, q_scale=8.0),
+    "c5-int2": dict(bits=2, batch=256, hq=64, hkv=8, d=64, seq=(64, 131072), dist="loguniform",
+                    outliers=False, identity=False, q_scale=8.0),
+    "c5-int4": dict(bits=4, batch=256, hq=64, hkv=8, d=64, seq=(64, 131072), dist="loguniform",
+                    outliers=False, identity=False, q_scale=8.0),
     "small": dict(bits=2, batch=16, hq=32, hkv=8, d=128, seq=(8192, 16384), dist="uniform",
                   outliers=True, identity=False, q_scale=8.0),
 }

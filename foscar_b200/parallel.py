@@ -96,9 +96,11 @@ def merge_states(o_shards: torch.Tensor, lse_shards: torch.Tensor,
 def sequence_split_decode(wrapper, q, cache, group=None, out: Optional[torch.Tensor] = None
                           ) -> torch.Tensor:
     """One decode step of a sequence-split context: this rank's wrapper (planned over its own
-    token range) produces (o, lse); the pairs are gathered and merged on every rank."""
+    token range) produces (o, lse); the pairs are gathered and merged on every rank. Plan the
+    wrapper with `o_data_type=torch.float32` so that the shards' outputs are not rounded to
+    bf16 before the merge."""
     b, hq, d = wrapper._batch_size, wrapper._num_qo_heads, wrapper._head_dim
-    local = torch.empty(b, hq, d, dtype=torch.float32, device=q.device)
+    local = torch.empty(b, hq, d, dtype=wrapper._o_data_type, device=q.device)
     lse = torch.empty(b, hq, dtype=torch.float32, device=q.device)
     wrapper.run(q, cache, out=local, lse=lse)
     o_all, l_all = gather_states(local, lse, group)
