@@ -366,7 +366,7 @@ def main():
             "gpu_launches": launches, "clocks": clocks.summary(), "device_status": status,
             "plan": {"kv_splits": w.kv_splits, "reduction": w.reduction},
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:   # the CPU leg is an N=1 figure
             threads = os.cpu_count() or 1
             torch.set_num_threads(threads)
             step, tokens, reqs = cpu_reference_step(cfg, args.seed, args.cpu_tokens)

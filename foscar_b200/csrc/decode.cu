@@ -212,9 +212,12 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   // this warp's copy of the item's per-head constants: sm_scale*log2e*q_descale, and that times
   // the sum of the head's query values
   float* head_k = reinterpret_cast<float*>(smem + SP::RED_OFF + 512 * G) + warp * 16;
-  // set per work item by group 0: pieces of the unit this CTA must merge (0: none)
-  volatile int* merge_flag = reinterpret_cast<volatile int*>(smem + SP::RED_OFF + 768 * G);
-  constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+  // written per work item by thread 0 of group 0: {pieces, request, KV head, head tile} of the
+  // unit this CTA must merge (pieces 0: none)
+  volatile int* merge_info = reinterpret_cast<volatile int*>(smem + SP::RED_OFF + 768 * G);
+  const volatile float* head_const =
+      reinterpret_cast<const volatile float*>(smem + SP::RED_OFF + 768 * G + 32);  // [2][16]
+  constexpr float LN2 = 0.6931471805599453f;
 
   // pool-wide P-scale exponent from the count table: lp = 135 - max(top nonzero bin, 27)
   int lp;
@@ -236,6 +239,87 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   const float p2lp = exp2f(static_cast<float>(lp));
   const float o_mul = exp2f(static_cast<float>(9 - lp));
 
+  // Merge of a split unit's partials: the arithmetic and slot order of merge_kernel. Heads h0,
+  // h0 + hstep, ... of the unit's head tile; thread t takes the channel at expanded position t.
+  auto merge_unit = [&](int k, int b, int kvh, int ht, int h0, int hstep) {
+    if (t >= D) return;
+    __threadfence();
+    const int ch = channel_of_expanded_pos<BITS>(t);
+    const long long rows = static_cast<long long>(P.a.batch) * P.a.num_qo_heads;
+      for (int h = h0; h < GP; h += hstep) {
+        const int hl = ht * 8 + h;
+        if (hl >= P.heads_per_kv) continue;
+        const long long head = static_cast<long long>(kvh) * P.heads_per_kv + hl;
+        const long long row = static_cast<long long>(b) * P.a.num_qo_heads + head;
+        // same arithmetic and slot order as merge_kernel; up to eight pieces are fetched in one
+        // round trip (this runs at the very end of the CTA that completes the unit)
+        float M = -INFINITY, den = 0.f, acc = 0.f;
+        if (k <= 8) {
+          float ms[8], ls[8], os[8];
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            const bool on = s < k;
+            ms[s] = on ? __ldcg(P.a.m_partial + s * rows + row) : -INFINITY;
+            ls[s] = on ? __ldcg(P.a.l_partial + s * rows + row) : 0.f;
+            os[s] = on ? __ldcg(P.a.o_partial + (s * rows + row) * D + ch) : 0.f;
+          }
+#pragma unroll
+          for (int s = 0; s < 8; ++s) M = fmaxf(M, ms[s]);
+          if (M > -INFINITY) {
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+              if (s < k) {
+                const float wgt = exp2f(ms[s] - M);
+                den += wgt * ls[s];
+                acc += wgt * os[s];
+              }
+            }
+          }
+        } else {
+          // more pieces: two passes, each fetching eight pieces per round trip
+          for (int s0 = 0; s0 < k; s0 += 8) {
+            float ms[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+              ms[s] = s0 + s < k ? __ldcg(P.a.m_partial + (s0 + s) * rows + row) : -INFINITY;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) M = fmaxf(M, ms[s]);
+          }
+          if (M > -INFINITY) {
+            for (int s0 = 0; s0 < k; s0 += 8) {
+              float ms[8], ls[8], os[8];
+#pragma unroll
+              for (int s = 0; s < 8; ++s) {
+                const bool on = s0 + s < k;
+                ms[s] = on ? __ldcg(P.a.m_partial + (s0 + s) * rows + row) : -INFINITY;
+                ls[s] = on ? __ldcg(P.a.l_partial + (s0 + s) * rows + row) : 0.f;
+                os[s] = on ? __ldcg(P.a.o_partial + ((s0 + s) * rows + row) * D + ch) : 0.f;
+              }
+#pragma unroll
+              for (int s = 0; s < 8; ++s) {
+                if (s0 + s < k) {
+                  const float wgt = exp2f(ms[s] - M);
+                  den += wgt * ls[s];
+                  acc += wgt * os[s];
+                }
+              }
+            }
+          }
+        }
+        const bool live = den > 0.f;
+        const float val = live ? acc / den * P.a.o_scale : 0.f;
+        const long long idx = row * D + ch;
+        if (P.a.out_dtype == 0) static_cast<__nv_bfloat16*>(P.a.out)[idx] = __float2bfloat16_rn(val);
+        else if (P.a.out_dtype == 1) static_cast<__half*>(P.a.out)[idx] = __float2half_rn(val);
+        else static_cast<float*>(P.a.out)[idx] = val;
+        if (t == 0 && P.a.lse != nullptr)
+          P.a.lse[row] = live ? (M + log2f(den)) * LN2 : -INFINITY;
+      }
+  };
+  // the split piece this CTA has written but not yet counted in (thread 0 of group 0 only)
+  int pend_k = 0, pend_unit = 0, pend_b = 0, pend_kvh = 0, pend_ht = 0;
+
+  int qi = 0;       // non-empty items so far: which query stage holds the item's rows
   int it0 = 0;      // running index of the current item's first tile (every role counts alike)
   int mine = wg;    // running index of this group's next tile
   int n = 0;        // tiles this group has taken: the phase of its barriers
@@ -245,31 +329,18 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     const WorkItem w = decode_item(P, wi);
     const int nt = max(w.t1 - w.t0, 0);
     float m[GP], l[GP], c[GP], oacc[GP];
+#pragma unroll
+    for (int h = 0; h < GP; ++h) { m[h] = -INFINITY; l[h] = 0.f; c[h] = 0.f; oacc[h] = 0.f; }
+    // The item's per-head constants (score scale, and score scale times the sum of the head's
+    // query values) were computed by the first producer when it staged the query rows, well
+    // ahead of the tiles; the warp keeps its own copy, read back from shared memory each tile
+    // instead of living in 16 registers of every thread.
     __syncwarp();   // the warp's reads of the previous item's values are over
-#pragma unroll
-    for (int h = 0; h < GP; ++h) {
-      m[h] = -INFINITY; l[h] = 0.f; c[h] = 0.f; oacc[h] = 0.f;
-      const int hl = w.ht * 8 + h;
-      float sum = 0.f, scale = 0.f;
-      if (hl < P.heads_per_kv && nt > 0) {
-        const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
-        const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
-        if (4 * lane < D) {
-          const uint32_t qw = __ldg(reinterpret_cast<const uint32_t*>(
-              static_cast<const uint8_t*>(P.a.q) + row * D + 4 * lane));
-          const float2 a = e4m3x2_to_f32x2(qw & 0xFFFF), b2 = e4m3x2_to_f32x2(qw >> 16);
-          sum = (a.x + a.y) + (b2.x + b2.y);
-        }
-        scale = P.a.sm_scale * LOG2E;
-        if (P.a.q_descale != nullptr)
-          scale *= __ldg(P.a.q_descale + w.b * P.a.q_descale_stride_b +
-                         head * P.a.q_descale_stride_h);
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
-      // per-head constants of the item: read back from shared memory each tile instead of
-      // living in 16 registers of every thread
-      if (lane == 0) { head_k[h] = scale; head_k[8 + h] = scale * sum; }
+    if (nt > 0) {
+      const int qb = qi & 1;
+      mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status, 14, wprof);
+      if (lane < 16) head_k[lane] = head_const[qb * 16 + lane];
+      ++qi;
     }
     __syncwarp();
     bool pending = false;
@@ -434,7 +505,13 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     it0 += nt;
     if (pending) accumulate();
 
-    // ---- item epilogue: group sums, then the groups' states merged by group 0
+    // ---- item epilogue. First, the count-in of the previous split piece (see step 1 below)
+    int seen = -1;
+    if (wg == 0 && t == 0 && pend_k > 0) {
+      __threadfence();
+      seen = atomicAdd(P.a.unit_counters + pend_unit, 1);
+    }
+    // group sums, then the groups' states merged by group 0
     float* rs = red_sum + (wg * 4 + wq) * 16;
 #pragma unroll
     for (int h = 0; h < GP; ++h) {
@@ -464,7 +541,6 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       }
     }
     named_barrier(1 + G, 128 * G);
-    int k_merge = 0;
     if (wg == 0 && w.slot != -2) {
       const int ch = channel_of_expanded_pos<BITS>(t);
       const bool on = t < D;   // head_dim 64: the upper half of the O rows is padding
@@ -507,81 +583,52 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           if (t == 0) { P.a.l_partial[prow] = L; P.a.m_partial[prow] = M; }
         }
       }
-      // ---- in-kernel merge, step 1: count this piece in; the piece that completes its unit
-      // makes the whole CTA merge the unit's partials after the barrier below
+    }
+    // ---- in-kernel merge, step 1. A split piece is counted in (release fence + one atomic on
+    // its unit's counter) not here but in the NEXT item's epilogue, or after the last item: by
+    // then its partials have long drained, and the atomic's round trip (issued above, before the
+    // group merge) has overlapped with this epilogue. Whoever finds the count complete makes
+    // the CTA merge that unit after the barrier below.
+    if (wg == 0 && t == 0) {
+      int km = 0;
+      if (pend_k > 0 && seen == pend_k - 1) {
+        P.a.unit_counters[pend_unit] = 0;   // nobody touches it again before the next launch
+        km = pend_k;
+      }
+      merge_info[0] = km; merge_info[1] = pend_b; merge_info[2] = pend_kvh; merge_info[3] = pend_ht;
+      pend_k = 0;
       if (w.slot >= 0 && P.a.unit_counters != nullptr) {
-        __threadfence();
-        named_barrier(1 + wg, 128);
-        if (t == 0) {
-          const int unit = (w.b * P.p.num_kv_heads + w.kvh) * P.head_tiles + w.ht;
-          const int k = P.a.split_counts != nullptr ? __ldg(P.a.split_counts + unit)
-                                                    : P.a.kv_splits;
-          const int seen = atomicAdd(P.a.unit_counters + unit, 1);
-          if (seen == k - 1) {
-            P.a.unit_counters[unit] = 0;   // nobody touches it again before the next launch
-            k_merge = k;
-          }
-        }
+        pend_unit = (w.b * P.p.num_kv_heads + w.kvh) * P.head_tiles + w.ht;
+        pend_k = P.a.split_counts != nullptr ? __ldg(P.a.split_counts + pend_unit)
+                                             : P.a.kv_splits;
+        pend_b = w.b; pend_kvh = w.kvh; pend_ht = w.ht;
       }
     }
-    if (wg == 0 && t == 0) *merge_flag = k_merge;
     // the exchange buffers are reused by the next item
     named_barrier(1 + G, 128 * G);
-    // ---- in-kernel merge, step 2: every group takes its share of the unit's heads (the flag is
-    // next written after the next item's first all-group barrier, which this read precedes)
-    if (const int k = *merge_flag; k > 0 && t < D) {
-      __threadfence();
-      const int ch = channel_of_expanded_pos<BITS>(t);
-      const long long rows = static_cast<long long>(P.a.batch) * P.a.num_qo_heads;
-      for (int h = wg; h < GP; h += G) {
-        const int hl = w.ht * 8 + h;
-        if (hl >= P.heads_per_kv) continue;
-        const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
-        const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
-        // same arithmetic and slot order as merge_kernel; up to eight pieces are fetched in one
-        // round trip (this runs at the very end of the CTA that completes the unit)
-        float M = -INFINITY, den = 0.f, acc = 0.f;
-        if (k <= 8) {
-          float ms[8], ls[8], os[8];
-#pragma unroll
-          for (int s = 0; s < 8; ++s) {
-            const bool on = s < k;
-            ms[s] = on ? __ldcg(P.a.m_partial + s * rows + row) : -INFINITY;
-            ls[s] = on ? __ldcg(P.a.l_partial + s * rows + row) : 0.f;
-            os[s] = on ? __ldcg(P.a.o_partial + (s * rows + row) * D + ch) : 0.f;
-          }
-#pragma unroll
-          for (int s = 0; s < 8; ++s) M = fmaxf(M, ms[s]);
-          if (M > -INFINITY) {
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-              if (s < k) {
-                const float wgt = exp2f(ms[s] - M);
-                den += wgt * ls[s];
-                acc += wgt * os[s];
-              }
-            }
-          }
-        } else {
-          for (int s = 0; s < k; ++s) M = fmaxf(M, __ldcg(P.a.m_partial + s * rows + row));
-          if (M > -INFINITY) {
-            for (int s = 0; s < k; ++s) {
-              const float wgt = exp2f(__ldcg(P.a.m_partial + s * rows + row) - M);
-              den += wgt * __ldcg(P.a.l_partial + s * rows + row);
-              acc += wgt * __ldcg(P.a.o_partial + (s * rows + row) * D + ch);
-            }
-          }
+    // ---- in-kernel merge, step 2: every group takes its share of the unit's heads (the words
+    // are next written after the next item's first all-group barrier, which this read precedes)
+    if (merge_info[0] > 0)
+      merge_unit(merge_info[0], merge_info[1], merge_info[2], merge_info[3], wg, G);
+  }
+  // The last split piece of this CTA is counted in here; if that completes its unit, the CTA
+  // merges it (every group its share of the heads, as above).
+  {
+    volatile int* last_info = merge_info + 4;   // slow groups may still be reading merge_info
+    if (wg == 0 && t == 0) {
+      int km = 0;
+      if (pend_k > 0) {
+        __threadfence();
+        if (atomicAdd(P.a.unit_counters + pend_unit, 1) == pend_k - 1) {
+          P.a.unit_counters[pend_unit] = 0;
+          km = pend_k;
         }
-        const bool live = den > 0.f;
-        const float val = live ? acc / den * P.a.o_scale : 0.f;
-        const long long idx = row * D + ch;
-        if (P.a.out_dtype == 0) static_cast<__nv_bfloat16*>(P.a.out)[idx] = __float2bfloat16_rn(val);
-        else if (P.a.out_dtype == 1) static_cast<__half*>(P.a.out)[idx] = __float2half_rn(val);
-        else static_cast<float*>(P.a.out)[idx] = val;
-        if (t == 0 && P.a.lse != nullptr)
-          P.a.lse[row] = live ? (M + log2f(den)) * LN2 : -INFINITY;
       }
+      last_info[0] = km; last_info[1] = pend_b; last_info[2] = pend_kvh; last_info[3] = pend_ht;
     }
+    named_barrier(1 + G, 128 * G);
+    if (last_info[0] > 0)
+      merge_unit(last_info[0], last_info[1], last_info[2], last_info[3], wg, G);
   }
 }
 
@@ -662,11 +709,20 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           const int r = chunk >> 3, cc = chunk & 7;
           uint4 v = make_uint4(0, 0, 0, 0);
           const int hl = w.ht * 8 + r;  // head inside the KV head's group
-          if (r < 8 && hl < P.heads_per_kv && 16 * cc < D) {
-            const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
+          const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
+          const bool live = r < 8 && hl < P.heads_per_kv;
+          float qsum = 0.f;
+          if (live && 16 * cc < D) {
             const uint4 in = __ldg(reinterpret_cast<const uint4*>(
                 static_cast<const uint8_t*>(P.a.q) +
                 (static_cast<long long>(w.b) * P.a.num_qo_heads + head) * D + 16 * cc));
+            const uint32_t words[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 lo = e4m3x2_to_f32x2(words[i] & 0xFFFF);
+              const float2 hi = e4m3x2_to_f32x2(words[i] >> 16);
+              qsum += (lo.x + lo.y) + (hi.x + hi.y);
+            }
             if (BITS == 2) {
               v.x = __byte_perm(in.x, in.y, 0x6420);
               v.y = __byte_perm(in.z, in.w, 0x6420);
@@ -678,6 +734,24 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           }
           *reinterpret_cast<uint4*>(smem + SP::Q_OFF + qb * SP::Q_BYTES + r * 128 +
                                     ((cc ^ (r & 7)) << 4)) = v;
+          if (j < 2) {
+            // the row's eight chunks sit in eight neighbouring lanes: per-head constants
+            qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, 1);
+            qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, 2);
+            qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, 4);
+            if (cc == 0) {
+              float scale = 0.f;
+              if (live) {
+                scale = P.a.sm_scale * 1.4426950408889634f;
+                if (P.a.q_descale != nullptr)
+                  scale *= __ldg(P.a.q_descale + w.b * P.a.q_descale_stride_b +
+                                 head * P.a.q_descale_stride_h);
+              }
+              float* hc = reinterpret_cast<float*>(smem + SP::RED_OFF + 768 * G + 32) + qb * 16;
+              hc[r] = scale;
+              hc[8 + r] = scale * qsum;
+            }
+          }
         }
         fence_proxy_async();
         __syncwarp();

@@ -50,8 +50,8 @@ struct SmemPlan {
   static constexpr int XCHG_OFF = P_OFF + WORKER_GROUPS * P_BYTES;
   static constexpr int RED_OFF = XCHG_OFF + (WORKER_GROUPS - 1) * XCHG_BYTES;  // reductions
   // column maxima 256 B and sums 256 B per group, then 64 B of per-head constants per warp,
-  // then the merge flag
-  static constexpr int RED_BYTES = (512 * WORKER_GROUPS + 64 * 4 * WORKER_GROUPS + 16 + 1023) / 1024 * 1024;
+  // then two 16-byte merge notices, then two items' per-head constants (2 x 64 B)
+  static constexpr int RED_BYTES = (512 * WORKER_GROUPS + 64 * 4 * WORKER_GROUPS + 32 + 128 + 1023) / 1024 * 1024;
   static constexpr int BAR_OFF = RED_OFF + RED_BYTES;
   static constexpr int BAR_BYTES = 2048;   // barriers, then flags and diagnostics
   static constexpr int RING_OFF = (BAR_OFF + BAR_BYTES + 1023) / 1024 * 1024;
