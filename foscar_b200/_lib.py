@@ -57,7 +57,7 @@ _PROTOTYPES = {
                            _P, _P]),
     "fq_merge_states": (C.c_int, [_P, _P, _I32, _I32, _I32, _I32, _P, _I32, _P, _P]),
     "fq_plan_splits": (C.c_int, [_I32, _I32, _I32, _I32, _I32, _I32, _I32]),
-    "fq_plan_worklist": (C.c_int, [_P, _I32, _I32, _I32, _I32, _I32, _P, _I32, _P]),
+    "fq_plan_worklist": (C.c_int, [_P, _I32, _I32, _I32, _I32, _I32, _P, _I32, _P, _I32]),
     "fq_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
     "fq_worklist_words": (_I64, [_I32, _I32, _I32, _I32]),
     "fq_umma_selftest": (C.c_int, [_I32, _P, _P, _P, _P, _P, _P, _P, _P]),

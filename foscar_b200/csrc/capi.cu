@@ -2,6 +2,7 @@
 // split planners (pure host arithmetic) and small queries.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -65,18 +66,26 @@ static long long worklist_words(long long units, int num_ctas) {
   return WORK_WORDS + starts + WORK_WORDS * (units + num_ctas);
 }
 
-// Balanced plan: the units (request, KV head, head tile) are laid end to end, each weighing its
-// tile count plus a fixed per-piece overhead, and the line is cut into `num_ctas` equal
-// segments; a CTA's segment becomes its pieces, in line order. List layout (int32 words):
+// Balanced plan: every piece (a unit, or a part of a unit cut between CTAs) costs its tile count
+// plus a fixed overhead, measured on B200 at ~5 us against ~0.34 us per INT2 tile (pipeline
+// drain and refill, group merge, output). The units (request, KV head, head tile) are dealt to
+// the CTAs in order; a CTA takes tiles until its share of the total cost is used up, and the
+// unit in hand continues on the next CTA as a new piece. List layout (int32 words):
 // header {pieces, units, ctas, rows' word offset, 0...}, cta_start[ctas + 1] padded to 8 words,
 // then one row of 8 words per piece.
 extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t num_kv_heads,
                                 int32_t head_tiles, int32_t num_ctas, int32_t max_splits,
-                                int32_t* worklist, int32_t max_words, int32_t* split_counts) {
+                                int32_t* worklist, int32_t max_words, int32_t* split_counts,
+                                int32_t bits) {
   if (!seq_lens || !worklist || !split_counts) return FQ_ERR_BAD_ARG;
   if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || num_ctas < 1 || max_splits < 1)
     return FQ_ERR_BAD_ARG;
-  constexpr long long OVH = 8;  // per-piece overhead in tile units
+  long long OVH = bits == 4 ? 10 : 14;   // per-piece overhead in tile units (an INT4 tile: ~0.5 us)
+  long long MIN_PIECE = 4;   // a CTA with less room than this for tiles passes the unit on
+  if (const char* env = getenv("FOSCAR_B200_PIECE_OVERHEAD")) {   // tuning knob for experiments
+    const int v = atoi(env);
+    if (v >= 0 && v <= 256) OVH = v;
+  }
   const int upr = num_kv_heads * head_tiles;
   const long long units = static_cast<long long>(batch) * upr;
   if (worklist_words(units, num_ctas) > max_words) return FQ_ERR_TOO_LARGE;
@@ -85,41 +94,45 @@ extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t 
   };
   long long total = 0;
   for (int b = 0; b < batch; ++b) total += (tiles_of(b) + OVH) * upr;
-  const long long seg = std::max<long long>(1, (total + num_ctas - 1) / num_ctas);
+  total += OVH * (num_ctas - 1);   // about one cut, hence one more piece, per CTA boundary
+  const long long share = std::max<long long>(OVH + 1, (total + num_ctas - 1) / num_ctas);
   const int starts_words = (num_ctas + 1 + 7) / 8 * 8;
   int32_t* cta_start = worklist + WORK_WORDS;
   int32_t* rows = worklist + WORK_WORDS + starts_words;
   std::memset(worklist, 0, sizeof(int32_t) * (WORK_WORDS + starts_words));
-  long long pos = 0;
-  int pieces_total = 0, next_cta = 0;
+  int pieces_total = 0, cta = 0;
+  long long room = share;   // cost the CTA in hand can still take
+  cta_start[0] = 0;
   for (long long u = 0; u < units; ++u) {
     const int b = static_cast<int>(u / upr), kvh = static_cast<int>(u % upr) / head_tiles,
               ht = static_cast<int>(u % upr) % head_tiles;
     const int tiles = static_cast<int>(tiles_of(b));
-    // tile t of this unit sits at line position start + t; a piece ends where its CTA's
-    // segment ends
-    const long long start = pos + OVH;
     const int first_row = pieces_total;
     int t0 = 0, pieces = 0;
-    do {
-      const int cta = static_cast<int>(std::min<long long>((start + t0) / seg, num_ctas - 1));
+    for (;;) {
+      const bool last_cta = cta == num_ctas - 1;
+      // room for the overhead plus a worthwhile number of tiles, or the rest of the unit
+      if (!last_cta && room < OVH + std::min<long long>(MIN_PIECE, tiles - t0)) {
+        cta_start[++cta] = pieces_total;
+        room = share;
+        continue;
+      }
       int t1 = tiles;
-      if (cta < num_ctas - 1 && start + tiles > (cta + 1) * seg)
-        t1 = static_cast<int>((cta + 1) * seg - start);
-      while (next_cta <= cta) cta_start[next_cta++] = pieces_total;
+      if (!last_cta && OVH + (tiles - t0) > room) t1 = t0 + static_cast<int>(room - OVH);
       int32_t* row = rows + static_cast<long long>(WORK_WORDS) * pieces_total;
       row[0] = b; row[1] = kvh; row[2] = ht; row[3] = t0; row[4] = t1; row[5] = pieces;
       row[6] = 0; row[7] = 0;
       ++pieces_total;
       ++pieces;
+      room -= OVH + (t1 - t0);
       t0 = t1;
-    } while (t0 < tiles);
+      if (t0 >= tiles) break;
+    }
     if (pieces > max_splits) return FQ_ERR_TOO_LARGE;
     if (pieces == 1) rows[static_cast<long long>(WORK_WORDS) * first_row + 5] = -1;
     split_counts[u] = pieces;
-    pos += OVH + tiles;
   }
-  while (next_cta <= num_ctas) cta_start[next_cta++] = pieces_total;
+  while (cta < num_ctas) cta_start[++cta] = pieces_total;
   worklist[0] = pieces_total;
   worklist[1] = static_cast<int32_t>(units);
   worklist[2] = num_ctas;

@@ -336,7 +336,8 @@ class PagedDecodeWrapper:
         work = np.zeros(words, dtype=np.int32)
         counts = np.zeros(units, dtype=np.int32)
         pieces = lib.fq_plan_worklist(lens.ctypes.data, self._batch_size, lay.num_kv_heads, ht,
-                                      ctas, cap, work.ctypes.data, words, counts.ctypes.data)
+                                      ctas, cap, work.ctypes.data, words, counts.ctypes.data,
+                                      lay.bits)
         if pieces == _lib.ERR_TOO_LARGE:
             # a unit would need more pieces than the workspace holds: plan uniformly instead
             self._plan_uniform(None, "auto")
@@ -633,7 +634,7 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
         words = g["words"]
         pieces = lib.fq_plan_worklist(lengths.ctypes.data, self._batch_size, lay.num_kv_heads,
                                       g["ht"], g["ctas"], g["cap"], buf.ctypes.data, words,
-                                      buf[words:].ctypes.data)
+                                      buf[words:].ctypes.data, lay.bits)
         if pieces < 0:
             _lib.check(pieces, "update")
 
