@@ -239,6 +239,63 @@ def run_reference(args, cfg):
     print(json.dumps(line))
 
 
+def run_cache_op(args, cfg):
+    """The cache writer or the read-back kernel alone (one GPU): algorithmic GB/s from CUDA
+    events over `steps` launches on 131,072 tokens of the workload's head shape (inputs and
+    outputs together exceed L2)."""
+    from foscar_b200 import QuantKVLayout
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    tokens, hkv, d, bits = 131072, cfg["hkv"], cfg["d"], cfg["bits"]
+    layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device=device)
+    pages = tokens // PAGE
+    cache = layout.allocate(pages)
+    g = torch.Generator(device=device).manual_seed(args.seed)
+    k = torch.randn(tokens, hkv, d, device=device, generator=g).to(torch.bfloat16)
+    v = torch.randn(tokens, hkv, d, device=device, generator=g).to(torch.bfloat16)
+    slots = torch.randperm(pages, device=device, generator=g).repeat_interleave(PAGE) * PAGE \
+        + torch.arange(PAGE, device=device).repeat(pages)
+    packed = tokens * hkv * (2 * d * bits // 8 + 16)
+    dense = tokens * hkv * 2 * d * 2
+    if args.op == "append":
+        def step():
+            cache.append(k, v, slots)
+        moved = dense + packed + tokens * 8
+    else:
+        cache.append(k, v, slots)
+        k_out, v_out = torch.empty_like(k), torch.empty_like(v)
+        indptr = torch.tensor([0, pages], dtype=torch.int32, device=device)
+        indices = (slots[::PAGE] // PAGE).to(torch.int32)
+        lens = torch.tensor([tokens], dtype=torch.int32, device=device)
+        out_indptr = torch.tensor([0], dtype=torch.int32, device=device)
+
+        def step():
+            cache.dequantize(k_out, v_out, indptr, indices, lens, out_indptr)
+        moved = dense + packed + pages * 4
+    for _ in range(args.warmup):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1) / args.steps
+    peak, kind = measured_peak()
+    gbs = moved / ms / 1e6
+    print(json.dumps({"metric": f"{args.op}_gb_per_s", "value": gbs, "unit": "GB/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                      "higher_is_better": True, "dtype": f"int{bits} codes, f32 scales",
+                      "data": "synthetic",
+                      "config": {"workload": f"{args.op}: {tokens} tokens x {hkv} KV heads x "
+                                             f"head_dim {d}, INT{bits}, random pages"},
+                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s",
+                                   "frac": gbs / peak, "of": kind, "traffic": None,
+                                   "algorithmic_bytes": moved},
+                      "device_status": cache.last_status()}))
+
+
 def workload_config(args, cfg, seq):
     return {"workload": f"{args.workload}: INT{cfg['bits']} paged GQA decode, batch {cfg['batch']}, "
                         f"{cfg['hq']}/{cfg['hkv']} heads, head_dim {cfg['d']}, page 64, seq_lens "
@@ -259,12 +316,17 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=16384,
                     help="KV tokens in the CPU baseline's bounded sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--op", default="decode", choices=["decode", "append", "dequantize"],
+                    help="decode: the headline step. append / dequantize: the cache writer or the "
+                         "read-back kernel alone on a slice of the workload, as GB/s")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args, cfg)
+    if args.op != "decode":
+        return run_cache_op(args, cfg)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
