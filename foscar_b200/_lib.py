@@ -30,7 +30,7 @@ class Pools(C.Structure):
 class DecodeArgs(C.Structure):
     _fields_ = [("batch", C.c_int32), ("num_qo_heads", C.c_int32), ("out_dtype", C.c_int32),
                 ("kv_splits", C.c_int32), ("max_splits", C.c_int32), ("num_work", C.c_int32),
-                ("max_ctas", C.c_int32), ("reserved", C.c_int32),
+                ("max_ctas", C.c_int32), ("flags", C.c_int32),
                 ("sm_scale", C.c_float), ("o_scale", C.c_float),
                 ("worklist", C.c_void_p), ("seq_lens", C.c_void_p), ("page_table", C.c_void_p),
                 ("table_offsets", C.c_void_p), ("table_len", C.c_int64), ("q", C.c_void_p),

@@ -681,6 +681,13 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
+  // Everything above touched only this CTA's shared and tensor memory. Under a programmatic
+  // launch it may have run while the launch before this one in the stream was still finishing:
+  // wait for that launch (complete and flushed) before the first global access, and let the
+  // launch after this one start its own set-up as SMs free up. Both are no-ops otherwise.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
   const ItemRange items = item_range(P);
   const uint32_t ring0 = smem0 + SP::RING_OFF;
   int wprof[WAIT_SITES] = {};   // used by the diagnostic build only
@@ -1028,6 +1035,19 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   int ctas = P.a.max_ctas > 0 ? P.a.max_ctas : device_sm_count();
   int grid = P.a.worklist ? ctas : std::min(ctas, P.num_items);
   if (grid < 1) grid = 1;
+  if (P.a.flags & 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(DECODE_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, P));
+  }
   kernel<<<grid, DECODE_THREADS, smem, stream>>>(P);
   return static_cast<int>(cudaGetLastError());
 }

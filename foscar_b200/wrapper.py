@@ -427,13 +427,15 @@ class PagedDecodeWrapper:
         scale_s = self._sm_scale if sm_scale is None else sm_scale
         scale_o = 1.0 if o_scale is None else o_scale
         with _dev.on_device(self.device):
-            return self._launch(q, kv_cache, out, scale_s, scale_o, three_d, q_descale, lse)
+            return self._launch(q, kv_cache, out, scale_s, scale_o, three_d, q_descale, lse,
+                                enable_pdl)
 
     def update(self, lengths) -> None:
         raise RuntimeError("update() is graph mode's per-step call: build the wrapper with "
                            "use_cuda_graph=True and plan() it first")
 
-    def _launch(self, q, cache, out, scale_s, scale_o, three_d, q_descale, lse):
+    def _launch(self, q, cache, out, scale_s, scale_o, three_d, q_descale, lse,
+                enable_pdl=True):
         b, hq, d = self._batch_size, self._num_qo_heads, self._head_dim
         if out is None:
             out = torch.empty((b, hq, d) if three_d else (b, 1, hq, d), dtype=self._o_data_type,
@@ -445,6 +447,7 @@ class PagedDecodeWrapper:
         args.out_dtype = _OUT_CODE[self._o_data_type]
         args.kv_splits = 1 if self._worklist is not None else self._kv_splits
         args.max_splits = self._max_splits
+        args.flags = 1 if enable_pdl else 0
         args.num_work = self._work_rows
         args.max_ctas = self._plan_ctas
         args.sm_scale, args.o_scale = scale_s, scale_o
@@ -667,7 +670,8 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
             g["events"][slot].record(stream)
             g["recorded"][slot] = True
 
-    def _launch(self, q, cache, out, scale_s, scale_o, three_d, q_descale, lse):
+    def _launch(self, q, cache, out, scale_s, scale_o, three_d, q_descale, lse,
+                enable_pdl=True):
         g = self._graph
         if out is None:
             raise ValueError("graph mode's run() needs out=: a captured call writes a buffer the "
@@ -677,4 +681,5 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
                              f"q_descale={g['q_descale']}; this call passes "
                              f"lse={'a tensor' if lse is not None else None} and "
                              f"q_descale={'a tensor' if q_descale is not None else None}")
-        return super()._launch(q, cache, out, scale_s, scale_o, three_d, q_descale, lse)
+        return super()._launch(q, cache, out, scale_s, scale_o, three_d, q_descale, lse,
+                               enable_pdl)

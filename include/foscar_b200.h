@@ -107,7 +107,10 @@ typedef struct fq_decode_args {
   int32_t max_splits;           /* leading extent of the partial buffers */
   int32_t num_work;             /* explicit mode: most rows the list may hold */
   int32_t max_ctas;             /* grid cap; 0 = one CTA per SM */
-  int32_t reserved;
+  int32_t flags;                /* bit 0: launch with programmatic stream serialization (PDL): the
+                                 * kernel's on-chip set-up overlaps the tail of the launch before it
+                                 * in the stream; it waits for that launch before its first global
+                                 * access (the reference's enable_pdl, wrapper.py:1111-1117) */
   float sm_scale;
   float o_scale;
   const int32_t* worklist;      /* NULL = implicit mode */

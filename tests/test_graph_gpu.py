@@ -44,9 +44,10 @@ def test_eager_run_replays_identically(bits):
     assert w.last_status() == 0
 
 
-def test_graph_mode_follows_updates():
+@pytest.mark.parametrize("bits,hq,hkv,d", [(2, 32, 8, 128), (4, 64, 8, 64), (2, 64, 8, 64)])
+def test_graph_mode_follows_updates(bits, hq, hkv, d):
     from foscar_b200 import PagedDecodeWrapper, QuantKVLayout, graph_workspace_bytes
-    bits, hq, hkv, d, batch, max_len = 2, 32, 8, 128, 3, 6000
+    batch, max_len = 3, 6000
     max_pages = -(-max_len // 64)
     layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device="cuda")
     cache = layout.allocate(batch * max_pages)
