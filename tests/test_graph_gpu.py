@@ -79,5 +79,8 @@ def test_graph_mode_follows_updates(bits, hq, hkv, d):
         torch.cuda.synchronize()
         want, _ = oracle_outputs(pools, q.cpu(), indptr, indices, lengths, d ** -0.5)
         err = (out.float().cpu() - want).abs()
-        assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3, (lengths, err.max())
+        # the bf16 output's own rounding (2^-9 relative) is allowed on top of the mean tolerance:
+        # at length 1 the output is a single V row of magnitude ~1
+        mean_tol = 2e-3 + want.abs().mean().item() * 2.0 ** -9
+        assert err.max().item() <= 2e-2 and err.mean().item() <= mean_tol, (lengths, err.max())
     assert w.last_status() == 0
