@@ -68,6 +68,11 @@ def algorithmic_bytes(cfg, seq):
     return int(seq.sum()) * hkv * per_token_head + b * hq * d * (1 + 2) + 4 * pages
 
 
+# DRAM bytes (read + write) of one decode launch from an ncu capture of the same command
+# (profiles/decode_kernel_c2_int2.md); other workloads have no capture.
+NCU_TRAFFIC = {"c2": 398_729_472}
+
+
 def measured_peak():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -419,7 +424,8 @@ def main():
             % cfg["bits"], "data": "synthetic", "config": workload_config(args, cfg, seq),
             "hbm_gbs": abytes / (step_ms * 1e-3) / 1e9,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "of": peak_kind, "traffic": None,
+                         "frac": achieved / peak, "of": peak_kind,
+                         "traffic": NCU_TRAFFIC.get(args.workload),
                          "kernel": "decode_kernel", "kernel_us": decode_ms * 1e3,
                          "algorithmic_bytes": abytes, "frac_of_8tbs_nominal": achieved / 8000.0},
             "e2e": {"value": world * b / (e2e_ms * 1e-3), "unit": "tokens/s",
