@@ -43,9 +43,18 @@
     wprof[site] += static_cast<int>(now_ - stamp_t);              \
     stamp_t = now_;                                               \
   } while (0)
+#define FQ_ITEM_STAMP_BEGIN() long long item_t = clock64()
+#define FQ_ITEM_STAMP(site)                                       \
+  do {                                                            \
+    const long long now_ = clock64();                             \
+    wprof[site] += static_cast<int>(now_ - item_t);               \
+    item_t = now_;                                                \
+  } while (0)
 #else
 #define FQ_STAMP_BEGIN() ((void)0)
 #define FQ_STAMP(site) ((void)0)
+#define FQ_ITEM_STAMP_BEGIN() ((void)0)
+#define FQ_ITEM_STAMP(site) ((void)0)
 #endif
 
 // Diagnostic builds only: a bit mask of roles whose arithmetic is skipped while every barrier
@@ -318,6 +327,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   };
   // the split piece this CTA has written but not yet counted in (thread 0 of group 0 only)
   int pend_k = 0, pend_unit = 0, pend_b = 0, pend_kvh = 0, pend_ht = 0;
+  int seen = -1;        // the pending piece's count-in result; -1: not counted in yet
+  int this_k = 0;       // pieces of the current item's unit (fetched at the item's start)
 
   int qi = 0;       // non-empty items so far: which query stage holds the item's rows
   int it0 = 0;      // running index of the current item's first tile (every role counts alike)
@@ -325,9 +336,11 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   int n = 0;        // tiles this group has taken: the phase of its barriers
   RingPos rp;       // ring position of tile `mine`
   rp.advance(wg, NS);
+  FQ_ITEM_STAMP_BEGIN();
   for (int wi = items.begin; wi < items.end; wi += items.step) {
     const WorkItem w = decode_item(P, wi);
     const int nt = max(w.t1 - w.t0, 0);
+    FQ_ITEM_STAMP(13);
     float m[GP], l[GP], c[GP], oacc[GP];
 #pragma unroll
     for (int h = 0; h < GP; ++h) { m[h] = -INFINITY; l[h] = 0.f; c[h] = 0.f; oacc[h] = 0.f; }
@@ -344,6 +357,11 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     }
     __syncwarp();
     bool pending = false;
+    if (wg == 0 && t == 0 && w.slot >= 0 && P.a.unit_counters != nullptr) {
+      const int unit = (w.b * P.p.num_kv_heads + w.kvh) * P.head_tiles + w.ht;
+      this_k = P.a.split_counts != nullptr ? __ldg(P.a.split_counts + unit) : P.a.kv_splits;
+    }
+    FQ_ITEM_STAMP(16);
 
     // Add the group's previous tile's O (its PV MMA has had most of a tile's time to finish).
     // The wait also frees the group's V stage and P rows for the tile in hand.
@@ -501,17 +519,25 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       if (lane == 0) mbar_arrive(bars.pv_ready(wg));
       FQ_STAMP(22);
       pending = true;
+      // The previous split piece of this CTA is counted in here, a tile into the next item: its
+      // partials have drained, and the fence and the atomic's round trip cost one thread of
+      // one group a microsecond in mid-stream instead of stalling an item boundary.
+      if (wg == 0 && t == 0 && pend_k > 0 && seen < 0) {
+        __threadfence();
+        seen = atomicAdd(P.a.unit_counters + pend_unit, 1);
+      }
     }
     it0 += nt;
+    FQ_ITEM_STAMP(24);
     if (pending) accumulate();
+    FQ_ITEM_STAMP(27);
 
     // ---- item epilogue. First, the count-in of the previous split piece (see step 1 below)
-    int seen = -1;
-    if (wg == 0 && t == 0 && pend_k > 0) {
+    if (wg == 0 && t == 0 && pend_k > 0 && seen < 0) {   // group 0 had no tile in this item
       __threadfence();
       seen = atomicAdd(P.a.unit_counters + pend_unit, 1);
     }
-    // group sums, then the groups' states merged by group 0
+    // group sums, then the groups' states through shared memory
     float* rs = red_sum + (wg * 4 + wq) * 16;
 #pragma unroll
     for (int h = 0; h < GP; ++h) {
@@ -530,8 +556,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       l[h] = (gs[h] + gs[16 + h]) + (gs[32 + h] + gs[48 + h]);
       c[h] = (gs[8 + h] + gs[24 + h]) + (gs[40 + h] + gs[56 + h]);
     }
-    if (wg > 0) {
-      float* xo = reinterpret_cast<float*>(smem + SP::XCHG_OFF + (wg - 1) * SP::XCHG_BYTES);
+    {   // every group leaves its state in shared memory
+      float* xo = reinterpret_cast<float*>(smem + SP::XCHG_OFF + wg * SP::XCHG_BYTES);
       float* xmeta = xo + TILE * 8;
 #pragma unroll
       for (int h = 0; h < GP; ++h) xo[t * 8 + h] = oacc[h];
@@ -541,19 +567,23 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       }
     }
     named_barrier(1 + G, 128 * G);
-    if (wg == 0 && w.slot != -2) {
+    FQ_ITEM_STAMP(30);
+    // The groups' states are merged in fixed order (group 0, then 1, 2, 3), each group taking a
+    // share of the heads. The loops stay rolled: this code runs once per item, and keeping it
+    // small keeps it cheap to fetch.
+    if (w.slot != -2) {
       const int ch = channel_of_expanded_pos<BITS>(t);
       const bool on = t < D;   // head_dim 64: the upper half of the O rows is padding
-#pragma unroll
-      for (int h = 0; h < GP; ++h) {
+      const float o_fix = o_mul * v_position_scale<BITS>(t);
+#pragma unroll 1
+      for (int h = wg; h < GP; h += G) {
         const int hl = w.ht * 8 + h;
         if (hl >= P.heads_per_kv) continue;
-        // fixed merge order: group 0, then 1, 2, 3
-        float M = m[h], L = l[h], C = c[h], O = oacc[h];
-#pragma unroll
-        for (int g = 1; g < G; ++g) {
+        float M = -INFINITY, L = 0.f, C = 0.f, O = 0.f;
+#pragma unroll 1
+        for (int g = 0; g < G; ++g) {
           const float* xo = reinterpret_cast<const float*>(smem + SP::XCHG_OFF +
-                                                           (g - 1) * SP::XCHG_BYTES);
+                                                           g * SP::XCHG_BYTES);
           const float* xmeta = xo + TILE * 8;
           const float m1 = xmeta[h], l1 = xmeta[8 + h], c1 = xmeta[16 + h], o1 = xo[t * 8 + h];
           const float Mn = fmaxf(M, m1);
@@ -564,7 +594,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           O = O * f0 + o1 * f1;
           M = Mn;
         }
-        O = O * (o_mul * v_position_scale<BITS>(t)) + C;
+        O = O * o_fix + C;
+        FQ_ITEM_STAMP(28);
         const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
         const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
         if (w.slot < 0) {
@@ -582,13 +613,13 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           if (on) P.a.o_partial[prow * D + ch] = O;
           if (t == 0) { P.a.l_partial[prow] = L; P.a.m_partial[prow] = M; }
         }
+        FQ_ITEM_STAMP(29);
       }
     }
     // ---- in-kernel merge, step 1. A split piece is counted in (release fence + one atomic on
-    // its unit's counter) not here but in the NEXT item's epilogue, or after the last item: by
-    // then its partials have long drained, and the atomic's round trip (issued above, before the
-    // group merge) has overlapped with this epilogue. Whoever finds the count complete makes
-    // the CTA merge that unit after the barrier below.
+    // its unit's counter) not here but a tile into the NEXT item (above), or after the last
+    // item. Whoever finds the count complete makes the CTA merge that unit after the barrier
+    // below.
     if (wg == 0 && t == 0) {
       int km = 0;
       if (pend_k > 0 && seen == pend_k - 1) {
@@ -597,19 +628,22 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       }
       merge_info[0] = km; merge_info[1] = pend_b; merge_info[2] = pend_kvh; merge_info[3] = pend_ht;
       pend_k = 0;
+      seen = -1;
       if (w.slot >= 0 && P.a.unit_counters != nullptr) {
         pend_unit = (w.b * P.p.num_kv_heads + w.kvh) * P.head_tiles + w.ht;
-        pend_k = P.a.split_counts != nullptr ? __ldg(P.a.split_counts + pend_unit)
-                                             : P.a.kv_splits;
+        pend_k = this_k;
         pend_b = w.b; pend_kvh = w.kvh; pend_ht = w.ht;
       }
     }
+    FQ_ITEM_STAMP(31);
     // the exchange buffers are reused by the next item
     named_barrier(1 + G, 128 * G);
+    FQ_ITEM_STAMP(25);
     // ---- in-kernel merge, step 2: every group takes its share of the unit's heads (the words
     // are next written after the next item's first all-group barrier, which this read precedes)
     if (merge_info[0] > 0)
       merge_unit(merge_info[0], merge_info[1], merge_info[2], merge_info[3], wg, G);
+    FQ_ITEM_STAMP(26);
   }
   // The last split piece of this CTA is counted in here; if that completes its unit, the CTA
   // merges it (every group its share of the heads, as above).
@@ -618,8 +652,11 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     if (wg == 0 && t == 0) {
       int km = 0;
       if (pend_k > 0) {
-        __threadfence();
-        if (atomicAdd(P.a.unit_counters + pend_unit, 1) == pend_k - 1) {
+        if (seen < 0) {
+          __threadfence();
+          seen = atomicAdd(P.a.unit_counters + pend_unit, 1);
+        }
+        if (seen == pend_k - 1) {
           P.a.unit_counters[pend_unit] = 0;
           km = pend_k;
         }

@@ -48,7 +48,7 @@ struct SmemPlan {
   static constexpr int P_OFF = Q_OFF + 2 * Q_BYTES;
   static constexpr int XCHG_BYTES = TILE * 8 * 4 + 128;   // one group's accumulators + (m,l,c)
   static constexpr int XCHG_OFF = P_OFF + WORKER_GROUPS * P_BYTES;
-  static constexpr int RED_OFF = XCHG_OFF + (WORKER_GROUPS - 1) * XCHG_BYTES;  // reductions
+  static constexpr int RED_OFF = XCHG_OFF + WORKER_GROUPS * XCHG_BYTES;  // reductions
   // column maxima 256 B and sums 256 B per group, then 64 B of per-head constants per warp,
   // then two 16-byte merge notices, then two items' per-head constants (2 x 64 B)
   static constexpr int RED_BYTES = (512 * WORKER_GROUPS + 64 * 4 * WORKER_GROUPS + 32 + 128 + 1023) / 1024 * 1024;
