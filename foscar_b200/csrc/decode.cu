@@ -191,6 +191,71 @@ __device__ inline float v_position_scale(int pos) {
   return BITS == 2 && ((pos >> 2) & 1) ? 0.25f : 1.f;
 }
 
+// Final value to the output tensor in its dtype.
+__device__ __forceinline__ void store_value(void* out, int out_dtype, long long idx, float val) {
+  if (out_dtype == 0) static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(val);
+  else if (out_dtype == 1) static_cast<__half*>(out)[idx] = __float2half_rn(val);
+  else static_cast<float*>(out)[idx] = val;
+}
+
+// Merge of a split unit's partials: the arithmetic and slot order of merge_kernel. Heads h0,
+// h0 + hstep, ... (< gp) of the unit's head tile; the calling thread takes channel `ch`. Kept
+// out of line and rolled: it runs a few times per launch, and the kernel's code footprint is
+// what an item boundary pays for in instruction fetches.
+__device__ __noinline__ void merge_unit_partials(const DecodeParams& P, int d, int gp, int ch,
+                                                 bool writes_lse, int k, int b, int kvh, int ht,
+                                                 int h0, int hstep) {
+  constexpr float LN2 = 0.6931471805599453f;
+  __threadfence();
+  const long long rows = static_cast<long long>(P.a.batch) * P.a.num_qo_heads;
+#pragma unroll 1
+  for (int h = h0; h < gp; h += hstep) {
+    const int hl = ht * 8 + h;
+    if (hl >= P.heads_per_kv) continue;
+    const long long head = static_cast<long long>(kvh) * P.heads_per_kv + hl;
+    const long long row = static_cast<long long>(b) * P.a.num_qo_heads + head;
+    float M = -INFINITY, den = 0.f, acc = 0.f;
+    if (k <= 4) {
+      // the common case in one round trip
+      float ms[4], ls[4], os[4];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const bool on = s < k;
+        ms[s] = on ? __ldcg(P.a.m_partial + s * rows + row) : -INFINITY;
+        ls[s] = on ? __ldcg(P.a.l_partial + s * rows + row) : 0.f;
+        os[s] = on ? __ldcg(P.a.o_partial + (s * rows + row) * d + ch) : 0.f;
+      }
+#pragma unroll
+      for (int s = 0; s < 4; ++s) M = fmaxf(M, ms[s]);
+      if (M > -INFINITY) {
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          if (s < k) {
+            const float wgt = exp2f(ms[s] - M);
+            den += wgt * ls[s];
+            acc += wgt * os[s];
+          }
+        }
+      }
+    } else {
+#pragma unroll 1
+      for (int s = 0; s < k; ++s) M = fmaxf(M, __ldcg(P.a.m_partial + s * rows + row));
+      if (M > -INFINITY) {
+#pragma unroll 4
+        for (int s = 0; s < k; ++s) {
+          const float wgt = exp2f(__ldcg(P.a.m_partial + s * rows + row) - M);
+          den += wgt * __ldcg(P.a.l_partial + s * rows + row);
+          acc += wgt * __ldcg(P.a.o_partial + (s * rows + row) * d + ch);
+        }
+      }
+    }
+    const bool live = den > 0.f;
+    store_value(P.a.out, P.a.out_dtype, row * d + ch, live ? acc / den * P.a.o_scale : 0.f);
+    if (writes_lse && P.a.lse != nullptr)
+      P.a.lse[row] = live ? (M + log2f(den)) * LN2 : -INFINITY;
+  }
+}
+
 // Worker role: one of four 128-thread groups. Group `wg` takes the tiles whose running index is
 // `wg` modulo 4 and carries each of them through every stage itself: unpack K into tensor memory,
 // unpack V into shared memory, fold the scales into the raw scores, softmax, write the P rows,
@@ -248,82 +313,10 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   const float p2lp = exp2f(static_cast<float>(lp));
   const float o_mul = exp2f(static_cast<float>(9 - lp));
 
-  // Merge of a split unit's partials: the arithmetic and slot order of merge_kernel. Heads h0,
-  // h0 + hstep, ... of the unit's head tile; thread t takes the channel at expanded position t.
   auto merge_unit = [&](int k, int b, int kvh, int ht, int h0, int hstep) {
-    if (t >= D) return;
-    __threadfence();
-    const int ch = channel_of_expanded_pos<BITS>(t);
-    const long long rows = static_cast<long long>(P.a.batch) * P.a.num_qo_heads;
-      for (int h = h0; h < GP; h += hstep) {
-        const int hl = ht * 8 + h;
-        if (hl >= P.heads_per_kv) continue;
-        const long long head = static_cast<long long>(kvh) * P.heads_per_kv + hl;
-        const long long row = static_cast<long long>(b) * P.a.num_qo_heads + head;
-        // same arithmetic and slot order as merge_kernel; up to eight pieces are fetched in one
-        // round trip (this runs at the very end of the CTA that completes the unit)
-        float M = -INFINITY, den = 0.f, acc = 0.f;
-        if (k <= 8) {
-          float ms[8], ls[8], os[8];
-#pragma unroll
-          for (int s = 0; s < 8; ++s) {
-            const bool on = s < k;
-            ms[s] = on ? __ldcg(P.a.m_partial + s * rows + row) : -INFINITY;
-            ls[s] = on ? __ldcg(P.a.l_partial + s * rows + row) : 0.f;
-            os[s] = on ? __ldcg(P.a.o_partial + (s * rows + row) * D + ch) : 0.f;
-          }
-#pragma unroll
-          for (int s = 0; s < 8; ++s) M = fmaxf(M, ms[s]);
-          if (M > -INFINITY) {
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-              if (s < k) {
-                const float wgt = exp2f(ms[s] - M);
-                den += wgt * ls[s];
-                acc += wgt * os[s];
-              }
-            }
-          }
-        } else {
-          // more pieces: two passes, each fetching eight pieces per round trip
-          for (int s0 = 0; s0 < k; s0 += 8) {
-            float ms[8];
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-              ms[s] = s0 + s < k ? __ldcg(P.a.m_partial + (s0 + s) * rows + row) : -INFINITY;
-#pragma unroll
-            for (int s = 0; s < 8; ++s) M = fmaxf(M, ms[s]);
-          }
-          if (M > -INFINITY) {
-            for (int s0 = 0; s0 < k; s0 += 8) {
-              float ms[8], ls[8], os[8];
-#pragma unroll
-              for (int s = 0; s < 8; ++s) {
-                const bool on = s0 + s < k;
-                ms[s] = on ? __ldcg(P.a.m_partial + (s0 + s) * rows + row) : -INFINITY;
-                ls[s] = on ? __ldcg(P.a.l_partial + (s0 + s) * rows + row) : 0.f;
-                os[s] = on ? __ldcg(P.a.o_partial + ((s0 + s) * rows + row) * D + ch) : 0.f;
-              }
-#pragma unroll
-              for (int s = 0; s < 8; ++s) {
-                if (s0 + s < k) {
-                  const float wgt = exp2f(ms[s] - M);
-                  den += wgt * ls[s];
-                  acc += wgt * os[s];
-                }
-              }
-            }
-          }
-        }
-        const bool live = den > 0.f;
-        const float val = live ? acc / den * P.a.o_scale : 0.f;
-        const long long idx = row * D + ch;
-        if (P.a.out_dtype == 0) static_cast<__nv_bfloat16*>(P.a.out)[idx] = __float2bfloat16_rn(val);
-        else if (P.a.out_dtype == 1) static_cast<__half*>(P.a.out)[idx] = __float2half_rn(val);
-        else static_cast<float*>(P.a.out)[idx] = val;
-        if (t == 0 && P.a.lse != nullptr)
-          P.a.lse[row] = live ? (M + log2f(den)) * LN2 : -INFINITY;
-      }
+    if (t < D)
+      merge_unit_partials(P, D, GP, channel_of_expanded_pos<BITS>(t), t == 0, k, b, kvh, ht, h0,
+                          hstep);
   };
   // the split piece this CTA has written but not yet counted in (thread 0 of group 0 only)
   int pend_k = 0, pend_unit = 0, pend_b = 0, pend_kvh = 0, pend_ht = 0;
@@ -571,15 +564,15 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     // The groups' states are merged in fixed order (group 0, then 1, 2, 3), each group taking a
     // share of the heads. The loops stay rolled: this code runs once per item, and keeping it
     // small keeps it cheap to fetch.
-    if (w.slot != -2) {
-      const int ch = channel_of_expanded_pos<BITS>(t);
-      const bool on = t < D;   // head_dim 64: the upper half of the O rows is padding
-      const float o_fix = o_mul * v_position_scale<BITS>(t);
-#pragma unroll 1
-      for (int h = wg; h < GP; h += G) {
-        const int hl = w.ht * 8 + h;
-        if (hl >= P.heads_per_kv) continue;
-        float M = -INFINITY, L = 0.f, C = 0.f, O = 0.f;
+    // (The results go to global memory only after the barrier below: a barrier that follows
+    // global stores waits for them to be acknowledged, about 2 us under this load.)
+    constexpr int HPG = (GP + G - 1) / G;   // heads a group merges
+    float rM[HPG], rL[HPG], rO[HPG];
+#pragma unroll
+    for (int i = 0; i < HPG; ++i) {
+      const int h = wg + i * G;
+      float M = -INFINITY, L = 0.f, C = 0.f, O = 0.f;
+      if (h < GP) {
 #pragma unroll 1
         for (int g = 0; g < G; ++g) {
           const float* xo = reinterpret_cast<const float*>(smem + SP::XCHG_OFF +
@@ -594,27 +587,9 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           O = O * f0 + o1 * f1;
           M = Mn;
         }
-        O = O * o_fix + C;
-        FQ_ITEM_STAMP(28);
-        const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
-        const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
-        if (w.slot < 0) {
-          const float val = L > 0.f ? O / L * P.a.o_scale : 0.f;
-          const long long idx = row * D + ch;
-          if (!on) {
-          } else if (P.a.out_dtype == 0) static_cast<__nv_bfloat16*>(P.a.out)[idx] = __float2bfloat16_rn(val);
-          else if (P.a.out_dtype == 1) static_cast<__half*>(P.a.out)[idx] = __float2half_rn(val);
-          else static_cast<float*>(P.a.out)[idx] = val;
-          if (t == 0 && P.a.lse != nullptr)
-            P.a.lse[row] = L > 0.f ? (M + log2f(L)) * LN2 : -INFINITY;
-        } else {
-          const long long prow =
-              static_cast<long long>(w.slot) * P.a.batch * P.a.num_qo_heads + row;
-          if (on) P.a.o_partial[prow * D + ch] = O;
-          if (t == 0) { P.a.l_partial[prow] = L; P.a.m_partial[prow] = M; }
-        }
-        FQ_ITEM_STAMP(29);
+        O = O * (o_mul * v_position_scale<BITS>(t)) + C;
       }
+      rM[i] = M; rL[i] = L; rO[i] = O;
     }
     // ---- in-kernel merge, step 1. A split piece is counted in (release fence + one atomic on
     // its unit's counter) not here but a tile into the NEXT item (above), or after the last
@@ -641,6 +616,30 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     FQ_ITEM_STAMP(25);
     // ---- in-kernel merge, step 2: every group takes its share of the unit's heads (the words
     // are next written after the next item's first all-group barrier, which this read precedes)
+    if (w.slot != -2) {
+      const int ch = channel_of_expanded_pos<BITS>(t);
+      const bool on = t < D;   // head_dim 64: the upper half of the O rows is padding
+#pragma unroll
+      for (int i = 0; i < HPG; ++i) {
+        const int h = wg + i * G;
+        const int hl = w.ht * 8 + h;
+        if (h >= GP || hl >= P.heads_per_kv) continue;
+        const float M = rM[i], L = rL[i], O = rO[i];
+        const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
+        const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
+        if (w.slot < 0) {
+          const float val = L > 0.f ? O / L * P.a.o_scale : 0.f;
+          if (on) store_value(P.a.out, P.a.out_dtype, row * D + ch, val);
+          if (t == 0 && P.a.lse != nullptr)
+            P.a.lse[row] = L > 0.f ? (M + log2f(L)) * LN2 : -INFINITY;
+        } else {
+          const long long prow =
+              static_cast<long long>(w.slot) * P.a.batch * P.a.num_qo_heads + row;
+          if (on) P.a.o_partial[prow * D + ch] = O;
+          if (t == 0) { P.a.l_partial[prow] = L; P.a.m_partial[prow] = M; }
+        }
+      }
+    }
     if (merge_info[0] > 0)
       merge_unit(merge_info[0], merge_info[1], merge_info[2], merge_info[3], wg, G);
     FQ_ITEM_STAMP(26);

@@ -61,7 +61,7 @@ struct SmemPlan {
 };
 
 // The items a launch runs, decoded the same way by every role of every CTA.
-__device__ inline WorkItem decode_item(const DecodeParams& P, int i) {
+__device__ __noinline__ WorkItem decode_item(const DecodeParams& P, int i) {
   WorkItem w;
   const fq_decode_args& a = P.a;
   if (a.worklist != nullptr) {
