@@ -62,6 +62,16 @@ __device__ inline void settle_count(uint32_t* hist, uint32_t old, uint32_t now) 
   if (c_old) atomicAdd(hist + b_old, 0xFFFFFFFFu);
 }
 
+// The same into a block-local table of signed deltas (flushed once per block): the pool's counts
+// live in a handful of bins, and a global atomic per raised cell serialises on those addresses.
+__device__ inline void settle_count_local(int* local, uint32_t old, uint32_t now) {
+  const bool c_old = (old & 0x7FFFFFFFu) != 0, c_new = (now & 0x7FFFFFFFu) != 0;
+  const uint32_t b_old = vmax_bucket(old), b_new = vmax_bucket(now);
+  if (c_old && c_new && b_old == b_new) return;
+  if (c_new) atomicAdd(local + b_new, 1);
+  if (c_old) atomicAdd(local + b_old, -1);
+}
+
 // -------------------------------------------------------------------------------------------
 // 1. page starts
 // -------------------------------------------------------------------------------------------
@@ -132,7 +142,22 @@ __device__ inline uint32_t quantize_fields(const float (&x)[CH], float s, float 
 }
 
 template <int BITS, int D, bool PREQ>
+__device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta);
+
+template <int BITS, int D, bool PREQ>
 __global__ void __launch_bounds__(256) append_kernel(WriterArgs a) {
+  __shared__ int hist_delta[FQ_VMAX_BINS];
+  for (int i = threadIdx.x; i < FQ_VMAX_BINS; i += blockDim.x) hist_delta[i] = 0;
+  __syncthreads();
+  append_rows<BITS, D, PREQ>(a, hist_delta);
+  __syncthreads();
+  if (a.p.v_max_hist != nullptr)
+    for (int i = threadIdx.x; i < FQ_VMAX_BINS; i += blockDim.x)
+      if (hist_delta[i] != 0) atomicAdd(a.p.v_max_hist + i, static_cast<uint32_t>(hist_delta[i]));
+}
+
+template <int BITS, int D, bool PREQ>
+__device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta) {
   constexpr int CH = D / 32;        // channels per lane
   constexpr int W = 32 / BITS;      // codes per word
   constexpr int LPW = W / CH;       // lanes sharing one code word (>= 1)
@@ -143,6 +168,28 @@ __global__ void __launch_bounds__(256) append_kernel(WriterArgs a) {
   const int hkv = a.p.num_kv_heads;
   if (warp >= a.num_tokens * hkv) return;
   const int token = warp / hkv, head = warp % hkv;
+  const int kg = a.p.k_groups;
+  const int c0 = lane * CH;
+  // The token's rows are requested before its slot is known: the slot, the rows and (below) the
+  // page's maximum cell are three global round trips, and only the last depends on another.
+  const __nv_bfloat16* kr = static_cast<const __nv_bfloat16*>(a.k) +
+                            token * a.k_stride + static_cast<long long>(head) * D + c0;
+  const __nv_bfloat16* vr = static_cast<const __nv_bfloat16*>(a.v) +
+                            token * a.v_stride + static_cast<long long>(head) * D + c0;
+  uint4 uk = make_uint4(0, 0, 0, 0), uv = make_uint4(0, 0, 0, 0);
+  if (!PREQ) {
+    if constexpr (CH == 8) {
+      uk = __ldg(reinterpret_cast<const uint4*>(kr));
+      uv = __ldg(reinterpret_cast<const uint4*>(vr));
+    } else if constexpr (CH == 4) {
+      const uint2 k2 = __ldg(reinterpret_cast<const uint2*>(kr));
+      const uint2 v2 = __ldg(reinterpret_cast<const uint2*>(vr));
+      uk.x = k2.x; uk.y = k2.y; uv.x = v2.x; uv.y = v2.y;
+    } else {
+      uk.x = __ldg(reinterpret_cast<const uint32_t*>(kr));
+      uv.x = __ldg(reinterpret_cast<const uint32_t*>(vr));
+    }
+  }
   const long long slot = a.slots[token];
   if (slot < 0) return;
   const long long page = slot >> 6;
@@ -151,20 +198,16 @@ __global__ void __launch_bounds__(256) append_kernel(WriterArgs a) {
     if (lane == 0 && a.status) atomicOr(a.status, FQ_STATUS_BAD_SLOT);
     return;
   }
-  const int kg = a.p.k_groups;
-  const int c0 = lane * CH;
+  // the page's current maximum, wanted only at the very end
+  uint32_t cell_seen = 0;
+  if (lane == 0 && a.p.v_page_max != nullptr)
+    cell_seen = *reinterpret_cast<volatile uint32_t*>(a.p.v_page_max + page * hkv + head);
   float sk, zk, sv, zv;
   uint32_t kw, vw;
 
   if (!PREQ) {
     float xk[CH], xv[CH];
-    const __nv_bfloat16* kr = static_cast<const __nv_bfloat16*>(a.k) +
-                              token * a.k_stride + static_cast<long long>(head) * D + c0;
-    const __nv_bfloat16* vr = static_cast<const __nv_bfloat16*>(a.v) +
-                              token * a.v_stride + static_cast<long long>(head) * D + c0;
     if constexpr (CH == 8) {
-      const uint4 uk = __ldg(reinterpret_cast<const uint4*>(kr));
-      const uint4 uv = __ldg(reinterpret_cast<const uint4*>(vr));
       const uint32_t wk[4] = {uk.x, uk.y, uk.z, uk.w}, wv[4] = {uv.x, uv.y, uv.z, uv.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -174,17 +217,13 @@ __global__ void __launch_bounds__(256) append_kernel(WriterArgs a) {
         xv[2 * i + 1] = __uint_as_float(wv[i] & 0xFFFF0000u);
       }
     } else if constexpr (CH == 4) {
-      const uint2 uk = __ldg(reinterpret_cast<const uint2*>(kr));
-      const uint2 uv = __ldg(reinterpret_cast<const uint2*>(vr));
       xk[0] = __uint_as_float(uk.x << 16); xk[1] = __uint_as_float(uk.x & 0xFFFF0000u);
       xk[2] = __uint_as_float(uk.y << 16); xk[3] = __uint_as_float(uk.y & 0xFFFF0000u);
       xv[0] = __uint_as_float(uv.x << 16); xv[1] = __uint_as_float(uv.x & 0xFFFF0000u);
       xv[2] = __uint_as_float(uv.y << 16); xv[3] = __uint_as_float(uv.y & 0xFFFF0000u);
     } else {
-      const uint32_t uk = __ldg(reinterpret_cast<const uint32_t*>(kr));
-      const uint32_t uv = __ldg(reinterpret_cast<const uint32_t*>(vr));
-      xk[0] = __uint_as_float(uk << 16); xk[1] = __uint_as_float(uk & 0xFFFF0000u);
-      xv[0] = __uint_as_float(uv << 16); xv[1] = __uint_as_float(uv & 0xFFFF0000u);
+      xk[0] = __uint_as_float(uk.x << 16); xk[1] = __uint_as_float(uk.x & 0xFFFF0000u);
+      xv[0] = __uint_as_float(uv.x << 16); xv[1] = __uint_as_float(uv.x & 0xFFFF0000u);
     }
     if (a.k_clip >= 0) {
       const float t = clip_threshold<CH>(xk, a.k_clip);
@@ -287,10 +326,9 @@ __global__ void __launch_bounds__(256) append_kernel(WriterArgs a) {
     }
     if (a.p.v_page_max != nullptr) {
       uint32_t* cell = a.p.v_page_max + page * hkv + head;
-      const uint32_t seen = *reinterpret_cast<volatile uint32_t*>(cell);
-      if (sv_bits > seen) {
+      if (sv_bits > cell_seen) {   // a stale (smaller) reading only costs a redundant atomicMax
         const uint32_t old = atomicMax(cell, sv_bits);
-        if (old < sv_bits) settle_count(a.p.v_max_hist, old, sv_bits);
+        if (old < sv_bits) settle_count_local(hist_delta, old, sv_bits);
       }
     }
   }
