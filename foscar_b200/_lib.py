@@ -20,6 +20,11 @@ WORK_WORDS = 8
 TILE_TOKENS = 128
 
 
+def tile_tokens(head_dim: int) -> int:
+    """Tokens per sequence tile of the decode kernel (two per tensor-memory lane at head_dim 64)."""
+    return 256 if head_dim == 64 else 128
+
+
 class Pools(C.Structure):
     _fields_ = [("bits", C.c_int32), ("head_dim", C.c_int32), ("num_kv_heads", C.c_int32),
                 ("k_groups", C.c_int32), ("scale_bf16", C.c_int32), ("num_pages", C.c_int32),
@@ -57,7 +62,7 @@ _PROTOTYPES = {
                            _P, _P]),
     "fq_merge_states": (C.c_int, [_P, _P, _I32, _I32, _I32, _I32, _P, _I32, _P, _P]),
     "fq_plan_splits": (C.c_int, [_I32, _I32, _I32, _I32, _I32, _I32, _I32]),
-    "fq_plan_worklist": (C.c_int, [_P, _I32, _I32, _I32, _I32, _I32, _P, _I32, _P, _I32]),
+    "fq_plan_worklist": (C.c_int, [_P, _I32, _I32, _I32, _I32, _I32, _P, _I32, _P, _I32, _I32]),
     "fq_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
     "fq_worklist_words": (_I64, [_I32, _I32, _I32, _I32]),
     "fq_umma_selftest": (C.c_int, [_I32, _P, _P, _P, _P, _P, _P, _P, _P]),

@@ -49,7 +49,8 @@ extern "C" int fq_plan_splits(int32_t batch, int32_t num_kv_heads, int32_t head_
   if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || sm_count < 1) return FQ_ERR_BAD_ARG;
   if (bits != 2 && bits != 4) return FQ_ERR_BAD_ARG;
   const long long base = static_cast<long long>(batch) * num_kv_heads * head_tiles;
-  const int tiles = std::max(1, (max_kv_len + TILE - 1) / TILE);
+  const int tt = tile_tokens(head_dim);
+  const int tiles = std::max(1, (max_kv_len + tt - 1) / tt);
   int best = 1;
   double best_cost = split_cost(base, tiles, 1, bits, sm_count);
   for (int s = 2; s <= 64; ++s) {
@@ -76,7 +77,7 @@ static long long worklist_words(long long units, int num_ctas) {
 extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t num_kv_heads,
                                 int32_t head_tiles, int32_t num_ctas, int32_t max_splits,
                                 int32_t* worklist, int32_t max_words, int32_t* split_counts,
-                                int32_t bits) {
+                                int32_t bits, int32_t head_dim) {
   if (!seq_lens || !worklist || !split_counts) return FQ_ERR_BAD_ARG;
   if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || num_ctas < 1 || max_splits < 1)
     return FQ_ERR_BAD_ARG;
@@ -87,10 +88,11 @@ extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t 
     if (v >= 0 && v <= 256) OVH = v;
   }
   const int upr = num_kv_heads * head_tiles;
+  const int tt = tile_tokens(head_dim);
   const long long units = static_cast<long long>(batch) * upr;
   if (worklist_words(units, num_ctas) > max_words) return FQ_ERR_TOO_LARGE;
   auto tiles_of = [&](int b) -> long long {
-    return seq_lens[b] > 0 ? (static_cast<long long>(seq_lens[b]) + TILE - 1) / TILE : 0;
+    return seq_lens[b] > 0 ? (static_cast<long long>(seq_lens[b]) + tt - 1) / tt : 0;
   };
   long long total = 0;
   for (int b = 0; b < batch; ++b) total += (tiles_of(b) + OVH) * upr;

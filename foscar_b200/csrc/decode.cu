@@ -112,15 +112,18 @@ struct RingPos {
   }
 };
 
-// Tensor-memory column plan (f32 columns): per worker group one K operand stage, one S and one
-// O buffer of 16 columns.
+// Tensor-memory column plan (f32 columns): per worker group one K operand stage (a 128-byte row
+// per lane at head_dim 64, where a lane holds two tokens), one S buffer of 16 columns and one O
+// buffer of 16 columns per token of a lane.
 template <int D>
 struct TmemPlan {
-  static constexpr int KOP_COLS = D / 4;
+  static constexpr bool PAIR = tile_tokens(D) == 2 * TILE;
+  static constexpr int KOP_COLS = PAIR ? 32 : D / 4;
+  static constexpr int O_COLS = PAIR ? 32 : 16;
   static constexpr int KOP = 0;
   static constexpr int S = WORKER_GROUPS * KOP_COLS;
   static constexpr int O = S + WORKER_GROUPS * 16;
-  static constexpr int USED = O + WORKER_GROUPS * 16;
+  static constexpr int USED = O + WORKER_GROUPS * O_COLS;
   static constexpr int ALLOC = USED <= 128 ? 128 : (USED <= 256 ? 256 : 512);
   static_assert(USED <= 512, "tensor memory plan exceeds 512 columns");
 };
@@ -278,7 +281,10 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   const uint32_t ring0 = smem0 + SP::RING_OFF;
   const uint32_t k_dst = tmem + lane_base + TP::KOP + wg * TP::KOP_COLS;
   const uint32_t s_src = tmem + lane_base + TP::S + wg * 16;
-  const uint32_t o_src = tmem + lane_base + TP::O + wg * 16;
+  constexpr int NT = SP::PAIR ? 2 : 1;   // tokens per lane
+  // a lane's O columns: at two tokens per lane, rows 0-63 (warps 0, 1) hold the first token
+  // set's channels and take its P columns, rows 64-127 the second's
+  const uint32_t o_src = tmem + lane_base + TP::O + wg * TP::O_COLS + (SP::PAIR && wq >= 2 ? 16 : 0);
   const uint32_t v_row = smem0 + SP::VOP_OFF + wg * SP::VOP_STAGE + t * SP::ROW;
   const uint32_t p_row = smem0 + SP::P_OFF + wg * SP::P_BYTES + t * 16;
   float* red_max = reinterpret_cast<float*>(smem + SP::RED_OFF);              // [wg][buf][warp][8]
@@ -375,21 +381,29 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       const uint32_t stage = ring0 + rp.s * SP::STAGE;
       mbar_wait(bars.ring_full(rp.s), rp.ph, abort_flag, status, 8, wprof);
       FQ_STAMP_BEGIN();
-      // ---- K row -> tensor memory (the S MMA's A operand). The stage is free: this group read
-      // the S of its previous tile, so that tile's MMA, the stage's last reader, is complete.
+      // ---- K row(s) -> tensor memory (the S MMA's A operand). The stage is free: this group
+      // read the S of its previous tile, so that tile's MMA, the stage's last reader, is
+      // complete. With two tokens per lane (head_dim 64) the second token's 64 bytes follow the
+      // first's in the lane's 128-byte row.
       {
-        uint32_t wk[D * BITS / 32], op[D / 4];
+        uint32_t op[NT * D / 4];
+#pragma unroll
+        for (int u = 0; u < NT; ++u) {
+          uint32_t wk[D * BITS / 32], part[D / 4];
 #if FQ_STUB_ROLES & 2
 #pragma unroll
-        for (int i = 0; i < D / 4; ++i) op[i] = n;
+          for (int i = 0; i < D / 4; ++i) part[i] = n;
 #else
-        load_row<BITS, D>(stage + SP::K_OFF + t * SP::RB, wk);
-        expand_words<BITS, D>(wk, op);
+          load_row<BITS, D>(stage + SP::K_OFF + (u * TILE + t) * SP::RB, wk);
+          expand_words<BITS, D>(wk, part);
 #endif
+#pragma unroll
+          for (int i = 0; i < D / 4; ++i) op[u * (D / 4) + i] = part[i];
+        }
         FQ_STAMP(3);
         tc_fence_after();
 #pragma unroll
-        for (int v = 0; v < D / 32; ++v) tmem_st8(k_dst + 8 * v, op + 8 * v);
+        for (int v = 0; v < NT * D / 32; ++v) tmem_st8(k_dst + 8 * v, op + 8 * v);
         tmem_st_wait();
         FQ_STAMP(5);
         tc_fence_before();
@@ -399,19 +413,26 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       FQ_STAMP(17);
       if (pending) accumulate();
       FQ_STAMP(18);
-      // ---- V row -> the group's 128-byte-swizzled shared-memory stage (the PV MMA's A operand)
+      // ---- V row(s) -> the group's 128-byte-swizzled shared-memory stage (the PV MMA's A
+      // operand), laid out like the K row
       {
-        uint32_t wv[D * BITS / 32], op[D / 4];
+        uint32_t op[NT * D / 4];
+#pragma unroll
+        for (int u = 0; u < NT; ++u) {
+          uint32_t wv[D * BITS / 32], part[D / 4];
 #if FQ_STUB_ROLES & 4
 #pragma unroll
-        for (int i = 0; i < D / 4; ++i) op[i] = n;
+          for (int i = 0; i < D / 4; ++i) part[i] = n;
 #else
-        load_row<BITS, D>(stage + SP::V_OFF + t * SP::RB, wv);
-        expand_words_v<BITS, D>(wv, op);
+          load_row<BITS, D>(stage + SP::V_OFF + (u * TILE + t) * SP::RB, wv);
+          expand_words_v<BITS, D>(wv, part);
 #endif
+#pragma unroll
+          for (int i = 0; i < D / 4; ++i) op[u * (D / 4) + i] = part[i];
+        }
         FQ_STAMP(6);
 #pragma unroll
-        for (int cc = 0; cc < D / 16; ++cc) {
+        for (int cc = 0; cc < NT * D / 16; ++cc) {
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(v_row + ((cc ^ (t & 7)) << 4)),
                        "r"(op[4 * cc]), "r"(op[4 * cc + 1]), "r"(op[4 * cc + 2]),
                        "r"(op[4 * cc + 3])
@@ -419,52 +440,65 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         }
       }
       FQ_STAMP(9);
-      // this token's records; then the ring stage goes back to the producers
-      float sk, zk, sv, zv;
-      asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-                   : "=f"(sk), "=f"(zk), "=f"(sv), "=f"(zv)
-                   : "r"(stage + SP::S_OFF + t * 16));
+      // the tokens' records; then the ring stage goes back to the producers
+      float sk[NT], zk[NT], sv[NT], zv[NT];
+#pragma unroll
+      for (int u = 0; u < NT; ++u)
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=f"(sk[u]), "=f"(zk[u]), "=f"(sv[u]), "=f"(zv[u])
+                     : "r"(stage + SP::S_OFF + (u * TILE + t) * 16));
       __syncwarp();
       if (lane == 0) mbar_arrive(bars.ring_empty(rp.s));
       FQ_STAMP(19);
-      // ---- raw scores of token row t
+      // ---- raw scores: columns [0, GP) for the lane's first token, [8, 8 + GP) for its second
       mbar_wait(bars.s_done(wg), n & 1, abort_flag, status, 12, wprof);
       tc_fence_after();
-      uint32_t raw[GP];
-      if constexpr (GP == 4) tmem_ld4(s_src, raw);
+      uint32_t raw[NT == 2 ? 16 : GP];
+      if constexpr (NT == 2) tmem_ld16(s_src, raw);
+      else if constexpr (GP == 4) tmem_ld4(s_src, raw);
       else tmem_ld8(s_src, raw);
       tmem_ld_wait();
       tc_fence_before();
       FQ_STAMP(20);
       FQ_STAMP(10);   // the cost of one stamp itself
+      uint32_t pw[NT][4];
 #if FQ_STUB_ROLES & 1
-      uint32_t pw[4] = {__float_as_uint(sk + zk) & 1u, raw[0] & 1u, __float_as_uint(sv + zv) & 1u, 0u};
+#pragma unroll
+      for (int u = 0; u < NT; ++u) {
+        pw[u][0] = __float_as_uint(sk[u] + zk[u]) & 1u; pw[u][1] = raw[0] & 1u;
+        pw[u][2] = __float_as_uint(sv[u] + zv[u]) & 1u; pw[u][3] = 0u;
+      }
 #else
       // Only a request's last tile has positions past its length: their scores become -inf and
       // their records are neutralised, so stale shared memory can never reach the output.
-      const bool valid = (tt + 1) * TILE <= w.len || tt * TILE + t < w.len;
-      const float a_k = sk * 512.f;
-      float wsc = sv * p2lp;
-      if (!valid) { wsc = 0.f; zv = 0.f; }
       // Scores against the group's running reference m, which may lag the true maximum by up to
       // MAX_LAG (p <= 2^MAX_LAG; the P scale leaves that headroom below the E4M3 range). Only
       // when some score of the tile exceeds that does the group take the exact column maximum
       // and rescale; the common tile costs one reducing barrier instead of an exchange through
       // shared memory.
-      float x[GP];
+      float x[NT][GP], wsc[NT];
       float over = -INFINITY;
 #pragma unroll
-      for (int h = 0; h < GP; ++h) {
-        const float xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[h]), head_k[8 + h] * zk);
-        x[h] = valid ? xv : -INFINITY;
-        over = fmaxf(over, x[h] - m[h]);
+      for (int u = 0; u < NT; ++u) {
+        const int pos = tt * SP::TT + u * TILE + t;
+        const bool valid = (tt + 1) * SP::TT <= w.len || pos < w.len;
+        const float a_k = sk[u] * 512.f;
+        wsc[u] = sv[u] * p2lp;
+        if (!valid) { wsc[u] = 0.f; zv[u] = 0.f; }
+#pragma unroll
+        for (int h = 0; h < GP; ++h) {
+          const float xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[8 * u + h]),
+                                head_k[8 + h] * zk[u]);
+          x[u][h] = valid ? xv : -INFINITY;
+          over = fmaxf(over, x[u][h] - m[h]);
+        }
       }
       if (named_barrier_or(1 + wg, 128, over > MAX_LAG)) {
         const int buf = n & 1;
         float* wmax = red_max + ((wg * 2 + buf) * 4 + wq) * 8;
 #pragma unroll
         for (int h = 0; h < GP; ++h) {
-          const float wm = warp_max_f32(x[h]);
+          const float wm = warp_max_f32(NT == 2 ? fmaxf(x[0][h], x[NT - 1][h]) : x[0][h]);
           if (lane == 0) wmax[h] = wm;
         }
         named_barrier(1 + wg, 128);
@@ -481,31 +515,36 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         }
       }
       // two heads per instruction in f16x2: p = 2^(x-m), w = p * s_v 2^lp, E4M3 hi + lo/16
-      uint32_t pw[4] = {0u, 0u, 0u, 0u};
-      const __half2 wsc2 = __float2half2_rn(wsc);
 #pragma unroll
-      for (int h = 0; h < GP; h += 2) {
-        const __half2 d2 = __floats2half2_rn(x[h] - m[h], x[h + 1] - m[h + 1]);
-        const __half2 e2 = h2_exp2(d2);
-        const float2 ef = __half22float2(e2);
-        l[h] += ef.x;
-        l[h + 1] += ef.y;
-        c[h] = fmaf(ef.x, zv, c[h]);
-        c[h + 1] = fmaf(ef.y, zv, c[h + 1]);
-        const __half2 w2 = __hmul2(e2, wsc2);
-        const uint32_t hi2 = f16x2_to_e4m3x2(w2);
-        const __half2 r2 = __hmul2(__hsub2(w2, e4m3x2_to_f16x2(hi2)), __float2half2_rn(16.f));
-        const uint32_t lo2 = f16x2_to_e4m3x2(r2);
-        pw[h >> 2] |= hi2 << (16 * ((h >> 1) & 1));
-        pw[2 + (h >> 2)] |= lo2 << (16 * ((h >> 1) & 1));
+      for (int u = 0; u < NT; ++u) {
+        pw[u][0] = pw[u][1] = pw[u][2] = pw[u][3] = 0u;
+        const __half2 wsc2 = __float2half2_rn(wsc[u]);
+#pragma unroll
+        for (int h = 0; h < GP; h += 2) {
+          const __half2 d2 = __floats2half2_rn(x[u][h] - m[h], x[u][h + 1] - m[h + 1]);
+          const __half2 e2 = h2_exp2(d2);
+          const float2 ef = __half22float2(e2);
+          l[h] += ef.x;
+          l[h + 1] += ef.y;
+          c[h] = fmaf(ef.x, zv[u], c[h]);
+          c[h + 1] = fmaf(ef.y, zv[u], c[h + 1]);
+          const __half2 w2 = __hmul2(e2, wsc2);
+          const uint32_t hi2 = f16x2_to_e4m3x2(w2);
+          const __half2 r2 = __hmul2(__hsub2(w2, e4m3x2_to_f16x2(hi2)), __float2half2_rn(16.f));
+          const uint32_t lo2 = f16x2_to_e4m3x2(r2);
+          pw[u][h >> 2] |= hi2 << (16 * ((h >> 1) & 1));
+          pw[u][2 + (h >> 2)] |= lo2 << (16 * ((h >> 1) & 1));
+        }
       }
 #endif
       FQ_STAMP(21);
-      // the P row: bytes [hi_0..hi_7 | lo_0..lo_7]; with the V rows above it completes the PV
-      // MMA's operands
-      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_row), "r"(pw[0]), "r"(pw[1]),
-                   "r"(pw[2]), "r"(pw[3])
-                   : "memory");
+      // the P row(s): bytes [hi_0..hi_7 | lo_0..lo_7], one plane of 128 rows per token of a lane;
+      // with the V rows above they complete the PV MMA's operands
+#pragma unroll
+      for (int u = 0; u < NT; ++u)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_row + u * TILE * 16),
+                     "r"(pw[u][0]), "r"(pw[u][1]), "r"(pw[u][2]), "r"(pw[u][3])
+                     : "memory");
       fence_proxy_async();
       FQ_STAMP(11);
       __syncwarp();
@@ -578,7 +617,10 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           const float* xo = reinterpret_cast<const float*>(smem + SP::XCHG_OFF +
                                                            g * SP::XCHG_BYTES);
           const float* xmeta = xo + TILE * 8;
-          const float m1 = xmeta[h], l1 = xmeta[8 + h], c1 = xmeta[16 + h], o1 = xo[t * 8 + h];
+          const float m1 = xmeta[h], l1 = xmeta[8 + h], c1 = xmeta[16 + h];
+          // at two tokens per lane, channel t's sum is split over rows t and t + 64
+          float o1 = xo[t * 8 + h];
+          if (SP::PAIR && t < 64) o1 += xo[(t + 64) * 8 + h];
           const float Mn = fmaxf(M, m1);
           const float f0 = M == -INFINITY ? 0.f : exp2f(M - Mn);
           const float f1 = m1 == -INFINITY ? 0.f : exp2f(m1 - Mn);
@@ -751,14 +793,18 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           const int chunk = lane + 32 * j;      // 16 rows of eight 16-byte chunks
           const int r = chunk >> 3, cc = chunk & 7;
           uint4 v = make_uint4(0, 0, 0, 0);
-          const int hl = w.ht * 8 + r;  // head inside the KV head's group
+          // At two tokens per lane rows 0-7 carry the heads against the first token's half of
+          // the K row (bytes 0-63) and rows 8-15 the same heads against the second's (64-127).
+          const int hl = w.ht * 8 + (SP::PAIR ? (r & 7) : r);  // head inside the KV head's group
           const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
-          const bool live = r < 8 && hl < P.heads_per_kv;
+          const bool live = (SP::PAIR || r < 8) && hl < P.heads_per_kv;
+          const bool mine = SP::PAIR ? ((r < 8) == (cc < 4)) : 16 * cc < D;
+          const int src = SP::PAIR ? (cc & 3) : cc;
           float qsum = 0.f;
-          if (live && 16 * cc < D) {
+          if (live && mine) {
             const uint4 in = __ldg(reinterpret_cast<const uint4*>(
                 static_cast<const uint8_t*>(P.a.q) +
-                (static_cast<long long>(w.b) * P.a.num_qo_heads + head) * D + 16 * cc));
+                (static_cast<long long>(w.b) * P.a.num_qo_heads + head) * D + 16 * src));
             const uint32_t words[4] = {in.x, in.y, in.z, in.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -801,8 +847,9 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         if (lane == 0) mbar_arrive(bars.q_full(qb));
       }
       ++qi;
+      constexpr int PPT = SP::PPT;   // pages per tile
       const int npages = (w.len + PAGE - 1) / PAGE;
-      const int pend = min(2 * w.t1, npages);
+      const int pend = min(PPT * w.t1, npages);
       auto fetch = [&](int pg0) {
         const int pg = pg0 + lane;
         int id = -1;
@@ -816,22 +863,23 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         }
         return id;
       };
-      int cur = fetch(2 * w.t0);
-      for (int base = 2 * w.t0; base < 2 * w.t1; base += 32) {
-        const int nxt = base + 32 < 2 * w.t1 ? fetch(base + 32) : -1;
-        for (int k = 0; k < 16 && base + 2 * k < 2 * w.t1; ++k, ++it) {
+      int cur = fetch(PPT * w.t0);
+      for (int base = PPT * w.t0; base < PPT * w.t1; base += 32) {
+        const int nxt = base + 32 < PPT * w.t1 ? fetch(base + 32) : -1;
+        for (int k = 0; k < 32 / PPT && base + PPT * k < PPT * w.t1; ++k, ++it) {
           const int s = rp.s;
           const uint32_t eph = rp.ph ^ 1u;
           rp.next(NS);
           if ((it & 1) != pi) continue;
-          const int id0 = __shfl_sync(0xFFFFFFFFu, cur, 2 * k);
-          const int id1 = __shfl_sync(0xFFFFFFFFu, cur, 2 * k + 1);
+          int ids[PPT];
+#pragma unroll
+          for (int j = 0; j < PPT; ++j) ids[j] = __shfl_sync(0xFFFFFFFFu, cur, PPT * k + j);
           mbar_wait(bars.ring_empty(s), eph, abort_flag, status, 0, wprof);
           const uint32_t full = bars.ring_full(s);
           const uint32_t dst = ring0 + s * SP::STAGE + 16 * lane;
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const int id = j ? id1 : id0;
+          for (int j = 0; j < PPT; ++j) {
+            const int id = ids[j];
             if (id < 0 || (FQ_STUB_ROLES & 8)) continue;
             const long long blk = static_cast<long long>(id) * P.p.num_kv_heads + w.kvh;
             const uint8_t* ks = P.p.k_codes + blk * SP::CODE_PAGE + 16 * lane;
@@ -881,7 +929,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           const uint32_t ka = tmem + TP::KOP + g * TP::KOP_COLS;
           umma_ts_c<Q_HI, IDESC_S, false>(sd, ka, q_lo);
 #pragma unroll
-          for (int k = 1; k < ((FQ_STUB_ROLES & 16) ? 1 : D / 32); ++k)
+          for (int k = 1; k < ((FQ_STUB_ROLES & 16) ? 1 : (SP::PAIR ? 2 : 1) * D / 32); ++k)
             umma_ts_c<Q_HI, IDESC_S, true>(sd, ka + 8 * k, q_lo + 2 * k);
           tc_commit(bars.s_done(g));
           if (t == w.t1 - 1) tc_commit(bars.q_empty(qb));
@@ -907,12 +955,17 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           tc_fence_after();
           const uint32_t v_lo = v_lo0 + g * (SP::VOP_STAGE >> 4);
           const uint32_t p_lo = p_lo0 + g * (SP::P_BYTES >> 4);
-          const uint32_t od = tmem + TP::O + g * 16;
-          umma_ss_c<V_HI, P_HI, IDESC_PV, false>(od, v_lo, p_lo);
+          const uint32_t od = tmem + TP::O + g * TP::O_COLS;
+          // one accumulator per token of a lane: the same V rows against that token's P plane
 #pragma unroll
-          for (int k = 1; k < ((FQ_STUB_ROLES & 32) ? 1 : TILE / 32); ++k)
-            umma_ss_c<V_HI, P_HI, IDESC_PV, true>(od, v_lo + k * (32 * SP::ROW >> 4),
-                                                  p_lo + k * (32 * 16 >> 4));
+          for (int u = 0; u < (SP::PAIR ? 2 : 1); ++u) {
+            const uint32_t pu = p_lo + u * (TILE * 16 >> 4);
+            umma_ss_c<V_HI, P_HI, IDESC_PV, false>(od + 16 * u, v_lo, pu);
+#pragma unroll
+            for (int k = 1; k < ((FQ_STUB_ROLES & 32) ? 1 : TILE / 32); ++k)
+              umma_ss_c<V_HI, P_HI, IDESC_PV, true>(od + 16 * u, v_lo + k * (32 * SP::ROW >> 4),
+                                                    pu + k * (32 * 16 >> 4));
+          }
           tc_commit(bars.pv_done(g));
           if (++g == G) { g = 0; gph ^= 1u; }
         }
@@ -1057,6 +1110,7 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   }
   if (stages < WORKER_GROUPS) return FQ_ERR_UNSUPPORTED;  // a group steps the ring by one lap at most
   P.ring_stages = stages;
+  P.tile_tokens = SP::TT;
   const int smem = SP::RING_OFF + stages * SP::STAGE + 1024;
   static bool configured[64] = {};  // per (BITS, D, GP) instantiation and device
   auto kernel = decode_kernel<BITS, D, GP>;

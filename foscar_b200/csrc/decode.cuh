@@ -5,7 +5,11 @@
 
 namespace fq {
 
-constexpr int TILE = 128;            // tokens per sequence tile: two pages
+constexpr int TILE = 128;            // MMA rows: tensor-memory lanes, threads of a worker group
+// Tokens per sequence tile. head_dim 128: one token per lane (two pages). head_dim 64: two tokens
+// per lane, t and 128 + t of the tile (four pages): their 64-byte operand rows sit side by side
+// in one 128-byte row, so a tile of 256 tokens costs what a 128-token tile of head_dim 128 costs.
+__host__ __device__ constexpr int tile_tokens(int head_dim) { return head_dim == 64 ? 256 : 128; }
 constexpr int WORK_WORDS = 8;        // int32 words per explicit work-list row
 #ifndef FQ_WORKER_GROUPS
 #define FQ_WORKER_GROUPS 4
@@ -21,6 +25,7 @@ struct DecodeParams {
   int head_tiles;    // ceil(ratio / 8)
   int num_items;     // implicit: B*HKV*head_tiles*kv_splits; explicit: row capacity
   int ring_stages;
+  int tile_tokens;   // tile_tokens(head_dim)
 };
 
 struct WorkItem {
@@ -33,16 +38,20 @@ struct SmemPlan {
   static constexpr int RB = D * BITS / 8;              // code row bytes
   static constexpr int CODE_PAGE = PAGE * RB;          // one page of K (or V) codes, one head
   static constexpr int SCALE_PAGE = PAGE * 16;         // f32 (s_k,z_k,s_v,z_v) records
-  static constexpr int K_OFF = 0;
-  static constexpr int V_OFF = 2 * CODE_PAGE;
-  static constexpr int S_OFF = 4 * CODE_PAGE;
-  static constexpr int STAGE = 4 * CODE_PAGE + 2 * SCALE_PAGE;
+  static constexpr int TT = tile_tokens(D);            // tokens per tile
+  static constexpr bool PAIR = TT == 2 * TILE;         // two tokens per lane
+  static constexpr int PPT = TT / PAGE;                // pages per tile
+  static constexpr int K_OFF = 0;                      // a ring stage: K pages, V pages, records
+  static constexpr int V_OFF = PPT * CODE_PAGE;
+  static constexpr int S_OFF = 2 * PPT * CODE_PAGE;
+  static constexpr int STAGE = 2 * PPT * CODE_PAGE + PPT * SCALE_PAGE;
   // Operand rows keep a 128-byte pitch (the swizzle atom) whatever D <= 128: head_dim 64 uses
   // the first half of each row.
   static constexpr int ROW = 128;
   static constexpr int VOP_STAGE = TILE * ROW;         // expanded V operand, one tile
   static constexpr int Q_BYTES = 16 * ROW;             // 16 MMA rows
-  static constexpr int P_BYTES = TILE * 16;            // 16 bytes (8 hi + 8 lo) per token
+  static constexpr int P_BYTES = TT * 16;              // 16 bytes (8 hi + 8 lo) per token, a
+                                                       // plane of 128 rows per token of a lane
   static constexpr int VOP_OFF = 0;
   static constexpr int Q_OFF = VOP_OFF + WORKER_GROUPS * VOP_STAGE;
   static constexpr int P_OFF = Q_OFF + 2 * Q_BYTES;
@@ -61,7 +70,7 @@ struct SmemPlan {
 };
 
 // The items a launch runs, decoded the same way by every role of every CTA.
-__device__ __noinline__ WorkItem decode_item(const DecodeParams& P, int i) {
+static __device__ __noinline__ WorkItem decode_item(const DecodeParams& P, int i) {
   WorkItem w;
   const fq_decode_args& a = P.a;
   if (a.worklist != nullptr) {
@@ -84,7 +93,7 @@ __device__ __noinline__ WorkItem decode_item(const DecodeParams& P, int i) {
   int len = __ldg(a.seq_lens + w.b);
   if (len < 0) len = 0;
   w.len = len;
-  const int tiles = (len + TILE - 1) / TILE;
+  const int tiles = (len + P.tile_tokens - 1) / P.tile_tokens;
   if (a.worklist == nullptr) {
     const int S = a.kv_splits;
     const int per = (tiles + S - 1) / S;

@@ -117,7 +117,7 @@ def graph_workspace_bytes(max_batch: int, num_qo_heads: int, layout: QuantKVLayo
         raise ValueError(f"the layout was resolved for {layout.arch} and {dev} is {arch}")
     _check_num_qo_heads(num_qo_heads, layout.num_kv_heads)
     sms = _dev.sm_count(dev)
-    tiles = -(-int(max_kv_len) // _lib.TILE_TOKENS)
+    tiles = -(-int(max_kv_len) // _lib.tile_tokens(layout.head_dim))
     words = 0
     for batch in range(1, max_batch + 1):
         splits = _graph_split_cap(batch, layout.num_kv_heads,
@@ -337,7 +337,7 @@ class PagedDecodeWrapper:
         counts = np.zeros(units, dtype=np.int32)
         pieces = lib.fq_plan_worklist(lens.ctypes.data, self._batch_size, lay.num_kv_heads, ht,
                                       ctas, cap, work.ctypes.data, words, counts.ctypes.data,
-                                      lay.bits)
+                                      lay.bits, lay.head_dim)
         if pieces == _lib.ERR_TOO_LARGE:
             # a unit would need more pieces than the workspace holds: plan uniformly instead
             self._plan_uniform(None, "auto")
@@ -600,7 +600,7 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
         ctas = _dev.sm_count(self.device)
         units = b * lay.num_kv_heads * ht
         words = int(lib.fq_worklist_words(b, lay.num_kv_heads, ht, ctas))
-        tiles = -(-self._max_kv_len // _lib.TILE_TOKENS)
+        tiles = -(-self._max_kv_len // _lib.tile_tokens(d))
         cap = _graph_split_cap(b, lay.num_kv_heads, ht, ctas, tiles)
         cap = min(cap, _fit_splits(self._float_workspace_buffer, b, hq, d))
         self._o_partial, self._l_partial, self._m_partial = _carve_partials(
@@ -637,7 +637,7 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
         words = g["words"]
         pieces = lib.fq_plan_worklist(lengths.ctypes.data, self._batch_size, lay.num_kv_heads,
                                       g["ht"], g["ctas"], g["cap"], buf.ctypes.data, words,
-                                      buf[words:].ctypes.data, lay.bits)
+                                      buf[words:].ctypes.data, lay.bits, lay.head_dim)
         if pieces < 0:
             _lib.check(pieces, "update")
 

@@ -184,13 +184,14 @@ int fq_merge_states(const float* o_shards, const float* lse_shards, int32_t num_
  * words; fq_worklist_words gives the size that always suffices) and the piece count of each
  * unit into split_counts [B * HKV * head_tiles]; returns the number of pieces, or a negative
  * FQ_ERR_* (FQ_ERR_TOO_LARGE when a unit would need more than max_splits pieces). `bits` (2 or
- * 4) sets the cost of a tile against the fixed cost of a piece. */
+ * 4) sets the cost of a tile against the fixed cost of a piece; `head_dim` the tokens of a tile
+ * (128; 256 at head_dim 64). */
 int fq_plan_splits(int32_t batch, int32_t num_kv_heads, int32_t head_tiles, int32_t max_kv_len,
                    int32_t bits, int32_t head_dim, int32_t sm_count);
 int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t num_kv_heads,
                      int32_t head_tiles, int32_t num_ctas, int32_t max_splits,
                      int32_t* worklist, int32_t max_words, int32_t* split_counts,
-                     int32_t bits);
+                     int32_t bits, int32_t head_dim);
 int64_t fq_worklist_words(int32_t batch, int32_t num_kv_heads, int32_t head_tiles,
                           int32_t num_ctas);
 int64_t fq_workspace_bytes(int32_t max_splits, int32_t batch, int32_t num_qo_heads,

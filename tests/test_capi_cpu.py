@@ -45,7 +45,7 @@ def _plan(lens, hkv, ht, ctas, cap=64):
     work = np.zeros(words, dtype=np.int32)
     counts = np.zeros(len(lens) * hkv * ht, dtype=np.int32)
     n = lib.fq_plan_worklist(lens.ctypes.data, len(lens), hkv, ht, ctas, cap, work.ctypes.data,
-                             words, counts.ctypes.data, 2)
+                             words, counts.ctypes.data, 2, 128)
     return n, work, counts
 
 
@@ -88,7 +88,7 @@ def test_worklist_respects_the_split_cap_and_buffer():
     small = np.zeros(16, dtype=np.int32)
     counts = np.zeros(8, dtype=np.int32)
     assert lib.fq_plan_worklist(lens.ctypes.data, 1, 8, 1, 148, 64, small.ctypes.data, 16,
-                                counts.ctypes.data, 2) == _lib.ERR_TOO_LARGE
+                                counts.ctypes.data, 2, 128) == _lib.ERR_TOO_LARGE
 
 
 def test_uniform_planner_behaviour():
