@@ -443,10 +443,21 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       // the tokens' records; then the ring stage goes back to the producers
       float sk[NT], zk[NT], sv[NT], zv[NT];
 #pragma unroll
-      for (int u = 0; u < NT; ++u)
-        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-                     : "=f"(sk[u]), "=f"(zk[u]), "=f"(sv[u]), "=f"(zv[u])
-                     : "r"(stage + SP::S_OFF + (u * TILE + t) * 16));
+      for (int u = 0; u < NT; ++u) {
+        const int row = u * TILE + t;
+        if (!P.p.scale_bf16) {
+          asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                       : "=f"(sk[u]), "=f"(zk[u]), "=f"(sv[u]), "=f"(zv[u])
+                       : "r"(stage + SP::S_OFF + row * 16));
+        } else {   // (s, z) as bf16 pairs, 8 bytes a token, each page at its f32-sized slot
+          uint32_t kr, vr;
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];"
+                       : "=r"(kr), "=r"(vr)
+                       : "r"(stage + SP::S_OFF + (row >> 6) * SP::SCALE_PAGE + (row & 63) * 8));
+          sk[u] = __uint_as_float(kr << 16); zk[u] = __uint_as_float(kr & 0xFFFF0000u);
+          sv[u] = __uint_as_float(vr << 16); zv[u] = __uint_as_float(vr & 0xFFFF0000u);
+        }
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(bars.ring_empty(rp.s));
       FQ_STAMP(19);
@@ -884,7 +895,9 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
             const long long blk = static_cast<long long>(id) * P.p.num_kv_heads + w.kvh;
             const uint8_t* ks = P.p.k_codes + blk * SP::CODE_PAGE + 16 * lane;
             const uint8_t* vs = P.p.v_codes + blk * SP::CODE_PAGE + 16 * lane;
-            const uint8_t* ss = static_cast<const uint8_t*>(P.p.scales) + blk * SP::SCALE_PAGE +
+            // records: 16 B per token in an f32 pool, 8 B in a bf16 pool (same slot in the ring)
+            const int scale_page = P.p.scale_bf16 ? SP::SCALE_PAGE / 2 : SP::SCALE_PAGE;
+            const uint8_t* ss = static_cast<const uint8_t*>(P.p.scales) + blk * scale_page +
                                 16 * lane;
 #pragma unroll
             for (int c = 0; c < SP::CODE_PAGE; c += 512)
@@ -894,7 +907,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
               cp_async16(dst + SP::V_OFF + j * SP::CODE_PAGE + c, vs + c);
 #pragma unroll
             for (int c = 0; c < SP::SCALE_PAGE; c += 512)
-              cp_async16(dst + SP::S_OFF + j * SP::SCALE_PAGE + c, ss + c);
+              if (c < scale_page) cp_async16(dst + SP::S_OFF + j * SP::SCALE_PAGE + c, ss + c);
           }
           cp_async_arrive(full);
         }
@@ -1150,7 +1163,7 @@ using namespace fq;
 extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void* stream) {
   if (!pools || !args) return FQ_ERR_BAD_ARG;
   if (!pools->k_codes || !pools->v_codes || !pools->scales) return FQ_ERR_BAD_ARG;
-  if (pools->k_groups != 1 || pools->scale_bf16) return FQ_ERR_UNSUPPORTED;
+  if (pools->k_groups != 1) return FQ_ERR_UNSUPPORTED;   // sub-head K groups: not in the decode yet
   if (pools->head_dim != 64 && pools->head_dim != 128) return FQ_ERR_UNSUPPORTED;
   if (pools->bits != 2 && pools->bits != 4) return FQ_ERR_UNSUPPORTED;
   const fq_decode_args& a = *args;
