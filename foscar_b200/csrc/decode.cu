@@ -264,7 +264,7 @@ __device__ __noinline__ void merge_unit_partials(const DecodeParams& P, int d, i
 // unpack V into shared memory, fold the scales into the raw scores, softmax, write the P rows,
 // and (one of its own tiles later) add the tile's O to its accumulators. The group keeps its own
 // running (m, l, c, O); the four groups are merged once per work item.
-template <int BITS, int D, int GP>
+template <int BITS, int D, int GP, int KG>
 __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem, uint32_t smem0,
                                             uint32_t tmem, const Bars& bars,
                                             volatile int* abort_flag, const ItemRange items,
@@ -291,12 +291,12 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   float* red_sum = reinterpret_cast<float*>(smem + SP::RED_OFF + 256 * G);    // [wg][warp][16]
   // this warp's copy of the item's per-head constants: sm_scale*log2e*q_descale, and that times
   // the sum of the head's query values
-  float* head_k = reinterpret_cast<float*>(smem + SP::RED_OFF + 512 * G) + warp * 16;
+  float* head_k = reinterpret_cast<float*>(smem + SP::HEADK_OFF) + warp * 24;
   // written per work item by thread 0 of group 0: {pieces, request, KV head, head tile} of the
   // unit this CTA must merge (pieces 0: none)
-  volatile int* merge_info = reinterpret_cast<volatile int*>(smem + SP::RED_OFF + 768 * G);
+  volatile int* merge_info = reinterpret_cast<volatile int*>(smem + SP::INFO_OFF);
   const volatile float* head_const =
-      reinterpret_cast<const volatile float*>(smem + SP::RED_OFF + 768 * G + 32);  // [2][16]
+      reinterpret_cast<const volatile float*>(smem + SP::HEADC_OFF);  // [2][24]
   constexpr float LN2 = 0.6931471805599453f;
 
   // pool-wide P-scale exponent from the count table: lp = 135 - max(top nonzero bin, 27)
@@ -351,7 +351,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     if (nt > 0) {
       const int qb = qi & 1;
       mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status, 14, wprof);
-      if (lane < 16) head_k[lane] = head_const[qb * 16 + lane];
+      if (lane < 24) head_k[lane] = head_const[qb * 24 + lane];
       ++qi;
     }
     __syncwarp();
@@ -442,10 +442,20 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       FQ_STAMP(9);
       // the tokens' records; then the ring stage goes back to the producers
       float sk[NT], zk[NT], sv[NT], zv[NT];
+      float sk1 = 0.f, zk1 = 0.f;   // the second K group's pair (KG == 2)
 #pragma unroll
       for (int u = 0; u < NT; ++u) {
         const int row = u * TILE + t;
-        if (!P.p.scale_bf16) {
+        if constexpr (KG == 2) {   // K ring: (s, z) of both groups; V ring after the page's K ring
+          uint32_t k0, k1, vr;
+          const uint32_t slot = stage + SP::S_OFF + (row >> 6) * SP::SCALE_PAGE;
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(k0), "=r"(k1)
+                       : "r"(slot + (row & 63) * 8));
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(vr) : "r"(slot + 8 * PAGE + (row & 63) * 4));
+          sk[u] = __uint_as_float(k0 << 16); zk[u] = __uint_as_float(k0 & 0xFFFF0000u);
+          sk1 = __uint_as_float(k1 << 16); zk1 = __uint_as_float(k1 & 0xFFFF0000u);
+          sv[u] = __uint_as_float(vr << 16); zv[u] = __uint_as_float(vr & 0xFFFF0000u);
+        } else if (!P.p.scale_bf16) {
           asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
                        : "=f"(sk[u]), "=f"(zk[u]), "=f"(sv[u]), "=f"(zv[u])
                        : "r"(stage + SP::S_OFF + row * 16));
@@ -464,8 +474,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       // ---- raw scores: columns [0, GP) for the lane's first token, [8, 8 + GP) for its second
       mbar_wait(bars.s_done(wg), n & 1, abort_flag, status, 12, wprof);
       tc_fence_after();
-      uint32_t raw[NT == 2 ? 16 : GP];
-      if constexpr (NT == 2) tmem_ld16(s_src, raw);
+      uint32_t raw[(NT == 2 || KG == 2) ? 16 : GP];
+      if constexpr (NT == 2 || KG == 2) tmem_ld16(s_src, raw);
       else if constexpr (GP == 4) tmem_ld4(s_src, raw);
       else tmem_ld8(s_src, raw);
       tmem_ld_wait();
@@ -498,8 +508,13 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         if (!valid) { wsc[u] = 0.f; zv[u] = 0.f; }
 #pragma unroll
         for (int h = 0; h < GP; ++h) {
-          const float xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[8 * u + h]),
-                                head_k[8 + h] * zk[u]);
+          float xv;
+          if constexpr (KG == 2)
+            xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[h]),
+                      fmaf(head_k[h] * (sk1 * 512.f), __uint_as_float(raw[8 + h]),
+                           fmaf(head_k[8 + h], zk[u], head_k[16 + h] * zk1)));
+          else
+            xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[8 * u + h]), head_k[8 + h] * zk[u]);
           x[u][h] = valid ? xv : -INFINITY;
           over = fmaxf(over, x[u][h] - m[h]);
         }
@@ -723,8 +738,9 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 
 }  // namespace
 
-template <int BITS, int D, int GP>
+template <int BITS, int D, int GP, int KG>
 __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeParams P) {
+  static_assert(KG == 1 || (KG == 2 && D == 128), "K groups of 64 channels at head_dim 128");
   static_assert(D == 64 || D == 128, "this build tiles head_dim 64 and 128");
   using SP = SmemPlan<BITS, D>;
   using TP = TmemPlan<D>;
@@ -806,10 +822,13 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           uint4 v = make_uint4(0, 0, 0, 0);
           // At two tokens per lane rows 0-7 carry the heads against the first token's half of
           // the K row (bytes 0-63) and rows 8-15 the same heads against the second's (64-127).
-          const int hl = w.ht * 8 + (SP::PAIR ? (r & 7) : r);  // head inside the KV head's group
+          // With two K groups of 64 channels (one token per lane) the same split of the rows
+          // yields each group's partial product in its own S column.
+          constexpr bool SPLIT = SP::PAIR || KG == 2;
+          const int hl = w.ht * 8 + (SPLIT ? (r & 7) : r);  // head inside the KV head's group
           const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
-          const bool live = (SP::PAIR || r < 8) && hl < P.heads_per_kv;
-          const bool mine = SP::PAIR ? ((r < 8) == (cc < 4)) : 16 * cc < D;
+          const bool live = (SPLIT || r < 8) && hl < P.heads_per_kv;
+          const bool mine = SPLIT ? ((r < 8) == (cc < 4)) : 16 * cc < D;
           const int src = SP::PAIR ? (cc & 3) : cc;
           float qsum = 0.f;
           if (live && mine) {
@@ -834,8 +853,9 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           }
           *reinterpret_cast<uint4*>(smem + SP::Q_OFF + qb * SP::Q_BYTES + r * 128 +
                                     ((cc ^ (r & 7)) << 4)) = v;
-          if (j < 2) {
+          if (j < 2 || KG == 2) {
             // the row's eight chunks sit in eight neighbouring lanes: per-head constants
+            // (rows 8-15: the second K group's query sums)
             qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, 1);
             qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, 2);
             qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, 4);
@@ -847,9 +867,13 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
                   scale *= __ldg(P.a.q_descale + w.b * P.a.q_descale_stride_b +
                                  head * P.a.q_descale_stride_h);
               }
-              float* hc = reinterpret_cast<float*>(smem + SP::RED_OFF + 768 * G + 32) + qb * 16;
-              hc[r] = scale;
-              hc[8 + r] = scale * qsum;
+              float* hc = reinterpret_cast<float*>(smem + SP::HEADC_OFF) + qb * 24;
+              if (r < 8) {
+                hc[r] = scale;
+                hc[8 + r] = scale * qsum;
+              } else {
+                hc[16 + (r - 8)] = scale * qsum;
+              }
             }
           }
         }
@@ -896,7 +920,9 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
             const uint8_t* ks = P.p.k_codes + blk * SP::CODE_PAGE + 16 * lane;
             const uint8_t* vs = P.p.v_codes + blk * SP::CODE_PAGE + 16 * lane;
             // records: 16 B per token in an f32 pool, 8 B in a bf16 pool (same slot in the ring)
-            const int scale_page = P.p.scale_bf16 ? SP::SCALE_PAGE / 2 : SP::SCALE_PAGE;
+            // (with two K groups: 8 B of K pairs per token, then 4 B of V pairs per token)
+            const int scale_page =
+                KG == 2 ? 12 * PAGE : (P.p.scale_bf16 ? SP::SCALE_PAGE / 2 : SP::SCALE_PAGE);
             const uint8_t* ss = static_cast<const uint8_t*>(P.p.scales) + blk * scale_page +
                                 16 * lane;
 #pragma unroll
@@ -907,7 +933,8 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
               cp_async16(dst + SP::V_OFF + j * SP::CODE_PAGE + c, vs + c);
 #pragma unroll
             for (int c = 0; c < SP::SCALE_PAGE; c += 512)
-              if (c < scale_page) cp_async16(dst + SP::S_OFF + j * SP::SCALE_PAGE + c, ss + c);
+              if (c + 16 * lane < scale_page)
+                cp_async16(dst + SP::S_OFF + j * SP::SCALE_PAGE + c, ss + c);
           }
           cp_async_arrive(full);
         }
@@ -987,7 +1014,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ workers
-    worker_role<BITS, D, GP>(P, smem, smem0, tmem, bars, abort_flag, items, wprof);
+    worker_role<BITS, D, GP, KG>(P, smem, smem0, tmem, bars, abort_flag, items, wprof);
   }
 
   tc_fence_before();
@@ -1112,7 +1139,7 @@ static int device_sm_count() {
   return sms > 0 ? sms : 148;
 }
 
-template <int BITS, int D, int GP>
+template <int BITS, int D, int GP, int KG = 1>
 static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   using SP = SmemPlan<BITS, D>;
   int stages = SP::max_ring_stages();
@@ -1126,7 +1153,7 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   P.tile_tokens = SP::TT;
   const int smem = SP::RING_OFF + stages * SP::STAGE + 1024;
   static bool configured[64] = {};  // per (BITS, D, GP) instantiation and device
-  auto kernel = decode_kernel<BITS, D, GP>;
+  auto kernel = decode_kernel<BITS, D, GP, KG>;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -1163,7 +1190,10 @@ using namespace fq;
 extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void* stream) {
   if (!pools || !args) return FQ_ERR_BAD_ARG;
   if (!pools->k_codes || !pools->v_codes || !pools->scales) return FQ_ERR_BAD_ARG;
-  if (pools->k_groups != 1) return FQ_ERR_UNSUPPORTED;   // sub-head K groups: not in the decode yet
+  // sub-head K groups: 64-channel groups at head_dim 128 (bf16 pair rings)
+  if (pools->k_groups != 1 &&
+      !(pools->k_groups == 2 && pools->head_dim == 128 && pools->scale_bf16))
+    return FQ_ERR_UNSUPPORTED;
   if (pools->head_dim != 64 && pools->head_dim != 128) return FQ_ERR_UNSUPPORTED;
   if (pools->bits != 2 && pools->bits != 4) return FQ_ERR_UNSUPPORTED;
   const fq_decode_args& a = *args;
@@ -1193,6 +1223,11 @@ extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void
   if (pools->head_dim == 64) {
     if (pools->bits == 2) return gp == 4 ? launch_decode<2, 64, 4>(P, s) : launch_decode<2, 64, 8>(P, s);
     return gp == 4 ? launch_decode<4, 64, 4>(P, s) : launch_decode<4, 64, 8>(P, s);
+  }
+  if (pools->k_groups == 2) {
+    if (pools->bits == 2)
+      return gp == 4 ? launch_decode<2, 128, 4, 2>(P, s) : launch_decode<2, 128, 8, 2>(P, s);
+    return gp == 4 ? launch_decode<4, 128, 4, 2>(P, s) : launch_decode<4, 128, 8, 2>(P, s);
   }
   if (pools->bits == 2) return gp == 4 ? launch_decode<2, 128, 4>(P, s) : launch_decode<2, 128, 8>(P, s);
   return gp == 4 ? launch_decode<4, 128, 4>(P, s) : launch_decode<4, 128, 8>(P, s);

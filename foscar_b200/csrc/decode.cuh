@@ -58,9 +58,13 @@ struct SmemPlan {
   static constexpr int XCHG_BYTES = TILE * 8 * 4 + 128;   // one group's accumulators + (m,l,c)
   static constexpr int XCHG_OFF = P_OFF + WORKER_GROUPS * P_BYTES;
   static constexpr int RED_OFF = XCHG_OFF + WORKER_GROUPS * XCHG_BYTES;  // reductions
-  // column maxima 256 B and sums 256 B per group, then 64 B of per-head constants per warp,
-  // then two 16-byte merge notices, then two items' per-head constants (2 x 64 B)
-  static constexpr int RED_BYTES = (512 * WORKER_GROUPS + 64 * 4 * WORKER_GROUPS + 32 + 128 + 1023) / 1024 * 1024;
+  // column maxima 256 B and sums 256 B per group; then 96 B of per-head constants per worker
+  // warp (score scale, and score scale times the query sum of each K group); two 16-byte merge
+  // notices; two items' per-head constants as the producer leaves them (2 x 96 B)
+  static constexpr int HEADK_OFF = RED_OFF + 512 * WORKER_GROUPS;
+  static constexpr int INFO_OFF = HEADK_OFF + 96 * 4 * WORKER_GROUPS;
+  static constexpr int HEADC_OFF = INFO_OFF + 32;
+  static constexpr int RED_BYTES = (HEADC_OFF + 192 - RED_OFF + 1023) / 1024 * 1024;
   static constexpr int BAR_OFF = RED_OFF + RED_BYTES;
   static constexpr int BAR_BYTES = 2048;   // barriers, then flags and diagnostics
   static constexpr int RING_OFF = (BAR_OFF + BAR_BYTES + 1023) / 1024 * 1024;

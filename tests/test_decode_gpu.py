@@ -20,13 +20,13 @@ MAX_ABS, MEAN_ABS, LSE_ABS = 2e-2, 2e-3, 5e-2
 
 def _run_case(bits, d, hq, hkv, seq, *, kv_splits=None, host_lens=True, outliers=False,
               q_scale=1.0, lse=True, q_descale=False, out_dtype=torch.bfloat16, seed=0,
-              reduction="auto", max_kv_len=None, scale_dtype=None):
+              reduction="auto", max_kv_len=None, scale_dtype=None, k_quant=None):
     from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
     batch = len(seq)
     indptr, indices, slots, npages = paged_batch(seq, seed=seed)
     k, v = make_kv(len(slots), hkv, d, seed=seed, outliers=outliers)
     layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device="cuda",
-                                  scale_dtype=scale_dtype)
+                                  scale_dtype=scale_dtype, k_quant=k_quant)
     cache = layout.allocate(npages + 1)
     cache.append(k, v, torch.from_numpy(slots).cuda())
     q = make_q(batch, hq, d, seed=seed + 1, scale=q_scale)
@@ -85,6 +85,15 @@ def test_bf16_scale_pools(bits, d):
     """Scale records stored as bf16 pairs (8 bytes a token): the decode reads the pool's own
     rounded values, as the oracle's dequantize does."""
     _run_case(bits, d, 32, 8, [1, 64, 130, 3000], seed=11, scale_dtype=torch.bfloat16)
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (16, 2)])
+def test_k_groups_of_64_channels(bits, hq, hkv):
+    """K quantized per token over 64-channel groups (two (s, z) pairs per token, bf16 rings):
+    each group's partial score comes out of its own S column."""
+    _run_case(bits, 128, hq, hkv, [1, 64, 130, 3000, 700], seed=13, k_quant=("token", 64),
+              outliers=True)
 
 
 @pytest.mark.parametrize("bits", [2, 4])
