@@ -301,6 +301,92 @@ def run_cache_op(args, cfg):
                       "device_status": cache.last_status()}))
 
 
+def run_sequence_split(args, cfg):
+    """One batch, every context split page-aligned over the ranks: each rank caches and decodes
+    its token range, one NCCL all_gather brings the (o, lse) pairs into local memory, a local
+    kernel merges them. Strong scaling: `value` is the batch's tokens/s at N GPUs."""
+    import torch.distributed as dist
+    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout, parallel
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    seq = seq_lens_of(cfg, args.seed)
+    ranges = [parallel.split_sequence(int(n), rank, world) for n in seq]
+    mine = np.array([b - a for a, b in ranges], dtype=np.int64)
+    pages = [-(-int(n) // PAGE) for n in mine]
+    total = max(sum(pages), 1)
+    rng = np.random.default_rng(args.seed + 1 + rank)
+    indices = rng.permutation(total).astype(np.int32)
+    indptr = np.concatenate([[0], np.cumsum(pages)]).astype(np.int32)
+    layout = QuantKVLayout.create(bits=cfg["bits"], head_dim=cfg["d"], num_kv_heads=cfg["hkv"],
+                                  device=device)
+    cache = layout.allocate(total)
+    g = torch.Generator(device=device).manual_seed(args.seed + rank)
+    for b, n in enumerate(mine):
+        n = int(n)
+        if n == 0:
+            continue
+        k = torch.randn(n, cfg["hkv"], cfg["d"], device=device, generator=g)
+        v = torch.randn(n, cfg["hkv"], cfg["d"], device=device, generator=g)
+        t = torch.arange(n, device=device)
+        pg = torch.from_numpy(indices[indptr[b]:indptr[b + 1]]).to(device).long()
+        cache.append(k.to(torch.bfloat16), v.to(torch.bfloat16), pg[t // PAGE] * PAGE + t % PAGE)
+    q = (torch.randn(cfg["batch"], cfg["hq"], cfg["d"], device=device,
+                     generator=torch.Generator(device=device).manual_seed(args.seed))
+         * cfg["q_scale"]).clamp(-448, 448).to(torch.float8_e4m3fn)
+    w = PagedDecodeWrapper(torch.empty(256 << 20, dtype=torch.uint8, device=device))
+    w.plan(torch.from_numpy(indptr).to(device), torch.from_numpy(indices).to(device),
+           torch.from_numpy(mine.astype(np.int32)), cfg["hq"], layout,
+           sm_scale=cfg["d"] ** -0.5 / cfg["q_scale"], o_data_type=torch.float32)
+    out = torch.empty(cfg["batch"], cfg["hq"], cfg["d"], dtype=torch.bfloat16, device=device)
+
+    def step():
+        if world > 1:
+            parallel.sequence_split_decode(w, q, cache, out=out)
+        else:
+            w.run(q, cache, out=torch.empty(cfg["batch"], cfg["hq"], cfg["d"], device=device))
+
+    for _ in range(args.warmup):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    if rank == 0:
+        peak, kind = measured_peak()
+        moved = algorithmic_bytes(cfg, seq)
+        gbs = moved / ms / 1e6
+        print(json.dumps({
+            "metric": "decode_tokens_per_s", "value": cfg["batch"] / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "us_per_step": ms * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": f"e4m3 x int{cfg['bits']} codes, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"{args.workload}, every context split over {world} GPUs "
+                                   f"(page-aligned ranges; all_gather of (o, lse) + local merge)",
+                       "parallelism": f"sequence split x{world}"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak * world, "unit": "GB/s",
+                         "frac": gbs / (peak * world), "of": kind, "traffic": None,
+                         "algorithmic_bytes": moved},
+            "device_status": w.last_status()}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def workload_config(args, cfg, seq):
     return {"workload": f"{args.workload}: INT{cfg['bits']} paged GQA decode, batch {cfg['batch']}, "
                         f"{cfg['hq']}/{cfg['hkv']} heads, head_dim {cfg['d']}, page 64, seq_lens "
@@ -321,6 +407,9 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=16384,
                     help="KV tokens in the CPU baseline's bounded sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--split", default="none", choices=["none", "sequence"],
+                    help="sequence: ONE batch whose every context is split page-aligned over the "
+                         "ranks (strong scaling; one all_gather of (o, lse) per step)")
     ap.add_argument("--op", default="decode", choices=["decode", "append", "dequantize"],
                     help="decode: the headline step. append / dequantize: the cache writer or the "
                          "read-back kernel alone on a slice of the workload, as GB/s")
@@ -332,6 +421,8 @@ def main():
         return run_reference(args, cfg)
     if args.op != "decode":
         return run_cache_op(args, cfg)
+    if args.split == "sequence":
+        return run_sequence_split(args, cfg)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
