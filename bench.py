@@ -222,7 +222,16 @@ def run_reference(args, cfg):
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     seq = seq_lens_of(cfg, args.seed)
-    step, tokens, reqs = cpu_reference_step(cfg, args.seed, args.cpu_tokens)
+    # Size the sample so that warm-up plus timed steps end within about three minutes: a probe
+    # on 2048 tokens gives the host's rate, the cost being linear in KV tokens.
+    probe, probe_tokens, _ = cpu_reference_step(cfg, args.seed, 2048)
+    probe()
+    t0 = time.perf_counter()
+    probe()
+    rate = probe_tokens / max(time.perf_counter() - t0, 1e-6)
+    budget = int(rate * 180.0 / (args.steps + args.warmup))
+    step, tokens, reqs = cpu_reference_step(cfg, args.seed,
+                                            max(1024, min(args.cpu_tokens, budget)))
     for _ in range(args.warmup):
         step()
     t0 = time.perf_counter()

@@ -99,3 +99,25 @@ def test_uniform_planner_behaviour():
     assert lib.fq_plan_splits(1, 8, 1, 256, 2, 128, 148) == 1          # too short to split
     assert lib.fq_plan_splits(0, 8, 1, 256, 2, 128, 148) == _lib.ERR_BAD_ARG
     assert lib.fq_workspace_bytes(4, 2, 32, 128) == 4 * 4 * 2 * 32 * 130
+
+
+def test_worklist_tiles_hold_256_tokens_at_head_dim_64():
+    """At head_dim 64 a tile is 256 tokens (two per tensor-memory lane): the planner's tile
+    ranges cover ceil(len / 256) tiles of every unit."""
+    lib = _lib.load()
+    lens = np.array([1, 256, 257, 5000, 100000], dtype=np.int32)
+    hkv, ht, ctas = 8, 1, 148
+    words = int(lib.fq_worklist_words(len(lens), hkv, ht, ctas))
+    work = np.zeros(words, dtype=np.int32)
+    counts = np.zeros(len(lens) * hkv * ht, dtype=np.int32)
+    n = lib.fq_plan_worklist(lens.ctypes.data, len(lens), hkv, ht, ctas, 64, work.ctypes.data,
+                             words, counts.ctypes.data, 2, 64)
+    assert n > 0
+    rows = work[work[3]:work[3] + 8 * n].reshape(n, 8)
+    covered = {}
+    for b, kvh, t, t0, t1, slot, _, _ in rows:
+        covered[(b, kvh)] = covered.get((b, kvh), 0) + (t1 - t0)
+    for b, l in enumerate(lens):
+        for kvh in range(hkv):
+            assert covered[(b, kvh)] == -(-int(l) // 256)
+    assert _lib.tile_tokens(64) == 256 and _lib.tile_tokens(128) == 128

@@ -185,6 +185,63 @@ def test_in_kernel_merge_equals_merge_launch(kv_splits):
         assert torch.equal(out, results[0][0]) and torch.equal(lse, results[0][1])
 
 
+def test_empty_request_in_a_batch():
+    """A request of length 0 next to live ones: its rows come out zero with lse = -inf, the
+    others are unaffected (uniform and balanced plans)."""
+    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
+    seq = [300, 0, 70]
+    indptr, indices, slots, npages = paged_batch(seq, seed=2)
+    k, v = make_kv(len(slots), 8, 128, seed=2)
+    layout = QuantKVLayout.create(bits=2, head_dim=128, num_kv_heads=8, device="cuda")
+    cache = layout.allocate(npages + 1)
+    cache.append(k, v, torch.from_numpy(slots).cuda())
+    q = make_q(3, 32, 128)
+    live = [0, 2]
+    for lens_on_host, splits in ((True, None), (False, 2)):
+        w = PagedDecodeWrapper(torch.empty(16 << 20, dtype=torch.uint8, device="cuda"))
+        lens = torch.tensor(seq, dtype=torch.int32)
+        w.plan(torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda(),
+               lens if lens_on_host else lens.cuda(), 32, layout, kv_splits=splits)
+        out = torch.full((3, 32, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+        lse = torch.full((3, 32), float("nan"), device="cuda")
+        w.run(q, cache, out=out, lse=lse)
+        torch.cuda.synchronize()
+        assert w.last_status() == 0
+        assert torch.all(out[1] == 0) and torch.all(torch.isneginf(lse[1]))
+        assert torch.isfinite(out[0].float()).all() and torch.isfinite(out[2].float()).all()
+        assert torch.isfinite(lse[0]).all() and torch.isfinite(lse[2]).all()
+        # the live rows equal a batch without the empty request
+        w2 = PagedDecodeWrapper(torch.empty(16 << 20, dtype=torch.uint8, device="cuda"))
+        keep = np.concatenate([indices[indptr[0]:indptr[1]], indices[indptr[2]:indptr[3]]])
+        ip2 = np.array([0, indptr[1] - indptr[0], indptr[1] - indptr[0] + indptr[3] - indptr[2]],
+                       dtype=np.int32)
+        w2.plan(torch.from_numpy(ip2).cuda(), torch.from_numpy(keep.astype(np.int32)).cuda(),
+                torch.tensor([300, 70], dtype=torch.int32), 32, layout, kv_splits=1)
+        ref = w2.run(q[live].contiguous(), cache)
+        torch.cuda.synchronize()
+        assert (out[live].float() - ref.float()).abs().max().item() <= 1e-2
+
+
+def test_pdl_flag_does_not_change_the_result():
+    """enable_pdl only changes how the launch is ordered after the one before it."""
+    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
+    seq = [2000, 130]
+    indptr, indices, slots, npages = paged_batch(seq, seed=21)
+    k, v = make_kv(len(slots), 8, 128, seed=21)
+    layout = QuantKVLayout.create(bits=4, head_dim=128, num_kv_heads=8, device="cuda")
+    cache = layout.allocate(npages)
+    cache.append(k, v, torch.from_numpy(slots).cuda())
+    q = make_q(2, 32, 128)
+    w = PagedDecodeWrapper(torch.empty(16 << 20, dtype=torch.uint8, device="cuda"))
+    w.plan(torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda(),
+           torch.tensor(seq, dtype=torch.int32), 32, layout)
+    a = w.run(q, cache, enable_pdl=True)
+    b = w.run(q, cache, enable_pdl=False)
+    c = w.run(q, cache, enable_pdl=True)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b) and torch.equal(a, c) and w.last_status() == 0
+
+
 def test_bad_page_id_sets_status_without_fault():
     from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
     layout = QuantKVLayout.create(bits=2, head_dim=128, num_kv_heads=2, device="cuda")
