@@ -349,9 +349,15 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     // instead of living in 16 registers of every thread.
     __syncwarp();   // the warp's reads of the previous item's values are over
     if (nt > 0) {
-      const int qb = qi & 1;
-      mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status, 14, wprof);
-      if (lane < 24) head_k[lane] = head_const[qb * 24 + lane];
+      // Only a group with a tile in the item waits for the item's query stage: the stage cannot
+      // be restaged before that group's K row has gone through the S MMA. A group without a tile
+      // would have nothing holding the producer back, and a phase-parity wait that falls two
+      // stagings behind never returns.
+      if (mine < it0 + nt) {
+        const int qb = qi & 1;
+        mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status, 14, wprof);
+        if (lane < 24) head_k[lane] = head_const[qb * 24 + lane];
+      }
       ++qi;
     }
     __syncwarp();
@@ -615,7 +621,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       c[h] = (gs[8 + h] + gs[24 + h]) + (gs[40 + h] + gs[56 + h]);
     }
     {   // every group leaves its state in shared memory
-      float* xo = reinterpret_cast<float*>(smem + SP::XCHG_OFF + wg * SP::XCHG_BYTES);
+      float* xo = reinterpret_cast<float*>(smem + SP::XCHG_OFF + wg * SP::XCHG_STRIDE);
       float* xmeta = xo + TILE * 8;
 #pragma unroll
       for (int h = 0; h < GP; ++h) xo[t * 8 + h] = oacc[h];
@@ -641,7 +647,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 #pragma unroll 1
         for (int g = 0; g < G; ++g) {
           const float* xo = reinterpret_cast<const float*>(smem + SP::XCHG_OFF +
-                                                           g * SP::XCHG_BYTES);
+                                                           g * SP::XCHG_STRIDE);
           const float* xmeta = xo + TILE * 8;
           const float m1 = xmeta[h], l1 = xmeta[8 + h], c1 = xmeta[16 + h];
           // at two tokens per lane, channel t's sum is split over rows t and t + 64
@@ -1148,6 +1154,11 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
     const int want = atoi(env);
     if (want >= WORKER_GROUPS && want < stages) stages = want;
   }
+  // An even ring: the two producers take alternate tiles, so with an even stage count a stage
+  // always belongs to the same producer, which then sees every release of it. With an odd count
+  // a producer meets a stage every second lap only and waits on a phase parity that an older,
+  // still outstanding release also satisfies (a 5-stage ring hung on exactly that).
+  stages &= ~1;
   if (stages < WORKER_GROUPS) return FQ_ERR_UNSUPPORTED;  // a group steps the ring by one lap at most
   P.ring_stages = stages;
   P.tile_tokens = SP::TT;

@@ -55,9 +55,14 @@ struct SmemPlan {
   static constexpr int VOP_OFF = 0;
   static constexpr int Q_OFF = VOP_OFF + WORKER_GROUPS * VOP_STAGE;
   static constexpr int P_OFF = Q_OFF + 2 * Q_BYTES;
-  static constexpr int XCHG_BYTES = TILE * 8 * 4 + 128;   // one group's accumulators + (m,l,c)
-  static constexpr int XCHG_OFF = P_OFF + WORKER_GROUPS * P_BYTES;
-  static constexpr int RED_OFF = XCHG_OFF + WORKER_GROUPS * XCHG_BYTES;  // reductions
+  // A group's state at the end of a work item (accumulators + (m,l,c), 4224 bytes) goes into the
+  // group's own V operand stage: its last PV MMA is complete by then, every group has read the
+  // states before the item's closing barrier, and V rows are next written after it.
+  static constexpr int XCHG_BYTES = TILE * 8 * 4 + 128;
+  static constexpr int XCHG_OFF = VOP_OFF;
+  static constexpr int XCHG_STRIDE = VOP_STAGE;
+  static_assert(XCHG_BYTES <= VOP_STAGE, "a group's state must fit its V stage");
+  static constexpr int RED_OFF = P_OFF + WORKER_GROUPS * P_BYTES;  // reductions
   // column maxima 256 B and sums 256 B per group; then 96 B of per-head constants per worker
   // warp (score scale, and score scale times the query sum of each K group); two 16-byte merge
   // notices; two items' per-head constants as the producer leaves them (2 x 96 B)

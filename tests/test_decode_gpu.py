@@ -222,6 +222,41 @@ def test_empty_request_in_a_batch():
         assert (out[live].float() - ref.float()).abs().max().item() <= 1e-2
 
 
+@pytest.mark.parametrize("bits,d", [(4, 64), (2, 128)])
+def test_many_single_tile_items(bits, d):
+    """Hundreds of one-tile work items per CTA: most worker groups have no tile in most items,
+    while the producer runs items ahead. Repeated launches must neither time out (status bit
+    0x10) nor differ."""
+    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
+    rng = np.random.default_rng(5)
+    seq = [int(x) for x in rng.integers(1, 200, 320)]
+    hq, hkv = 64, 8
+    indptr, indices, slots, npages = paged_batch(seq, seed=5)
+    k, v = make_kv(len(slots), hkv, d, seed=5)
+    layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device="cuda")
+    cache = layout.allocate(npages)
+    cache.append(k, v, torch.from_numpy(slots).cuda())
+    q = make_q(len(seq), hq, d)
+    w = PagedDecodeWrapper(torch.empty(64 << 20, dtype=torch.uint8, device="cuda"))
+    w.plan(torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda(),
+           torch.tensor(seq, dtype=torch.int32), hq, layout)
+    first = None
+    for _ in range(30):
+        out = w.run(q, cache)
+        if first is None:
+            first = out.clone()
+    torch.cuda.synchronize()
+    assert w.last_status() == 0, w.last_status()
+    assert torch.equal(out, first)
+    pools = cpu_twin(cache, k, v, slots)
+    some = [0, 17, 319]
+    for b in some:
+        want, _ = oracle_outputs(pools, q.cpu()[b:b + 1], indptr[b:b + 2] - indptr[b],
+                                 indices[indptr[b]:indptr[b + 1]], [seq[b]], d ** -0.5)
+        err = (out[b].float().cpu() - want[0]).abs()
+        assert err.max().item() <= MAX_ABS, (b, err.max().item())
+
+
 def test_pdl_flag_does_not_change_the_result():
     """enable_pdl only changes how the launch is ordered after the one before it."""
     from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
