@@ -257,6 +257,15 @@ def test_many_single_tile_items(bits, d):
         assert err.max().item() <= MAX_ABS, (b, err.max().item())
 
 
+@pytest.mark.parametrize("stages", ["4", "5", "6", "7"])
+def test_shallow_rings(stages, monkeypatch):
+    """The shared-memory ring at its smallest depths (the library rounds an odd request down):
+    same results, no timeout. INT4 at head_dim 64 runs at six stages in production."""
+    monkeypatch.setenv("FOSCAR_B200_RING_STAGES", stages)
+    _run_case(2, 128, 32, 8, [9000, 4097, 130], seed=31)
+    _run_case(4, 64, 64, 8, [9000, 300], seed=32)
+
+
 def test_pdl_flag_does_not_change_the_result():
     """enable_pdl only changes how the launch is ordered after the one before it."""
     from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
