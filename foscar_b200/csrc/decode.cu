@@ -33,6 +33,20 @@
 // Every role walks the same list of work items, so the pipeline never drains inside an item.
 // Byte-expansion yields channels in a fixed permuted order; Q is loaded in that order and O is
 // stored through it, so no per-element fix-up exists anywhere.
+//
+// Variants of the same code (template parameters):
+//   head_dim 64   a tile is 256 tokens, two per lane (t and 128 + t): their K rows side by side
+//                 in the lane's 128-byte tensor-memory row, their V rows side by side in one
+//                 shared-memory row; query rows 0-7 act on bytes 0-63 and rows 8-15 on bytes
+//                 64-127, so one chain of S MMAs gives both tokens' scores (columns h, 8 + h);
+//                 the PV MMA runs once per token set into its own 16 accumulator columns.
+//   KG == 2       K quantized over two 64-channel groups (head_dim 128): the same split of the
+//                 query rows puts each group's partial score in its own column.
+//   scale pools   f32 (16 bytes a token) or bf16 pairs (8 bytes), chosen at run time.
+// Split units are merged inside this launch: a piece that wrote partials is counted in on its
+// unit's counter one tile into the CTA's next item (or after its last), and the CTA that
+// completes the count merges the unit (merge_unit_partials).
+// The ring's stage count is kept even, so that each stage belongs to one of the two producers.
 #include "decode.cuh"
 
 #ifdef FQ_WAIT_PROFILE
