@@ -60,7 +60,7 @@ _PROTOTYPES = {
     "fq_decode_split_static": (C.c_int, [C.POINTER(Pools), C.POINTER(DecodeArgs), _P]),
     "fq_merge": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _F32, _P, _I32,
                            _P, _P]),
-    "fq_merge_states": (C.c_int, [_P, _P, _I32, _I32, _I32, _I32, _P, _I32, _P, _P]),
+    "fq_merge_states": (C.c_int, [_P, _P, _I32, _I32, _I32, _I32, _P, _I32, _P, _I64, _I64, _P]),
     "fq_plan_splits": (C.c_int, [_I32, _I32, _I32, _I32, _I32, _I32, _I32]),
     "fq_plan_worklist": (C.c_int, [_P, _I32, _I32, _I32, _I32, _I32, _P, _I32, _P, _I32, _I32]),
     "fq_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),

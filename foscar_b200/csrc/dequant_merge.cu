@@ -173,18 +173,18 @@ __global__ void merge_kernel(const float* __restrict__ o_partial,
 
 // Merge of attention states held as (normalised o, natural-log lse) from R sequence shards.
 __global__ void merge_states_kernel(const float* __restrict__ o, const float* __restrict__ lse_in,
-                                    int shards, long long rows, int d, void* out, int out_dtype,
-                                    float* lse) {
+                                    int shards, long long rows, int d, long long o_stride,
+                                    long long lse_stride, void* out, int out_dtype, float* lse) {
   const int row = blockIdx.x;
   const int c = threadIdx.x;
   float L = -INFINITY;
-  for (int r = 0; r < shards; ++r) L = fmaxf(L, __ldg(lse_in + r * rows + row));
+  for (int r = 0; r < shards; ++r) L = fmaxf(L, __ldg(lse_in + (r * rows + row) * lse_stride));
   float den = 0.f, acc = 0.f;
   if (L > -INFINITY) {
     for (int r = 0; r < shards; ++r) {
-      const float w = expf(__ldg(lse_in + r * rows + row) - L);
+      const float w = expf(__ldg(lse_in + (r * rows + row) * lse_stride) - L);
       den += w;
-      if (c < d) acc += w * __ldg(o + (r * rows + row) * d + c);
+      if (c < d) acc += w * __ldg(o + (r * rows + row) * o_stride + c);
     }
   }
   const bool live = den > 0.f;
@@ -250,7 +250,7 @@ extern "C" int fq_merge(const float* o_partial, const float* l_partial, const fl
 extern "C" int fq_merge_states(const float* o_shards, const float* lse_shards,
                                int32_t num_shards, int32_t batch, int32_t num_qo_heads,
                                int32_t head_dim, void* out, int32_t out_dtype, float* lse,
-                               void* stream) {
+                               int64_t o_row_stride, int64_t lse_stride, void* stream) {
   if (!o_shards || !lse_shards || !out || num_shards < 1) return FQ_ERR_BAD_ARG;
   if (batch <= 0 || num_qo_heads <= 0 || head_dim <= 0 || head_dim > 1024) return FQ_ERR_BAD_ARG;
   if (out_dtype < 0 || out_dtype > 2) return FQ_ERR_BAD_ARG;
@@ -258,6 +258,7 @@ extern "C" int fq_merge_states(const float* o_shards, const float* lse_shards,
   fq::merge_states_kernel<<<batch * num_qo_heads, threads, 0,
                             static_cast<cudaStream_t>(stream)>>>(
       o_shards, lse_shards, num_shards, static_cast<long long>(batch) * num_qo_heads, head_dim,
-      out, out_dtype, lse);
+      o_row_stride > 0 ? o_row_stride : head_dim, lse_stride > 0 ? lse_stride : 1, out, out_dtype,
+      lse);
   return static_cast<int>(cudaGetLastError());
 }

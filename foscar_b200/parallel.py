@@ -88,9 +88,33 @@ def merge_states(o_shards: torch.Tensor, lse_shards: torch.Tensor,
     with _dev.on_device(o_shards.device):
         _lib.check(_lib.load().fq_merge_states(
             o_shards.data_ptr(), lse_shards.data_ptr(), n, b, hq, d, out.data_ptr(), code,
-            None if lse is None else lse.data_ptr(),
+            None if lse is None else lse.data_ptr(), 0, 0,
             _dev.current_stream_ptr(o_shards.device)), "merge_states")
     return out
+
+
+def gather_and_merge(out: torch.Tensor, lse: torch.Tensor, group=None,
+                     merged: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The exchange step of a sequence split in ONE collective: this rank's (out [B, HQ, D],
+    lse [B, HQ]) are packed as rows of D + 1 floats, all_gathered into local memory, and merged
+    in place by the library's kernel (strided reads; no unpacking)."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    b, hq, d = out.shape
+    pack = torch.empty(b, hq, d + 1, dtype=torch.float32, device=out.device)
+    pack[..., :d].copy_(out)
+    pack[..., d].copy_(lse)
+    packed = torch.empty(world * b, hq, d + 1, dtype=torch.float32, device=out.device)
+    dist.all_gather_into_tensor(packed, pack, group=group)
+    if merged is None:
+        merged = torch.empty(b, hq, d, dtype=torch.bfloat16, device=out.device)
+    code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[merged.dtype]
+    base = packed.data_ptr()
+    with _dev.on_device(out.device):
+        _lib.check(_lib.load().fq_merge_states(
+            base, base + 4 * d, world, b, hq, d, merged.data_ptr(), code, None, d + 1, d + 1,
+            _dev.current_stream_ptr(out.device)), "merge_states")
+    return merged
 
 
 def sequence_split_decode(wrapper, q, cache, group=None, out: Optional[torch.Tensor] = None
@@ -103,5 +127,4 @@ def sequence_split_decode(wrapper, q, cache, group=None, out: Optional[torch.Ten
     local = torch.empty(b, hq, d, dtype=wrapper._o_data_type, device=q.device)
     lse = torch.empty(b, hq, dtype=torch.float32, device=q.device)
     wrapper.run(q, cache, out=local, lse=lse)
-    o_all, l_all = gather_states(local, lse, group)
-    return merge_states(o_all, l_all, out=out)
+    return gather_and_merge(local, lse, group, merged=out)

@@ -173,10 +173,13 @@ int fq_merge(const float* o_partial, const float* l_partial, const float* m_part
 /* Merge attention states from several sequence shards: out = sum_r exp(lse_r - L) o_r,
  * L = logsumexp_r lse_r, o f32 [R, B, HQ, D], lse f32 [R, B, HQ] (natural log). The reference
  * has no counterpart (single-GPU library); this is the local half of the cross-GPU
- * sequence split. */
+ * sequence split. o_row_stride / lse_stride: elements between consecutive rows of o and of lse
+ * (0: dense, D and 1), so that one gathered buffer of [R, B, HQ, D + 1] rows (o, then lse) can
+ * be merged in place. */
 int fq_merge_states(const float* o_shards, const float* lse_shards, int32_t num_shards,
                     int32_t batch, int32_t num_qo_heads, int32_t head_dim, void* out,
-                    int32_t out_dtype, float* lse, void* stream);
+                    int32_t out_dtype, float* lse, int64_t o_row_stride, int64_t lse_stride,
+                    void* stream);
 
 /* Host-only planning. fq_plan_splits: uniform split count for the longest request (closed-form
  * cost model; stands in for plan_splits_sm100, src/foscar/_sm100/scheduler.py:129-160).
