@@ -165,12 +165,12 @@ __device__ inline __half2 e4m3x2_to_f16x2(uint32_t v) {
 
 // Load this thread's token row (RB bytes at `src`) as packed words.
 template <int BITS, int D>
-__device__ inline void load_row(uint32_t src, uint32_t (&w)[D * BITS / 32]) {
+__device__ inline void load_row(uint32_t src, uint32_t (&w)[D * BITS / 32], int swz) {
 #pragma unroll
   for (int v = 0; v < D * BITS / 128; ++v)
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(w[4 * v]), "=r"(w[4 * v + 1]), "=r"(w[4 * v + 2]), "=r"(w[4 * v + 3])
-                 : "r"(src + 16 * v));
+                 : "r"(src + ((v ^ swz) << 4)));   // chunk v sits at chunk v ^ swz of the row
 }
 // Unpack packed words into exact operand bytes, one per code, in expansion order:
 // out[(8/BITS) * wi + k] = (w[wi] >> (BITS * k)) & mask.
@@ -414,7 +414,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 #pragma unroll
           for (int i = 0; i < D / 4; ++i) part[i] = n;
 #else
-          load_row<BITS, D>(stage + SP::K_OFF + (u * TILE + t) * SP::RB, wk);
+          load_row<BITS, D>(stage + SP::K_OFF + (u * TILE + t) * SP::RB, wk, SP::row_swizzle(t));
           expand_words<BITS, D>(wk, part);
 #endif
 #pragma unroll
@@ -444,7 +444,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 #pragma unroll
           for (int i = 0; i < D / 4; ++i) part[i] = n;
 #else
-          load_row<BITS, D>(stage + SP::V_OFF + (u * TILE + t) * SP::RB, wv);
+          load_row<BITS, D>(stage + SP::V_OFF + (u * TILE + t) * SP::RB, wv, SP::row_swizzle(t));
           expand_words_v<BITS, D>(wv, part);
 #endif
 #pragma unroll
@@ -931,7 +931,12 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           for (int j = 0; j < PPT; ++j) ids[j] = __shfl_sync(0xFFFFFFFFu, cur, PPT * k + j);
           mbar_wait(bars.ring_empty(s), eph, abort_flag, status, 0, wprof);
           const uint32_t full = bars.ring_full(s);
-          const uint32_t dst = ring0 + s * SP::STAGE + 16 * lane;
+          // code chunks go to their swizzled place in the row (SmemPlan::row_swizzle); a lane's
+          // 16 bytes are chunk lane % CHUNKS of row lane / CHUNKS (+ a multiple of 8 rows)
+          const int code_lane = (lane & ~(SP::CHUNKS - 1)) |
+                                ((lane & (SP::CHUNKS - 1)) ^ SP::row_swizzle(lane / SP::CHUNKS));
+          const uint32_t dst = ring0 + s * SP::STAGE + 16 * code_lane;
+          const uint32_t dst_rec = ring0 + s * SP::STAGE + 16 * lane;
 #pragma unroll
           for (int j = 0; j < PPT; ++j) {
             const int id = ids[j];
@@ -954,7 +959,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
 #pragma unroll
             for (int c = 0; c < SP::SCALE_PAGE; c += 512)
               if (c + 16 * lane < scale_page)
-                cp_async16(dst + SP::S_OFF + j * SP::SCALE_PAGE + c, ss + c);
+                cp_async16(dst_rec + SP::S_OFF + j * SP::SCALE_PAGE + c, ss + c);
           }
           cp_async_arrive(full);
         }

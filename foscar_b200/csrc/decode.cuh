@@ -38,6 +38,14 @@ struct SmemPlan {
   static constexpr int RB = D * BITS / 8;              // code row bytes
   static constexpr int CODE_PAGE = PAGE * RB;          // one page of K (or V) codes, one head
   static constexpr int SCALE_PAGE = PAGE * 16;         // f32 (s_k,z_k,s_v,z_v) records
+  // Code rows in the ring are 16, 32 or 64 bytes; threads of a quarter-warp read the same
+  // 16-byte chunk of eight consecutive rows, which at 32 and 64 bytes a row falls on two or
+  // four bank groups only. The producers therefore store chunk c of row r at chunk
+  // c ^ row_swizzle(r), which spreads those eight reads over all banks.
+  static constexpr int CHUNKS = RB / 16;
+  __host__ __device__ static constexpr int row_swizzle(int row) {
+    return CHUNKS == 4 ? (row >> 1) & 3 : (CHUNKS == 2 ? (row >> 2) & 1 : 0);
+  }
   static constexpr int TT = tile_tokens(D);            // tokens per tile
   static constexpr bool PAIR = TT == 2 * TILE;         // two tokens per lane
   static constexpr int PPT = TT / PAGE;                // pages per tile
