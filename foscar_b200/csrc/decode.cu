@@ -42,7 +42,7 @@
 //                 the PV MMA runs once per token set into its own 16 accumulator columns.
 //   KG == 2       K quantized over two 64-channel groups (head_dim 128): the same split of the
 //                 query rows puts each group's partial score in its own column.
-//   scale pools   f32 (16 bytes a token) or bf16 pairs (8 bytes), chosen at run time.
+//   KG == 3       whole-head K with bf16 record pairs (8 bytes a token) instead of f32 (16).
 // Split units are merged inside this launch: a piece that wrote partials is counted in on its
 // unit's counter one tile into the CTA's next item (or after its last), and the CTA that
 // completes the count merges the unit (merge_unit_partials).
@@ -475,7 +475,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           sk[u] = __uint_as_float(k0 << 16); zk[u] = __uint_as_float(k0 & 0xFFFF0000u);
           sk1 = __uint_as_float(k1 << 16); zk1 = __uint_as_float(k1 & 0xFFFF0000u);
           sv[u] = __uint_as_float(vr << 16); zv[u] = __uint_as_float(vr & 0xFFFF0000u);
-        } else if (!P.p.scale_bf16) {
+        } else if constexpr (KG != 3) {   // KG == 1: f32 records; KG == 3: bf16 pairs
           asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
                        : "=f"(sk[u]), "=f"(zk[u]), "=f"(sv[u]), "=f"(zv[u])
                        : "r"(stage + SP::S_OFF + row * 16));
@@ -760,7 +760,9 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 
 template <int BITS, int D, int GP, int KG>
 __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeParams P) {
-  static_assert(KG == 1 || (KG == 2 && D == 128), "K groups of 64 channels at head_dim 128");
+  // KG: 1 whole-head K with f32 records, 3 the same with bf16 pairs, 2 two 64-channel K groups
+  static_assert(KG == 1 || KG == 3 || (KG == 2 && D == 128),
+                "K groups of 64 channels at head_dim 128");
   static_assert(D == 64 || D == 128, "this build tiles head_dim 64 and 128");
   using SP = SmemPlan<BITS, D>;
   using TP = TmemPlan<D>;
@@ -946,8 +948,8 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
             const uint8_t* vs = P.p.v_codes + blk * SP::CODE_PAGE + 16 * lane;
             // records: 16 B per token in an f32 pool, 8 B in a bf16 pool (same slot in the ring)
             // (with two K groups: 8 B of K pairs per token, then 4 B of V pairs per token)
-            const int scale_page =
-                KG == 2 ? 12 * PAGE : (P.p.scale_bf16 ? SP::SCALE_PAGE / 2 : SP::SCALE_PAGE);
+            constexpr int scale_page =
+                KG == 2 ? 12 * PAGE : (KG == 3 ? SP::SCALE_PAGE / 2 : SP::SCALE_PAGE);
             const uint8_t* ss = static_cast<const uint8_t*>(P.p.scales) + blk * scale_page +
                                 16 * lane;
 #pragma unroll
@@ -1250,17 +1252,20 @@ extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void
   }
   const int gp = std::min(P.heads_per_kv, 8) <= 4 ? 4 : 8;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define FQ_DISPATCH(DD, KK)                                                                   \
+  do {                                                                                        \
+    if (pools->bits == 2)                                                                     \
+      return gp == 4 ? launch_decode<2, DD, 4, KK>(P, s) : launch_decode<2, DD, 8, KK>(P, s); \
+    return gp == 4 ? launch_decode<4, DD, 4, KK>(P, s) : launch_decode<4, DD, 8, KK>(P, s);   \
+  } while (0)
+  if (pools->k_groups == 2) FQ_DISPATCH(128, 2);
   if (pools->head_dim == 64) {
-    if (pools->bits == 2) return gp == 4 ? launch_decode<2, 64, 4>(P, s) : launch_decode<2, 64, 8>(P, s);
-    return gp == 4 ? launch_decode<4, 64, 4>(P, s) : launch_decode<4, 64, 8>(P, s);
+    if (pools->scale_bf16) FQ_DISPATCH(64, 3);
+    FQ_DISPATCH(64, 1);
   }
-  if (pools->k_groups == 2) {
-    if (pools->bits == 2)
-      return gp == 4 ? launch_decode<2, 128, 4, 2>(P, s) : launch_decode<2, 128, 8, 2>(P, s);
-    return gp == 4 ? launch_decode<4, 128, 4, 2>(P, s) : launch_decode<4, 128, 8, 2>(P, s);
-  }
-  if (pools->bits == 2) return gp == 4 ? launch_decode<2, 128, 4>(P, s) : launch_decode<2, 128, 8>(P, s);
-  return gp == 4 ? launch_decode<4, 128, 4>(P, s) : launch_decode<4, 128, 8>(P, s);
+  if (pools->scale_bf16) FQ_DISPATCH(128, 3);
+  FQ_DISPATCH(128, 1);
+#undef FQ_DISPATCH
 }
 
 // ---------------------------------------------------------------------------------------------
