@@ -280,6 +280,15 @@ class PagedDecodeWrapper:
             raise NotImplementedError(
                 f"this build decodes token-wise layouts; k_quant={layout.k_quant} "
                 f"v_quant={layout.v_quant} has a channel-wise tensor")
+        if layout.head_dim not in (64, 128):
+            raise NotImplementedError(
+                f"this build's decode kernel takes head_dim 64 and 128; the layout has "
+                f"{layout.head_dim} (the cache writer and read-back do take it)")
+        if layout.k_quant[1] < layout.head_dim and not (
+                layout.head_dim == 128 and layout.k_quant[1] == 64):
+            raise NotImplementedError(
+                f"this build decodes K groups of 64 channels at head_dim 128 only; got "
+                f"k_quant={layout.k_quant} at head_dim {layout.head_dim}")
         self._layout = layout
         self._bits = layout.bits
         self._q_data_type, self._o_data_type = q_dtype, o_dtype

@@ -372,3 +372,19 @@ def test_graph_mode_refusals_before_any_device_work(fake_b200):
         wr._graph_host_lengths([5, 11], 2, 10)
     with pytest.raises(ValueError, match="integer lengths"):
         wr._graph_host_lengths([5.0, 1.0], 2, 10)
+
+
+def test_plan_refuses_shapes_the_decode_kernel_lacks(recorder):
+    """head_dim 256 and K groups other than 64 channels at head_dim 128 are written and read
+    back by this build but not decoded: plan() says so instead of failing at run()."""
+    w = PagedDecodeWrapper(torch.zeros(1 << 20, dtype=torch.uint8))
+    indptr, indices = _plan_args()
+    seq = torch.tensor([256, 200], dtype=torch.int32)
+    with pytest.raises(NotImplementedError, match="head_dim 64 and 128"):
+        w.plan(indptr, indices, seq, 16, _layout(head_dim=256, num_kv_heads=2))
+    _, cache = _cache(None)
+    with pytest.raises(RuntimeError, match="Call plan"):
+        w.run(torch.zeros(2, 32, 128).to(torch.float8_e4m3fn), cache)
+    ok = _layout(head_dim=128, k_quant=("token", 64))
+    w.plan(indptr, indices, seq, 32, ok)
+    assert w.bits == ok.bits
