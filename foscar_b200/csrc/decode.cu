@@ -818,6 +818,9 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   const ItemRange items = item_range(P);
   const uint32_t ring0 = smem0 + SP::RING_OFF;
   int wprof[WAIT_SITES] = {};   // used by the diagnostic build only
+#ifdef FQ_WAIT_PROFILE
+  if (threadIdx.x == 0) wprof[22] = static_cast<int>(clock64() - kernel_t0);   // set-up
+#endif
 
   if (warp == W_PRODUCER || warp == W_PRODUCER2) {
     // ------------------------------------------------------------------ producers
@@ -1042,6 +1045,9 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   } else {
     // ------------------------------------------------------------------ workers
     worker_role<BITS, D, GP, KG>(P, smem, smem0, tmem, bars, abort_flag, items, wprof);
+#ifdef FQ_WAIT_PROFILE
+    if (threadIdx.x == 0) wprof[21] = static_cast<int>(clock64() - kernel_t0);   // workers done
+#endif
   }
 
   tc_fence_before();
