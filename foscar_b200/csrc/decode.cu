@@ -350,8 +350,9 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   RingPos rp;       // ring position of tile `mine`
   rp.advance(wg, NS);
   FQ_ITEM_STAMP_BEGIN();
-  for (int wi = items.begin; wi < items.end; wi += items.step) {
-    const WorkItem w = decode_item(P, wi);
+  const WorkItem* const item_cache = reinterpret_cast<const WorkItem*>(smem + SP::ITEM_OFF);
+  for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
+    const WorkItem w = item_at(P, item_cache, SP::ITEM_SLOTS, ik, wi);
     const int nt = max(w.t1 - w.t0, 0);
     FQ_ITEM_STAMP(13);
     float m[GP], l[GP], c[GP], oacc[GP];
@@ -816,6 +817,15 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const ItemRange items = item_range(P);
+  // The CTA's first items, decoded by one thread each: their dependent loads (row, length, table
+  // offset) go out side by side, once, instead of in every role at every item boundary.
+  WorkItem* const item_cache = reinterpret_cast<WorkItem*>(smem + SP::ITEM_OFF);
+  {
+    const int k = threadIdx.x;
+    const long long wi = items.begin + static_cast<long long>(k) * items.step;
+    if (k < SP::ITEM_SLOTS && wi < items.end) item_cache[k] = decode_item(P, static_cast<int>(wi));
+  }
+  __syncthreads();
   const uint32_t ring0 = smem0 + SP::RING_OFF;
   int wprof[WAIT_SITES] = {};   // used by the diagnostic build only
 #ifdef FQ_WAIT_PROFILE
@@ -834,8 +844,8 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     const int pi = warp == W_PRODUCER ? 0 : 1;
     int it = 0, qi = 0;
     RingPos rp;
-    for (int wi = items.begin; wi < items.end; wi += items.step) {
-      const WorkItem w = decode_item(P, wi);
+    for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
+      const WorkItem w = item_at(P, item_cache, SP::ITEM_SLOTS, ik, wi);
       if (w.t1 <= w.t0) continue;
       if (pi == 0) {
         const int qb = qi & 1;
@@ -986,8 +996,8 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       constexpr uint32_t Q_HI = smem_desc_hi(1024, 2);
       int qi = 0, g = 0;   // tiles go to the groups in turn
       uint32_t gph = 0;    // phase of the groups' barriers: flips once per round of G tiles
-      for (int wi = items.begin; wi < items.end; wi += items.step) {
-        const WorkItem w = decode_item(P, wi);
+      for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
+        const WorkItem w = item_at(P, item_cache, SP::ITEM_SLOTS, ik, wi);
         if (w.t1 <= w.t0) continue;
         const int qb = qi & 1;
         mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status, 1, wprof);
@@ -1018,8 +1028,8 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       const uint32_t p_lo0 = smem_desc_lo(smem0 + SP::P_OFF, 128);
       int g = 0;
       uint32_t gph = 0;
-      for (int wi = items.begin; wi < items.end; wi += items.step) {
-        const WorkItem w = decode_item(P, wi);
+      for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
+        const WorkItem w = item_at(P, item_cache, SP::ITEM_SLOTS, ik, wi);
         for (int t = w.t0; t < w.t1; ++t) {
           mbar_wait(bars.pv_ready(g), gph, abort_flag, status, 4, wprof);
           tc_fence_after();

@@ -79,7 +79,10 @@ struct SmemPlan {
   static constexpr int HEADC_OFF = INFO_OFF + 32;
   static constexpr int RED_BYTES = (HEADC_OFF + 192 - RED_OFF + 1023) / 1024 * 1024;
   static constexpr int BAR_OFF = RED_OFF + RED_BYTES;
-  static constexpr int BAR_BYTES = 2048;   // barriers, then flags and diagnostics
+  static constexpr int BAR_BYTES = 2048;   // barriers, then flags and diagnostics, then the
+                                           // CTA's first work items as decoded at its start
+  static constexpr int ITEM_OFF = BAR_OFF + 1280;
+  static constexpr int ITEM_SLOTS = (BAR_BYTES - 1280) / 32;
   static constexpr int RING_OFF = (BAR_OFF + BAR_BYTES + 1023) / 1024 * 1024;
   static constexpr int max_ring_stages() {
     return (SMEM_LIMIT - 1024 /*alignment slack*/ - RING_OFF) / STAGE;
@@ -133,6 +136,15 @@ static __device__ __noinline__ WorkItem decode_item(const DecodeParams& P, int i
 struct ItemRange {
   int begin, end, step;
 };
+
+// The CTA's k-th item (list index wi). The first ITEM_SLOTS items of a CTA are decoded once, in
+// parallel, when the CTA starts and kept in shared memory, so that no role pays the chain of
+// dependent global loads at an item boundary; later ones are decoded on demand.
+__device__ __forceinline__ WorkItem item_at(const DecodeParams& P, const WorkItem* cached,
+                                            int slots, int k, int wi) {
+  if (k < slots) return cached[k];
+  return decode_item(P, wi);
+}
 __device__ inline ItemRange item_range(const DecodeParams& P) {
   if (P.a.worklist == nullptr)
     return ItemRange{static_cast<int>(blockIdx.x), P.num_items, static_cast<int>(gridDim.x)};
