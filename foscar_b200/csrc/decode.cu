@@ -639,7 +639,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       float* xo = reinterpret_cast<float*>(smem + SP::XCHG_OFF + wg * SP::XCHG_STRIDE);
       float* xmeta = xo + TILE * 8;
 #pragma unroll
-      for (int h = 0; h < GP; ++h) xo[t * 8 + h] = oacc[h];
+      for (int h = 0; h < GP; ++h) xo[h * TILE + t] = oacc[h];   // head-major: no bank conflicts
       if (t == 0) {
 #pragma unroll
         for (int h = 0; h < GP; ++h) { xmeta[h] = m[h]; xmeta[8 + h] = l[h]; xmeta[16 + h] = c[h]; }
@@ -648,8 +648,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     named_barrier(1 + G, 128 * G);
     FQ_ITEM_STAMP(30);
     // The groups' states are merged in fixed order (group 0, then 1, 2, 3), each group taking a
-    // share of the heads. The loops stay rolled: this code runs once per item, and keeping it
-    // small keeps it cheap to fetch.
+    // share of the heads; the loop over the groups is unrolled so that its loads go out together.
     // (The results go to global memory only after the barrier below: a barrier that follows
     // global stores waits for them to be acknowledged, about 2 us under this load.)
     constexpr int HPG = (GP + G - 1) / G;   // heads a group merges
@@ -659,15 +658,15 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       const int h = wg + i * G;
       float M = -INFINITY, L = 0.f, C = 0.f, O = 0.f;
       if (h < GP) {
-#pragma unroll 1
+#pragma unroll
         for (int g = 0; g < G; ++g) {
           const float* xo = reinterpret_cast<const float*>(smem + SP::XCHG_OFF +
                                                            g * SP::XCHG_STRIDE);
           const float* xmeta = xo + TILE * 8;
           const float m1 = xmeta[h], l1 = xmeta[8 + h], c1 = xmeta[16 + h];
           // at two tokens per lane, channel t's sum is split over rows t and t + 64
-          float o1 = xo[t * 8 + h];
-          if (SP::PAIR && t < 64) o1 += xo[(t + 64) * 8 + h];
+          float o1 = xo[h * TILE + t];
+          if (SP::PAIR && t < 64) o1 += xo[h * TILE + t + 64];
           const float Mn = fmaxf(M, m1);
           const float f0 = M == -INFINITY ? 0.f : exp2f(M - Mn);
           const float f1 = m1 == -INFINITY ? 0.f : exp2f(m1 - Mn);
