@@ -149,6 +149,19 @@ class PagedDecodeWrapper:
     # restores the separate merge launch (fq_merge) after every decode.
     fused_merge = True
 
+    # What fq_decode's argument block takes from the plan. The block is built once per plan and
+    # reused by every run(); assigning any of these attributes drops it.
+    _PLAN_STATE = frozenset((
+        "_float_workspace_buffer", "_status", "_o_data_type", "_num_qo_heads", "_batch_size",
+        "_kv_splits", "_seqlens", "_table_offsets", "_page_table", "_o_partial", "_l_partial",
+        "_m_partial", "_max_splits", "_worklist", "_split_counts", "_unit_counters",
+        "_work_rows", "_plan_ctas", "_merge"))
+
+    def __setattr__(self, name, value):
+        if name in self._PLAN_STATE:
+            object.__setattr__(self, "_plan_args", None)
+        object.__setattr__(self, name, value)
+
     def __init__(self, float_workspace_buffer: torch.Tensor, use_cuda_graph: bool = False):
         if not isinstance(float_workspace_buffer, torch.Tensor):
             raise TypeError("float_workspace_buffer must be a torch.Tensor")
@@ -443,35 +456,20 @@ class PagedDecodeWrapper:
         raise RuntimeError("update() is graph mode's per-step call: build the wrapper with "
                            "use_cuda_graph=True and plan() it first")
 
-    def _launch(self, q, cache, out, scale_s, scale_o, three_d, q_descale, lse,
-                enable_pdl=True):
-        b, hq, d = self._batch_size, self._num_qo_heads, self._head_dim
-        if out is None:
-            out = torch.empty((b, hq, d) if three_d else (b, 1, hq, d), dtype=self._o_data_type,
-                              device=self.device)
-        lib = _lib.load()
-        stream = _dev.current_stream_ptr(self.device)
+    def _build_plan_args(self):
+        """fq_decode's argument block with everything the plan fixes filled in."""
         args = _lib.DecodeArgs()
-        args.batch, args.num_qo_heads = b, hq
+        args.batch, args.num_qo_heads = self._batch_size, self._num_qo_heads
         args.out_dtype = _OUT_CODE[self._o_data_type]
         args.kv_splits = 1 if self._worklist is not None else self._kv_splits
         args.max_splits = self._max_splits
-        args.flags = 1 if enable_pdl else 0
         args.num_work = self._work_rows
         args.max_ctas = self._plan_ctas
-        args.sm_scale, args.o_scale = scale_s, scale_o
         args.worklist = None if self._worklist is None else self._worklist.data_ptr()
         args.seq_lens = self._seqlens.data_ptr()
         args.page_table = self._page_table.data_ptr()
         args.table_offsets = self._table_offsets.data_ptr()
         args.table_len = self._page_table.numel()
-        args.q = q.data_ptr()
-        if q_descale is not None:
-            args.q_descale = q_descale.data_ptr()
-            args.q_descale_stride_b, args.q_descale_stride_h = q_descale.stride()
-        args.out = out.data_ptr()
-        # with a merge pass the decode's own final rows (one-piece units) still take the lse
-        args.lse = None if lse is None else lse.data_ptr()
         if self._o_partial is not None:
             args.o_partial = self._o_partial.data_ptr()
             args.l_partial = self._l_partial.data_ptr()
@@ -481,11 +479,35 @@ class PagedDecodeWrapper:
             ws = self._float_workspace_buffer.data_ptr()
             args.o_partial = args.l_partial = args.m_partial = ws
         args.status = self._status_ptr()
-        fused = self._merge and self._unit_counters is not None
-        if fused:
+        if self._merge and self._unit_counters is not None:
             args.unit_counters = self._unit_counters.data_ptr()
             if self._split_counts is not None:
                 args.split_counts = self._split_counts.data_ptr()
+        return args
+
+    def _launch(self, q, cache, out, scale_s, scale_o, three_d, q_descale, lse,
+                enable_pdl=True):
+        b, hq, d = self._batch_size, self._num_qo_heads, self._head_dim
+        if out is None:
+            out = torch.empty((b, hq, d) if three_d else (b, 1, hq, d), dtype=self._o_data_type,
+                              device=self.device)
+        lib = _lib.load()
+        stream = _dev.current_stream_ptr(self.device)
+        args = self._plan_args
+        if args is None:
+            args = self._plan_args = self._build_plan_args()
+        fused = self._merge and self._unit_counters is not None
+        args.flags = 1 if enable_pdl else 0
+        args.sm_scale, args.o_scale = scale_s, scale_o
+        args.q = q.data_ptr()
+        if q_descale is not None:
+            args.q_descale = q_descale.data_ptr()
+            args.q_descale_stride_b, args.q_descale_stride_h = q_descale.stride()
+        else:
+            args.q_descale = None
+        args.out = out.data_ptr()
+        # with a merge pass the decode's own final rows (one-piece units) still take the lse
+        args.lse = None if lse is None else lse.data_ptr()
         _lib.check(lib.fq_decode(ctypes.byref(cache._c_pools), ctypes.byref(args), stream),
                    "decode")
         self.launches += 1
