@@ -417,9 +417,11 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=16384,
                     help="KV tokens in the CPU baseline's bounded sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--split", default="none", choices=["none", "sequence"],
+    ap.add_argument("--split", default="none", choices=["none", "sequence", "heads"],
                     help="sequence: ONE batch whose every context is split page-aligned over the "
-                         "ranks (strong scaling; one all_gather of (o, lse) per step)")
+                         "ranks (strong scaling; one all_gather of (o, lse) per step). heads: ONE "
+                         "batch whose KV heads (and their query heads) are dealt out to the ranks "
+                         "(tensor parallel, strong scaling, no collective)")
     ap.add_argument("--op", default="decode", choices=["decode", "append", "dequantize"],
                     help="decode: the headline step. append / dequantize: the cache writer or the "
                          "read-back kernel alone on a slice of the workload, as GB/s")
@@ -444,7 +446,13 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
 
-    case = build_gpu_case(cfg, device, args.seed + 17 * rank)
+    by_heads = args.split == "heads"
+    if by_heads:
+        # every rank decodes the same requests (same lengths: same seed) for its own KV heads
+        from foscar_b200 import parallel
+        hq, hkv = parallel.shard_kv_heads(cfg["hq"], cfg["hkv"], rank, world)
+        cfg = dict(cfg, hq=hq.stop - hq.start, hkv=hkv.stop - hkv.start)
+    case = build_gpu_case(cfg, device, args.seed + (0 if by_heads else 17 * rank))
     w, cache, q, seq = case["wrapper"], case["cache"], case["q"], case["seq"]
     b, hq, d = cfg["batch"], cfg["hq"], cfg["d"]
     out = torch.empty(b, hq, d, dtype=torch.bfloat16, device=device)
@@ -518,10 +526,12 @@ def main():
         abytes = algorithmic_bytes(cfg, seq)
         achieved = abytes / (decode_ms * 1e-3) / 1e9
         line = {
-            "metric": "decode_tokens_per_s", "value": world * b / (step_ms * 1e-3),
+            "metric": "decode_tokens_per_s",
+            "value": (1 if by_heads else world) * b / (step_ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": step_ms, "us_per_step": step_ms * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x int%d codes, f32 accumulate"
+            "scaling": "strong" if by_heads else "weak", "vs_baseline": None,
+            "dtype": "e4m3 x int%d codes, f32 accumulate"
             % cfg["bits"], "data": "synthetic", "config": workload_config(args, cfg, seq),
             "hbm_gbs": abytes / (step_ms * 1e-3) / 1e9,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -529,12 +539,16 @@ def main():
                          "traffic": NCU_TRAFFIC.get(args.workload),
                          "kernel": "decode_kernel", "kernel_us": decode_ms * 1e3,
                          "algorithmic_bytes": abytes, "frac_of_8tbs_nominal": achieved / 8000.0},
-            "e2e": {"value": world * b / (e2e_ms * 1e-3), "unit": "tokens/s",
+            "e2e": {"value": (1 if by_heads else world) * b / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "us_per_step": e2e_ms * 1e3, "h2d_bytes_per_step": int(q_host.numel()),
                     "d2h_bytes_per_step": int(out_host.numel() * 2)},
             "gpu_launches": launches, "clocks": clocks.summary(), "device_status": status,
             "plan": {"kv_splits": w.kv_splits, "reduction": w.reduction},
         }
+        if by_heads:
+            line["config"]["parallelism"] = (
+                f"kv-head tensor parallel x{world}: {cfg['hkv']} KV heads per GPU, the same "
+                f"batch on every GPU, no collective")
         if not args.no_cpu_baseline and world == 1:   # the CPU leg is an N=1 figure
             threads = os.cpu_count() or 1
             torch.set_num_threads(threads)
