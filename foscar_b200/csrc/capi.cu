@@ -81,7 +81,9 @@ extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t 
   if (!seq_lens || !worklist || !split_counts) return FQ_ERR_BAD_ARG;
   if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || num_ctas < 1 || max_splits < 1)
     return FQ_ERR_BAD_ARG;
-  long long OVH = bits == 4 ? 10 : 14;   // per-piece overhead in tile units (an INT4 tile: ~0.5 us)
+  // per-piece overhead in tile units, as measured: 14 tiles, 10 where a tile is as slow as an
+  // INT4 tile of 128 tokens at head_dim 128 (~0.5 us)
+  long long OVH = bits == 4 && head_dim != 64 ? 10 : 14;
   long long MIN_PIECE = 4;   // a CTA with less room than this for tiles passes the unit on
   if (const char* env = getenv("FOSCAR_B200_PIECE_OVERHEAD")) {   // tuning knob for experiments
     const int v = atoi(env);
