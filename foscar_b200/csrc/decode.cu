@@ -351,8 +351,10 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   rp.advance(wg, NS);
   FQ_ITEM_STAMP_BEGIN();
   const WorkItem* const item_cache = reinterpret_cast<const WorkItem*>(smem + SP::ITEM_OFF);
+  const WorkItem* const item_more =
+      reinterpret_cast<const WorkItem*>(smem + SP::RING_OFF + NS * SP::STAGE);
   for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
-    const WorkItem w = item_at(P, item_cache, SP::ITEM_SLOTS, ik, wi);
+    const WorkItem w = item_at(P, item_cache, item_more, SP::ITEM_SLOTS, ik, wi);
     const int nt = max(w.t1 - w.t0, 0);
     FQ_ITEM_STAMP(13);
     float m[GP], l[GP], c[GP], oacc[GP];
@@ -819,10 +821,15 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   // The CTA's first items, decoded by one thread each: their dependent loads (row, length, table
   // offset) go out side by side, once, instead of in every role at every item boundary.
   WorkItem* const item_cache = reinterpret_cast<WorkItem*>(smem + SP::ITEM_OFF);
+  WorkItem* const item_more = reinterpret_cast<WorkItem*>(smem + SP::RING_OFF + NS * SP::STAGE);
   {
     const int k = threadIdx.x;
     const long long wi = items.begin + static_cast<long long>(k) * items.step;
-    if (k < SP::ITEM_SLOTS && wi < items.end) item_cache[k] = decode_item(P, static_cast<int>(wi));
+    if (k < P.item_slots && wi < items.end) {
+      const WorkItem w = decode_item(P, static_cast<int>(wi));
+      if (k < SP::ITEM_SLOTS) item_cache[k] = w;
+      else item_more[k - SP::ITEM_SLOTS] = w;
+    }
   }
   __syncthreads();
   const uint32_t ring0 = smem0 + SP::RING_OFF;
@@ -844,7 +851,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     int it = 0, qi = 0;
     RingPos rp;
     for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
-      const WorkItem w = item_at(P, item_cache, SP::ITEM_SLOTS, ik, wi);
+      const WorkItem w = item_at(P, item_cache, item_more, SP::ITEM_SLOTS, ik, wi);
       if (w.t1 <= w.t0) continue;
       if (pi == 0) {
         const int qb = qi & 1;
@@ -996,7 +1003,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       int qi = 0, g = 0;   // tiles go to the groups in turn
       uint32_t gph = 0;    // phase of the groups' barriers: flips once per round of G tiles
       for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
-        const WorkItem w = item_at(P, item_cache, SP::ITEM_SLOTS, ik, wi);
+        const WorkItem w = item_at(P, item_cache, item_more, SP::ITEM_SLOTS, ik, wi);
         if (w.t1 <= w.t0) continue;
         const int qb = qi & 1;
         mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status, 1, wprof);
@@ -1028,7 +1035,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       int g = 0;
       uint32_t gph = 0;
       for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
-        const WorkItem w = item_at(P, item_cache, SP::ITEM_SLOTS, ik, wi);
+        const WorkItem w = item_at(P, item_cache, item_more, SP::ITEM_SLOTS, ik, wi);
         for (int t = w.t0; t < w.t1; ++t) {
           mbar_wait(bars.pv_ready(g), gph, abort_flag, status, 4, wprof);
           tc_fence_after();
@@ -1198,7 +1205,12 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   if (stages < WORKER_GROUPS) return FQ_ERR_UNSUPPORTED;  // a group steps the ring by one lap at most
   P.ring_stages = stages;
   P.tile_tokens = SP::TT;
-  const int smem = SP::RING_OFF + stages * SP::STAGE + 1024;
+  // Shared memory the ring leaves over holds more decoded work items (32 bytes each), up to
+  // one per thread of the CTA's start-up pass.
+  const int spare = SMEM_LIMIT - 1024 - SP::RING_OFF - stages * SP::STAGE;
+  const int more = std::max(0, std::min(spare / 32, DECODE_THREADS - SP::ITEM_SLOTS));
+  P.item_slots = SP::ITEM_SLOTS + more;
+  const int smem = SP::RING_OFF + stages * SP::STAGE + more * 32 + 1024;
   static bool configured[64] = {};  // per (BITS, D, GP) instantiation and device
   auto kernel = decode_kernel<BITS, D, GP, KG>;
   int dev = 0;

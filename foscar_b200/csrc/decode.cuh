@@ -26,6 +26,7 @@ struct DecodeParams {
   int num_items;     // implicit: B*HKV*head_tiles*kv_splits; explicit: row capacity
   int ring_stages;
   int tile_tokens;   // tile_tokens(head_dim)
+  int item_slots;    // work items a CTA keeps decoded in shared memory
 };
 
 struct WorkItem {
@@ -137,12 +138,14 @@ struct ItemRange {
   int begin, end, step;
 };
 
-// The CTA's k-th item (list index wi). The first ITEM_SLOTS items of a CTA are decoded once, in
-// parallel, when the CTA starts and kept in shared memory, so that no role pays the chain of
+// The CTA's k-th item (list index wi). The first items of a CTA (ITEM_SLOTS, plus as many as fit
+// in the shared memory the ring leaves over: DecodeParams::item_slots in all) are decoded once,
+// in parallel, when the CTA starts and kept in shared memory, so that no role pays the chain of
 // dependent global loads at an item boundary; later ones are decoded on demand.
 __device__ __forceinline__ WorkItem item_at(const DecodeParams& P, const WorkItem* cached,
-                                            int slots, int k, int wi) {
+                                            const WorkItem* more, int slots, int k, int wi) {
   if (k < slots) return cached[k];
+  if (k < P.item_slots) return more[k - slots];   // shared memory the ring leaves over
   return decode_item(P, wi);
 }
 __device__ inline ItemRange item_range(const DecodeParams& P) {
