@@ -195,6 +195,24 @@ __device__ inline void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, u
 __device__ inline void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
+// The same copy for data read once per launch: marked evict-first in L2, so that the stream of
+// cache pages does not push out what is used again (query rows, work items, and above all the
+// kernel's own instructions: a phase that runs once per work item otherwise refetches its code
+// from DRAM every time).
+__device__ inline uint64_t l2_evict_first_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ inline void cp_async16_stream(uint32_t dst, const void* src, uint64_t policy) {
+#ifdef FQ_PLAIN_COPIES
+  cp_async16(dst, src);
+#else
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst),
+               "l"(src), "l"(policy)
+               : "memory");
+#endif
+}
 __device__ inline void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }

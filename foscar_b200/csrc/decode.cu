@@ -681,6 +681,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       }
       rM[i] = M; rL[i] = L; rO[i] = O;
     }
+    FQ_ITEM_STAMP(28);
     // ---- in-kernel merge, step 1. A split piece is counted in (release fence + one atomic on
     // its unit's counter) not here but a tile into the NEXT item (above), or after the last
     // item. Whoever finds the count complete makes the CTA merge that unit after the barrier
@@ -848,6 +849,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     // The first producer also stages each item's query rows, in expansion order, as the S MMA's
     // B operand; it runs a ring's depth ahead of the MMAs, which hides the load.
     const int pi = warp == W_PRODUCER ? 0 : 1;
+    const uint64_t stream_policy = l2_evict_first_policy();
     int it = 0, qi = 0;
     RingPos rp;
     for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
@@ -973,14 +975,15 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
                                 16 * lane;
 #pragma unroll
             for (int c = 0; c < SP::CODE_PAGE; c += 512)
-              cp_async16(dst + SP::K_OFF + j * SP::CODE_PAGE + c, ks + c);
+              cp_async16_stream(dst + SP::K_OFF + j * SP::CODE_PAGE + c, ks + c, stream_policy);
 #pragma unroll
             for (int c = 0; c < SP::CODE_PAGE; c += 512)
-              cp_async16(dst + SP::V_OFF + j * SP::CODE_PAGE + c, vs + c);
+              cp_async16_stream(dst + SP::V_OFF + j * SP::CODE_PAGE + c, vs + c, stream_policy);
 #pragma unroll
             for (int c = 0; c < SP::SCALE_PAGE; c += 512)
               if (c + 16 * lane < scale_page)
-                cp_async16(dst_rec + SP::S_OFF + j * SP::SCALE_PAGE + c, ss + c);
+                cp_async16_stream(dst_rec + SP::S_OFF + j * SP::SCALE_PAGE + c, ss + c,
+                                  stream_policy);
           }
           cp_async_arrive(full);
         }
