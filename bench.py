@@ -71,7 +71,7 @@ def algorithmic_bytes(cfg, seq):
 # DRAM bytes (read + write) of one decode launch from an ncu capture of the same command
 # (profiles/decode_kernel_c2_int2.md, profiles/decode_kernel_c2_int4.md); other workloads have
 # no capture.
-NCU_TRAFFIC = {"c2": 427_103_744, "c2-int4": 744_366_848}
+NCU_TRAFFIC = {"c2": 401_548_800, "c2-int4": 716_985_600}
 
 
 def measured_peak():
