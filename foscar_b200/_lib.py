@@ -17,12 +17,23 @@ STATUS_BITS = {0x1: "slot outside the cache", 0x2: "page id outside the pool",
                0x4: "output row outside the buffer", 0x8: "bad sequence length",
                0x10: "device wait timed out"}
 WORK_WORDS = 8
-TILE_TOKENS = 128
+STATUS_TIMEOUT = 0x10
 
 
-def tile_tokens(head_dim: int) -> int:
-    """Tokens per sequence tile of the decode kernel (two per tensor-memory lane at head_dim 64)."""
-    return 256 if head_dim == 64 else 128
+def tile_tokens(bits: int, head_dim: int) -> int:
+    """Tokens per sequence tile of the decode kernel's build for (bits, head_dim)."""
+    n = load().fq_tile_tokens(bits, head_dim)
+    if n < 0:
+        check(n, "tile_tokens")
+    return int(n)
+
+
+def piece_overhead(bits: int, head_dim: int) -> int:
+    """Fixed cost of a work piece in tile units, as the balanced planner counts it."""
+    n = load().fq_piece_overhead(bits, head_dim)
+    if n < 0:
+        check(n, "piece_overhead")
+    return int(n)
 
 
 class Pools(C.Structure):
@@ -43,7 +54,7 @@ class DecodeArgs(C.Structure):
                 ("q_descale_stride_h", C.c_int64), ("out", C.c_void_p), ("lse", C.c_void_p),
                 ("o_partial", C.c_void_p), ("l_partial", C.c_void_p), ("m_partial", C.c_void_p),
                 ("status", C.c_void_p), ("unit_counters", C.c_void_p),
-                ("split_counts", C.c_void_p)]
+                ("split_counts", C.c_void_p), ("wait_budget_cycles", C.c_int64)]
 
 
 _P = C.c_void_p
@@ -66,6 +77,9 @@ _PROTOTYPES = {
     "fq_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
     "fq_worklist_words": (_I64, [_I32, _I32, _I32, _I32]),
     "fq_umma_selftest": (C.c_int, [_I32, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "fq_tile_tokens": (C.c_int, [_I32, _I32]),
+    "fq_piece_overhead": (C.c_int, [_I32, _I32]),
+    "fq_wait_selftest": (C.c_int, [_I64, _P, _P, _P]),
 }
 EXPORTS = tuple(_PROTOTYPES)
 

@@ -49,7 +49,7 @@ extern "C" int fq_plan_splits(int32_t batch, int32_t num_kv_heads, int32_t head_
   if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || sm_count < 1) return FQ_ERR_BAD_ARG;
   if (bits != 2 && bits != 4) return FQ_ERR_BAD_ARG;
   const long long base = static_cast<long long>(batch) * num_kv_heads * head_tiles;
-  const int tt = tile_tokens(head_dim);
+  const int tt = tile_tokens(bits, head_dim);
   const int tiles = std::max(1, (max_kv_len + tt - 1) / tt);
   int best = 1;
   double best_cost = split_cost(base, tiles, 1, bits, sm_count);
@@ -67,11 +67,28 @@ static long long worklist_words(long long units, int num_ctas) {
   return WORK_WORDS + starts + WORK_WORDS * (units + num_ctas);
 }
 
+// Fixed cost of a piece in tile units (pipeline refill, the group hand-off of the item's state and
+// the output), as measured on B200 against the cost of streaming one tile.
+static long long piece_overhead(int bits, int head_dim) {
+  long long ovh = bits == 4 && head_dim != 64 ? 10 : 14;
+  if (const char* env = getenv("FOSCAR_B200_PIECE_OVERHEAD")) {   // tuning knob for experiments
+    const int v = atoi(env);
+    if (v >= 0 && v <= 256) ovh = v;
+  }
+  return ovh;
+}
+
+extern "C" int fq_piece_overhead(int32_t bits, int32_t head_dim) {
+  if (bits != 2 && bits != 4) return FQ_ERR_BAD_ARG;
+  return static_cast<int>(piece_overhead(bits, head_dim));
+}
+
 // Balanced plan: every piece (a unit, or a part of a unit cut between CTAs) costs its tile count
-// plus a fixed overhead, measured on B200 at ~5 us against ~0.34 us per INT2 tile (pipeline
-// drain and refill, group merge, output). The units (request, KV head, head tile) are dealt to
-// the CTAs in order; a CTA takes tiles until its share of the total cost is used up, and the
-// unit in hand continues on the next CTA as a new piece. List layout (int32 words):
+// plus a fixed overhead. The units (request, KV head, head tile) are dealt to the CTAs in order;
+// a CTA takes tiles until its share of the total cost is used up, and the unit in hand continues
+// on the next CTA as a new piece. No unit is cut into more than max_splits pieces: the share is
+// raised until the longest unit fits that many, and a unit's last allowed piece takes all that
+// is left of it (the CTAs after it then take less). List layout (int32 words):
 // header {pieces, units, ctas, rows' word offset, 0...}, cta_start[ctas + 1] padded to 8 words,
 // then one row of 8 words per piece.
 extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t num_kv_heads,
@@ -81,25 +98,26 @@ extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t 
   if (!seq_lens || !worklist || !split_counts) return FQ_ERR_BAD_ARG;
   if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || num_ctas < 1 || max_splits < 1)
     return FQ_ERR_BAD_ARG;
-  // per-piece overhead in tile units, as measured: 14 tiles, 10 where a tile is as slow as an
-  // INT4 tile of 128 tokens at head_dim 128 (~0.5 us)
-  long long OVH = bits == 4 && head_dim != 64 ? 10 : 14;
-  long long MIN_PIECE = 4;   // a CTA with less room than this for tiles passes the unit on
-  if (const char* env = getenv("FOSCAR_B200_PIECE_OVERHEAD")) {   // tuning knob for experiments
-    const int v = atoi(env);
-    if (v >= 0 && v <= 256) OVH = v;
-  }
+  if (bits != 2 && bits != 4) return FQ_ERR_BAD_ARG;
+  const long long OVH = piece_overhead(bits, head_dim);
+  const long long MIN_PIECE = 4;   // a CTA with less room than this for tiles passes the unit on
   const int upr = num_kv_heads * head_tiles;
-  const int tt = tile_tokens(head_dim);
+  const int tt = tile_tokens(bits, head_dim);
   const long long units = static_cast<long long>(batch) * upr;
   if (worklist_words(units, num_ctas) > max_words) return FQ_ERR_TOO_LARGE;
   auto tiles_of = [&](int b) -> long long {
     return seq_lens[b] > 0 ? (static_cast<long long>(seq_lens[b]) + tt - 1) / tt : 0;
   };
-  long long total = 0;
-  for (int b = 0; b < batch; ++b) total += (tiles_of(b) + OVH) * upr;
+  long long total = 0, longest = 0;
+  for (int b = 0; b < batch; ++b) {
+    total += (tiles_of(b) + OVH) * upr;
+    longest = std::max(longest, tiles_of(b));
+  }
   total += OVH * (num_ctas - 1);   // about one cut, hence one more piece, per CTA boundary
-  const long long share = std::max<long long>(OVH + 1, (total + num_ctas - 1) / num_ctas);
+  long long share = std::max<long long>(OVH + 1, (total + num_ctas - 1) / num_ctas);
+  // the longest unit in max_splits pieces: one may be the remainder of a CTA, the others full
+  const long long full_pieces = std::max(1, max_splits - 1);
+  share = std::max(share, OVH + (longest + full_pieces - 1) / full_pieces);
   const int starts_words = (num_ctas + 1 + 7) / 8 * 8;
   int32_t* cta_start = worklist + WORK_WORDS;
   int32_t* rows = worklist + WORK_WORDS + starts_words;
@@ -115,14 +133,17 @@ extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t 
     int t0 = 0, pieces = 0;
     for (;;) {
       const bool last_cta = cta == num_ctas - 1;
+      const bool last_piece = pieces == max_splits - 1;   // the unit may not be cut again
       // room for the overhead plus a worthwhile number of tiles, or the rest of the unit
-      if (!last_cta && room < OVH + std::min<long long>(MIN_PIECE, tiles - t0)) {
+      if (!last_cta && room < OVH + std::min<long long>(MIN_PIECE, tiles - t0) &&
+          !(last_piece && pieces > 0 && room > OVH)) {
         cta_start[++cta] = pieces_total;
-        room = share;
+        room = share + std::min<long long>(room, 0);   // an overfull CTA is paid for by the next
         continue;
       }
       int t1 = tiles;
-      if (!last_cta && OVH + (tiles - t0) > room) t1 = t0 + static_cast<int>(room - OVH);
+      if (!last_cta && !last_piece && OVH + (tiles - t0) > room)
+        t1 = t0 + static_cast<int>(room - OVH);
       int32_t* row = rows + static_cast<long long>(WORK_WORDS) * pieces_total;
       row[0] = b; row[1] = kvh; row[2] = ht; row[3] = t0; row[4] = t1; row[5] = pieces;
       row[6] = 0; row[7] = 0;
@@ -132,7 +153,7 @@ extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t 
       t0 = t1;
       if (t0 >= tiles) break;
     }
-    if (pieces > max_splits) return FQ_ERR_TOO_LARGE;
+    if (pieces > max_splits) return FQ_ERR_TOO_LARGE;   // cannot happen; kept as a check
     if (pieces == 1) rows[static_cast<long long>(WORK_WORDS) * first_row + 5] = -1;
     split_counts[u] = pieces;
   }

@@ -1,4 +1,4 @@
-// Shared device helpers: pool-format arithmetic and sm_100a PTX wrappers (mbarrier, bulk async
+// Shared device helpers: pool-format arithmetic and sm_100a PTX wrappers (mbarrier, asynchronous
 // copies, tcgen05 tensor-memory and MMA instructions). Every wait is bounded by a cycle budget:
 // when it runs out the waiter raises the CTA's abort flag and the caller's status word and
 // falls through, so a protocol error ends the kernel instead of hanging the GPU.
@@ -57,10 +57,6 @@ __device__ inline void mbar_init(uint32_t bar, uint32_t count) {
 __device__ inline void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ inline void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
 __device__ inline bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -73,58 +69,34 @@ __device__ inline bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// The same with a suspend-time hint (ns): the waiting thread sleeps in hardware until the phase
-// completes or the hint elapses, instead of re-polling the shared-memory pipe.
-__device__ inline bool mbar_try_sleep(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(100000u)
-      : "memory");
-  return ok != 0;
-}
-
-// Cycle budget of one wait: about a second at B200 clocks.
+// Cycle budget of one wait unless the launch sets another: about a second at B200 clocks.
 constexpr long long WAIT_BUDGET_CYCLES = 2000000000LL;
 
 // Wait for a barrier phase, bounded. `abort_flag` is a CTA-shared word: once any waiter has
-// given up every later wait returns at once, so the CTA drains in bounded time.
+// given up every later wait returns at once, so the CTA drains in bounded time. The cycle
+// budget of a wait sits two words after the flag (set_wait_budget).
 // `site` names the call site for the optional wait profile (see FQ_WAIT_PROFILE): the cycles
-// lane 0 of each warp spent blocked are summed per site in the words after the abort flag.
+// lane 0 of each warp spent blocked are summed per site in the words after the budget.
 constexpr int WAIT_SITES = 32;
+__device__ inline void set_wait_budget(volatile int* abort_flag, long long cycles) {
+  *reinterpret_cast<volatile long long*>(abort_flag + 2) = cycles;
+}
 static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity,
                                             volatile int* abort_flag, int* status) {
-  // mbarrier.try_wait suspends the thread in hardware for a bounded time by itself; a
-  // suspend-time hint on top of it compiles to a software loop of clock reads and nanosleeps
-  // whose instructions, over twenty waiting warps, took a third of the SM's issue slots. The
-  // abort flag and the clock are looked at once every 32 failed tries only.
-#ifdef FQ_WAIT_SLEEP_HINT
-  const long long t0 = clock64();
-  while (!mbar_try_sleep(bar, parity)) {
-    if (*abort_flag) return;
-    if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
-      *abort_flag = 1;
-      if (status) atomicOr(status, FQ_STATUS_TIMEOUT);
-      return;
-    }
-  }
-#else
+  // mbarrier.try_wait suspends the thread in hardware for a bounded time by itself; the abort
+  // flag and the clock are looked at once every 32 failed tries only.
   long long t0 = 0;
   for (uint32_t tries = 1; !mbar_try(bar, parity); ++tries) {
     if ((tries & 31u) != 0) continue;
     if (*abort_flag) return;
     const long long now = clock64();
     if (t0 == 0) t0 = now;
-    if (now - t0 > WAIT_BUDGET_CYCLES) {
+    if (now - t0 > *reinterpret_cast<volatile long long*>(abort_flag + 2)) {
       *abort_flag = 1;
       if (status) atomicOr(status, FQ_STATUS_TIMEOUT);
       return;
     }
   }
-#endif
 }
 #ifndef FQ_WAIT_PROFILE
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity,
@@ -146,10 +118,10 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity,
 
 // Bounded wait that ignores the abort flag: used once, at exit, to let a CTA's own bulk copies
 // land before its shared memory is released.
-__device__ inline void mbar_wait_drain(uint32_t bar, uint32_t parity) {
+__device__ inline void mbar_wait_drain(uint32_t bar, uint32_t parity, long long budget) {
   const long long t0 = clock64();
   while (!mbar_try(bar, parity)) {
-    if (clock64() - t0 > WAIT_BUDGET_CYCLES / 16) return;
+    if (clock64() - t0 > budget) return;
   }
 }
 
@@ -179,15 +151,8 @@ __device__ inline bool named_barrier_or(int id, int threads, bool pred) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// PTX: bulk async copy global -> shared, completing on an mbarrier
+// PTX: asynchronous copies global -> shared
 // ---------------------------------------------------------------------------------------------
-
-__device__ inline void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
 
 // 16-byte asynchronous copy global -> shared issued by a thread (LSU path, bypassing L1), and the
 // arrive that fires on an mbarrier once all of this thread's earlier copies have landed. The

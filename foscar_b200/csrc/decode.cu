@@ -44,8 +44,9 @@
 //                 query rows puts each group's partial score in its own column.
 //   KG == 3       whole-head K with bf16 record pairs (8 bytes a token) instead of f32 (16).
 // Split units are merged inside this launch: a piece that wrote partials is counted in on its
-// unit's counter one tile into the CTA's next item (or after its last), and the CTA that
-// completes the count merges the unit (merge_unit_partials).
+// unit's counter one tile into the CTA's next item (or after its last), once every worker warp
+// has reported its stores of the piece on a barrier, and the CTA that completes the count merges
+// the unit (merge_unit_partials).
 // The ring's stage count is kept even, so that each stage belongs to one of the two producers.
 #include "decode.cuh"
 
@@ -110,7 +111,10 @@ struct Bars {
   __device__ uint32_t s_done(int g) const { return at(2 * ns + 4 + G + g); }
   __device__ uint32_t pv_ready(int g) const { return at(2 * ns + 4 + 2 * G + g); }
   __device__ uint32_t pv_done(int g) const { return at(2 * ns + 4 + 3 * G + g); }
-  // 2*ns + 4 + 4*G words of 8 bytes
+  // stored: every worker warp has issued its output or partial stores of the work item (one
+  // phase per item): what orders a split piece's partials before its count-in
+  __device__ uint32_t stored() const { return at(2 * ns + 4 + 4 * G); }
+  // 2*ns + 5 + 4*G words of 8 bytes
 };
 
 // Position in the code ring: stage and phase, advanced without a division.
@@ -131,7 +135,7 @@ struct RingPos {
 // buffer of 16 columns per token of a lane.
 template <int D>
 struct TmemPlan {
-  static constexpr bool PAIR = tile_tokens(D) == 2 * TILE;
+  static constexpr bool PAIR = D == 64;
   static constexpr int KOP_COLS = PAIR ? 32 : D / 4;
   static constexpr int O_COLS = PAIR ? 32 : 16;
   static constexpr int KOP = 0;
@@ -340,6 +344,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   };
   // the split piece this CTA has written but not yet counted in (thread 0 of group 0 only)
   int pend_k = 0, pend_unit = 0, pend_b = 0, pend_kvh = 0, pend_ht = 0;
+  uint32_t pend_phase = 0;   // phase of the `stored` barrier that covers the pending piece
   int seen = -1;        // the pending piece's count-in result; -1: not counted in yet
   int this_k = 0;       // pieces of the current item's unit (fetched at the item's start)
 
@@ -602,8 +607,11 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       pending = true;
       // The previous split piece of this CTA is counted in here, a tile into the next item: its
       // partials have drained, and the fence and the atomic's round trip cost one thread of
-      // one group a microsecond in mid-stream instead of stalling an item boundary.
+      // one group a microsecond in mid-stream instead of stalling an item boundary. The wait
+      // (long satisfied) is what orders every worker warp's partial stores before this
+      // thread's release fence and atomic.
       if (wg == 0 && t == 0 && pend_k > 0 && seen < 0) {
+        mbar_wait(bars.stored(), pend_phase, abort_flag, status, 29, wprof);
         __threadfence();
         seen = atomicAdd(P.a.unit_counters + pend_unit, 1);
       }
@@ -615,6 +623,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 
     // ---- item epilogue. First, the count-in of the previous split piece (see step 1 below)
     if (wg == 0 && t == 0 && pend_k > 0 && seen < 0) {   // group 0 had no tile in this item
+      mbar_wait(bars.stored(), pend_phase, abort_flag, status, 29, wprof);
       __threadfence();
       seen = atomicAdd(P.a.unit_counters + pend_unit, 1);
     }
@@ -699,6 +708,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         pend_unit = (w.b * P.p.num_kv_heads + w.kvh) * P.head_tiles + w.ht;
         pend_k = this_k;
         pend_b = w.b; pend_kvh = w.kvh; pend_ht = w.ht;
+        pend_phase = static_cast<uint32_t>(ik & 1);
       }
     }
     FQ_ITEM_STAMP(31);
@@ -731,6 +741,9 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         }
       }
     }
+    // this warp's stores of the item are issued
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bars.stored());
     if (merge_info[0] > 0)
       merge_unit(merge_info[0], merge_info[1], merge_info[2], merge_info[3], wg, G);
     FQ_ITEM_STAMP(26);
@@ -743,6 +756,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       int km = 0;
       if (pend_k > 0) {
         if (seen < 0) {
+          mbar_wait(bars.stored(), pend_phase, abort_flag, status, 29, wprof);
           __threadfence();
           seen = atomicAdd(P.a.unit_counters + pend_unit, 1);
         }
@@ -784,11 +798,12 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   int* status = P.a.status;
 #ifdef FQ_WAIT_PROFILE
   const long long kernel_t0 = clock64();
-  if (threadIdx.x < WAIT_SITES) const_cast<int*>(abort_flag)[1 + threadIdx.x] = 0;
+  if (threadIdx.x < WAIT_SITES) const_cast<int*>(abort_flag)[4 + threadIdx.x] = 0;
 #endif
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    set_wait_budget(abort_flag, P.wait_budget);
     for (int s = 0; s < NS; ++s) {
       mbar_init(bars.ring_full(s), 32);  // one cp.async arrival per producer lane
       mbar_init(bars.ring_empty(s), 4);  // the four warps of the group that took the tile
@@ -803,6 +818,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
       mbar_init(bars.q_full(s), 1);
       mbar_init(bars.q_empty(s), 1);
     }
+    mbar_init(bars.stored(), 4 * G);   // one arrival per worker warp
     fence_barrier_init();
   }
   if (warp == W_S) tmem_alloc(smem_u32(tmem_slot), TP::ALLOC);
@@ -993,7 +1009,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     // drain: every copy this warp issued has landed once its stage reports full
     for (int back = 0; back < NS && back < it; ++back) {
       if (--rp.s < 0) { rp.s = NS - 1; rp.ph ^= 1u; }
-      mbar_wait_drain(bars.ring_full(rp.s), rp.ph);
+      mbar_wait_drain(bars.ring_full(rp.s), rp.ph, P.wait_budget / 16);
     }
   } else if (warp == W_S) {
     // ------------------------------------------------------------------ S issuer
@@ -1079,11 +1095,11 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
   if (lane == 0) {
 #pragma unroll
     for (int i = 0; i < WAIT_SITES; ++i)
-      if (wprof[i]) atomicAdd(const_cast<int*>(abort_flag) + 1 + i, wprof[i] >> 4);
+      if (wprof[i]) atomicAdd(const_cast<int*>(abort_flag) + 4 + i, wprof[i] >> 4);
   }
   __syncthreads();
   if (g_wait_profile != nullptr && threadIdx.x < WAIT_SITES) {
-    int v = const_cast<int*>(abort_flag)[1 + threadIdx.x];
+    int v = const_cast<int*>(abort_flag)[4 + threadIdx.x];
     if (threadIdx.x == 23) v = static_cast<int>((clock64() - kernel_t0) >> 4);
     g_wait_profile[blockIdx.x * WAIT_SITES + threadIdx.x] = v;
   }
@@ -1098,13 +1114,14 @@ umma_selftest_kernel(int mode, const uint8_t* k_bytes, const uint8_t* q_bytes,
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* const smem = smem_raw + (smem0 - smem_u32(smem_raw));
-  constexpr int KOFF = 0, VOFF = 16384, QOFF = 32768, POFF = 34816, MISC = 36864;
+  constexpr int KOFF = 0, VOFF = 16384, QOFF = 32768, POFF = 34816, MISC = 36864;   // MISC: barrier, tensor-memory slot, abort flag + wait budget
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + MISC + 16);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + MISC + 8);
   const uint32_t bar = smem0 + MISC;
   if (t == 0) {
     *abort_flag = 0;
+    set_wait_budget(abort_flag, WAIT_BUDGET_CYCLES);
     mbar_init(bar, 1);
     fence_barrier_init();
   }
@@ -1174,6 +1191,28 @@ umma_selftest_kernel(int mode, const uint8_t* k_bytes, const uint8_t* q_bytes,
   }
 }
 
+// Wait self test (see foscar_b200.h): every thread waits, with the given cycle budget, for a
+// barrier phase that nothing completes. The first waiter to run out raises the CTA's abort flag
+// and FQ_STATUS_TIMEOUT; the others fall through; the kernel returns.
+__global__ void __launch_bounds__(64, 1) wait_selftest_kernel(long long budget, int* status,
+                                                              int* gave_up) {
+  __shared__ __align__(8) unsigned long long bar_word;
+  __shared__ __align__(8) int ctl_words[4];
+  volatile int* abort_flag = ctl_words;
+  const uint32_t bar = smem_u32(&bar_word);
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    set_wait_budget(abort_flag, budget);
+    mbar_init(bar, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  mbar_wait(bar, 0, abort_flag, status);    // runs out
+  mbar_wait(bar, 0, abort_flag, status);    // returns at once: the CTA has given up
+  __syncthreads();
+  if (threadIdx.x == 0 && gave_up != nullptr) *gave_up = *abort_flag;
+}
+
 }  // namespace fq
 
 // ---------------------------------------------------------------------------------------------
@@ -1208,6 +1247,7 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   if (stages < WORKER_GROUPS) return FQ_ERR_UNSUPPORTED;  // a group steps the ring by one lap at most
   P.ring_stages = stages;
   P.tile_tokens = SP::TT;
+  P.wait_budget = P.a.wait_budget_cycles > 0 ? P.a.wait_budget_cycles : WAIT_BUDGET_CYCLES;
   // Shared memory the ring leaves over holds more decoded work items (32 bytes each), up to
   // one per thread of the CTA's start-up pass.
   const int spare = SMEM_LIMIT - 1024 - SP::RING_OFF - stages * SP::STAGE;
@@ -1249,9 +1289,21 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
 
 using namespace fq;
 
+extern "C" int fq_tile_tokens(int32_t bits, int32_t head_dim) {
+  if ((bits != 2 && bits != 4) || (head_dim != 64 && head_dim != 128)) return FQ_ERR_UNSUPPORTED;
+  return tile_tokens(bits, head_dim);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void* stream) {
   if (!pools || !args) return FQ_ERR_BAD_ARG;
   if (!pools->k_codes || !pools->v_codes || !pools->scales) return FQ_ERR_BAD_ARG;
+  if (pools->num_kv_heads <= 0 || pools->num_pages <= 0) return FQ_ERR_BAD_ARG;
+  // the kernels read these with 16-byte vector loads and copies
+  if (!aligned16(pools->k_codes) || !aligned16(pools->v_codes) || !aligned16(pools->scales) ||
+      !aligned16(args->q) || (args->worklist && !aligned16(args->worklist)))
+    return FQ_ERR_BAD_ARG;
   // sub-head K groups: 64-channel groups at head_dim 128 (bf16 pair rings)
   if (pools->k_groups != 1 &&
       !(pools->k_groups == 2 && pools->head_dim == 128 && pools->scale_bf16))
@@ -1359,5 +1411,13 @@ extern "C" int fq_umma_selftest(int32_t mode, const uint8_t* k_bytes, const uint
   if (e != cudaSuccess) return static_cast<int>(e);
   umma_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
       mode, k_bytes, q_bytes, v_bytes, p_bytes, s_out, o_out, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fq_wait_selftest(int64_t budget_cycles, int32_t* status, int32_t* gave_up,
+                                void* stream) {
+  if (budget_cycles < 1 || budget_cycles > WAIT_BUDGET_CYCLES) return FQ_ERR_BAD_ARG;
+  wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(budget_cycles, status,
+                                                                         gave_up);
   return static_cast<int>(cudaGetLastError());
 }

@@ -9,7 +9,9 @@ constexpr int TILE = 128;            // MMA rows: tensor-memory lanes, threads o
 // Tokens per sequence tile. head_dim 128: one token per lane (two pages). head_dim 64: two tokens
 // per lane, t and 128 + t of the tile (four pages): their 64-byte operand rows sit side by side
 // in one 128-byte row, so a tile of 256 tokens costs what a 128-token tile of head_dim 128 costs.
-__host__ __device__ constexpr int tile_tokens(int head_dim) { return head_dim == 64 ? 256 : 128; }
+__host__ __device__ constexpr int tile_tokens(int /*bits*/, int head_dim) {
+  return head_dim == 64 ? 256 : 128;
+}
 constexpr int WORK_WORDS = 8;        // int32 words per explicit work-list row
 #ifndef FQ_WORKER_GROUPS
 #define FQ_WORKER_GROUPS 4
@@ -25,8 +27,9 @@ struct DecodeParams {
   int head_tiles;    // ceil(ratio / 8)
   int num_items;     // implicit: B*HKV*head_tiles*kv_splits; explicit: row capacity
   int ring_stages;
-  int tile_tokens;   // tile_tokens(head_dim)
+  int tile_tokens;   // tile_tokens(bits, head_dim)
   int item_slots;    // work items a CTA keeps decoded in shared memory
+  long long wait_budget;   // cycle budget of one device wait
 };
 
 struct WorkItem {
@@ -47,7 +50,7 @@ struct SmemPlan {
   __host__ __device__ static constexpr int row_swizzle(int row) {
     return CHUNKS == 4 ? (row >> 1) & 3 : (CHUNKS == 2 ? (row >> 2) & 1 : 0);
   }
-  static constexpr int TT = tile_tokens(D);            // tokens per tile
+  static constexpr int TT = tile_tokens(BITS, D);      // tokens per tile
   static constexpr bool PAIR = TT == 2 * TILE;         // two tokens per lane
   static constexpr int PPT = TT / PAGE;                // pages per tile
   static constexpr int K_OFF = 0;                      // a ring stage: K pages, V pages, records

@@ -4,7 +4,7 @@ CUDA-graph mode.
 Host-side mirror of the reference wrapper for the Blackwell arm (src/foscar/wrapper.py:569-1350
 eager, :1353-1676 graph mode): same call forms, argument meaning, properties and refusals.
 Planning differs by design. A plan is a list of pieces (request, KV head, head tile, range of
-128-token tiles) sized from the step's lengths and the SM count so that every CTA streams the
+sequence tiles) sized from the step's lengths and the SM count so that every CTA streams the
 same number of tiles; the reference picks one uniform split count from the longest request.
 When the lengths may not be read on the host (`max_kv_len=` given with device `seq_lens`) the
 plan is a uniform split count resolved on the device.
@@ -117,20 +117,29 @@ def graph_workspace_bytes(max_batch: int, num_qo_heads: int, layout: QuantKVLayo
         raise ValueError(f"the layout was resolved for {layout.arch} and {dev} is {arch}")
     _check_num_qo_heads(num_qo_heads, layout.num_kv_heads)
     sms = _dev.sm_count(dev)
-    tiles = -(-int(max_kv_len) // _lib.tile_tokens(layout.head_dim))
+    tiles = -(-int(max_kv_len) // _lib.tile_tokens(layout.bits, layout.head_dim))
+    ovh = _lib.piece_overhead(layout.bits, layout.head_dim)
     words = 0
     for batch in range(1, max_batch + 1):
         splits = _graph_split_cap(batch, layout.num_kv_heads,
-                                  _head_tiles(num_qo_heads, layout.num_kv_heads), sms, tiles)
+                                  _head_tiles(num_qo_heads, layout.num_kv_heads), sms, tiles, ovh)
         words = max(words, splits * batch * num_qo_heads * (layout.head_dim + 2))
     return 4 * words
 
 
-def _graph_split_cap(batch, hkv, head_tiles, sms, max_tiles):
-    """Most pieces one unit can get from the balanced planner: one more than the CTAs left once
-    every other unit holds one, and never more than its tiles."""
-    units = batch * hkv * head_tiles
-    return int(max(1, min(MAX_SPLITS, max_tiles, sms - min(units, sms) + 2)))
+def _graph_split_cap(batch, hkv, head_tiles, sms, max_tiles, overhead):
+    """The split cap a graph-mode bucket plans with (the leading extent of its partial buffers).
+
+    The balanced planner never cuts a unit into more pieces than the cap it is given (it raises
+    every CTA's share until the longest unit fits), so any cap is valid; this one is what the
+    most skewed step of the bucket wants: one request at `max_tiles` tiles and every other at a
+    single tile, which gives the smallest share per CTA against the longest unit."""
+    per_request = hkv * head_tiles
+    worst_total = (per_request * (max_tiles + overhead)
+                   + (batch - 1) * per_request * (1 + overhead) + overhead * (sms - 1))
+    share = max(overhead + 1, -(-worst_total // sms))
+    wanted = -(-max_tiles // max(1, share - overhead)) + 2
+    return int(max(1, min(MAX_SPLITS, max_tiles, sms, wanted)))
 
 
 class PagedDecodeWrapper:
@@ -168,9 +177,8 @@ class PagedDecodeWrapper:
         self._float_workspace_buffer = float_workspace_buffer
         self.device = float_workspace_buffer.device
         self._status = None
-        #: kernels this wrapper has launched (decode and merge), for benchmark accounting
+        #: kernels this wrapper has launched (decode and merge)
         self.launches = 0
-        self._decode_done_event = None
         self._invalidate_plan()
 
     def _invalidate_plan(self):
@@ -210,8 +218,18 @@ class PagedDecodeWrapper:
         return self._bits
 
     def last_status(self) -> int:
-        """Device status word of this wrapper's launches (0 = no fault). Waits for the device."""
-        return 0 if self._status is None else int(self._status.item())
+        """Device status word of this wrapper's launches (0 = no fault). Waits for the device.
+
+        A launch that ended on a device wait that ran out (bit 0x10) may have left the arrival
+        counters of split units non-zero; they are cleared here, on this stream, so that the next
+        launch or graph replay merges correctly again."""
+        if self._status is None:
+            return 0
+        word = int(self._status.item())
+        if word & _lib.STATUS_TIMEOUT and self._unit_counters is not None:
+            with _dev.on_device(self.device):
+                self._unit_counters.zero_()
+        return word
 
     def _status_ptr(self):
         if self._status is None:
@@ -511,8 +529,6 @@ class PagedDecodeWrapper:
         _lib.check(lib.fq_decode(ctypes.byref(cache._c_pools), ctypes.byref(args), stream),
                    "decode")
         self.launches += 1
-        if self._decode_done_event is not None:
-            self._decode_done_event.record()       # lets a benchmark time the decode kernel alone
         if self._merge and not fused:
             self.launches += 1
             counts = None if self._split_counts is None else self._split_counts.data_ptr()
@@ -631,8 +647,9 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
         ctas = _dev.sm_count(self.device)
         units = b * lay.num_kv_heads * ht
         words = int(lib.fq_worklist_words(b, lay.num_kv_heads, ht, ctas))
-        tiles = -(-self._max_kv_len // _lib.tile_tokens(d))
-        cap = _graph_split_cap(b, lay.num_kv_heads, ht, ctas, tiles)
+        tiles = -(-self._max_kv_len // _lib.tile_tokens(lay.bits, d))
+        cap = _graph_split_cap(b, lay.num_kv_heads, ht, ctas, tiles,
+                               _lib.piece_overhead(lay.bits, d))
         cap = min(cap, _fit_splits(self._float_workspace_buffer, b, hq, d))
         self._o_partial, self._l_partial, self._m_partial = _carve_partials(
             self._float_workspace_buffer, cap, b, hq, d)

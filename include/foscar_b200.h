@@ -136,6 +136,10 @@ typedef struct fq_decode_args {
    * split_counts: int32 per unit, pieces of each unit in an explicit list (NULL: kv_splits). */
   int32_t* unit_counters;
   const int32_t* split_counts;
+  /* Cycle budget of one device wait; 0 = the default (about a second). When a wait runs out the
+   * CTA gives up, FQ_STATUS_TIMEOUT is set and the output is invalid; unit_counters may then be
+   * left non-zero and must be cleared before the next launch. */
+  int64_t wait_budget_cycles;
 } fq_decode_args;
 
 int fq_decode(const fq_pools* pools, const fq_decode_args* args, void* stream);
@@ -187,8 +191,11 @@ int fq_merge_states(const float* o_shards, const float* lse_shards, int32_t num_
  * words; fq_worklist_words gives the size that always suffices) and the piece count of each
  * unit into split_counts [B * HKV * head_tiles]; returns the number of pieces, or a negative
  * FQ_ERR_* (FQ_ERR_TOO_LARGE when a unit would need more than max_splits pieces). `bits` (2 or
- * 4) sets the cost of a tile against the fixed cost of a piece; `head_dim` the tokens of a tile
- * (128; 256 at head_dim 64). */
+ * 4) and `head_dim` set the tokens of a tile (fq_tile_tokens) and the cost of a tile against the
+ * fixed cost of a piece (fq_piece_overhead, in tiles). No unit gets more than max_splits pieces:
+ * the planner raises every CTA's share until the longest unit fits. fq_tile_tokens has no
+ * reference counterpart (the reference's tile is fixed per build,
+ * src/foscar/_sm100/int_fold_decode.py:1509-1530). */
 int fq_plan_splits(int32_t batch, int32_t num_kv_heads, int32_t head_tiles, int32_t max_kv_len,
                    int32_t bits, int32_t head_dim, int32_t sm_count);
 int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t num_kv_heads,
@@ -197,6 +204,8 @@ int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t num_kv_head
                      int32_t bits, int32_t head_dim);
 int64_t fq_worklist_words(int32_t batch, int32_t num_kv_heads, int32_t head_tiles,
                           int32_t num_ctas);
+int fq_tile_tokens(int32_t bits, int32_t head_dim);
+int fq_piece_overhead(int32_t bits, int32_t head_dim);
 int64_t fq_workspace_bytes(int32_t max_splits, int32_t batch, int32_t num_qo_heads,
                            int32_t head_dim);
 
@@ -206,6 +215,13 @@ int64_t fq_workspace_bytes(int32_t max_splits, int32_t batch, int32_t num_qo_hea
 int fq_umma_selftest(int32_t mode, const uint8_t* k_bytes, const uint8_t* q_bytes,
                      const uint8_t* v_bytes, const uint8_t* p_bytes, float* s_out, float* o_out,
                      int32_t* status, void* stream);
+
+/* Wait self test: one small kernel whose threads wait, with the given cycle budget, for a
+ * barrier phase that nothing completes. The wait runs out, the kernel sets FQ_STATUS_TIMEOUT in
+ * *status and 1 in *gave_up and returns; the context stays usable. It exercises the give-up path
+ * every bounded device wait of this library shares (the reference traps instead,
+ * src/foscar/_sm100/int_fold_decode.py:131-175). */
+int fq_wait_selftest(int64_t budget_cycles, int32_t* status, int32_t* gave_up, void* stream);
 
 #ifdef __cplusplus
 }

@@ -76,3 +76,22 @@ def assert_pools_equal(cache, pools: CpuPools, pages=None):
         assert np.array_equal(vpm, pools.v_page_max), "v_page_max differs"
         hist = cache.v_max_hist.view(torch.int32).cpu().numpy().view(np.uint32)
         assert np.array_equal(hist, pools.v_max_hist), "v_max_hist differs"
+
+
+def pools_of_requests(cache, indptr, indices, requests):
+    """The oracle's pools filled with the cache's own bytes for the pages of `requests` only,
+    renumbered from 0: (pools, indptr', indices'). For batches too large to write twice (once on
+    the GPU, once by the CPU writer); the writer's bytes are compared elsewhere."""
+    lay = cache.layout
+    pages, new_indptr = [], [0]
+    for b in requests:
+        pages.extend(int(p) for p in indices[indptr[b]:indptr[b + 1]])
+        new_indptr.append(len(pages))
+    sel = torch.as_tensor(pages, dtype=torch.long, device=cache.k_codes.device)
+    kg = lay.k_quant[1] if lay.k_quant[1] < lay.head_dim else None
+    pools = CpuPools(len(pages), lay.num_kv_heads, lay.head_dim, lay.bits, k_group=kg,
+                     scale_dtype=lay.scale_dtype)
+    pools.k_codes = cache.k_codes[sel].cpu()
+    pools.v_codes = cache.v_codes[sel].cpu()
+    pools.scales = cache.scales[sel].cpu()
+    return pools, np.asarray(new_indptr, dtype=np.int32), np.arange(len(pages), dtype=np.int32)

@@ -38,28 +38,38 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
         _lib.load()
 
 
-def _plan(lens, hkv, ht, ctas, cap=64):
+def _plan(lens, hkv, ht, ctas, cap=64, bits=4, d=128):
     lib = _lib.load()
     lens = np.asarray(lens, dtype=np.int32)
     words = int(lib.fq_worklist_words(len(lens), hkv, ht, ctas))
     work = np.zeros(words, dtype=np.int32)
     counts = np.zeros(len(lens) * hkv * ht, dtype=np.int32)
     n = lib.fq_plan_worklist(lens.ctypes.data, len(lens), hkv, ht, ctas, cap, work.ctypes.data,
-                             words, counts.ctypes.data, 2, 128)
+                             words, counts.ctypes.data, bits, d)
     return n, work, counts
+
+
+def _pieces_by_unit(n, work):
+    rows = work[work[3]:work[3] + 8 * n].reshape(n, 8)
+    seen = {}
+    for b, kvh, t, t0, t1, slot, _, _ in rows:
+        seen.setdefault((b, kvh, t), []).append((t0, t1, slot))
+    return rows, seen
 
 
 @pytest.mark.parametrize("lens,hkv,ht,ctas", [
     ([128, 128], 8, 1, 148), ([1, 63, 64, 65, 5000, 131072], 8, 1, 148), ([100352], 8, 1, 148),
     (list(range(1, 300, 7)), 2, 2, 148), ([0, 5, 0], 1, 1, 4), ([70000] * 3, 1, 1, 7),
 ])
-def test_worklist_covers_every_tile_once(lens, hkv, ht, ctas):
-    n, work, counts = _plan(lens, hkv, ht, ctas)
+@pytest.mark.parametrize("bits", [2, 4])
+def test_worklist_covers_every_tile_once(lens, hkv, ht, ctas, bits):
+    tt = _lib.tile_tokens(bits, 128)
+    n, work, counts = _plan(lens, hkv, ht, ctas, bits=bits)
     assert n > 0 and work[0] == n and work[1] == len(lens) * hkv * ht and work[2] == ctas
     starts = work[8:8 + ctas + 1]
     assert starts[0] == 0 and starts[-1] == n and np.all(np.diff(starts) >= 0)
     rows = work[work[3]:work[3] + 8 * n].reshape(n, 8)
-    tiles = {b: -(-l // 128) if l > 0 else 0 for b, l in enumerate(lens)}
+    tiles = {b: -(-l // tt) if l > 0 else 0 for b, l in enumerate(lens)}
     seen = {}
     for b, kvh, t, t0, t1, slot, _, _ in rows:
         assert 0 <= b < len(lens) and 0 <= kvh < hkv and 0 <= t < ht and 0 <= t0 <= t1
@@ -80,9 +90,28 @@ def test_worklist_covers_every_tile_once(lens, hkv, ht, ctas):
         assert load.max() <= total / ctas * 1.15 + 8
 
 
-def test_worklist_respects_the_split_cap_and_buffer():
-    n, _, _ = _plan([131072], 1, 1, 148, cap=4)
-    assert n == _lib.ERR_TOO_LARGE
+@pytest.mark.parametrize("lens,hkv,ht,cap", [
+    ([131072], 1, 1, 4), ([100000] + [1] * 18, 8, 1, 2), ([131072] + [128] * 63, 8, 1, 2),
+    ([100352], 1, 1, 64), ([100352], 1, 1, 1), ([5000, 70000, 3], 2, 2, 3),
+    ([131072] * 3 + [64] * 300, 1, 1, 5),
+])
+def test_worklist_never_exceeds_the_split_cap(lens, hkv, ht, cap):
+    """No unit is cut into more pieces than the cap, whatever the skew: the planner raises the
+    share per CTA instead of refusing (a graph-mode update() must never fail on valid lengths)."""
+    n, work, counts = _plan(lens, hkv, ht, 148, cap=cap)
+    assert n > 0
+    assert counts.max() <= cap
+    rows, seen = _pieces_by_unit(n, work)
+    tt = _lib.tile_tokens(4, 128)
+    for (b, kvh, t), pieces in seen.items():
+        pieces.sort()
+        assert len(pieces) <= cap
+        assert pieces[0][0] == 0 and pieces[-1][1] == -(-lens[b] // tt)
+        for (a0, a1, _), (b0, _, _) in zip(pieces, pieces[1:]):
+            assert a1 == b0
+
+
+def test_worklist_refuses_a_short_buffer():
     lib = _lib.load()
     lens = np.array([100], dtype=np.int32)
     small = np.zeros(16, dtype=np.int32)
@@ -120,4 +149,7 @@ def test_worklist_tiles_hold_256_tokens_at_head_dim_64():
     for b, l in enumerate(lens):
         for kvh in range(hkv):
             assert covered[(b, kvh)] == -(-int(l) // 256)
-    assert _lib.tile_tokens(64) == 256 and _lib.tile_tokens(128) == 128
+    assert _lib.tile_tokens(2, 64) == 256 and _lib.tile_tokens(4, 64) == 256
+    assert _lib.tile_tokens(4, 128) == 128
+    assert _lib.tile_tokens(2, 128) in (128, 256)     # two tokens per lane in the INT2 build
+    assert _lib.piece_overhead(2, 128) > 0

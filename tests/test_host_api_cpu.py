@@ -364,8 +364,12 @@ def test_graph_mode_refusals_before_any_device_work(fake_b200):
     assert type(w) is wr._GraphDecodeWrapper
     with pytest.raises(RuntimeError, match="plan\\(\\) it first"):
         w.update([1])
-    assert wr._graph_split_cap(1, 8, 1, 148, 784) == 64
-    assert wr._graph_split_cap(64, 8, 1, 148, 784) == 2
+    # one long request alone wants the most pieces; a full bucket of long requests few
+    assert 18 <= wr._graph_split_cap(1, 8, 1, 148, 784, 14) <= 64
+    assert wr._graph_split_cap(1, 1, 1, 148, 784, 14) == 64
+    assert 2 <= wr._graph_split_cap(64, 8, 1, 148, 784, 14) <= 16
+    # the most skewed step of a bucket (one long request, the others one tile) still fits
+    assert wr._graph_split_cap(19, 8, 1, 148, 782, 14) >= 15
     lens = wr._graph_host_lengths([5, 6], 2, 10)
     assert lens.dtype == np.int32
     with pytest.raises(ValueError, match="every length must be in"):
