@@ -116,6 +116,24 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity,
 }
 #endif
 
+// Bounded wait for a shared-memory word that only grows (a count of events) to reach `want`.
+// One thread polls; the caller follows with a warp or group synchronisation.
+static __device__ __noinline__ void count_wait(volatile int* word, int want,
+                                               volatile int* abort_flag, int* status) {
+  long long t0 = 0;
+  for (uint32_t tries = 1; *word < want; ++tries) {
+    if ((tries & 31u) != 0) continue;
+    if (*abort_flag) return;
+    const long long now = clock64();
+    if (t0 == 0) t0 = now;
+    if (now - t0 > *reinterpret_cast<volatile long long*>(abort_flag + 2)) {
+      *abort_flag = 1;
+      if (status) atomicOr(status, FQ_STATUS_TIMEOUT);
+      return;
+    }
+  }
+}
+
 // Bounded wait that ignores the abort flag: used once, at exit, to let a CTA's own bulk copies
 // land before its shared memory is released.
 __device__ inline void mbar_wait_drain(uint32_t bar, uint32_t parity, long long budget) {
@@ -263,6 +281,19 @@ __device__ inline void umma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo
       : "memory");
 }
 
+// The same with the accumulate flag at run time (the first MMA of a chain that either starts or
+// continues an accumulator).
+template <uint32_t A_HI, uint32_t B_HI, uint32_t IDESC>
+__device__ inline void umma_ss_r(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "n"(A_HI), "n"(B_HI), "n"(IDESC), "r"(acc)
+      : "memory");
+}
+
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ inline void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                uint32_t accumulate) {
@@ -318,6 +349,44 @@ __device__ inline void tmem_st8(uint32_t taddr, const uint32_t* r) {
                "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
                "r"(r[7])
                : "memory");
+}
+__device__ inline void tmem_ld8p(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+                 "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ inline void tmem_ld16p(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ inline void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// One 128-byte operand row per lane in one instruction.
+__device__ inline void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+      "%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+      "r"(r[30]), "r"(r[31])
+      : "memory");
 }
 __device__ inline void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");

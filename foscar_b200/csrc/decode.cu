@@ -146,137 +146,6 @@ struct TmemPlan {
   static_assert(USED <= 512, "tensor memory plan exceeds 512 columns");
 };
 
-__device__ inline float warp_max_f32(float x) {
-  float r;
-  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
-  return r;
-}
-__device__ inline __half2 h2_exp2(__half2 x) {
-  uint32_t r, a = *reinterpret_cast<uint32_t*>(&x);
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(r) : "r"(a));
-  return *reinterpret_cast<__half2*>(&r);
-}
-__device__ inline uint32_t f16x2_to_e4m3x2(__half2 x) {
-  uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(r) : "r"(*reinterpret_cast<uint32_t*>(&x)));
-  return r;
-}
-__device__ inline __half2 e4m3x2_to_f16x2(uint32_t v) {
-  uint32_t r;
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(static_cast<uint16_t>(v)));
-  return *reinterpret_cast<__half2*>(&r);
-}
-
-// Load this thread's token row (RB bytes at `src`) as packed words.
-template <int BITS, int D>
-__device__ inline void load_row(uint32_t src, uint32_t (&w)[D * BITS / 32], int swz) {
-#pragma unroll
-  for (int v = 0; v < D * BITS / 128; ++v)
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(w[4 * v]), "=r"(w[4 * v + 1]), "=r"(w[4 * v + 2]), "=r"(w[4 * v + 3])
-                 : "r"(src + ((v ^ swz) << 4)));   // chunk v sits at chunk v ^ swz of the row
-}
-// Unpack packed words into exact operand bytes, one per code, in expansion order:
-// out[(8/BITS) * wi + k] = (w[wi] >> (BITS * k)) & mask.
-template <int BITS, int D>
-__device__ inline void expand_words(const uint32_t (&w)[D * BITS / 32], uint32_t (&out)[D / 4]) {
-  constexpr uint32_t MASK = BITS == 2 ? 0x03030303u : 0x0F0F0F0Fu;
-  constexpr int PER = 8 / BITS;  // output words per input word
-#pragma unroll
-  for (int i = 0; i < D * BITS / 32; ++i)
-#pragma unroll
-    for (int k = 0; k < PER; ++k) out[PER * i + k] = (w[i] >> (BITS * k)) & MASK;
-}
-// The cheaper unpack for INT2 V rows: odd output words keep their codes two bits up, i.e. hold
-// 4 * code, which is still an exact E4M3 byte (values up to 15 * 2^-9 are linear in the byte).
-// Five instead of seven instructions per packed word; the channels at those positions
-// (expanded position p with (p >> 2) & 1) come out of the PV MMA four times too large and are
-// scaled back once per work item (v_position_scale).
-template <int BITS, int D>
-__device__ inline void expand_words_v(const uint32_t (&w)[D * BITS / 32], uint32_t (&out)[D / 4]) {
-  if constexpr (BITS == 2) {
-#pragma unroll
-    for (int i = 0; i < D * BITS / 32; ++i) {
-      const uint32_t hi = w[i] >> 4;
-      out[4 * i + 0] = w[i] & 0x03030303u;
-      out[4 * i + 1] = w[i] & 0x0C0C0C0Cu;
-      out[4 * i + 2] = hi & 0x03030303u;
-      out[4 * i + 3] = hi & 0x0C0C0C0Cu;
-    }
-  } else {
-    expand_words<BITS, D>(w, out);
-  }
-}
-template <int BITS>
-__device__ inline float v_position_scale(int pos) {
-  return BITS == 2 && ((pos >> 2) & 1) ? 0.25f : 1.f;
-}
-
-// Final value to the output tensor in its dtype.
-__device__ __forceinline__ void store_value(void* out, int out_dtype, long long idx, float val) {
-  if (out_dtype == 0) static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(val);
-  else if (out_dtype == 1) static_cast<__half*>(out)[idx] = __float2half_rn(val);
-  else static_cast<float*>(out)[idx] = val;
-}
-
-// Merge of a split unit's partials: the arithmetic and slot order of merge_kernel. Heads h0,
-// h0 + hstep, ... (< gp) of the unit's head tile; the calling thread takes channel `ch`. Kept
-// out of line and rolled: it runs a few times per launch, and the kernel's code footprint is
-// what an item boundary pays for in instruction fetches.
-__device__ __noinline__ void merge_unit_partials(const DecodeParams& P, int d, int gp, int ch,
-                                                 bool writes_lse, int k, int b, int kvh, int ht,
-                                                 int h0, int hstep) {
-  constexpr float LN2 = 0.6931471805599453f;
-  __threadfence();
-  const long long rows = static_cast<long long>(P.a.batch) * P.a.num_qo_heads;
-#pragma unroll 1
-  for (int h = h0; h < gp; h += hstep) {
-    const int hl = ht * 8 + h;
-    if (hl >= P.heads_per_kv) continue;
-    const long long head = static_cast<long long>(kvh) * P.heads_per_kv + hl;
-    const long long row = static_cast<long long>(b) * P.a.num_qo_heads + head;
-    float M = -INFINITY, den = 0.f, acc = 0.f;
-    if (k <= 4) {
-      // the common case in one round trip
-      float ms[4], ls[4], os[4];
-#pragma unroll
-      for (int s = 0; s < 4; ++s) {
-        const bool on = s < k;
-        ms[s] = on ? __ldcg(P.a.m_partial + s * rows + row) : -INFINITY;
-        ls[s] = on ? __ldcg(P.a.l_partial + s * rows + row) : 0.f;
-        os[s] = on ? __ldcg(P.a.o_partial + (s * rows + row) * d + ch) : 0.f;
-      }
-#pragma unroll
-      for (int s = 0; s < 4; ++s) M = fmaxf(M, ms[s]);
-      if (M > -INFINITY) {
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-          if (s < k) {
-            const float wgt = exp2f(ms[s] - M);
-            den += wgt * ls[s];
-            acc += wgt * os[s];
-          }
-        }
-      }
-    } else {
-#pragma unroll 1
-      for (int s = 0; s < k; ++s) M = fmaxf(M, __ldcg(P.a.m_partial + s * rows + row));
-      if (M > -INFINITY) {
-#pragma unroll 4
-        for (int s = 0; s < k; ++s) {
-          const float wgt = exp2f(__ldcg(P.a.m_partial + s * rows + row) - M);
-          den += wgt * __ldcg(P.a.l_partial + s * rows + row);
-          acc += wgt * __ldcg(P.a.o_partial + (s * rows + row) * d + ch);
-        }
-      }
-    }
-    const bool live = den > 0.f;
-    store_value(P.a.out, P.a.out_dtype, row * d + ch, live ? acc / den * P.a.o_scale : 0.f);
-    if (writes_lse && P.a.lse != nullptr)
-      P.a.lse[row] = live ? (M + log2f(den)) * LN2 : -INFINITY;
-  }
-}
-
 // Worker role: one of four 128-thread groups. Group `wg` takes the tiles whose running index is
 // `wg` modulo 4 and carries each of them through every stage itself: unpack K into tensor memory,
 // unpack V into shared memory, fold the scales into the raw scores, softmax, write the P rows,
@@ -1290,7 +1159,8 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
 using namespace fq;
 
 extern "C" int fq_tile_tokens(int32_t bits, int32_t head_dim) {
-  if ((bits != 2 && bits != 4) || (head_dim != 64 && head_dim != 128)) return FQ_ERR_UNSUPPORTED;
+  if ((bits != 2 && bits != 4) || (head_dim != 64 && head_dim != 128 && head_dim != 256))
+    return FQ_ERR_UNSUPPORTED;
   return tile_tokens(bits, head_dim);
 }
 
@@ -1308,7 +1178,9 @@ extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void
   if (pools->k_groups != 1 &&
       !(pools->k_groups == 2 && pools->head_dim == 128 && pools->scale_bf16))
     return FQ_ERR_UNSUPPORTED;
-  if (pools->head_dim != 64 && pools->head_dim != 128) return FQ_ERR_UNSUPPORTED;
+  if (pools->head_dim != 64 && pools->head_dim != 128 && pools->head_dim != 256)
+    return FQ_ERR_UNSUPPORTED;
+  if (pools->head_dim == 256 && pools->k_groups != 1) return FQ_ERR_UNSUPPORTED;
   if (pools->bits != 2 && pools->bits != 4) return FQ_ERR_UNSUPPORTED;
   const fq_decode_args& a = *args;
   if (a.batch <= 0 || a.num_qo_heads <= 0 || a.num_qo_heads % pools->num_kv_heads) return FQ_ERR_BAD_ARG;
@@ -1334,6 +1206,7 @@ extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void
   }
   const int gp = std::min(P.heads_per_kv, 8) <= 4 ? 4 : 8;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pools->head_dim == 256) return launch_decode_wide(P, s);
 #define FQ_DISPATCH(DD, KK)                                                                   \
   do {                                                                                        \
     if (pools->bits == 2)                                                                     \

@@ -311,10 +311,10 @@ class PagedDecodeWrapper:
             raise NotImplementedError(
                 f"this build decodes token-wise layouts; k_quant={layout.k_quant} "
                 f"v_quant={layout.v_quant} has a channel-wise tensor")
-        if layout.head_dim not in (64, 128):
+        if layout.head_dim == 256 and layout.k_quant[1] < layout.head_dim:
             raise NotImplementedError(
-                f"this build's decode kernel takes head_dim 64 and 128; the layout has "
-                f"{layout.head_dim} (the cache writer and read-back do take it)")
+                f"this build decodes whole-head K groups at head_dim 256; got "
+                f"k_quant={layout.k_quant}")
         if layout.k_quant[1] < layout.head_dim and not (
                 layout.head_dim == 128 and layout.k_quant[1] == 64):
             raise NotImplementedError(

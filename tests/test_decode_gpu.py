@@ -80,6 +80,21 @@ def test_head_dim_64(bits, hq, hkv):
     _run_case(bits, 64, hq, hkv, [1, 64, 130, 2000, 9000], seed=3 + bits)
 
 
+@pytest.mark.parametrize("bits", [2, 4])
+@pytest.mark.parametrize("hq,hkv", [(16, 2), (8, 2), (24, 1)])
+def test_head_dim_256(bits, hq, hkv):
+    """head_dim 256 (two operand rows per token, two channel halves of the PV product): ragged
+    batch, planned splits, GQA 8 / 4 / 24 (three head tiles)."""
+    _run_case(bits, 256, hq, hkv, [1, 63, 64, 65, 129, 1000, 4097, 9000], seed=17 + bits)
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+def test_head_dim_256_splits_scales_and_outliers(bits):
+    _run_case(bits, 256, 16, 2, [5000, 257], kv_splits=3, host_lens=False)
+    _run_case(bits, 256, 16, 2, [3000, 130], scale_dtype=torch.bfloat16, seed=19)
+    _run_case(bits, 256, 16, 2, [20000, 700], outliers=True, q_scale=8.0, seed=23, q_descale=True)
+
+
 @pytest.mark.parametrize("bits,d", [(2, 128), (4, 128), (2, 64), (4, 64)])
 def test_bf16_scale_pools(bits, d):
     """Scale records stored as bf16 pairs (8 bytes a token): the decode reads the pool's own
@@ -222,7 +237,7 @@ def test_empty_request_in_a_batch():
         assert (out[live].float() - ref.float()).abs().max().item() <= 1e-2
 
 
-@pytest.mark.parametrize("bits,d", [(4, 64), (2, 128)])
+@pytest.mark.parametrize("bits,d", [(4, 64), (2, 128), (4, 256)])
 def test_many_single_tile_items(bits, d):
     """Hundreds of one-tile work items per CTA: most worker groups have no tile in most items,
     while the producer runs items ahead. Repeated launches must neither time out (status bit

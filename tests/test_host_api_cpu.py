@@ -379,16 +379,20 @@ def test_graph_mode_refusals_before_any_device_work(fake_b200):
 
 
 def test_plan_refuses_shapes_the_decode_kernel_lacks(recorder):
-    """head_dim 256 and K groups other than 64 channels at head_dim 128 are written and read
-    back by this build but not decoded: plan() says so instead of failing at run()."""
+    """K groups other than 64 channels at head_dim 128 (and any sub-head K group at head_dim 256)
+    are written and read back by this build but not decoded: plan() says so instead of failing
+    at run()."""
     w = PagedDecodeWrapper(torch.zeros(1 << 20, dtype=torch.uint8))
     indptr, indices = _plan_args()
     seq = torch.tensor([256, 200], dtype=torch.int32)
-    with pytest.raises(NotImplementedError, match="head_dim 64 and 128"):
-        w.plan(indptr, indices, seq, 16, _layout(head_dim=256, num_kv_heads=2))
+    with pytest.raises(NotImplementedError, match="whole-head K groups at head_dim 256"):
+        w.plan(indptr, indices, seq, 16, _layout(head_dim=256, num_kv_heads=2,
+                                                 k_quant=("token", 128)))
     _, cache = _cache(None)
     with pytest.raises(RuntimeError, match="Call plan"):
         w.run(torch.zeros(2, 32, 128).to(torch.float8_e4m3fn), cache)
+    w.plan(indptr, indices, seq, 16, _layout(head_dim=256, num_kv_heads=2))
+    assert w.bits == 4 or w.bits == 2
     ok = _layout(head_dim=128, k_quant=("token", 64))
     w.plan(indptr, indices, seq, 32, ok)
     assert w.bits == ok.bits
