@@ -39,6 +39,7 @@ def piece_overhead(bits: int, head_dim: int) -> int:
 class Pools(C.Structure):
     _fields_ = [("bits", C.c_int32), ("head_dim", C.c_int32), ("num_kv_heads", C.c_int32),
                 ("k_groups", C.c_int32), ("scale_bf16", C.c_int32), ("num_pages", C.c_int32),
+                ("k_channel_group", C.c_int32), ("reserved", C.c_int32),
                 ("k_codes", C.c_void_p), ("v_codes", C.c_void_p), ("scales", C.c_void_p),
                 ("v_page_max", C.c_void_p), ("v_max_hist", C.c_void_p)]
 
@@ -64,6 +65,8 @@ _PROTOTYPES = {
     "fq_error_string": (C.c_char_p, [C.c_int]),
     "fq_append": (C.c_int, [C.POINTER(Pools), _P, _P, _I64, _I64, _P, _I32, _I32, _I32, _P, _P]),
     "fq_append_quantized": (C.c_int, [C.POINTER(Pools), _P, _P, _P, _P, _P, _P, _P, _I32, _P, _P]),
+    "fq_append_page_groups": (C.c_int, [C.POINTER(Pools), _P, _P, _I64, _I64, _P, _P, _I32, _P,
+                                        _P]),
     "fq_dequantize": (C.c_int, [C.POINTER(Pools), _P, _P, _I64, _I64, _I64, _P, _P, _I32, _P, _P,
                                 _I32, _I32, _P, _P]),
     "fq_recount_vmax": (C.c_int, [C.POINTER(Pools), _P]),

@@ -62,10 +62,28 @@ __global__ void __launch_bounds__(128) dequant_kernel(DequantArgs a) {
   const long long blk = static_cast<long long>(page) * hkv + head;
   const int kg = a.p.k_groups;
   const int esz = a.p.scale_bf16 ? 2 : 4;
-  const long long block_elems = kg == 1 ? 4 * PAGE : 2 * kg * PAGE + 2 * PAGE;
+  const bool kch = a.p.k_channel_group != 0;   // K records per channel of the page
+  const long long block_elems =
+      kch ? 2 * PAGE + 2 * D : (kg == 1 ? 4 * PAGE : 2 * kg * PAGE + 2 * PAGE);
   const char* sblock = static_cast<const char*>(a.p.scales) + blk * block_elems * esz;
   const int c0 = lane * CH;
   const int grp = lane / (32 / kg);
+  // channel-wise K: this lane's channels' (s_d, z_d), the same for every row of the page
+  float sch[CH], zch[CH];
+  if (kch) {
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      if (!a.p.scale_bf16) {
+        const float* rec = reinterpret_cast<const float*>(sblock) + 2 * PAGE;
+        sch[i] = __ldg(rec + c0 + i);
+        zch[i] = __ldg(rec + D + c0 + i);
+      } else {
+        const __nv_bfloat16* rec = reinterpret_cast<const __nv_bfloat16*>(sblock) + 2 * PAGE;
+        sch[i] = __bfloat162float(rec[c0 + i]);
+        zch[i] = __bfloat162float(rec[D + c0 + i]);
+      }
+    }
+  }
 
   for (int t = warp; t < rows; t += 4) {
     const long long orow = out0 + t;
@@ -73,8 +91,16 @@ __global__ void __launch_bounds__(128) dequant_kernel(DequantArgs a) {
       if (lane == 0 && a.status) atomicOr(a.status, FQ_STATUS_BAD_ROW);
       continue;
     }
-    float sk, zk, sv, zv;
-    if (!a.p.scale_bf16) {
+    float sk = 0.f, zk = 0.f, sv, zv;
+    if (kch) {
+      if (!a.p.scale_bf16) {
+        const float2 r = __ldg(reinterpret_cast<const float2*>(sblock) + t);
+        sv = r.x; zv = r.y;
+      } else {
+        const uint32_t vr = __ldg(reinterpret_cast<const uint32_t*>(sblock) + t);
+        sv = __uint_as_float(vr << 16); zv = __uint_as_float(vr & 0xFFFF0000u);
+      }
+    } else if (!a.p.scale_bf16) {
       const float4 r = __ldg(reinterpret_cast<const float4*>(sblock) + t);
       sk = r.x; zk = r.y; sv = r.z; zv = r.w;
     } else {
@@ -99,7 +125,8 @@ __global__ void __launch_bounds__(128) dequant_kernel(DequantArgs a) {
       const int off = code_bit_offset<BITS>(c0 + i);
       const uint32_t qk = (__ldg(krow + (off >> 5)) >> (off & 31)) & MASK;
       const uint32_t qv = (__ldg(vrow + (off >> 5)) >> (off & 31)) & MASK;
-      ko[i] = __float2bfloat16_rn(__fmaf_rn(sk, static_cast<float>(qk), zk));
+      ko[i] = __float2bfloat16_rn(kch ? __fmaf_rn(sch[i], static_cast<float>(qk), zch[i])
+                                      : __fmaf_rn(sk, static_cast<float>(qk), zk));
       vo[i] = __float2bfloat16_rn(__fmaf_rn(sv, static_cast<float>(qv), zv));
     }
     __nv_bfloat16* kd = a.k_out + orow * a.k_stride + static_cast<long long>(head) * D + c0;

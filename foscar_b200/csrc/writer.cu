@@ -32,10 +32,25 @@ struct WriterArgs {
   const float* v_scale;
   const float* v_zero;
   const long long* slots;
+  // page-group mode (slots == nullptr): token i is row i % 64 of group i / 64, which goes to
+  // page page_ids[i / 64]; rows at or past valid[i / 64] are skipped
+  const int* page_ids;
+  const int* valid;
   int num_tokens;
   int k_clip, v_clip;
   int* status;
 };
+
+// Where a token goes: its slot (page * 64 + position), negative for a token to skip.
+__device__ inline long long slot_of(const WriterArgs& a, int token) {
+  if (a.slots != nullptr) return a.slots[token];
+  const int group = token >> 6, pos = token & (PAGE - 1);
+  if (a.valid != nullptr && pos >= __ldg(a.valid + group)) return -1;
+  const int page = __ldg(a.page_ids + group);
+  // a page id outside the pool is reported by the row pass as a slot outside the cache
+  if (page < 0) return static_cast<long long>(a.p.num_pages) * PAGE;
+  return static_cast<long long>(page) * PAGE + pos;
+}
 
 __device__ inline float warp_group_min(float x, int lanes) {
   for (int o = lanes >> 1; o > 0; o >>= 1) x = fminf(x, __shfl_xor_sync(0xFFFFFFFFu, x, o));
@@ -49,7 +64,8 @@ __device__ inline float warp_group_max(float x, int lanes) {
 // Bytes of one (page, head) scale block and where a token's records sit in it.
 __device__ inline long long scale_block_bytes(const fq_pools& p) {
   const int esz = p.scale_bf16 ? 2 : 4;
-  const int elems = p.k_groups == 1 ? 4 * PAGE : 2 * p.k_groups * PAGE + 2 * PAGE;
+  int elems = p.k_groups == 1 ? 4 * PAGE : 2 * p.k_groups * PAGE + 2 * PAGE;
+  if (p.k_channel_group != 0) elems = 2 * PAGE + 2 * p.head_dim;   // V ring, K channel rows
   return static_cast<long long>(elems) * esz;
 }
 
@@ -81,7 +97,7 @@ __global__ void page_start_kernel(WriterArgs a) {
   const int hkv = a.p.num_kv_heads;
   if (warp >= a.num_tokens * hkv) return;
   const int token = warp / hkv, head = warp % hkv;
-  const long long slot = a.slots[token];
+  const long long slot = slot_of(a, token);
   if (slot < 0 || (slot & (PAGE - 1)) != 0) return;
   const long long page = slot >> 6;
   if (page >= a.p.num_pages) return;  // reported by append_kernel
@@ -169,6 +185,7 @@ __device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta
   if (warp >= a.num_tokens * hkv) return;
   const int token = warp / hkv, head = warp % hkv;
   const int kg = a.p.k_groups;
+  const bool kch = a.p.k_channel_group != 0;   // K goes by whole pages (append_k_channel_kernel)
   const int c0 = lane * CH;
   // The token's rows are requested before its slot is known: the slot, the rows and (below) the
   // page's maximum cell are three global round trips, and only the last depends on another.
@@ -179,18 +196,18 @@ __device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta
   uint4 uk = make_uint4(0, 0, 0, 0), uv = make_uint4(0, 0, 0, 0);
   if (!PREQ) {
     if constexpr (CH == 8) {
-      uk = __ldg(reinterpret_cast<const uint4*>(kr));
+      if (!kch) uk = __ldg(reinterpret_cast<const uint4*>(kr));
       uv = __ldg(reinterpret_cast<const uint4*>(vr));
     } else if constexpr (CH == 4) {
-      const uint2 k2 = __ldg(reinterpret_cast<const uint2*>(kr));
+      const uint2 k2 = kch ? make_uint2(0, 0) : __ldg(reinterpret_cast<const uint2*>(kr));
       const uint2 v2 = __ldg(reinterpret_cast<const uint2*>(vr));
       uk.x = k2.x; uk.y = k2.y; uv.x = v2.x; uv.y = v2.y;
     } else {
-      uk.x = __ldg(reinterpret_cast<const uint32_t*>(kr));
+      if (!kch) uk.x = __ldg(reinterpret_cast<const uint32_t*>(kr));
       uv.x = __ldg(reinterpret_cast<const uint32_t*>(vr));
     }
   }
-  const long long slot = a.slots[token];
+  const long long slot = slot_of(a, token);
   if (slot < 0) return;
   const long long page = slot >> 6;
   const int pos = static_cast<int>(slot & (PAGE - 1));
@@ -286,7 +303,7 @@ __device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta
   const long long row_index = (page * hkv + head) * PAGE + pos;
   if (lane % LPW == 0) {
     const int word = c0 / W;
-    reinterpret_cast<uint32_t*>(a.p.k_codes + row_index * RB)[word] = kw;
+    if (!kch) reinterpret_cast<uint32_t*>(a.p.k_codes + row_index * RB)[word] = kw;
     reinterpret_cast<uint32_t*>(a.p.v_codes + row_index * RB)[word] = vw;
   }
 
@@ -300,7 +317,18 @@ __device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta
   if (lane == 0) {
     char* block = static_cast<char*>(a.p.scales) + (page * hkv + head) * scale_block_bytes(a.p);
     uint32_t sv_bits;
-    if (!a.p.scale_bf16) {
+    if (kch) {
+      // V ring at the front of the block: token t's (s_v, z_v) at element 2t
+      if (!a.p.scale_bf16) {
+        reinterpret_cast<float2*>(block)[pos] = make_float2(sv, zv);
+        sv_bits = __float_as_uint(sv);
+      } else {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(sv, zv);
+        const uint32_t vrec = *reinterpret_cast<const uint32_t*>(&h);
+        reinterpret_cast<uint32_t*>(block)[pos] = vrec;
+        sv_bits = vrec << 16;
+      }
+    } else if (!a.p.scale_bf16) {
       // f32 pool: whole-head K only
       reinterpret_cast<float4*>(block)[pos] = make_float4(sk, zk, sv, zv);
       sv_bits = __float_as_uint(sv);
@@ -331,6 +359,84 @@ __device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta
         if (old < sv_bits) settle_count_local(hist_delta, old, sv_bits);
       }
     }
+  }
+}
+
+// -------------------------------------------------------------------------------------------
+// 3. K per channel over a page's tokens
+// -------------------------------------------------------------------------------------------
+// One CTA per (page group, KV head): the group's K rows go to shared memory; thread d takes
+// channel d through the token-wise quantizer's arithmetic along the token axis (exact min/max
+// over the valid tokens, z = clamp(min), s = max(max - z, 1e-8) / qmax, codes from the f32 s)
+// and leaves one code byte per (token, channel); the CTA then assembles the packed token rows
+// (src/foscar/_sm100/code_layout.py:24-43) and stores them and the channel records.
+template <int BITS, int D>
+__global__ void __launch_bounds__(256) append_k_channel_kernel(WriterArgs a) {
+  constexpr int QMAX = (1 << BITS) - 1;
+  constexpr int W = 32 / BITS;             // codes per word
+  constexpr int WORDS = D * BITS / 32;     // words per token row
+  extern __shared__ __align__(16) uint8_t smem_k[];
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_k);   // [64][D]
+  uint8_t* codes = smem_k + PAGE * D * 2;                            // [64][D]
+  const int hkv = a.p.num_kv_heads;
+  const int group = blockIdx.x / hkv, head = blockIdx.x % hkv;
+  int n = a.valid != nullptr ? __ldg(a.valid + group) : PAGE;
+  if (n > PAGE) n = PAGE;
+  if (n <= 0) return;
+  const int page = __ldg(a.page_ids + group);
+  if (page < 0 || page >= a.p.num_pages) return;   // reported by the row pass
+  // the group's rows, 16 bytes per thread and step
+  constexpr int CPR = D / 8;   // 16-byte chunks per row
+  for (int i = threadIdx.x; i < n * CPR; i += blockDim.x) {
+    const int j = i / CPR, c = i % CPR;
+    const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(a.k) +
+                               (static_cast<long long>(group) * PAGE + j) * a.k_stride +
+                               static_cast<long long>(head) * D + 8 * c;
+    reinterpret_cast<uint4*>(tile + j * D)[c] = __ldg(reinterpret_cast<const uint4*>(src));
+  }
+  __syncthreads();
+  const long long blk = static_cast<long long>(page) * hkv + head;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float mn = __bfloat162float(tile[d]), mx = mn;
+    for (int j = 1; j < n; ++j) {
+      const float x = __bfloat162float(tile[j * D + d]);
+      mn = fminf(mn, x);
+      mx = fmaxf(mx, x);
+    }
+    const bool inside = mx <= ENVELOPE && mn >= -ENVELOPE;
+    const float z = fminf(fmaxf(mn, -ENVELOPE), ENVELOPE);
+    const float top = fminf(fmaxf(mx, -ENVELOPE), ENVELOPE);
+    const float s = __fdiv_rn(fmaxf(__fsub_rn(top, z), S_CLAMP), static_cast<float>(QMAX));
+    for (int j = 0; j < n; ++j) {
+      float x = __bfloat162float(tile[j * D + d]);
+      if (!inside) x = fminf(fmaxf(x, -ENVELOPE), ENVELOPE);
+      const float dividend = fmaxf(__fsub_rn(x, z), DIVIDEND_FLOOR);
+      const int q = min(__float2int_rn(__fdiv_rn(dividend, s)), QMAX);
+      codes[j * D + d] = static_cast<uint8_t>(q);
+    }
+    // the channel's record after the block's V ring: row 0 s_d, row 1 z_d
+    char* block = static_cast<char*>(a.p.scales) + blk * scale_block_bytes(a.p);
+    if (!a.p.scale_bf16) {
+      float* rec = reinterpret_cast<float*>(block) + 2 * PAGE;
+      rec[d] = s;
+      rec[D + d] = z;
+    } else {
+      __nv_bfloat16* rec = reinterpret_cast<__nv_bfloat16*>(block) + 2 * PAGE;
+      rec[d] = __float2bfloat16_rn(s);
+      rec[D + d] = __float2bfloat16_rn(z);
+    }
+  }
+  __syncthreads();
+  // packed rows: field f of word w holds channel W*w + f/2 + (W/2)*(f%2)
+  uint32_t* rows = reinterpret_cast<uint32_t*>(a.p.k_codes + blk * PAGE * (D * BITS / 8));
+  for (int i = threadIdx.x; i < n * WORDS; i += blockDim.x) {
+    const int j = i / WORDS, w = i % WORDS;
+    const uint8_t* src = codes + j * D + W * w;
+    uint32_t word = 0;
+#pragma unroll
+    for (int f = 0; f < W; ++f)
+      word |= static_cast<uint32_t>(src[(f >> 1) + (W / 2) * (f & 1)]) << (BITS * f);
+    rows[j * WORDS + w] = word;
   }
 }
 
@@ -371,8 +477,27 @@ static int launch_append(const WriterArgs& a, cudaStream_t stream) {
   return FQ_ERR_UNSUPPORTED;
 }
 
+template <int BITS, int D>
+static int launch_k_channel(const WriterArgs& a, int groups, cudaStream_t stream) {
+  const int smem = PAGE * D * 3;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !configured[dev])) {
+    cudaError_t e = cudaFuncSetAttribute(append_k_channel_kernel<BITS, D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  append_k_channel_kernel<BITS, D>
+      <<<static_cast<unsigned>(groups) * a.p.num_kv_heads, 256, smem, stream>>>(a);
+  return static_cast<int>(cudaGetLastError());
+}
+
 static int check_pools(const fq_pools* p) {
   if (!p || !p->k_codes || !p->v_codes || !p->scales) return FQ_ERR_BAD_ARG;
+  if (p->k_channel_group != 0 && (p->k_channel_group != PAGE || p->k_groups != 1))
+    return FQ_ERR_UNSUPPORTED;
   if (p->bits != 2 && p->bits != 4) return FQ_ERR_UNSUPPORTED;
   if (p->head_dim != 64 && p->head_dim != 128 && p->head_dim != 256) return FQ_ERR_UNSUPPORTED;
   if (p->k_groups != 1 && p->k_groups != 2 && p->k_groups != 4) return FQ_ERR_UNSUPPORTED;
@@ -385,11 +510,48 @@ static int check_pools(const fq_pools* p) {
 
 }  // namespace fq
 
+extern "C" int fq_append_page_groups(const fq_pools* pools, const void* k, const void* v,
+                                     int64_t k_token_stride, int64_t v_token_stride,
+                                     const int32_t* page_ids, const int32_t* valid,
+                                     int32_t num_page_groups, int32_t* status, void* stream) {
+  if (int e = fq::check_pools(pools)) return e;
+  if (pools->k_channel_group != FQ_PAGE_SIZE) return FQ_ERR_UNSUPPORTED;
+  if (num_page_groups < 0 || (num_page_groups > 0 && (!k || !v || !page_ids)))
+    return FQ_ERR_BAD_ARG;
+  if (num_page_groups == 0) return 0;
+  if (num_page_groups > (0x7FFFFFFF >> 6)) return FQ_ERR_TOO_LARGE;
+  if ((reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
+      (k_token_stride * 2) % 16 || (v_token_stride * 2) % 16)
+    return FQ_ERR_BAD_ARG;
+  fq::WriterArgs a{};
+  a.p = *pools;
+  a.k = k; a.v = v;
+  a.k_stride = k_token_stride; a.v_stride = v_token_stride;
+  a.page_ids = page_ids;
+  a.valid = valid;
+  a.num_tokens = num_page_groups * FQ_PAGE_SIZE;
+  a.k_clip = a.v_clip = -1;
+  a.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // V rows, V records, page maxima: the token-wise row pass (it skips K for these pools)
+  if (int e = fq::launch_append<false>(a, s)) return e;
+#define FQ_LAUNCH(B, DD) \
+  if (pools->bits == B && pools->head_dim == DD) return fq::launch_k_channel<B, DD>(a, num_page_groups, s);
+  FQ_LAUNCH(2, 64) FQ_LAUNCH(2, 128) FQ_LAUNCH(2, 256)
+  FQ_LAUNCH(4, 64) FQ_LAUNCH(4, 128) FQ_LAUNCH(4, 256)
+#undef FQ_LAUNCH
+  return FQ_ERR_UNSUPPORTED;
+}
+
 extern "C" int fq_append(const fq_pools* pools, const void* k, const void* v,
                          int64_t k_token_stride, int64_t v_token_stride,
                          const int64_t* slot_mapping, int32_t num_tokens, int32_t k_clip,
                          int32_t v_clip, int32_t* status, void* stream) {
   if (int e = fq::check_pools(pools)) return e;
+  if (pools->k_channel_group != 0) return FQ_ERR_UNSUPPORTED;   // fq_append_page_groups
+  if ((reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
+      (k_token_stride * 2) % 16 || (v_token_stride * 2) % 16)
+    return FQ_ERR_BAD_ARG;
   if (num_tokens < 0 || (num_tokens > 0 && (!k || !v || !slot_mapping))) return FQ_ERR_BAD_ARG;
   if (k_clip >= pools->head_dim || v_clip >= pools->head_dim) return FQ_ERR_BAD_ARG;
   fq::WriterArgs a{};
@@ -410,6 +572,7 @@ extern "C" int fq_append_quantized(const fq_pools* pools, const uint8_t* k_codes
                                    const float* v_zero, const int64_t* slot_mapping,
                                    int32_t num_tokens, int32_t* status, void* stream) {
   if (int e = fq::check_pools(pools)) return e;
+  if (pools->k_channel_group != 0) return FQ_ERR_UNSUPPORTED;
   if (num_tokens < 0 || (num_tokens > 0 && (!k_codes || !v_codes || !k_scale || !k_zero ||
                                             !v_scale || !v_zero || !slot_mapping)))
     return FQ_ERR_BAD_ARG;

@@ -133,6 +133,12 @@ class QuantKVLayout:
     def is_token_wise(self) -> bool:
         return self.k_quant[0] == "token" and self.v_quant[0] == "token"
 
+    @property
+    def is_page_channel_k(self) -> bool:
+        """K per channel over the 64 tokens of a page, V per token over the whole head: the
+        channel-wise layout this build writes (by whole pages), reads back and decodes."""
+        return self.k_quant == ("channel", PAGE_SIZE) and self.v_quant == ("token", self.head_dim)
+
     def pool_dtypes(self) -> dict:
         return {"k_codes": torch.uint8, "v_codes": torch.uint8, "scales": self.scale_dtype,
                 "v_page_max": V_PAGE_MAX_DTYPE if self.has_v_page_max else None}
@@ -241,7 +247,9 @@ class QuantKVCache:
         self._c_pools = _lib.Pools(
             bits=layout.bits, head_dim=layout.head_dim, num_kv_heads=layout.num_kv_heads,
             k_groups=k_groups, scale_bf16=int(layout.scale_dtype == torch.bfloat16),
-            num_pages=self.num_pages, k_codes=k_codes.data_ptr(), v_codes=v_codes.data_ptr(),
+            num_pages=self.num_pages,
+            k_channel_group=layout.k_quant[1] if layout.k_quant[0] == "channel" else 0,
+            k_codes=k_codes.data_ptr(), v_codes=v_codes.data_ptr(),
             scales=scales.data_ptr(),
             v_page_max=None if v_page_max is None else v_page_max.data_ptr(),
             v_max_hist=None if v_max_hist is None else v_max_hist.data_ptr())
@@ -256,7 +264,9 @@ class QuantKVCache:
         if not lay.is_token_wise:
             raise NotImplementedError(
                 f"{method}() writes token-wise layouts only; k_quant={lay.k_quant} "
-                f"v_quant={lay.v_quant} has a channel-wise tensor")
+                f"v_quant={lay.v_quant} has a channel-wise tensor"
+                + (" (write it by whole pages with append_page_groups())"
+                   if lay.is_page_channel_k else ""))
 
     def _check_slots(self, slot_mapping, num_tokens):
         if (not isinstance(slot_mapping, torch.Tensor) or slot_mapping.dtype != torch.int64
@@ -315,6 +325,59 @@ class QuantKVCache:
                 slot_mapping.data_ptr(), k.shape[0], kc, vc, self.status.data_ptr(),
                 _dev.current_stream_ptr(self.device)), "append")
 
+    def append_page_groups(self, k: torch.Tensor, v: torch.Tensor, page_indices: torch.Tensor,
+                           valid_tokens: Optional[torch.Tensor] = None) -> None:
+        """Quantize and write whole pages of a cache whose K is quantized per channel over the
+        64 tokens of a page (`k_quant=("channel", 64)`, V per token). The reference's decode
+        reads this layout (src/foscar/_sm100/int_fold_decode.py:5012-5036) but its `append`
+        refuses it (src/foscar/kv_cache.py:643-644); this is the writer it lacks.
+
+        k, v: bfloat16 [P * 64, HKV, D] (same layout rules as `append`), page i's tokens being
+        rows [64 i, 64 i + valid_tokens[i]); page_indices int32 [P]; valid_tokens int32 [P] or
+        None (every page full). A channel's (s, z) come from the page's valid tokens only, so a
+        page that gains tokens (the last page of a growing context) is written again with all of
+        them; an engine keeps those few tokens in bf16 until then."""
+        lay = self.layout
+        if not lay.is_page_channel_k:
+            raise NotImplementedError(
+                f"append_page_groups() writes k_quant=('channel', {PAGE_SIZE}) with token-wise V; "
+                f"this cache has k_quant={lay.k_quant} v_quant={lay.v_quant}")
+        if (not isinstance(page_indices, torch.Tensor) or page_indices.dtype != torch.int32
+                or page_indices.dim() != 1 or not page_indices.is_contiguous()
+                or page_indices.device != self.device):
+            raise ValueError(f"page_indices must be a contiguous int32 [P] tensor on {self.device}")
+        groups = page_indices.numel()
+        if valid_tokens is not None and (
+                not isinstance(valid_tokens, torch.Tensor) or valid_tokens.dtype != torch.int32
+                or tuple(valid_tokens.shape) != (groups,) or not valid_tokens.is_contiguous()
+                or valid_tokens.device != self.device):
+            raise ValueError(f"valid_tokens must be a contiguous int32 [{groups}] tensor on "
+                             f"{self.device}")
+        shape = (groups * PAGE_SIZE, lay.num_kv_heads, lay.head_dim)
+        for name, x in (("k", k), ("v", v)):
+            if not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 \
+                    or tuple(x.shape) != shape:
+                raise ValueError(f"{name} must be a bfloat16 {list(shape)} tensor (64 rows per "
+                                 f"page); got {getattr(x, 'dtype', None)} "
+                                 f"{tuple(getattr(x, 'shape', ()))}")
+            if x.device != self.device:
+                raise ValueError(f"{name} is on {x.device}; the cache is on {self.device}")
+            if x.stride(2) != 1 or x.stride(1) != lay.head_dim:
+                raise ValueError(f"{name} must have a contiguous [num_kv_heads, head_dim] row "
+                                 f"per token (strides (*, {lay.head_dim}, 1)); got "
+                                 f"{tuple(x.stride())}")
+            if x.data_ptr() % 16 or (x.stride(0) * x.element_size()) % 16:
+                raise ValueError(f"every token row of {name} must start 16-byte aligned")
+        if groups == 0:
+            return
+        with _dev.on_device(self.device):
+            _lib.check(_lib.load().fq_append_page_groups(
+                ctypes.byref(self._c_pools), k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0),
+                page_indices.data_ptr(),
+                None if valid_tokens is None else valid_tokens.data_ptr(), groups,
+                self.status.data_ptr(), _dev.current_stream_ptr(self.device)),
+                "append_page_groups")
+
     def append_quantized(self, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero,
                          slot_mapping) -> None:
         """Layout-only write of engine-quantized tokens (src/foscar/kv_cache.py:689-767): codes
@@ -361,9 +424,10 @@ class QuantKVCache:
         (src/foscar/kv_cache.py:792-877). No host wait, no allocation, capturable. Out-of-range
         page ids, rows or lengths are skipped and set a status bit (the reference traps)."""
         lay = self.layout
-        if not lay.is_token_wise:
+        if not lay.is_token_wise and not lay.is_page_channel_k:
             raise NotImplementedError(
-                f"dequantize() reads token-wise layouts only, the layouts append() writes; "
+                f"dequantize() reads token-wise layouts only, the layouts append() writes (and "
+                f"K per channel over a page, which append_page_groups() writes); "
                 f"k_quant={lay.k_quant} v_quant={lay.v_quant} has a channel-wise tensor")
         H, D = lay.num_kv_heads, lay.head_dim
         for name, x in (("k_out", k_out), ("v_out", v_out)):

@@ -38,7 +38,9 @@ extern "C" {
 /* One layer's pools (reference: QuantKVCache, src/foscar/kv_cache.py:477-533).
  * k_codes, v_codes: uint8 [num_pages, num_kv_heads, 64, head_dim*bits/8].
  * scales: [num_pages, num_kv_heads, 64, 4] (s_k,z_k,s_v,z_v) when k_groups == 1, else the
- *   sectioned block [num_pages, num_kv_heads, 2*k_groups*64 + 128]; f32 or bf16.
+ *   sectioned block [num_pages, num_kv_heads, 2*k_groups*64 + 128]; f32 or bf16. With
+ *   k_channel_group == 64 (k_groups 1) the block is [128 + 2*head_dim]: token t's (s_v, z_v) at
+ *   2t, then the page's K channel rows s_d and z_d (src/foscar/quant_layout.py:9-21, 57-85).
  * v_page_max: uint32 [num_pages, num_kv_heads]; v_max_hist: uint32 [256]. */
 typedef struct fq_pools {
   int32_t bits;          /* 2 or 4 */
@@ -47,6 +49,8 @@ typedef struct fq_pools {
   int32_t k_groups;      /* head_dim / K token-wise group: 1, 2 or 4 */
   int32_t scale_bf16;    /* 0: f32 records, 1: bf16 records */
   int32_t num_pages;
+  int32_t k_channel_group; /* 0: K per token; 64: K per channel over the 64 tokens of a page */
+  int32_t reserved;
   uint8_t* k_codes;
   uint8_t* v_codes;
   void* scales;
@@ -72,6 +76,19 @@ int fq_append_quantized(const fq_pools* pools, const uint8_t* k_codes, const flo
                         const float* k_zero, const uint8_t* v_codes, const float* v_scale,
                         const float* v_zero, const int64_t* slot_mapping, int32_t num_tokens,
                         int32_t* status, void* stream);
+
+/* Quantize and write whole page groups of a cache whose K is quantized per channel over the 64
+ * tokens of a page (k_channel_group == 64) and whose V is per token: k, v bf16, page i's tokens
+ * being rows [64 i, 64 i + valid[i]) (token strides in elements); page_ids int32 [P]; valid
+ * int32 [P] or NULL (all 64). K statistics run over a page's valid tokens only; code rows past
+ * them are not written and their V records are cleared. A page that gains tokens is written
+ * again with all of them. The reference has no counterpart: its append refuses these layouts
+ * (src/foscar/kv_cache.py:643-644) although its decode reads them
+ * (src/foscar/_sm100/int_fold_decode.py:5012-5036). */
+int fq_append_page_groups(const fq_pools* pools, const void* k, const void* v,
+                          int64_t k_token_stride, int64_t v_token_stride,
+                          const int32_t* page_ids, const int32_t* valid, int32_t num_page_groups,
+                          int32_t* status, void* stream);
 
 /* Read K,V of a batch back into bf16 rows [N, HKV, D]: out[out_indptr[b]+t] =
  * bf16(fma(s, q, z)) for t < seq_lens[b]. Stands in for QuantKVCache.dequantize

@@ -200,8 +200,18 @@ def test_append_argument_refusals(fake_b200):
     lay2, cache2 = _cache(fake_b200, k_quant=("channel", 64))
     with pytest.raises(NotImplementedError, match="token-wise layouts only"):
         cache2.append(k, k, slots)
+    # K per channel over a page is written by whole pages and read back; a channel-wise V is not
+    with pytest.raises(NotImplementedError, match="append_page_groups"):
+        cache2.append(k, k, slots)
+    with pytest.raises(ValueError, match="page_indices must be a contiguous int32"):
+        cache2.append_page_groups(k, k, slots)
+    with pytest.raises(ValueError, match="64 rows per page"):
+        cache2.append_page_groups(k, k, torch.zeros(1, dtype=torch.int32))
+    with pytest.raises(NotImplementedError, match="append_page_groups\\(\\) writes k_quant"):
+        cache.append_page_groups(k, k, torch.zeros(1, dtype=torch.int32))
+    lay3, cache3 = _cache(fake_b200, k_quant=("channel", 64), v_quant=("channel", 64))
     with pytest.raises(NotImplementedError, match="token-wise layouts only"):
-        cache2.dequantize(k, k, slots.int(), slots.int(), slots.int(), slots.int())
+        cache3.dequantize(k, k, slots.int(), slots.int(), slots.int(), slots.int())
 
 
 def test_append_quantized_and_dequantize_refusals(fake_b200):
