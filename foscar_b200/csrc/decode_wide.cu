@@ -27,18 +27,29 @@
 //
 // Three worker groups (the expanded V operand of a tile is 32 KB), two producers, two MMA
 // issuers: 16 warps, 128 registers a thread.
+//
+// K quantized per channel over the 64 tokens of a page (the reference's
+// (("channel", 64), ("token", 256)) layout, src/foscar/_sm100/int_fold_decode.py:613-618,
+// 5012-5133): the page's (s_d, z_d) fold into the query side, so the S MMA's B operand differs
+// per page. Each group builds it per tile in its own stage: 48 rows = for each of the tile's two
+// pages three E4M3 planes (p0 + p1/16 + p2/256) of s_d q_d 2^-m for up to 8 heads (the reference
+// rounds Q' to one plane), S has 24 columns per page, and the bias sum_d z_d q_d is reduced per
+// page over the group. Two worker groups in that build.
 #include "decode.cuh"
 
 namespace fq {
 namespace wide {
 
 constexpr int D = 256;
-constexpr int G = 3;                       // worker groups
-constexpr int THREADS = 32 * (4 * G + 4);  // + 2 producers + 2 MMA issuers
 constexpr int SPT = 2;                     // ring stages (pages) per tile
+// worker groups: three; two when K is quantized per channel (the groups' own query stages and
+// the larger scale blocks take the third group's shared memory)
+__host__ __device__ constexpr int groups_of(bool kch) { return kch ? 2 : 3; }
+__host__ __device__ constexpr int threads_of(bool kch) { return 32 * (4 * groups_of(kch) + 4); }
 
-template <int BITS>
+template <int BITS, bool KCH>
 struct Plan {
+  static constexpr int G = groups_of(KCH);
   static constexpr int RB = D * BITS / 8;            // code row bytes: 64 or 128
   static constexpr int CHUNKS = RB / 16;             // 4 or 8
   // chunk c of ring row r sits at chunk c ^ row_swizzle(r): eight consecutive rows read at the
@@ -47,7 +58,9 @@ struct Plan {
     return CHUNKS == 8 ? (row & 7) : (row >> 1) & 3;
   }
   static constexpr int CODE_PAGE = PAGE * RB;
-  static constexpr int SCALE_PAGE = PAGE * 16;
+  // records of a page in a ring stage: 16 bytes a token, or (K per channel) the block of
+  // [128 + 2 D] f32: V ring, then the channel rows s_d, z_d
+  static constexpr int SCALE_PAGE = KCH ? (2 * PAGE + 2 * D) * 4 : PAGE * 16;
   static constexpr int K_OFF = 0, V_OFF = CODE_PAGE, S_OFF = 2 * CODE_PAGE;
   static constexpr int STAGE = 2 * CODE_PAGE + SCALE_PAGE;
   static constexpr int ROW = 128;
@@ -55,12 +68,21 @@ struct Plan {
   static constexpr int VOP_STAGE = 2 * VOP_PLANE;
   static constexpr int Q_ATOM = 16 * ROW;              // 16 query rows x 128 bytes
   static constexpr int Q_BYTES = 2 * Q_ATOM;
+  // K per channel: the S MMA's B operand is built per tile by the group itself (QP: 48 rows,
+  // 24 per page = three E4M3 planes of 8 heads, two atoms of 48 x 128 bytes); the producer
+  // stages the raw query rows (QRAW)
+  static constexpr int QP_ROWS = 48;
+  static constexpr int QP_ATOM = QP_ROWS * ROW;
+  static constexpr int QP_BYTES = 2 * QP_ATOM;
+  static constexpr int QRAW_BYTES = 8 * D;
   static constexpr int P_BYTES = TILE * 16;
   static constexpr int VOP_OFF = 0;
   static constexpr int Q_OFF = VOP_OFF + G * VOP_STAGE;
-  static constexpr int P_OFF = Q_OFF + 2 * Q_BYTES;
+  static constexpr int QRAW_OFF = Q_OFF + G * QP_BYTES;             // (K per channel)
+  static constexpr int P_OFF = KCH ? QRAW_OFF + 2 * QRAW_BYTES : Q_OFF + 2 * Q_BYTES;
   static constexpr int RED_OFF = P_OFF + G * P_BYTES;              // column maxima [G][4][8]
-  static constexpr int HEADK_OFF = RED_OFF + 128 * G;              // per-warp head constants
+  static constexpr int STATS_OFF = RED_OFF + 128 * G;              // page statistics [G][2][2][12]
+  static constexpr int HEADK_OFF = STATS_OFF + (KCH ? 192 * G : 0);  // per-warp head constants
   static constexpr int HEADC_OFF = HEADK_OFF + 96 * 4 * G;         // producer's, two items
   static constexpr int META_WORDS = 72;                            // m[8], 4 x (l[8], c[8])
   static constexpr int STATE_OFF = HEADC_OFF + 192;
@@ -73,8 +95,9 @@ struct Plan {
   static constexpr int ITEM_SLOTS = 16;
   static constexpr int RING_OFF = (ITEM_OFF + 32 * ITEM_SLOTS + 1023) / 1024 * 1024;
   static constexpr int max_ring_stages() { return (SMEM_LIMIT - 1024 - RING_OFF) / STAGE; }
-  // tensor memory (f32 columns) per group: K operand 64, S 16, two O accumulators of 32
-  static constexpr int KOP_COLS = 64, S_COLS = 16, O_COLS = 32;
+  // tensor memory (f32 columns) per group: K operand 64, S 16 (K per channel: 24 per page, 64
+  // reserved), two O accumulators of 32
+  static constexpr int KOP_COLS = 64, S_COLS = KCH ? 64 : 16, O_COLS = 32;
   static constexpr int T_KOP = 0, T_S = G * KOP_COLS, T_O = T_S + G * S_COLS;
   static constexpr int T_USED = T_O + G * 2 * O_COLS;
   static_assert(T_USED <= 512, "tensor memory plan exceeds 512 columns");
@@ -83,6 +106,7 @@ struct Plan {
 struct Bars {
   uint32_t base;
   int ns;
+  int G;
   __device__ uint32_t at(int i) const { return base + 8u * i; }
   __device__ uint32_t ring_full(int s) const { return at(s); }
   __device__ uint32_t ring_empty(int s) const { return at(ns + s); }
@@ -111,7 +135,7 @@ struct RingPos {
 // chunk v ^ swz.
 template <int BITS>
 __device__ inline void load_half_row(uint32_t row_addr, int half, int swz, uint32_t* w) {
-  constexpr int HC = Plan<BITS>::CHUNKS / 2;   // chunks per half row
+  constexpr int HC = D * BITS / 8 / 32;   // 16-byte chunks per half row
 #pragma unroll
   for (int v = 0; v < HC; ++v)
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -167,11 +191,12 @@ __device__ __noinline__ void count_in_piece(const DecodeParams& P, int gp, int w
   }
 }
 
-template <int BITS, int GP>
+template <int BITS, int GP, bool KCH>
 __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem, uint32_t smem0,
                                             uint32_t tmem, const Bars& bars,
                                             volatile int* abort_flag, const ItemRange items) {
-  using SP = Plan<BITS>;
+  using SP = Plan<BITS, KCH>;
+  constexpr int G = SP::G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wg = warp >> 2, wq = warp & 3;
   const int t = threadIdx.x & 127;   // token row while unpacking and in softmax, channel in O
@@ -265,6 +290,20 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     __syncwarp();
     if (mytiles > 0 && lane < 24) head_k[lane] = head_const[qb * 24 + lane];
     __syncwarp();
+    // K per channel: this thread builds four positions (4 * (t % 64) ...) of its page's half of
+    // the S MMA's B operand; it keeps the item's query values at those positions
+    float qf[KCH ? GP : 1][4];
+    if constexpr (KCH) {
+      if (mytiles > 0) {
+#pragma unroll
+        for (int h = 0; h < GP; ++h) {
+          const uint32_t raw = *reinterpret_cast<const uint32_t*>(
+              smem + SP::QRAW_OFF + qb * SP::QRAW_BYTES + h * D + 4 * srow);
+          const float2 a = e4m3x2_to_f32x2(raw & 0xFFFF), b = e4m3x2_to_f32x2(raw >> 16);
+          qf[h][0] = a.x; qf[h][1] = a.y; qf[h][2] = b.x; qf[h][3] = b.y;
+        }
+      }
+    }
 
     bool pending = false;   // the group has a PV MMA of this item in flight or done
     for (int done = 0; done < mytiles; ++done, mine += G, rp.advance(SPT * G, NS), ++n) {
@@ -274,6 +313,89 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       const uint32_t stage = ring0 + (su ? rp1.s : rp.s) * SP::STAGE;
       mbar_wait(bars.ring_full(rp.s), rp.ph, abort_flag, status);
       mbar_wait(bars.ring_full(rp1.s), rp1.ph, abort_flag, status);
+      // ---- K per channel: the page's (s_d, z_d) fold into the query side. Per page and head
+      //   score = 2^m * (sum_d Q'_d c_d) + sum_d z_d q_d,   Q'_d = s_d q_d 2^-m as three E4M3 planes
+      // p0 + p1/16 + p2/256 (the reference's Q' and bias, src/foscar/_sm100/int_fold_asm.py:21-63,
+      // src/foscar/_sm100/int_fold_decode.py:5038-5133, round Q' to one plane; with outlier
+      // channels two planes still left 1e-2 on a score, three leave 1e-3), m from
+      // the bound max_d s_d * max_d |q_d| so that one number per page is reduced, not one per
+      // head. The group builds the operand (48 rows: three planes of up to 8 heads for each of
+      // the tile's two pages) in its own stage; its previous tile's S MMA, the stage's last reader,
+      // is complete (the group read that S).
+      float up[KCH ? GP : 1], ab[KCH ? GP : 1];   // per head: 2^m * 512 * A, and A * bias
+      if constexpr (KCH) {
+        const int pos0 = 4 * srow;                      // first of this thread's four positions
+        const uint32_t rec = stage + SP::S_OFF;         // [V ring 128 | s_d 256 | z_d 256]
+        float sd[4], zd[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int ch = (pos0 & 128) + channel_of_expanded_pos<BITS>((pos0 & 127) + i);
+          if (P.p.scale_bf16) {
+            const uint16_t a = *reinterpret_cast<const uint16_t*>(
+                smem + (rec - smem0) + (2 * PAGE + ch) * 2);
+            const uint16_t b = *reinterpret_cast<const uint16_t*>(
+                smem + (rec - smem0) + (2 * PAGE + D + ch) * 2);
+            sd[i] = __uint_as_float(static_cast<uint32_t>(a) << 16);
+            zd[i] = __uint_as_float(static_cast<uint32_t>(b) << 16);
+          } else {
+            sd[i] = *reinterpret_cast<const float*>(smem + (rec - smem0) + (2 * PAGE + ch) * 4);
+            zd[i] = *reinterpret_cast<const float*>(smem + (rec - smem0) + (2 * PAGE + D + ch) * 4);
+          }
+        }
+        float* stats = reinterpret_cast<float*>(smem + SP::STATS_OFF) + ((wg * 2 + su) * 2 + (wq & 1)) * 12;
+        {
+          const uint32_t smax_bits = __reduce_max_sync(
+              0xFFFFFFFFu, __float_as_uint(fmaxf(fmaxf(sd[0], sd[1]), fmaxf(sd[2], sd[3]))));
+          if (lane == 0) stats[0] = __uint_as_float(smax_bits);
+#pragma unroll
+          for (int h = 0; h < GP; ++h) {
+            float bp = fmaf(zd[0], qf[h][0], fmaf(zd[1], qf[h][1],
+                                                 fmaf(zd[2], qf[h][2], zd[3] * qf[h][3])));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) bp += __shfl_xor_sync(0xFFFFFFFFu, bp, o);
+            if (lane == 0) stats[1 + h] = bp;
+          }
+        }
+        named_barrier(1 + wg, 128);
+        const float* st0 = reinterpret_cast<const float*>(smem + SP::STATS_OFF) + (wg * 2 + su) * 2 * 12;
+        const float smax = fmaxf(st0[0], st0[12]);
+        uint32_t pl[3][GP];   // this thread's four positions of the three planes of each head
+#pragma unroll
+        for (int h = 0; h < GP; ++h) {
+          // m = floor(log2(smax * qamax)) - 7, so that |s_d q_d| 2^-m < 256
+          const uint32_t eb = min(max((__float_as_uint(smax * head_k[8 + h]) >> 23) & 0xFFu, 40u),
+                                  214u);
+          const float dn = __uint_as_float((261u - eb) << 23);       // 2^-m = 2^(134 - e)
+          const float upm = __uint_as_float((eb - 7u) << 23);        // 2^m  = 2^(e - 134)
+          up[h] = upm * 512.f * head_k[h];
+          ab[h] = head_k[h] * (st0[1 + h] + st0[13 + h]);
+          float y[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) y[i] = sd[i] * qf[h][i] * dn;
+          // y = p0 + p1 / 16 + p2 / 256, each plane the E4M3 rounding of what is left
+#pragma unroll
+          for (int k = 0; k < 3; ++k) {
+            const uint32_t a = f32x2_to_e4m3x2(y[0], y[1]), b = f32x2_to_e4m3x2(y[2], y[3]);
+            pl[k][h] = a | (b << 16);
+            const float2 fa = e4m3x2_to_f32x2(a), fb = e4m3x2_to_f32x2(b);
+            y[0] = (y[0] - fa.x) * 16.f; y[1] = (y[1] - fa.y) * 16.f;
+            y[2] = (y[2] - fb.x) * 16.f; y[3] = (y[3] - fb.y) * 16.f;
+          }
+        }
+        // rows 24 * page + 8 * plane + h; atom = channel half
+        const uint32_t qp = smem0 + SP::Q_OFF + wg * SP::QP_BYTES + (pos0 >> 7) * SP::QP_ATOM +
+                            (pos0 & 15);
+        const int chunk = (pos0 & 127) >> 4;
+#pragma unroll
+        for (int k = 0; k < 3; ++k)
+#pragma unroll
+          for (int h = 0; h < GP; ++h) {
+            const int r = 24 * su + 8 * k + h;
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(qp + r * 128 + ((chunk ^ (r & 7)) << 4)),
+                         "r"(pl[k][h]) : "memory");
+          }
+        fence_proxy_async();
+      }
       // ---- K row -> tensor memory, two 128-byte operand rows (the S MMA's A operand). The
       // columns are free: this group read the S of its previous tile, so that tile's MMA, their
       // last reader, is complete.
@@ -310,8 +432,17 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         }
       }
       // the token's record; then both ring stages go back to the producers
-      float sk, zk, sv, zv;
-      if (P.p.scale_bf16) {   // (s, z) as bf16 pairs, 8 bytes a token
+      float sk = 0.f, zk = 0.f, sv, zv;
+      if constexpr (KCH) {   // V ring at the front of the page's block
+        if (P.p.scale_bf16) {
+          uint32_t vr;
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(vr) : "r"(stage + SP::S_OFF + srow * 4));
+          sv = __uint_as_float(vr << 16); zv = __uint_as_float(vr & 0xFFFF0000u);
+        } else {
+          asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(sv), "=f"(zv)
+                       : "r"(stage + SP::S_OFF + srow * 8));
+        }
+      } else if (P.p.scale_bf16) {   // (s, z) as bf16 pairs, 8 bytes a token
         uint32_t kr, vr;
         asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(kr), "=r"(vr)
                      : "r"(stage + SP::S_OFF + srow * 8));
@@ -330,6 +461,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       // positions past the request's length (its last tile only): score -inf, record neutral
       const bool valid = tt * TILE + t < w.len;
       const float ak = sk * 512.f;
+      (void)ak; (void)zk;
       const float wsc = valid ? sv * p2lp : 0.f;
       if (!valid) zv = 0.f;
       // ---- raw scores; d = score - reference in one fused chain per head. The group's first
@@ -340,17 +472,29 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       float d[GP];
       const bool fresh = !pending;
       {
-        uint32_t raw[8];
+        uint32_t raw[KCH ? 24 : 8];
         tc_fence_after();
-        tmem_ld8p(s_src, raw);
+        if constexpr (KCH) {   // the token's page's columns: three planes of eight heads
+          tmem_ld8p(s_src + 24 * su, raw);
+          tmem_ld8p(s_src + 24 * su + 8, raw + 8);
+          tmem_ld8p(s_src + 24 * su + 16, raw + 16);
+        } else {
+          tmem_ld8p(s_src, raw);
+        }
         tmem_ld_wait();
         tc_fence_before();
         float over = -INFINITY;
 #pragma unroll
         for (int h = 0; h < GP; ++h) {
           const float nm = fresh ? 0.f : -m[h];
-          const float dd =
-              fmaf(head_k[h] * ak, __uint_as_float(raw[h]), fmaf(head_k[8 + h], zk, nm));
+          float dd;
+          if constexpr (KCH)
+            dd = fmaf(up[h],
+                      fmaf(fmaf(__uint_as_float(raw[16 + h]), 0.0625f, __uint_as_float(raw[8 + h])),
+                           0.0625f, __uint_as_float(raw[h])),
+                      ab[h] + nm);
+          else
+            dd = fmaf(head_k[h] * ak, __uint_as_float(raw[h]), fmaf(head_k[8 + h], zk, nm));
           d[h] = valid ? dd : -INFINITY;
           over = fmaxf(over, d[h]);
         }
@@ -567,9 +711,10 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     count_in_piece<BITS>(P, GP, wg, t, piece_b, piece_kvh, piece_ht, group_info);
 }
 
-template <int BITS, int GP>
-__global__ void __launch_bounds__(THREADS, 1) decode_wide_kernel(const DecodeParams P) {
-  using SP = Plan<BITS>;
+template <int BITS, int GP, bool KCH>
+__global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const DecodeParams P) {
+  using SP = Plan<BITS, KCH>;
+  constexpr int G = SP::G;
   constexpr int W_PRODUCER = 4 * G, W_S = W_PRODUCER + 1, W_PV = W_PRODUCER + 2,
                 W_PRODUCER2 = W_PRODUCER + 3;
   extern __shared__ uint8_t smem_raw[];
@@ -577,7 +722,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_wide_kernel(const DecodePar
   uint8_t* const smem = smem_raw + (smem0 - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int NS = P.ring_stages;
-  Bars bars{smem0 + SP::BAR_OFF, NS};
+  Bars bars{smem0 + SP::BAR_OFF, NS, G};
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SP::FLAG_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SP::FLAG_OFF + 24);
   int* status = P.a.status;
@@ -645,15 +790,17 @@ __global__ void __launch_bounds__(THREADS, 1) decode_wide_kernel(const DecodePar
         const int qb = qi & 1;
         mbar_wait(bars.q_empty(qb), ((qi >> 1) & 1) ^ 1, abort_flag, status);
         // 16 rows of sixteen 16-byte chunks: a row's chunks sit in 16 neighbouring lanes
+        // (K per channel: the 8 head rows only, unswizzled, for the workers to build the
+        // operand from; the per-head constants are then the score scale and max |q|)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < (KCH ? 4 : 8); ++j) {
           const int chunk = lane + 32 * j;
           const int r = chunk >> 4, cc = chunk & 15;
           uint4 v = make_uint4(0, 0, 0, 0);
           const int hl = w.ht * 8 + r;
           const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
           const bool live = r < 8 && hl < P.heads_per_kv;
-          float qsum = 0.f;
+          float qsum = 0.f;   // the row's sum of q (K per channel: its max |q|)
           if (live) {
             const uint4 in = __ldg(reinterpret_cast<const uint4*>(
                 static_cast<const uint8_t*>(P.a.q) +
@@ -663,7 +810,11 @@ __global__ void __launch_bounds__(THREADS, 1) decode_wide_kernel(const DecodePar
             for (int i = 0; i < 4; ++i) {
               const float2 lo = e4m3x2_to_f32x2(words[i] & 0xFFFF);
               const float2 hi = e4m3x2_to_f32x2(words[i] >> 16);
-              qsum += (lo.x + lo.y) + (hi.x + hi.y);
+              if constexpr (KCH)
+                qsum = fmaxf(fmaxf(qsum, fmaxf(fabsf(lo.x), fabsf(lo.y))),
+                             fmaxf(fabsf(hi.x), fabsf(hi.y)));
+              else
+                qsum += (lo.x + lo.y) + (hi.x + hi.y);
             }
             if (BITS == 2) {
               v.x = __byte_perm(in.x, in.y, 0x6420);
@@ -674,14 +825,20 @@ __global__ void __launch_bounds__(THREADS, 1) decode_wide_kernel(const DecodePar
               v = in;
             }
           }
-          // atom cc / 8 holds channels [128 * (cc / 8), + 128); chunk cc % 8 of row r swizzled
-          *reinterpret_cast<uint4*>(smem + SP::Q_OFF + qb * SP::Q_BYTES + (cc >> 3) * SP::Q_ATOM +
-                                    r * 128 + (((cc & 7) ^ (r & 7)) << 4)) = v;
+          if constexpr (KCH) {
+            *reinterpret_cast<uint4*>(smem + SP::QRAW_OFF + qb * SP::QRAW_BYTES + r * D + 16 * cc) = v;
+          } else {
+            // atom cc / 8 holds channels [128 * (cc / 8), + 128); chunk cc % 8 of row r swizzled
+            *reinterpret_cast<uint4*>(smem + SP::Q_OFF + qb * SP::Q_BYTES +
+                                      (cc >> 3) * SP::Q_ATOM + r * 128 +
+                                      (((cc & 7) ^ (r & 7)) << 4)) = v;
+          }
           if (j < 4) {   // rows 0-7: per-head constants
-            qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, 1);
-            qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, 2);
-            qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, 4);
-            qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, 8);
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) {
+              const float other = __shfl_xor_sync(0xFFFFFFFFu, qsum, o);
+              qsum = KCH ? fmaxf(qsum, other) : qsum + other;
+            }
             if (cc == 0) {
               float scale = 0.f;
               if (live) {
@@ -692,7 +849,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_wide_kernel(const DecodePar
               }
               float* hc = reinterpret_cast<float*>(smem + SP::HEADC_OFF) + qb * 24;
               hc[r] = scale;
-              hc[8 + r] = scale * qsum;
+              hc[8 + r] = KCH ? qsum : scale * qsum;
             }
           }
         }
@@ -736,7 +893,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_wide_kernel(const DecodePar
             const long long blk = static_cast<long long>(id) * P.p.num_kv_heads + w.kvh;
             const uint8_t* ks = P.p.k_codes + blk * SP::CODE_PAGE + 16 * lane;
             const uint8_t* vs = P.p.v_codes + blk * SP::CODE_PAGE + 16 * lane;
-            const int scale_page = P.p.scale_bf16 ? SP::SCALE_PAGE / 2 : SP::SCALE_PAGE;
+            const int scale_page = P.p.scale_bf16 ? SP::SCALE_PAGE / 2 : SP::SCALE_PAGE;   // bytes
             const uint8_t* ss = static_cast<const uint8_t*>(P.p.scales) + blk * scale_page +
                                 16 * lane;
             const uint32_t dst0 = ring0 + s * SP::STAGE;
@@ -768,8 +925,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_wide_kernel(const DecodePar
   } else if (warp == W_S) {
     // ------------------------------------------------------------------ S issuer
     if (lane == 0) {
-      constexpr uint32_t IDESC_S = make_idesc_e4m3(128, 16, 0, 0);
+      constexpr uint32_t IDESC_S = make_idesc_e4m3(128, KCH ? SP::QP_ROWS : 16, 0, 0);
       constexpr uint32_t Q_HI = smem_desc_hi(1024, 2);
+      constexpr int ATOM16 = (KCH ? SP::QP_ATOM : SP::Q_ATOM) >> 4;
       int qi = 0, g = 0;
       uint32_t gph = 0;
       for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
@@ -777,18 +935,22 @@ __global__ void __launch_bounds__(THREADS, 1) decode_wide_kernel(const DecodePar
         if (w.t1 <= w.t0) continue;
         const int qb = qi & 1;
         mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status);
-        const uint32_t q_lo = smem_desc_lo(smem0 + SP::Q_OFF + qb * SP::Q_BYTES, 16);
+        const uint32_t q_item = smem_desc_lo(smem0 + SP::Q_OFF + qb * SP::Q_BYTES, 16);
         for (int t = w.t0; t < w.t1; ++t) {
           mbar_wait(bars.k_ready(g), gph, abort_flag, status);
           tc_fence_after();
           const uint32_t sd = tmem + SP::T_S + g * SP::S_COLS;
           const uint32_t ka = tmem + SP::T_KOP + g * SP::KOP_COLS;
+          // the B operand: the item's query stage, or (K per channel) the operand the group
+          // built for this tile
+          const uint32_t q_lo =
+              KCH ? smem_desc_lo(smem0 + SP::Q_OFF + g * SP::QP_BYTES, 16) : q_item;
           // eight K steps of 32 channels: the lane's two operand rows against the two atoms
           umma_ts_c<Q_HI, IDESC_S, false>(sd, ka, q_lo);
 #pragma unroll
           for (int k = 1; k < 8; ++k)
             umma_ts_c<Q_HI, IDESC_S, true>(sd, ka + 8 * k,
-                                           q_lo + (k >> 2) * (SP::Q_ATOM >> 4) + 2 * (k & 3));
+                                           q_lo + (k >> 2) * ATOM16 + 2 * (k & 3));
           tc_commit(bars.s_done(g));
           if (t == w.t1 - 1) tc_commit(bars.q_empty(qb));
           if (++g == G) { g = 0; gph ^= 1u; }
@@ -832,7 +994,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_wide_kernel(const DecodePar
     }
     __syncwarp();
   } else {
-    worker_role<BITS, GP>(P, smem, smem0, tmem, bars, abort_flag, items);
+    worker_role<BITS, GP, KCH>(P, smem, smem0, tmem, bars, abort_flag, items);
   }
 
   tc_fence_before();
@@ -850,9 +1012,11 @@ __global__ void __launch_bounds__(THREADS, 1) decode_wide_kernel(const DecodePar
 // ---------------------------------------------------------------------------------------------
 namespace wide {
 
-template <int BITS, int GP>
+template <int BITS, int GP, bool KCH>
 static int launch(DecodeParams& P, cudaStream_t stream) {
-  using SP = Plan<BITS>;
+  using SP = Plan<BITS, KCH>;
+  constexpr int G = SP::G;
+  constexpr int THREADS = threads_of(KCH);
   int stages = SP::max_ring_stages();
   if (stages > SP::MAX_STAGES) stages = SP::MAX_STAGES;
   if (const char* env = getenv("FOSCAR_B200_RING_STAGES")) {   // tuning knob for experiments
@@ -871,7 +1035,7 @@ static int launch(DecodeParams& P, cudaStream_t stream) {
   P.item_slots = SP::ITEM_SLOTS + more;
   const int smem = SP::RING_OFF + stages * SP::STAGE + more * 32 + 1024;
   static bool configured[64] = {};
-  auto kernel = decode_wide_kernel<BITS, GP>;
+  auto kernel = decode_wide_kernel<BITS, GP, KCH>;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -911,9 +1075,14 @@ static int launch(DecodeParams& P, cudaStream_t stream) {
 // Launch of the head_dim 256 build (called by fq_decode once the arguments are checked).
 int launch_decode_wide(DecodeParams& P, cudaStream_t stream) {
   const int gp = (P.heads_per_kv < 8 ? P.heads_per_kv : 8) <= 4 ? 4 : 8;
+  if (P.p.k_channel_group != 0) {
+    if (P.p.bits == 2)
+      return gp == 4 ? wide::launch<2, 4, true>(P, stream) : wide::launch<2, 8, true>(P, stream);
+    return gp == 4 ? wide::launch<4, 4, true>(P, stream) : wide::launch<4, 8, true>(P, stream);
+  }
   if (P.p.bits == 2)
-    return gp == 4 ? wide::launch<2, 4>(P, stream) : wide::launch<2, 8>(P, stream);
-  return gp == 4 ? wide::launch<4, 4>(P, stream) : wide::launch<4, 8>(P, stream);
+    return gp == 4 ? wide::launch<2, 4, false>(P, stream) : wide::launch<2, 8, false>(P, stream);
+  return gp == 4 ? wide::launch<4, 4, false>(P, stream) : wide::launch<4, 8, false>(P, stream);
 }
 
 }  // namespace fq

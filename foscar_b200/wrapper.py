@@ -307,15 +307,18 @@ class PagedDecodeWrapper:
         self._planned = True
 
     def _set_common(self, layout, num_qo_heads, q_dtype, o_dtype, sm_scale, batch):
-        if not layout.is_token_wise:
+        if not layout.is_token_wise and not (layout.is_page_channel_k and layout.head_dim == 256):
             raise NotImplementedError(
-                f"this build decodes token-wise layouts; k_quant={layout.k_quant} "
-                f"v_quant={layout.v_quant} has a channel-wise tensor")
-        if layout.head_dim == 256 and layout.k_quant[1] < layout.head_dim:
+                f"this build decodes token-wise layouts, and K per channel over a page "
+                f"(k_quant=('channel', 64), token-wise V) at head_dim 256; k_quant="
+                f"{layout.k_quant} v_quant={layout.v_quant} at head_dim {layout.head_dim} is "
+                f"neither")
+        if layout.head_dim == 256 and layout.is_token_wise \
+                and layout.k_quant[1] < layout.head_dim:
             raise NotImplementedError(
                 f"this build decodes whole-head K groups at head_dim 256; got "
                 f"k_quant={layout.k_quant}")
-        if layout.k_quant[1] < layout.head_dim and not (
+        if layout.is_token_wise and layout.k_quant[1] < layout.head_dim and not (
                 layout.head_dim == 128 and layout.k_quant[1] == 64):
             raise NotImplementedError(
                 f"this build decodes K groups of 64 channels at head_dim 128 only; got "

@@ -117,13 +117,13 @@ def _decode_case(bits, hq, hkv, seq, seed, kv_splits=None, q_scale=8.0, scale_dt
     torch.cuda.synchronize()
     assert w.last_status() == 0
     kv = ref_dequantize_channel(pools, indptr, indices, seq, rounded=False)
-    for b in range(len(seq)):
-        want, lse_want = ref_attention(q[b].float().cpu(), kv[b][0], kv[b][1], sm_scale)
-        err = (out[b].float().cpu() - want).abs()
-        assert torch.isfinite(out[b].float()).all()
-        assert err.max().item() <= MAX_ABS, f"request {b}: max-abs {err.max().item():.3e}"
-        assert err.mean().item() <= MEAN_ABS, f"request {b}: mean-abs {err.mean().item():.3e}"
-        assert (lse[b].cpu() - lse_want).abs().max().item() <= LSE_ABS
+    wants, lses = zip(*(ref_attention(q[b].float().cpu(), kv[b][0], kv[b][1], sm_scale)
+                        for b in range(len(seq))))
+    err = (out.float().cpu() - torch.stack(wants)).abs()      # over the batch, as the
+    assert torch.isfinite(out.float()).all()                  # token-wise decode tests do
+    assert err.max().item() <= MAX_ABS, f"max-abs {err.max().item():.3e}"
+    assert err.mean().item() <= MEAN_ABS, f"mean-abs {err.mean().item():.3e}"
+    assert (lse.cpu() - torch.stack(lses)).abs().max().item() <= LSE_ABS
 
 
 @pytest.mark.parametrize("bits", [4, 2])
