@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_C")
 LIB_PATH = os.path.join(OUT_DIR, "libfoscar_b200.so")
-SOURCES = ("writer.cu", "dequant_merge.cu", "decode.cu", "decode_wide.cu", "capi.cu")
+SOURCES = ("writer.cu", "dequant_merge.cu", "decode.cu", "decode_wide.cu", "exchange.cu", "capi.cu")
 HEADERS = ("common.cuh", "decode.cuh", os.path.join("..", "..", "include", "foscar_b200.h"))
 NVCC_FLAGS = ("-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC", "-shared", "-diag-suppress", "177")

@@ -75,6 +75,9 @@ _PROTOTYPES = {
     "fq_merge": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _F32, _P, _I32,
                            _P, _P]),
     "fq_merge_states": (C.c_int, [_P, _P, _I32, _I32, _I32, _I32, _P, _I32, _P, _I64, _I64, _P]),
+    "fq_exchange_bytes": (_I64, [_I32, _I32, _I32, _I32]),
+    "fq_exchange_merge": (C.c_int, [_P, _I32, _I32, _P, _P, _I32, _I32, _I32, _I64, _P, _I32, _P,
+                                    _I64, _P, _P]),
     "fq_plan_splits": (C.c_int, [_I32, _I32, _I32, _I32, _I32, _I32, _I32]),
     "fq_plan_worklist": (C.c_int, [_P, _I32, _I32, _I32, _I32, _I32, _P, _I32, _P, _I32, _I32]),
     "fq_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),

@@ -7,9 +7,11 @@ its decode path partitions:
   matching query heads, with its own cache, workspace and wrapper. Units are independent, so
   there is NO communication on the data path.
 * Sequence split (one very long context): rank r holds the pages of a page-aligned token range
-  and decodes it to a normalised (o, lse) pair; one all_gather of [B, HQ, D] + [B, HQ] floats
-  per rank over NCCL (NVLink/NVSwitch) brings the pairs into every rank's own memory, and a
-  local kernel merges them: out = sum_r exp(lse_r - L) o_r, L = logsumexp_r lse_r.
+  and decodes it to a normalised (o, lse) pair; the pairs reach every rank's own memory and are
+  merged there: out = sum_r exp(lse_r - L) o_r, L = logsumexp_r lse_r. Two forms of that
+  exchange: `SequenceSplitExchange` (ONE launch per rank: plain stores into every peer's staging
+  buffer through peer-mapped pointers, a flag, a bounded wait and the merge, all in the
+  library's own kernel) and `gather_and_merge` (one NCCL all_gather plus the merge kernel).
 
 One process per GPU; `torch.distributed` is the plumbing.
 """
@@ -117,14 +119,88 @@ def gather_and_merge(out: torch.Tensor, lse: torch.Tensor, group=None,
     return merged
 
 
-def sequence_split_decode(wrapper, q, cache, group=None, out: Optional[torch.Tensor] = None
-                          ) -> torch.Tensor:
+class SequenceSplitExchange:
+    """The cross-GPU step of a sequence split as one kernel launch per rank.
+
+    Construction is collective over `group`: every rank allocates a staging buffer in torch's
+    symmetric memory (peer-mapped into every process of the group) and learns the others'
+    addresses. `run()` then launches the library's exchange kernel on the current stream: this
+    rank's (o, lse) rows go into its slot of every rank's buffer with plain stores, the step is
+    posted on a flag, the peers' flags are waited for (bounded: a peer that never posts sets the
+    time-out status bit and leaves `out` untouched) and the rows are merged from this rank's own
+    memory. No NCCL call, no copy kernel, no multicast on the data path."""
+
+    def __init__(self, batch: int, num_qo_heads: int, head_dim: int, group=None, device=None):
+        import os
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        # plain peer mappings only: no NVLink multicast object is bound to the buffer
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.shape = (batch, num_qo_heads, head_dim)
+        self.device = torch.device("cuda", _dev.cuda_index(device))
+        lib = _lib.load()
+        nbytes = int(lib.fq_exchange_bytes(self.world, batch, num_qo_heads, head_dim))
+        if nbytes < 0:
+            _lib.check(nbytes, "exchange_bytes")
+        self.buffer = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.buffer.zero_()
+        handle = symm.rendezvous(self.buffer, self.group)
+        self._handle = handle
+        self._ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in handle.buffer_ptrs])
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.step = 0
+        # every rank's zeroed flags are in place before anyone posts a step
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def last_status(self) -> int:
+        return int(self.status.item())
+
+    def run(self, o_local: torch.Tensor, lse_local: torch.Tensor, out: torch.Tensor,
+            lse: Optional[torch.Tensor] = None, wait_budget_cycles: int = 0) -> torch.Tensor:
+        """o_local f32 [B, HQ, D] and lse_local f32 [B, HQ] of this rank; `out` receives the
+        merged rows (bf16 / f16 / f32), `lse` (optional) the merged log-sum-exp."""
+        b, hq, d = self.shape
+        if o_local.dtype != torch.float32 or tuple(o_local.shape) != (b, hq, d) \
+                or not o_local.is_contiguous():
+            raise ValueError(f"o_local must be a contiguous f32 [{b}, {hq}, {d}] tensor (plan the "
+                             f"wrapper with o_data_type=torch.float32)")
+        if lse_local.dtype != torch.float32 or tuple(lse_local.shape) != (b, hq) \
+                or not lse_local.is_contiguous():
+            raise ValueError(f"lse_local must be a contiguous f32 [{b}, {hq}] tensor")
+        if tuple(out.shape) != (b, hq, d) or not out.is_contiguous():
+            raise ValueError(f"out must be a contiguous [{b}, {hq}, {d}] tensor")
+        code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[out.dtype]
+        self.step += 1
+        with _dev.on_device(self.device):
+            _lib.check(_lib.load().fq_exchange_merge(
+                self._ptrs, self.rank, self.world, o_local.data_ptr(), lse_local.data_ptr(), b,
+                hq, d, self.step, out.data_ptr(), code,
+                None if lse is None else lse.data_ptr(), wait_budget_cycles,
+                self.status.data_ptr(), _dev.current_stream_ptr(self.device)), "exchange_merge")
+        return out
+
+
+def sequence_split_decode(wrapper, q, cache, group=None, out: Optional[torch.Tensor] = None,
+                          exchange: Optional[SequenceSplitExchange] = None,
+                          scratch=None) -> torch.Tensor:
     """One decode step of a sequence-split context: this rank's wrapper (planned over its own
-    token range) produces (o, lse); the pairs are gathered and merged on every rank. Plan the
-    wrapper with `o_data_type=torch.float32` so that the shards' outputs are not rounded to
-    bf16 before the merge."""
+    token range, with `o_data_type=torch.float32` so that the shards' outputs are not rounded to
+    bf16 before the merge) produces (o, lse); the pairs are exchanged and merged on every rank:
+    by `exchange` (one launch) when given, else by one NCCL all_gather and the merge kernel.
+    `scratch` = (o f32 [B, HQ, D], lse f32 [B, HQ]) reuses caller-owned buffers."""
     b, hq, d = wrapper._batch_size, wrapper._num_qo_heads, wrapper._head_dim
-    local = torch.empty(b, hq, d, dtype=wrapper._o_data_type, device=q.device)
-    lse = torch.empty(b, hq, dtype=torch.float32, device=q.device)
+    if scratch is None:
+        local = torch.empty(b, hq, d, dtype=wrapper._o_data_type, device=q.device)
+        lse = torch.empty(b, hq, dtype=torch.float32, device=q.device)
+    else:
+        local, lse = scratch
     wrapper.run(q, cache, out=local, lse=lse)
+    if exchange is not None:
+        if out is None:
+            out = torch.empty(b, hq, d, dtype=torch.bfloat16, device=q.device)
+        return exchange.run(local, lse, out)
     return gather_and_merge(local, lse, group, merged=out)

@@ -202,6 +202,21 @@ int fq_merge_states(const float* o_shards, const float* lse_shards, int32_t num_
                     int32_t out_dtype, float* lse, int64_t o_row_stride, int64_t lse_stride,
                     void* stream);
 
+/* The cross-GPU step of a sequence-split decode in one launch per rank: this rank's attention
+ * state (o f32 [B, HQ, D] normalised, lse f32 [B, HQ] natural log) is written into a staging slot
+ * in every rank's memory through peer-mapped pointers (plain stores), the step is posted on a flag
+ * there, the peers' flags are waited for in this rank's own memory (bounded by
+ * wait_budget_cycles, 0 = default; FQ_STATUS_TIMEOUT and an untouched output when a peer never
+ * posts) and the gathered rows are merged locally as fq_merge_states merges them.
+ * staging: host array of `world` device pointers, entry r being rank r's staging buffer of
+ * fq_exchange_bytes bytes as mapped in this process (zeroed before the first step); step: 1, 2,
+ * 3, ... the same on every rank. The reference has no counterpart (single-GPU library). */
+int64_t fq_exchange_bytes(int32_t world, int32_t batch, int32_t num_qo_heads, int32_t head_dim);
+int fq_exchange_merge(void* const* staging, int32_t rank, int32_t world, const float* o_local,
+                      const float* lse_local, int32_t batch, int32_t num_qo_heads,
+                      int32_t head_dim, int64_t step, void* out, int32_t out_dtype,
+                      float* lse_out, int64_t wait_budget_cycles, int32_t* status, void* stream);
+
 /* Host-only planning. fq_plan_splits: uniform split count for the longest request (closed-form
  * cost model; stands in for plan_splits_sm100, src/foscar/_sm100/scheduler.py:129-160).
  * fq_plan_worklist: balanced pieces from host seq_lens: writes the list (at most max_words int32

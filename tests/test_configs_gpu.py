@@ -246,3 +246,47 @@ def test_a_wait_that_runs_out_returns_and_leaves_the_context_usable():
     torch.cuda.synchronize()
     assert w.last_status() == 0
     assert torch.equal(before, after)
+
+
+def test_exchange_kernel_alone_and_its_give_up_path():
+    """The sequence split's exchange kernel on one GPU: a world of one merges its own rows; in a
+    world of two whose other rank never posts, the bounded wait runs out, the time-out bit is
+    set, the output is left as it was and the context stays usable."""
+    import ctypes
+    from foscar_b200 import _lib
+    lib = _lib.load()
+    b, hq, d = 2, 8, 128
+    o = torch.randn(b, hq, d, device="cuda")
+    lse = torch.randn(b, hq, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # world of one
+    buf = torch.zeros(int(lib.fq_exchange_bytes(1, b, hq, d)), dtype=torch.uint8, device="cuda")
+    ptrs = (ctypes.c_void_p * 1)(buf.data_ptr())
+    out = torch.zeros(b, hq, d, device="cuda")
+    lse_out = torch.zeros(b, hq, device="cuda")
+    for step in (1, 2, 3):
+        assert lib.fq_exchange_merge(ptrs, 0, 1, o.data_ptr(), lse.data_ptr(), b, hq, d, step,
+                                     out.data_ptr(), 2, lse_out.data_ptr(), 0, status.data_ptr(),
+                                     stream) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.allclose(out, o, atol=1e-6) and torch.allclose(lse_out, lse, atol=1e-6)
+    # world of two, the other rank silent: ~1 ms, then the give-up path
+    n2 = int(lib.fq_exchange_bytes(2, b, hq, d))
+    mine = torch.zeros(n2, dtype=torch.uint8, device="cuda")
+    other = torch.zeros(n2, dtype=torch.uint8, device="cuda")
+    ptrs2 = (ctypes.c_void_p * 2)(mine.data_ptr(), other.data_ptr())
+    out.fill_(7.0)
+    # (step 2: the even steps use the first half of the staging area)
+    assert lib.fq_exchange_merge(ptrs2, 0, 2, o.data_ptr(), lse.data_ptr(), b, hq, d, 2,
+                                 out.data_ptr(), 2, None, 2_000_000, status.data_ptr(),
+                                 stream) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == _lib.STATUS_TIMEOUT
+    assert torch.all(out == 7.0)
+    # the silent rank's slot holds what this rank sent it
+    sent = other.view(torch.float32)[:b * hq * (d + 1)].view(b * hq, d + 1)
+    assert torch.equal(sent[:, :d], o.view(b * hq, d)) and torch.equal(sent[:, d], lse.view(-1))
+    assert lib.fq_exchange_merge(ptrs2, 2, 2, o.data_ptr(), lse.data_ptr(), b, hq, d, 1,
+                                 out.data_ptr(), 2, None, 0, None, stream) == _lib.ERR_BAD_ARG

@@ -5,7 +5,8 @@
   checked against the fp32 oracle over the whole context (tolerance of the decode tests).
 * KV-head tensor parallel: rank r caches and decodes its KV heads only; no communication on the
   data path; its output equals the oracle's slice for its query heads.
-NVLS is switched off and the peers are reached through NCCL only (no peer pointers in kernels)."""
+NVLS is switched off; the peers are reached through NCCL, and through plain stores and loads on
+peer-mapped pointers in the library's exchange kernel (no multicast, no bulk copies)."""
 import os
 
 import numpy as np
@@ -46,6 +47,15 @@ def _rank(rank, world, port, ret):
         out = parallel.sequence_split_decode(w, q, cache)
         torch.cuda.synchronize(dev)
         assert w.last_status() == 0
+        # the same step through the one-launch exchange (peer stores + flags), three times over
+        # (both parities of its staging area): the rows equal the all_gather form's
+        ex = parallel.SequenceSplitExchange(1, hq, d, device=dev)
+        fused_ok = True
+        for _ in range(3):
+            out2 = parallel.sequence_split_decode(w, q, cache, exchange=ex)
+            torch.cuda.synchronize(dev)
+            fused_ok = fused_ok and ex.last_status() == 0 and \
+                (out2.float() - out.float()).abs().max().item() <= 1e-2
         # oracle over the whole context, cached the same way (token-wise records do not depend
         # on which page a token sits in)
         f_indptr, f_indices, f_slots, f_pages = paged_batch([seq], seed=9)
@@ -70,7 +80,7 @@ def _rank(rank, world, port, ret):
         torch.cuda.synchronize(dev)
         err2 = (out_tp.float().cpu() - want[:, qh.start:qh.stop]).abs()
         tp_ok = err2.max().item() <= MAX_ABS and err2.mean().item() <= MEAN_ABS
-        ret[rank] = (bool(seq_ok), bool(tp_ok), float(err.max()), float(err2.max()))
+        ret[rank] = (bool(seq_ok and fused_ok), bool(tp_ok), float(err.max()), float(err2.max()))
     finally:
         dist.destroy_process_group()
 
