@@ -41,6 +41,10 @@ WORKLOADS = {
                    outliers=True, identity=False, q_scale=8.0),
     "c3-b64": dict(bits=2, batch=64, hq=32, hkv=8, d=128, seq=(100352, 100352), dist="uniform",
                    outliers=True, identity=False, q_scale=8.0),
+    "c4": dict(bits=4, batch=64, hq=16, hkv=2, d=256, seq=(256, 65536), dist="loguniform",
+               outliers=True, identity=False, q_scale=8.0, k_channel=True),
+    "c4-token": dict(bits=4, batch=64, hq=16, hkv=2, d=256, seq=(256, 65536), dist="loguniform",
+                     outliers=True, identity=False, q_scale=8.0),
     "c5-int2": dict(bits=2, batch=256, hq=64, hkv=8, d=64, seq=(64, 131072), dist="loguniform",
                     outliers=False, identity=False, q_scale=8.0),
     "c5-int4": dict(bits=4, batch=256, hq=64, hkv=8, d=64, seq=(64, 131072), dist="loguniform",
@@ -61,17 +65,20 @@ def seq_lens_of(cfg, seed):
 
 
 def algorithmic_bytes(cfg, seq):
-    """Packed K and V codes + scale records of every token, q and out, page-table entries."""
+    """Packed K and V codes + scale records of every token, q and out, page-table entries.
+    Records: 16 bytes per (token, KV head), or with K per channel over a page the token's V pair
+    (8) plus the page's channel rows spread over its 64 tokens (2 * D * 4 / 64)."""
     d, bits, hkv, hq, b = cfg["d"], cfg["bits"], cfg["hkv"], cfg["hq"], cfg["batch"]
-    per_token_head = 2 * d * bits // 8 + 16
+    records = 8 + 2 * d * 4 // PAGE if cfg.get("k_channel") else 16
+    per_token_head = 2 * d * bits // 8 + records
     pages = int(sum(-(-int(n) // PAGE) for n in seq))
     return int(seq.sum()) * hkv * per_token_head + b * hq * d * (1 + 2) + 4 * pages
 
 
-# DRAM bytes (read + write) of one decode launch from an ncu capture of the same command
-# (profiles/decode_kernel_c2_int2.md, profiles/decode_kernel_c2_int4.md); other workloads have
-# no capture.
-NCU_TRAFFIC = {"c2": 401_548_800, "c2-int4": 716_985_600}
+# DRAM bytes (read + write) of one decode launch of the named workload, from a separate ncu
+# capture of this command at its default arguments (not a figure of this run): reported as
+# `traffic` only when the run's arguments are those of the capture.
+CAPTURED_TRAFFIC = {"c2": 401_548_800, "c2-int4": 716_985_600}
 
 
 def measured_peak():
@@ -154,22 +161,33 @@ def build_gpu_case(cfg, device, seed):
     order = np.arange(total) if cfg["identity"] else rng.permutation(total)
     indptr = np.concatenate([[0], np.cumsum(pages)]).astype(np.int32)
     indices = order.astype(np.int32)
+    kch = bool(cfg.get("k_channel"))
     layout = QuantKVLayout.create(bits=cfg["bits"], head_dim=cfg["d"], num_kv_heads=cfg["hkv"],
-                                  device=device)
+                                  device=device, k_quant=("channel", PAGE) if kch else None)
     cache = layout.allocate(total)
     g = torch.Generator(device=device).manual_seed(seed)
     mult = torch.exp(torch.randn(1, cfg["hkv"], cfg["d"], device=device, generator=g)) \
         if cfg["outliers"] else None
+    chunk = 1 << 18     # tokens written per append (bounds the bf16 staging)
     for b, n in enumerate(seq):
         n = int(n)
-        k = torch.randn(n, cfg["hkv"], cfg["d"], device=device, generator=g)
-        if mult is not None:
-            k = k * mult
-        v = torch.randn(n, cfg["hkv"], cfg["d"], device=device, generator=g)
-        t = torch.arange(n, device=device)
-        pg = torch.from_numpy(indices[indptr[b]:indptr[b + 1]]).to(device).long()
-        slots = pg[t // PAGE] * PAGE + t % PAGE
-        cache.append(k.to(torch.bfloat16), v.to(torch.bfloat16), slots)
+        pg_all = torch.from_numpy(indices[indptr[b]:indptr[b + 1]]).to(device)
+        for a in range(0, n, chunk):
+            m = min(chunk, n - a)
+            rows = -(-m // PAGE) * PAGE if kch else m     # whole pages for the page writer
+            k = torch.randn(rows, cfg["hkv"], cfg["d"], device=device, generator=g)
+            if mult is not None:
+                k = k * mult
+            v = torch.randn(rows, cfg["hkv"], cfg["d"], device=device, generator=g)
+            if kch:
+                pages = pg_all[a // PAGE:a // PAGE + rows // PAGE].int().contiguous()
+                valid = torch.full((rows // PAGE,), PAGE, dtype=torch.int32, device=device)
+                valid[-1] = m - (rows - PAGE)
+                cache.append_page_groups(k.to(torch.bfloat16), v.to(torch.bfloat16), pages, valid)
+            else:
+                t = torch.arange(a, a + m, device=device)
+                slots = pg_all.long()[t // PAGE] * PAGE + t % PAGE
+                cache.append(k.to(torch.bfloat16), v.to(torch.bfloat16), slots)
     q = (torch.randn(cfg["batch"], cfg["hq"], cfg["d"], device=device, generator=g)
          * cfg["q_scale"]).clamp(-448, 448).to(torch.float8_e4m3fn)
     ws = torch.empty(256 << 20, dtype=torch.uint8, device=device)
@@ -241,10 +259,14 @@ def run_reference(args, cfg):
     dt = (time.perf_counter() - t0) / args.steps
     full = dt * float(seq.sum()) / tokens          # linear in KV tokens
     value = cfg["batch"] / full
-    sample = f"{reqs} requests, {tokens} KV tokens of {int(seq.sum())}, scaled linearly in tokens"
+    sample = (f"{reqs} requests, {tokens} KV tokens of {int(seq.sum())}: a timed step is one "
+              f"decode of that sample ({dt * 1e3:.1f} ms); value = batch / (that time scaled "
+              f"linearly in KV tokens to the whole batch, {full:.2f} s); N(0,1) K without outlier "
+              f"channels on an identity page table (the timing does not depend on the values)")
     line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": value,
             "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": full * 1e3, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": dt * 1e3, "whole_batch_ms_per_step": full * 1e3,
+            "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(args, cfg, seq),
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
@@ -311,90 +333,217 @@ def run_cache_op(args, cfg):
                       "device_status": cache.last_status()}))
 
 
-def run_sequence_split(args, cfg):
-    """One batch, every context split page-aligned over the ranks: each rank caches and decodes
-    its token range, one NCCL all_gather brings the (o, lse) pairs into local memory, a local
-    kernel merges them. Strong scaling: `value` is the batch's tokens/s at N GPUs."""
-    import torch.distributed as dist
-    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout, parallel
+def _event_ms(step, steps, warmup, device, barrier):
+    """Milliseconds per step from CUDA events on the launching stream, after `warmup` steps."""
+    for _ in range(warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def _max_over_ranks(ms, dist, device):
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _request_rows(cfg, seed, b, n, device):
+    """K, V bf16 [n, HKV, D] of request b: the same rows on whichever rank generates them."""
+    g = torch.Generator(device=device).manual_seed(seed * 100003 + b)
+    k = torch.randn(n, cfg["hkv"], cfg["d"], device=device, generator=g)
+    if cfg["outliers"]:
+        k = k * torch.exp(torch.randn(1, cfg["hkv"], cfg["d"], device=device, generator=g))
+    v = torch.randn(n, cfg["hkv"], cfg["d"], device=device, generator=g)
+    return k.to(torch.bfloat16), v.to(torch.bfloat16)
+
+
+def _cache_of_ranges(cfg, seed, ranges, device, rng_seed):
+    """A cache holding token range [a, b) of every request, with its plan inputs."""
+    from foscar_b200 import QuantKVLayout
+    mine = np.array([b - a for a, b in ranges], dtype=np.int64)
+    pages = [-(-int(n) // PAGE) for n in mine]
+    total = max(sum(pages), 1)
+    indices = np.random.default_rng(rng_seed).permutation(total).astype(np.int32)
+    indptr = np.concatenate([[0], np.cumsum(pages)]).astype(np.int32)
+    layout = QuantKVLayout.create(bits=cfg["bits"], head_dim=cfg["d"], num_kv_heads=cfg["hkv"],
+                                  device=device)
+    cache = layout.allocate(total)
+    for b, (lo, hi) in enumerate(ranges):
+        if hi <= lo:
+            continue
+        k, v = _request_rows(cfg, seed, b, cfg["seq"][1], device)
+        t = torch.arange(hi - lo, device=device)
+        pg = torch.from_numpy(indices[indptr[b]:indptr[b + 1]]).to(device).long()
+        cache.append(k[lo:hi], v[lo:hi], pg[t // PAGE] * PAGE + t % PAGE)
+    return layout, cache, indptr, indices, mine
+
+
+def measure_sequence_split(cfg, seed, steps, warmup, dist, device, rank, world):
+    """ONE batch whose every context is split page-aligned over the ranks: each rank caches and
+    decodes its token range; the (o, lse) rows are exchanged and merged by the library's
+    one-launch exchange (peer stores, flags; foscar_b200.parallel.SequenceSplitExchange). Rank 0
+    also decodes request 0 unsplit and reports the largest difference of its rows. Uniform
+    lengths only (the long-context workloads). Returns (ms per step over ranks, max abs error)."""
+    from foscar_b200 import PagedDecodeWrapper, parallel
+    n = cfg["seq"][1]
+    ranges = [parallel.split_sequence(n, rank, world) for _ in range(cfg["batch"])]
+    layout, cache, indptr, indices, mine = _cache_of_ranges(cfg, seed, ranges, device,
+                                                            seed + 1 + rank)
+    q = (torch.randn(cfg["batch"], cfg["hq"], cfg["d"], device=device,
+                     generator=torch.Generator(device=device).manual_seed(seed))
+         * cfg["q_scale"]).clamp(-448, 448).to(torch.float8_e4m3fn)
+    sm = cfg["d"] ** -0.5 / cfg["q_scale"]
+    w = PagedDecodeWrapper(torch.empty(256 << 20, dtype=torch.uint8, device=device))
+    w.plan(torch.from_numpy(indptr).to(device), torch.from_numpy(indices).to(device),
+           torch.from_numpy(mine.astype(np.int32)), cfg["hq"], layout, sm_scale=sm,
+           o_data_type=torch.float32 if world > 1 else torch.bfloat16)
+    shape = (cfg["batch"], cfg["hq"], cfg["d"])
+    out = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    if world > 1:
+        ex = parallel.SequenceSplitExchange(*shape, device=device)
+        scratch = (torch.empty(shape, dtype=torch.float32, device=device),
+                   torch.empty(shape[:2], dtype=torch.float32, device=device))
+
+        def step():
+            parallel.sequence_split_decode(w, q, cache, out=out, exchange=ex, scratch=scratch)
+    else:
+        def step():
+            w.run(q, cache, out=out)
+    ms = _max_over_ranks(_event_ms(step, steps, warmup, device, barrier), dist, device)
+    status = w.last_status() | (ex.last_status() if world > 1 else 0)
+    err = None
+    if rank == 0:
+        # request 0 unsplit on this GPU
+        one = dict(cfg, batch=1)
+        lay1, cache1, ip1, ix1, _ = _cache_of_ranges(one, seed, [(0, n)], device, seed + 99)
+        w1 = PagedDecodeWrapper(torch.empty(64 << 20, dtype=torch.uint8, device=device))
+        w1.plan(torch.from_numpy(ip1).to(device), torch.from_numpy(ix1).to(device),
+                torch.tensor([n], dtype=torch.int32), cfg["hq"], lay1, sm_scale=sm)
+        ref = w1.run(q[:1].contiguous(), cache1)
+        torch.cuda.synchronize(device)
+        err = float((out[0].float() - ref[0].float()).abs().max().item())
+    return ms, err, status
+
+
+def measure_head_split(cfg, seed, steps, warmup, dist, device, rank, world):
+    """ONE batch whose KV heads (and their query heads) are dealt out to the ranks: every rank
+    caches and decodes the same requests for its own heads; no collective on the data path.
+    Rank 0 checks one request of its output against fp32 attention over the cache's own
+    read-back rows (the reference's GPU test metric) and reports the relative L2 error.
+    Returns (ms per step over ranks, rel-L2, status)."""
+    from foscar_b200 import parallel
+    hq, hkv = parallel.shard_kv_heads(cfg["hq"], cfg["hkv"], rank, world)
+    mine = dict(cfg, hq=len(hq), hkv=len(hkv))
+    case = build_gpu_case(mine, device, seed)
+    w, cache, q = case["wrapper"], case["cache"], case["q"]
+    out = torch.empty(mine["batch"], mine["hq"], mine["d"], dtype=torch.bfloat16, device=device)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    ms = _max_over_ranks(_event_ms(lambda: w.run(q, cache, out=out), steps, warmup, device,
+                                   barrier), dist, device)
+    rel = None
+    if rank == 0:
+        seq, indptr, indices = case["seq"], case["indptr"], case["indices"]
+        b = int(np.argmin(np.where(seq >= 512, seq, 1 << 30)))      # a short request
+        n = int(seq[b])
+        k_back = torch.empty(n, mine["hkv"], mine["d"], dtype=torch.bfloat16, device=device)
+        v_back = torch.empty_like(k_back)
+        pages = torch.from_numpy(indices[indptr[b]:indptr[b + 1]].copy()).to(device)
+        cache.dequantize(k_back, v_back,
+                         torch.tensor([0, pages.numel()], dtype=torch.int32, device=device), pages,
+                         torch.tensor([n], dtype=torch.int32, device=device),
+                         torch.tensor([0], dtype=torch.int32, device=device))
+        g = mine["hq"] // mine["hkv"]
+        kb = k_back.float().repeat_interleave(g, dim=1)
+        vb = v_back.float().repeat_interleave(g, dim=1)
+        sm = mine["d"] ** -0.5 / mine["q_scale"]
+        p = torch.softmax(torch.einsum("hd,nhd->hn", q[b].float(), kb) * sm, dim=-1)
+        want = torch.einsum("hn,nhd->hd", p, vb)
+        rel = float(((out[b].float() - want).norm() / want.norm()).item())
+    return ms, rel, w.last_status()
+
+
+def run_split(args, cfg):
+    """`--split sequence|heads`: one batch over all the ranks (strong scaling)."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    dist = None
     if world > 1:
+        import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
-    seq = seq_lens_of(cfg, args.seed)
-    ranges = [parallel.split_sequence(int(n), rank, world) for n in seq]
-    mine = np.array([b - a for a, b in ranges], dtype=np.int64)
-    pages = [-(-int(n) // PAGE) for n in mine]
-    total = max(sum(pages), 1)
-    rng = np.random.default_rng(args.seed + 1 + rank)
-    indices = rng.permutation(total).astype(np.int32)
-    indptr = np.concatenate([[0], np.cumsum(pages)]).astype(np.int32)
-    layout = QuantKVLayout.create(bits=cfg["bits"], head_dim=cfg["d"], num_kv_heads=cfg["hkv"],
-                                  device=device)
-    cache = layout.allocate(total)
-    g = torch.Generator(device=device).manual_seed(args.seed + rank)
-    for b, n in enumerate(mine):
-        n = int(n)
-        if n == 0:
-            continue
-        k = torch.randn(n, cfg["hkv"], cfg["d"], device=device, generator=g)
-        v = torch.randn(n, cfg["hkv"], cfg["d"], device=device, generator=g)
-        t = torch.arange(n, device=device)
-        pg = torch.from_numpy(indices[indptr[b]:indptr[b + 1]]).to(device).long()
-        cache.append(k.to(torch.bfloat16), v.to(torch.bfloat16), pg[t // PAGE] * PAGE + t % PAGE)
-    q = (torch.randn(cfg["batch"], cfg["hq"], cfg["d"], device=device,
-                     generator=torch.Generator(device=device).manual_seed(args.seed))
-         * cfg["q_scale"]).clamp(-448, 448).to(torch.float8_e4m3fn)
-    w = PagedDecodeWrapper(torch.empty(256 << 20, dtype=torch.uint8, device=device))
-    w.plan(torch.from_numpy(indptr).to(device), torch.from_numpy(indices).to(device),
-           torch.from_numpy(mine.astype(np.int32)), cfg["hq"], layout,
-           sm_scale=cfg["d"] ** -0.5 / cfg["q_scale"], o_data_type=torch.float32)
-    out = torch.empty(cfg["batch"], cfg["hq"], cfg["d"], dtype=torch.bfloat16, device=device)
-
-    def step():
-        if world > 1:
-            parallel.sequence_split_decode(w, q, cache, out=out)
-        else:
-            w.run(q, cache, out=torch.empty(cfg["batch"], cfg["hq"], cfg["d"], device=device))
-
-    for _ in range(args.warmup):
-        step()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize(device)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize(device)
-    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms = float(ms.item())
+    fn = measure_sequence_split if args.split == "sequence" else measure_head_split
+    ms, check, status = fn(cfg, args.seed, args.steps, args.warmup, dist, device, rank, world)
     if rank == 0:
-        peak, kind = measured_peak()
-        moved = algorithmic_bytes(cfg, seq)
-        gbs = moved / ms / 1e6
         print(json.dumps({
             "metric": "decode_tokens_per_s", "value": cfg["batch"] / (ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "us_per_step": ms * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
             "dtype": f"e4m3 x int{cfg['bits']} codes, f32 accumulate", "data": "synthetic",
-            "config": {"workload": f"{args.workload}, every context split over {world} GPUs "
-                                   f"(page-aligned ranges; all_gather of (o, lse) + local merge)",
-                       "parallelism": f"sequence split x{world}"},
-            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak * world, "unit": "GB/s",
-                         "frac": gbs / (peak * world), "of": kind, "traffic": None,
-                         "algorithmic_bytes": moved},
-            "device_status": w.last_status()}))
-    if world > 1:
+            "config": {"workload": f"{args.workload} as ONE batch over {world} GPUs",
+                       "parallelism": f"{args.split} split x{world}"},
+            "check": {"what": "request 0 vs its unsplit decode on one GPU (max abs)"
+                      if args.split == "sequence" else
+                      "one request vs fp32 attention over the cache's read-back (rel L2)",
+                      "value": check},
+            "device_status": status}))
+    if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def split_extras(args, dist, device, rank, world):
+    """The two partitions of the path across GPUs, timed in the run's own process group and
+    attached to its JSON line: the serving sweep shape dealt out by KV heads, and the
+    100,352-token context split by sequence at batch 1 and 16. Each entry carries this run's
+    time at `world` GPUs and rank 0's time for the whole batch on one GPU."""
+    steps, warm = min(args.steps, 20), 3
+    extras = {}
+
+    def both(fn, cfg):
+        ms_n, check, status = fn(cfg, args.seed, steps, warm, dist, device, rank, world)
+        ms_1 = None
+        if dist is not None:
+            dist.barrier()
+        if rank == 0:
+            ms_1, _, _ = fn(cfg, args.seed, steps, warm, None, device, 0, 1)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.empty_cache()
+        if rank != 0:
+            return None
+        return {"us_per_step": ms_n * 1e3, "tokens_per_s": cfg["batch"] / (ms_n * 1e-3),
+                "us_per_step_1gpu": ms_1 * 1e3, "speedup_vs_1gpu": ms_1 / ms_n,
+                "check": check, "device_status": status}
+
+    if WORKLOADS["c5-int2"]["hkv"] % world == 0:
+        extras["tp_heads"] = {"c5-int2": both(measure_head_split, WORKLOADS["c5-int2"]),
+                              "check": "rel L2 of one request vs fp32 attention over the "
+                                       "cache's read-back rows"}
+    extras["seq_split"] = {"c3-b1": both(measure_sequence_split, WORKLOADS["c3-b1"]),
+                           "c3-b16": both(measure_sequence_split, WORKLOADS["c3-b16"]),
+                           "check": "max abs of request 0 vs its unsplit decode on one GPU"}
+    return extras
 
 
 def workload_config(args, cfg, seq):
@@ -404,6 +553,113 @@ def workload_config(args, cfg, seq):
                         f"random page table, token-wise asymmetric groups, q fp8 e4m3",
             "l2": "inputs larger than L2 (packed cache streamed once per step)",
             "parallelism": f"dp{args.gpus} (independent batches per GPU, no collective)"}
+
+
+def cache_op_figures(cfg, device, seed):
+    """The cache writer and the read-back kernel alone on 131,072 tokens of the workload's head
+    shape: algorithmic GB/s from CUDA events (inputs and outputs exceed L2)."""
+    from foscar_b200 import QuantKVLayout
+    tokens, hkv, d, bits = 131072, cfg["hkv"], cfg["d"], cfg["bits"]
+    layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device=device)
+    pages = tokens // PAGE
+    cache = layout.allocate(pages)
+    g = torch.Generator(device=device).manual_seed(seed)
+    k = torch.randn(tokens, hkv, d, device=device, generator=g).to(torch.bfloat16)
+    v = torch.randn(tokens, hkv, d, device=device, generator=g).to(torch.bfloat16)
+    slots = torch.randperm(pages, device=device, generator=g).repeat_interleave(PAGE) * PAGE \
+        + torch.arange(PAGE, device=device).repeat(pages)
+    packed = tokens * hkv * (2 * d * bits // 8 + 16)
+    dense = tokens * hkv * 2 * d * 2
+    k_out, v_out = torch.empty_like(k), torch.empty_like(v)
+    indptr = torch.tensor([0, pages], dtype=torch.int32, device=device)
+    indices = (slots[::PAGE] // PAGE).to(torch.int32)
+    lens = torch.tensor([tokens], dtype=torch.int32, device=device)
+    out_indptr = torch.tensor([0], dtype=torch.int32, device=device)
+
+    def sync():
+        torch.cuda.synchronize(device)
+    ms_a = _event_ms(lambda: cache.append(k, v, slots), 10, 3, device, sync)
+    ms_d = _event_ms(lambda: cache.dequantize(k_out, v_out, indptr, indices, lens, out_indptr),
+                     10, 3, device, sync)
+    return {"append_gbs": (dense + packed + tokens * 8) / ms_a / 1e6, "append_ms": ms_a,
+            "dequantize_gbs": (dense + packed + pages * 4) / ms_d / 1e6, "dequantize_ms": ms_d,
+            "shape": f"{tokens} tokens x {hkv} KV heads x head_dim {d}, INT{bits}, random pages"}
+
+
+GRID_SHAPES = {"hq32-hkv8-d128": (32, 8, 128), "hq8-hkv1-d128": (8, 1, 128),
+               "hq16-hkv2-d64": (16, 2, 64)}
+# The reference's published B200 kernel times, us (benchmarks/decode_latency.csv of the
+# reference, quoted in its README.md:165-172, 192, 227): (INT2, INT4) per (shape, batch, context).
+GRID_PUBLISHED = {
+    ("hq32-hkv8-d128", 1, 32768): (15.3, 17.6), ("hq32-hkv8-d128", 1, 131072): (36.7, 44.2),
+    ("hq32-hkv8-d128", 1, 262144): (62.4, 74.8), ("hq32-hkv8-d128", 1, 524288): (114.3, 135.6),
+    ("hq32-hkv8-d128", 8, 32768): (62.5, 75.1), ("hq32-hkv8-d128", 8, 131072): (218.3, 251.9),
+    ("hq32-hkv8-d128", 8, 262144): (399.1, 456.2), ("hq32-hkv8-d128", 8, 524288): (758.1, 865.7),
+    ("hq8-hkv1-d128", 8, 524288): (114.8, 126.3), ("hq16-hkv2-d64", 8, 524288): (168.4, 206.1),
+}
+
+
+def run_grid(args):
+    """The reference's own benchmark grid with its protocol (benchmarks/timer.py:35-50,
+    benchmarks/run_bench.py:53-81 there): K, V ~ N(0,1), token-wise groups over the whole head,
+    f32 records, random page permutation, q = e4m3(8 q) with sm_scale / 8; a 1 GiB write before
+    every timed call (cold L2), 5 warm-up + 5 timed calls, the median of the decode launch's
+    device time. Prints one JSON object with a row per cell."""
+    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    flush = torch.empty(1 << 30, dtype=torch.uint8, device=device)
+    g = torch.Generator(device=device).manual_seed(0)
+    rows = []
+    for name, (hq, hkv, d) in GRID_SHAPES.items():
+        # one block of random tokens, written again and again: timing does not read values
+        blk = 65536
+        k = torch.randn(blk, hkv, d, device=device, generator=g).to(torch.bfloat16)
+        v = torch.randn(blk, hkv, d, device=device, generator=g).to(torch.bfloat16)
+        for bits in (2, 4):
+            layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device=device)
+            for batch in (1, 8):
+                for ctx in (32768, 131072, 262144, 524288):
+                    pages_per = ctx // PAGE
+                    total = batch * pages_per
+                    cache = layout.allocate(total)
+                    order = torch.randperm(total, device=device, generator=g)
+                    for a in range(0, total * PAGE, blk):
+                        m = min(blk, total * PAGE - a)      # (32K contexts are half a block)
+                        t = torch.arange(a, a + m, device=device)
+                        cache.append(k[:m], v[:m], order[t // PAGE] * PAGE + t % PAGE)
+                    q = (torch.randn(batch, hq, d, device=device, generator=g) * 8.0) \
+                        .clamp(-448, 448).to(torch.float8_e4m3fn)
+                    w = PagedDecodeWrapper(torch.empty(256 << 20, dtype=torch.uint8,
+                                                       device=device))
+                    indptr = torch.arange(batch + 1, dtype=torch.int32) * pages_per
+                    w.plan(indptr.to(device), order.to(torch.int32),
+                           torch.full((batch,), ctx, dtype=torch.int32), hq, layout,
+                           sm_scale=d ** -0.5 / 8.0)
+                    out = torch.empty(batch, hq, d, dtype=torch.bfloat16, device=device)
+                    times = []
+                    for i in range(10):
+                        flush.fill_(i)
+                        e0 = torch.cuda.Event(enable_timing=True)
+                        e1 = torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                        w.run(q, cache, out=out)
+                        e1.record()
+                        torch.cuda.synchronize(device)
+                        if i >= 5:
+                            times.append(e0.elapsed_time(e1) * 1e3)
+                    us = float(np.median(times))
+                    moved = batch * ctx * hkv * (2 * d * bits // 8 + 16)
+                    pub = GRID_PUBLISHED.get((name, batch, ctx))
+                    rows.append({"shape": name, "bits": bits, "batch": batch, "ctx": ctx,
+                                 "us": us, "tbs": moved / us / 1e6,
+                                 "published_us": None if pub is None else pub[bits // 4],
+                                 "status": w.last_status()})
+                    del cache, w
+                    torch.cuda.empty_cache()
+    print(json.dumps({"grid": rows, "protocol": "1 GiB write before every timed call; 5 warm-up "
+                      "+ 5 timed; median of CUDA-event time around the decode launch (the merge "
+                      "of split units runs inside it)"}))
 
 
 def main():
@@ -417,24 +673,31 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=16384,
                     help="KV tokens in the CPU baseline's bounded sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the writer / read-back figures (N = 1) and the head-split and "
+                         "sequence-split runs (N > 1) attached to the line")
     ap.add_argument("--split", default="none", choices=["none", "sequence", "heads"],
                     help="sequence: ONE batch whose every context is split page-aligned over the "
-                         "ranks (strong scaling; one all_gather of (o, lse) per step). heads: ONE "
+                         "ranks (strong scaling; one exchange of (o, lse) per step). heads: ONE "
                          "batch whose KV heads (and their query heads) are dealt out to the ranks "
                          "(tensor parallel, strong scaling, no collective)")
     ap.add_argument("--op", default="decode", choices=["decode", "append", "dequantize"],
                     help="decode: the headline step. append / dequantize: the cache writer or the "
                          "read-back kernel alone on a slice of the workload, as GB/s")
+    ap.add_argument("--grid", action="store_true",
+                    help="the reference's own benchmark grid with its cold-L2 protocol (one GPU)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args, cfg)
+    if args.grid:
+        return run_grid(args)
     if args.op != "decode":
         return run_cache_op(args, cfg)
-    if args.split == "sequence":
-        return run_sequence_split(args, cfg)
+    if args.split != "none":
+        return run_split(args, cfg)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -446,13 +709,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
 
-    by_heads = args.split == "heads"
-    if by_heads:
-        # every rank decodes the same requests (same lengths: same seed) for its own KV heads
-        from foscar_b200 import parallel
-        hq, hkv = parallel.shard_kv_heads(cfg["hq"], cfg["hkv"], rank, world)
-        cfg = dict(cfg, hq=hq.stop - hq.start, hkv=hkv.stop - hkv.start)
-    case = build_gpu_case(cfg, device, args.seed + (0 if by_heads else 17 * rank))
+    case = build_gpu_case(cfg, device, args.seed + 17 * rank)
     w, cache, q, seq = case["wrapper"], case["cache"], case["q"], case["seq"]
     b, hq, d = cfg["batch"], cfg["hq"], cfg["d"]
     out = torch.empty(b, hq, d, dtype=torch.bfloat16, device=device)
@@ -465,7 +722,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    # ---- device-resident timing: value (decode + merge) and the decode kernel alone
+    # ---- device-resident timing: the step (one launch: decode with the merge of split units
+    # inside it), and that launch's own device time from an event pair around every step
     for _ in range(args.warmup):
         w.run(q, cache, out=out)
     torch.cuda.synchronize(device)
@@ -517,34 +775,44 @@ def main():
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     step_ms, e2e_ms, decode_ms = (float(x) for x in stats.cpu())
     status = w.last_status()
+    default_args = args.seed == 0 and args.workload in CAPTURED_TRAFFIC
+    line = None
     if rank == 0:
         peak, peak_kind = measured_peak()
         abytes = algorithmic_bytes(cfg, seq)
         achieved = abytes / (decode_ms * 1e-3) / 1e9
         line = {
-            "metric": "decode_tokens_per_s",
-            "value": (1 if by_heads else world) * b / (step_ms * 1e-3),
+            "metric": "decode_tokens_per_s", "value": world * b / (step_ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": step_ms, "us_per_step": step_ms * 1e3, "higher_is_better": True,
-            "scaling": "strong" if by_heads else "weak", "vs_baseline": None,
+            "scaling": "weak", "vs_baseline": None,
             "dtype": "e4m3 x int%d codes, f32 accumulate"
             % cfg["bits"], "data": "synthetic", "config": workload_config(args, cfg, seq),
             "hbm_gbs": abytes / (step_ms * 1e-3) / 1e9,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "of": peak_kind,
-                         "traffic": NCU_TRAFFIC.get(args.workload),
+                         "traffic": CAPTURED_TRAFFIC[args.workload] if default_args else None,
+                         "traffic_from": "a separate ncu capture of this command's decode launch "
+                                         "(dram__bytes_read.sum + dram__bytes_write.sum), not "
+                                         "measured by this run" if default_args else None,
                          "kernel": "decode_kernel", "kernel_us": decode_ms * 1e3,
                          "algorithmic_bytes": abytes, "frac_of_8tbs_nominal": achieved / 8000.0},
-            "e2e": {"value": (1 if by_heads else world) * b / (e2e_ms * 1e-3), "unit": "tokens/s",
+            "e2e": {"value": world * b / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "us_per_step": e2e_ms * 1e3, "h2d_bytes_per_step": int(q_host.numel()),
                     "d2h_bytes_per_step": int(out_host.numel() * 2)},
             "gpu_launches": launches, "clocks": clocks.summary(), "device_status": status,
             "plan": {"kv_splits": w.kv_splits, "reduction": w.reduction},
         }
-        if by_heads:
-            line["config"]["parallelism"] = (
-                f"kv-head tensor parallel x{world}: {cfg['hkv']} KV heads per GPU, the same "
-                f"batch on every GPU, no collective")
+    del case, w, cache
+    torch.cuda.empty_cache()
+    if not args.no_extras:
+        if world > 1:
+            extras = split_extras(args, dist, device, rank, world)
+            if rank == 0:
+                line.update(extras)
+        elif rank == 0:
+            line["cache_ops"] = cache_op_figures(cfg, device, args.seed)
+    if rank == 0:
         if not args.no_cpu_baseline and world == 1:   # the CPU leg is an N=1 figure
             threads = os.cpu_count() or 1
             torch.set_num_threads(threads)
@@ -559,8 +827,11 @@ def main():
             full = dt * float(seq.sum()) / tokens
             line["cpu_baseline"] = {
                 "value": b / full, "unit": "tokens/s", "cores": threads, "kind": "port",
-                "sample": f"{reqs} requests, {tokens} KV tokens of {int(seq.sum())}, scaled "
-                          f"linearly in tokens; oracle read-back + fp32 softmax attention (torch)"}
+                "sample": f"{reqs} requests, {tokens} KV tokens of {int(seq.sum())}: {dt * 1e3:.1f} "
+                          f"ms per step of the sample, scaled linearly in KV tokens to the whole "
+                          f"batch; oracle read-back + fp32 softmax attention (torch); N(0,1) K "
+                          f"without outlier channels on an identity page table (the timing does "
+                          f"not depend on the values)"}
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()

@@ -115,8 +115,12 @@ extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t 
   }
   total += OVH * (num_ctas - 1);   // about one cut, hence one more piece, per CTA boundary
   long long share = std::max<long long>(OVH + 1, (total + num_ctas - 1) / num_ctas);
-  // the longest unit in max_splits pieces: one may be the remainder of a CTA, the others full
-  const long long full_pieces = std::max(1, max_splits - 1);
+  // The longest unit in so many pieces: one may be the remainder of a CTA, the others full.
+  // Beyond the caller's cap, a unit of T tiles is not worth more than about sqrt(2 T) pieces:
+  // every piece adds a slot to the unit's merge, which the unit's last piece runs alone (a
+  // 32K-token context alone on the GPU was otherwise cut into 40 to 60 pieces of two tiles).
+  const int worth = std::max(2, static_cast<int>(std::sqrt(2.0 * static_cast<double>(longest))));
+  const long long full_pieces = std::max(1, std::min(max_splits, worth) - 1);
   share = std::max(share, OVH + (longest + full_pieces - 1) / full_pieces);
   const int starts_words = (num_ctas + 1 + 7) / 8 * 8;
   int32_t* cta_start = worklist + WORK_WORDS;

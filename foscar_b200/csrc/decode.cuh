@@ -243,53 +243,55 @@ __device__ __forceinline__ void store_value(void* out, int out_dtype, long long 
 }
 
 // Merge of a split unit's partials: the arithmetic and slot order of merge_kernel. Heads h0,
-// h0 + hstep, ... (< gp) of the unit's head tile; the calling thread takes channel `ch`. Kept
-// out of line and rolled: it runs a few times per launch, and the kernel's code footprint is
-// what an item boundary pays for in instruction fetches.
+// h0 + hstep, ... (< gp) of the unit's head tile; the calling thread takes channel `ch`. Called
+// by whole warps whose threads all work on the same heads: the slots' (m, l) pairs are fetched
+// one per lane (the unit has at most 64 pieces) and handed round by shuffles, and the slots' o
+// values eight at a time, so that a merge costs a few memory round trips whatever the piece
+// count (with the loads in sequence a 20-piece merge took longer than a short context's whole
+// decode). Kept out of line: it runs a few times per launch.
 static __device__ __noinline__ void merge_unit_partials(const DecodeParams& P, int d, int gp, int ch,
                                                  bool writes_lse, int k, int b, int kvh, int ht,
                                                  int h0, int hstep) {
   constexpr float LN2 = 0.6931471805599453f;
   __threadfence();
   const long long rows = static_cast<long long>(P.a.batch) * P.a.num_qo_heads;
+  const int lane = threadIdx.x & 31;
+  if (k > 64) k = 64;
 #pragma unroll 1
   for (int h = h0; h < gp; h += hstep) {
     const int hl = ht * 8 + h;
     if (hl >= P.heads_per_kv) continue;
     const long long head = static_cast<long long>(kvh) * P.heads_per_kv + hl;
     const long long row = static_cast<long long>(b) * P.a.num_qo_heads + head;
-    float M = -INFINITY, den = 0.f, acc = 0.f;
-    if (k <= 4) {
-      // the common case in one round trip
-      float ms[4], ls[4], os[4];
+    // slot s: lane s % 32, word s / 32
+    float ms[2], ls[2];
 #pragma unroll
-      for (int s = 0; s < 4; ++s) {
-        const bool on = s < k;
-        ms[s] = on ? __ldcg(P.a.m_partial + s * rows + row) : -INFINITY;
-        ls[s] = on ? __ldcg(P.a.l_partial + s * rows + row) : 0.f;
-        os[s] = on ? __ldcg(P.a.o_partial + (s * rows + row) * d + ch) : 0.f;
-      }
+    for (int j = 0; j < 2; ++j) {
+      const int s = lane + 32 * j;
+      ms[j] = s < k ? __ldcg(P.a.m_partial + s * rows + row) : -INFINITY;
+      ls[j] = s < k ? __ldcg(P.a.l_partial + s * rows + row) : 0.f;
+    }
+    float M = fmaxf(ms[0], ms[1]);
 #pragma unroll
-      for (int s = 0; s < 4; ++s) M = fmaxf(M, ms[s]);
-      if (M > -INFINITY) {
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+    float wl[2];   // this lane's slots' weights (0 for a slot past k or without a maximum)
 #pragma unroll
-        for (int s = 0; s < 4; ++s) {
-          if (s < k) {
-            const float wgt = exp2f(ms[s] - M);
-            den += wgt * ls[s];
-            acc += wgt * os[s];
-          }
-        }
-      }
-    } else {
+    for (int j = 0; j < 2; ++j) wl[j] = (M > -INFINITY && lane + 32 * j < k) ? exp2f(ms[j] - M) : 0.f;
+    float den = 0.f, acc = 0.f;
 #pragma unroll 1
-      for (int s = 0; s < k; ++s) M = fmaxf(M, __ldcg(P.a.m_partial + s * rows + row));
-      if (M > -INFINITY) {
-#pragma unroll 4
-        for (int s = 0; s < k; ++s) {
-          const float wgt = exp2f(__ldcg(P.a.m_partial + s * rows + row) - M);
-          den += wgt * __ldcg(P.a.l_partial + s * rows + row);
-          acc += wgt * __ldcg(P.a.o_partial + (s * rows + row) * d + ch);
+    for (int s0 = 0; s0 < k; s0 += 8) {
+      float os[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        os[i] = s0 + i < k ? __ldcg(P.a.o_partial + ((s0 + i) * rows + row) * d + ch) : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int s = s0 + i;                     // (warp-uniform)
+        const float wgt = __shfl_sync(0xFFFFFFFFu, s < 32 ? wl[0] : wl[1], s & 31);
+        const float lv = __shfl_sync(0xFFFFFFFFu, s < 32 ? ls[0] : ls[1], s & 31);
+        if (s < k) {
+          den += wgt * lv;
+          acc += wgt * os[i];
         }
       }
     }
