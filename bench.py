@@ -388,7 +388,8 @@ def _cache_of_ranges(cfg, seed, ranges, device, rng_seed):
 def measure_sequence_split(cfg, seed, steps, warmup, dist, device, rank, world):
     """ONE batch whose every context is split page-aligned over the ranks: each rank caches and
     decodes its token range; the (o, lse) rows are exchanged and merged by the library's
-    one-launch exchange (peer stores, flags; foscar_b200.parallel.SequenceSplitExchange). Rank 0
+    one-launch exchange (peer stores, flags; foscar_b200.parallel.SequenceSplitExchange); a step
+    (decode launch + exchange launch) is replayed from a CUDA graph, at one GPU too. Rank 0
     also decodes request 0 unsplit and reports the largest difference of its rows. Uniform
     lengths only (the long-context workloads). Returns (ms per step over ranks, max abs error)."""
     from foscar_b200 import PagedDecodeWrapper, parallel
@@ -422,7 +423,16 @@ def measure_sequence_split(cfg, seed, steps, warmup, dist, device, rank, world):
     else:
         def step():
             w.run(q, cache, out=out)
-    ms = _max_over_ranks(_event_ms(step, steps, warmup, device, barrier), dist, device)
+    # the step as a CUDA graph (decode launch + exchange launch): at these step times the
+    # host's dispatch of two launches would otherwise be what is measured
+    for _ in range(3):
+        step()
+    barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    barrier()
+    ms = _max_over_ranks(_event_ms(graph.replay, steps, warmup, device, barrier), dist, device)
     status = w.last_status() | (ex.last_status() if world > 1 else 0)
     err = None
     if rank == 0:

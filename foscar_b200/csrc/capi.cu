@@ -31,44 +31,9 @@ extern "C" int64_t fq_workspace_bytes(int32_t max_splits, int32_t batch, int32_t
   return 4ll * max_splits * batch * num_qo_heads * (head_dim + 2);
 }
 
-// Cost of running `base` units cut into s pieces each on `sms` CTAs (microseconds). Constants
-// are per 128-token tile of this library's kernel; the form (waves x (tiles + per-piece) +
-// merge) is the one the reference's planner uses (src/foscar/_sm100/scheduler.py:101-127).
-static double split_cost(long long base, int tiles, int s, int bits, int sms) {
-  const double t_tile = bits == 2 ? 0.085 : 0.13;  // us per 128-token tile per CTA
-  const double t_piece = 2.5, t_merge = 3.0;
-  const double waves = std::ceil(static_cast<double>(base) * s / sms);
-  return waves * (t_tile * std::ceil(static_cast<double>(tiles) / s) + t_piece) +
-         (s > 1 ? t_merge : 0.0);
-}
-
-extern "C" int fq_plan_splits(int32_t batch, int32_t num_kv_heads, int32_t head_tiles,
-                              int32_t max_kv_len, int32_t bits, int32_t head_dim,
-                              int32_t sm_count) {
-  (void)head_dim;
-  if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || sm_count < 1) return FQ_ERR_BAD_ARG;
-  if (bits != 2 && bits != 4) return FQ_ERR_BAD_ARG;
-  const long long base = static_cast<long long>(batch) * num_kv_heads * head_tiles;
-  const int tt = tile_tokens(bits, head_dim);
-  const int tiles = std::max(1, (max_kv_len + tt - 1) / tt);
-  int best = 1;
-  double best_cost = split_cost(base, tiles, 1, bits, sm_count);
-  for (int s = 2; s <= 64; ++s) {
-    if (tiles / s < 4) break;  // at least 512 tokens per piece
-    const double c = split_cost(base, tiles, s, bits, sm_count);
-    if (c < best_cost - 1e-9) { best = s; best_cost = c; }
-  }
-  return best;
-}
-
-// Words an explicit list needs for `units` units on `num_ctas` CTAs (a cut adds one piece).
-static long long worklist_words(long long units, int num_ctas) {
-  const long long starts = (static_cast<long long>(num_ctas) + 1 + 7) / 8 * 8;
-  return WORK_WORDS + starts + WORK_WORDS * (units + num_ctas);
-}
-
-// Fixed cost of a piece in tile units (pipeline refill, the group hand-off of the item's state and
-// the output), as measured on B200 against the cost of streaming one tile.
+// Fixed cost of a piece in tile units (pipeline refill, the merge of the groups' states and the
+// output), as measured on B200 against the cost of streaming one tile (about 4.7 us against
+// 0.34 us per 128-token INT2 tile at head_dim 128).
 static long long piece_overhead(int bits, int head_dim) {
   long long ovh = bits == 4 && head_dim != 64 ? 10 : 14;
   if (const char* env = getenv("FOSCAR_B200_PIECE_OVERHEAD")) {   // tuning knob for experiments
@@ -81,6 +46,43 @@ static long long piece_overhead(int bits, int head_dim) {
 extern "C" int fq_piece_overhead(int32_t bits, int32_t head_dim) {
   if (bits != 2 && bits != 4) return FQ_ERR_BAD_ARG;
   return static_cast<int>(piece_overhead(bits, head_dim));
+}
+
+// Cost, in tile units, of running `base` units cut into s pieces each on `sms` CTAs: the form
+// (waves x (tiles + per-piece) + merge) is the one the reference's planner uses
+// (src/foscar/_sm100/scheduler.py:101-127); the constants are the balanced planner's: the
+// per-piece overhead above, and a merge of s slots by the unit's last piece (about 2 us plus
+// 0.1 us a slot).
+static double split_cost(long long base, int tiles, int s, long long ovh, int sms) {
+  const double waves = std::ceil(static_cast<double>(base) * s / sms);
+  return waves * (std::ceil(static_cast<double>(tiles) / s) + static_cast<double>(ovh)) +
+         (s > 1 ? 6.0 + 0.3 * s : 0.0);
+}
+
+extern "C" int fq_plan_splits(int32_t batch, int32_t num_kv_heads, int32_t head_tiles,
+                              int32_t max_kv_len, int32_t bits, int32_t head_dim,
+                              int32_t sm_count) {
+  if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || sm_count < 1) return FQ_ERR_BAD_ARG;
+  if (bits != 2 && bits != 4) return FQ_ERR_BAD_ARG;
+  const long long base = static_cast<long long>(batch) * num_kv_heads * head_tiles;
+  const long long ovh = piece_overhead(bits, head_dim);
+  const int tt = tile_tokens(bits, head_dim);
+  const int tiles = std::max(1, (max_kv_len + tt - 1) / tt);
+  int best = 1;
+  double best_cost = split_cost(base, tiles, 1, ovh, sm_count);
+  for (int s = 2; s <= 64; ++s) {
+    if (tiles / s < 4) break;  // at least four tiles per piece
+    const double c = split_cost(base, tiles, s, ovh, sm_count);
+    // more pieces only for a gain of a few percent: every piece adds partial traffic
+    if (c < 0.97 * best_cost) { best = s; best_cost = c; }
+  }
+  return best;
+}
+
+// Words an explicit list needs for `units` units on `num_ctas` CTAs (a cut adds one piece).
+static long long worklist_words(long long units, int num_ctas) {
+  const long long starts = (static_cast<long long>(num_ctas) + 1 + 7) / 8 * 8;
+  return WORK_WORDS + starts + WORK_WORDS * (units + num_ctas);
 }
 
 // Balanced plan: every piece (a unit, or a part of a unit cut between CTAs) costs its tile count

@@ -14,8 +14,11 @@
 //
 // Layout of one rank's staging buffer (floats unless said): for parity p in {0, 1}:
 //   rows  [world][rows_per_rank][d + 1]   (o row, then lse), slot r written by rank r
-// then  flags int64 [2][world]  (the step a rank has posted for that parity), then a launch
-// counter int32 [2] used by this rank's own launches only.
+// then  flags int64 [2][world]  (the step a rank has posted for that parity), then words used by
+// this rank's own launches only: arrival counters int32 [2], an exit counter int32 and the
+// number of steps this rank has run int64. With step == 0 a launch takes its step from that
+// count (every rank launches the same number of times), so that a captured launch can be
+// replayed: nothing the host passes changes from step to step.
 #include "common.cuh"
 
 namespace fq {
@@ -39,7 +42,7 @@ __host__ __device__ inline long long exchange_rows_floats(int world, int rows, i
 }
 __host__ __device__ inline long long exchange_bytes(int world, int rows, int d) {
   const long long data = 2 * exchange_rows_floats(world, rows, d) * 4;
-  return (data + 15) / 16 * 16 + 2 * world * 8 + 16;
+  return (data + 15) / 16 * 16 + 2 * world * 8 + 32;
 }
 
 __device__ inline void store_out_x(void* out, int out_dtype, long long idx, float val) {
@@ -51,6 +54,16 @@ __device__ inline void store_out_x(void* out, int out_dtype, long long idx, floa
 // All CTAs of the launch are resident at once (the host keeps the grid at or below the SM
 // count): they wait on one another through a counter and on the peers through flags.
 __global__ void __launch_bounds__(256) exchange_merge_kernel(ExchangeArgs a) {
+  __shared__ long long s_step;
+  {
+    const long long par_f = exchange_rows_floats(a.world, a.rows, a.d);
+    char* own = reinterpret_cast<char*>(a.staging[a.rank]) + (2 * par_f * 4 + 15) / 16 * 16 +
+                2 * a.world * 8;
+    volatile long long* steps_run = reinterpret_cast<volatile long long*>(own + 16);
+    if (threadIdx.x == 0) s_step = a.step > 0 ? a.step : *steps_run + 1;
+    __syncthreads();
+    a.step = s_step;
+  }
   const int par = static_cast<int>(a.step & 1);
   const long long slot_floats = static_cast<long long>(a.rows) * (a.d + 1);
   const long long par_floats = exchange_rows_floats(a.world, a.rows, a.d);
@@ -103,8 +116,9 @@ __global__ void __launch_bounds__(256) exchange_merge_kernel(ExchangeArgs a) {
     s_flag = ok;
   }
   __syncthreads();
-  if (!s_flag) return;   // a peer never posted: the output is left as it was
-  // 4. merge the gathered rows (all in this rank's memory)
+  // 4. merge the gathered rows (all in this rank's memory); a peer that never posted leaves the
+  // output as it was
+  if (s_flag) {
   const float* base = mine + par * par_floats;
   for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
     float L = -INFINITY;
@@ -126,6 +140,15 @@ __global__ void __launch_bounds__(256) exchange_merge_kernel(ExchangeArgs a) {
         a.lse_out[row] = den > 0.f ? L + logf(den) : -INFINITY;
     }
   }
+  }
+  // 5. the launch's last CTA to leave counts the step (every CTA has read the count by now)
+  if (threadIdx.x == 0) {
+    int* exits = counter - par + 2;
+    if (atomicAdd(exits, 1) == static_cast<int>(gridDim.x) - 1) {
+      *exits = 0;
+      *reinterpret_cast<volatile long long*>(reinterpret_cast<char*>(counter - par) + 16) = a.step;
+    }
+  }
 }
 
 }  // namespace fq
@@ -144,7 +167,7 @@ extern "C" int fq_exchange_merge(void* const* staging, int32_t rank, int32_t wor
                                  int32_t* status, void* stream) {
   if (!staging || !o_local || !lse_local || !out) return FQ_ERR_BAD_ARG;
   if (world < 1 || world > fq::MAX_RANKS || rank < 0 || rank >= world) return FQ_ERR_BAD_ARG;
-  if (batch < 1 || num_qo_heads < 1 || head_dim < 1 || step < 1) return FQ_ERR_BAD_ARG;
+  if (batch < 1 || num_qo_heads < 1 || head_dim < 1 || step < 0) return FQ_ERR_BAD_ARG;
   if (out_dtype < 0 || out_dtype > 2) return FQ_ERR_BAD_ARG;
   fq::ExchangeArgs a{};
   for (int r = 0; r < world; ++r) {

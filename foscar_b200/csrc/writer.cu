@@ -163,6 +163,11 @@ __device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta
 template <int BITS, int D, bool PREQ>
 __global__ void __launch_bounds__(256) append_kernel(WriterArgs a) {
   __shared__ int hist_delta[FQ_VMAX_BINS];
+  // A launch that follows this one under programmatic stream serialization (the decode of the
+  // same step, flags bit 0 of fq_decode_args) may begin its on-chip set-up now; it waits for
+  // this grid to complete before its first global access (the reference's writer does the
+  // same, src/foscar/_append_core.py:1154-1159). A no-op otherwise.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   for (int i = threadIdx.x; i < FQ_VMAX_BINS; i += blockDim.x) hist_delta[i] = 0;
   __syncthreads();
   append_rows<BITS, D, PREQ>(a, hist_delta);

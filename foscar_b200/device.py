@@ -24,12 +24,12 @@ def _cc(index: int) -> tuple:
 
 def cuda_index(device=None) -> int:
     """The CUDA ordinal of `device`; None or an index-less CUDA device is the current device."""
-    if device is None:
+    spec = None if device is None else torch.device(device)
+    if spec is not None and spec.type != "cuda":
+        raise ValueError(f"{spec} is not a CUDA device")
+    if spec is None or spec.index is None:
         return torch.cuda.current_device()
-    device = torch.device(device)
-    if device.type != "cuda":
-        raise ValueError(f"{device} is not a CUDA device")
-    return torch.cuda.current_device() if device.index is None else device.index
+    return spec.index
 
 
 def device_arch(device=None) -> Optional[str]:
@@ -53,10 +53,9 @@ def sm_count(device=None) -> int:
 
 def on_device(device):
     """Context making `device` current (launches bind the current device's stream)."""
-    index = cuda_index(device)
-    if torch.cuda.current_device() == index:
-        return contextlib.nullcontext()
-    return torch.cuda.device(index)
+    wanted = cuda_index(device)
+    already = torch.cuda.current_device() == wanted
+    return contextlib.nullcontext() if already else torch.cuda.device(wanted)
 
 
 def current_stream_ptr(device=None) -> int:

@@ -29,11 +29,13 @@ READER = "IntDecodeSm100"
 def clip_index(ratio, head_dim: int) -> int:
     """Order-statistic index of `append`'s per-row clip, -1 for none: a ratio r in (0, 1] clamps a
     row to +-(its |x| sorted ascending)[min(int(r*D), D-1)] (src/foscar/kv_cache.py:104-118)."""
-    if ratio is None:
-        return -1
-    if isinstance(ratio, bool) or not isinstance(ratio, (int, float)) or not 0.0 < ratio <= 1.0:
-        raise ValueError(f"a clip ratio is a number in (0, 1], or None for no clip; got {ratio!r}")
-    return min(int(ratio * head_dim), head_dim - 1)
+    if ratio is not None:
+        numeric = isinstance(ratio, (int, float)) and not isinstance(ratio, bool)
+        if not numeric or ratio <= 0.0 or ratio > 1.0:
+            raise ValueError(f"a clip ratio is a number in (0, 1], or None for no clip; got "
+                             f"{ratio!r}")
+        return min(head_dim - 1, int(ratio * head_dim))
+    return -1
 
 
 def _positive_int(name, value):
@@ -178,34 +180,36 @@ class QuantKVLayout:
         _positive_int("num_pages", num_pages)
         if not isinstance(buffer, torch.Tensor):
             raise TypeError(f"bind() takes a torch.Tensor; got {type(buffer).__name__}")
-        if buffer.dtype != torch.uint8:
-            raise ValueError(f"bind() takes a uint8 buffer; got {buffer.dtype}")
-        if not buffer.is_contiguous():
-            raise ValueError("bind() takes a C-contiguous buffer")
         need = num_pages * self.bytes_per_page()
-        if buffer.numel() < need:
-            raise ValueError(f"a {num_pages}-page cache of this layout needs {need} bytes; the "
-                             f"buffer holds {buffer.numel()}")
-        if buffer.data_ptr() % 16:
-            raise ValueError("bind() takes a buffer whose start is 16-byte aligned")
+        problems = (
+            (buffer.dtype != torch.uint8, f"bind() takes a uint8 buffer; got {buffer.dtype}"),
+            (not buffer.is_contiguous(), "bind() takes a C-contiguous buffer"),
+            (buffer.numel() < need, f"a {num_pages}-page cache of this layout needs {need} "
+                                    f"bytes; the buffer holds {buffer.numel()}"),
+            (buffer.data_ptr() % 16 != 0, "bind() takes a buffer whose start is 16-byte aligned"),
+        )
+        for wrong, message in problems:
+            if wrong:
+                raise ValueError(message)
         _require_device(self, buffer.device)
-        flat = buffer.view(-1)
+        # one region per pool, in the order of _page_bytes(), each as long as its pages
+        raw = buffer.reshape(-1)
         shapes, dtypes = self.pool_shapes(num_pages), self.pool_dtypes()
-        pools, start = {}, 0
-        for name, per_page in self._page_bytes().items():
-            region = flat[start:start + num_pages * per_page]
-            if name == "v_page_max":
-                region.zero_()
-            if dtypes[name] != torch.uint8:
-                region = region.view(dtypes[name])
-            pools[name] = region.view(shapes[name])
-            start += num_pages * per_page
-        v_page_max, v_max_hist = pools.get("v_page_max"), None
-        if v_page_max is not None:
-            v_max_hist = torch.zeros(VMAX_BINS, dtype=torch.int32,
-                                     device=buffer.device).view(V_PAGE_MAX_DTYPE)
-        return QuantKVCache._build(self, pools["k_codes"], pools["v_codes"], pools["scales"],
-                                   v_page_max, v_max_hist)
+        views, offset = {}, 0
+        for pool, per_page in self._page_bytes().items():
+            length = num_pages * per_page
+            chunk = raw.narrow(0, offset, length)
+            offset += length
+            if pool == "v_page_max":
+                chunk.zero_()
+            typed = chunk if dtypes[pool] == torch.uint8 else chunk.view(dtypes[pool])
+            views[pool] = typed.view(shapes[pool])
+        hist = None
+        if "v_page_max" in views:
+            hist = torch.zeros(VMAX_BINS, dtype=torch.int32, device=buffer.device)
+            hist = hist.view(V_PAGE_MAX_DTYPE)
+        return QuantKVCache._build(self, views["k_codes"], views["v_codes"], views["scales"],
+                                   views.get("v_page_max"), hist)
 
 
 def _require_device(layout, device):
@@ -236,24 +240,25 @@ class QuantKVCache:
 
     @classmethod
     def _build(cls, layout, k_codes, v_codes, scales, v_page_max, v_max_hist) -> "QuantKVCache":
-        self = object.__new__(cls)
-        self.layout = layout
-        self.num_pages = int(k_codes.shape[0])
-        self.device = k_codes.device
-        self.k_codes, self.v_codes, self.scales = k_codes, v_codes, scales
-        self.v_page_max, self.v_max_hist = v_page_max, v_max_hist
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        k_groups = (layout.head_dim // layout.k_quant[1]) if layout.k_quant[0] == "token" else 1
-        self._c_pools = _lib.Pools(
+        cache = object.__new__(cls)
+        fields = dict(layout=layout, num_pages=int(k_codes.shape[0]), device=k_codes.device,
+                      k_codes=k_codes, v_codes=v_codes, scales=scales, v_page_max=v_page_max,
+                      v_max_hist=v_max_hist,
+                      status=torch.zeros(1, dtype=torch.int32, device=k_codes.device))
+        for name, value in fields.items():
+            setattr(cache, name, value)
+        k_axis, k_group = layout.k_quant
+
+        def address(t):
+            return None if t is None else t.data_ptr()
+        cache._c_pools = _lib.Pools(
             bits=layout.bits, head_dim=layout.head_dim, num_kv_heads=layout.num_kv_heads,
-            k_groups=k_groups, scale_bf16=int(layout.scale_dtype == torch.bfloat16),
-            num_pages=self.num_pages,
-            k_channel_group=layout.k_quant[1] if layout.k_quant[0] == "channel" else 0,
-            k_codes=k_codes.data_ptr(), v_codes=v_codes.data_ptr(),
-            scales=scales.data_ptr(),
-            v_page_max=None if v_page_max is None else v_page_max.data_ptr(),
-            v_max_hist=None if v_max_hist is None else v_max_hist.data_ptr())
-        return self
+            k_groups=layout.head_dim // k_group if k_axis == "token" else 1,
+            scale_bf16=int(layout.scale_dtype == torch.bfloat16), num_pages=cache.num_pages,
+            k_channel_group=k_group if k_axis == "channel" else 0,
+            k_codes=address(k_codes), v_codes=address(v_codes), scales=address(scales),
+            v_page_max=address(v_page_max), v_max_hist=address(v_max_hist))
+        return cache
 
     def last_status(self) -> int:
         """The device status word (0 = no fault). Waits for the device."""
@@ -269,13 +274,16 @@ class QuantKVCache:
                    if lay.is_page_channel_k else ""))
 
     def _check_slots(self, slot_mapping, num_tokens):
-        if (not isinstance(slot_mapping, torch.Tensor) or slot_mapping.dtype != torch.int64
-                or tuple(slot_mapping.shape) != (num_tokens,)
-                or not slot_mapping.is_contiguous()):
+        ok = (isinstance(slot_mapping, torch.Tensor) and slot_mapping.dtype == torch.int64
+              and slot_mapping.dim() == 1 and slot_mapping.shape[0] == num_tokens
+              and slot_mapping.is_contiguous())
+        if not ok:
             raise ValueError(f"slot_mapping must be a contiguous int64 [{num_tokens}] tensor")
-        if slot_mapping.device != self.device:
-            raise ValueError(f"slot_mapping is on {slot_mapping.device}; the cache is on "
-                             f"{self.device}")
+        self._same_device("slot_mapping", slot_mapping)
+
+    def _same_device(self, name, x):
+        if x.device != self.device:
+            raise ValueError(f"{name} is on {x.device}; the cache is on {self.device}")
 
     def recount_v_max(self) -> None:
         """Clear every page maximum's sign bit and rebuild `v_max_hist` from the cells, on the
@@ -287,6 +295,25 @@ class QuantKVCache:
                                                    _dev.current_stream_ptr(self.device)),
                        "recount_v_max")
 
+    def _check_token_rows(self, name, x, rows=None):
+        """bf16 [T, HKV, D] input rows (T = `rows` when given): each token's [HKV, D] block
+        contiguous, token stride free, rows 16-byte aligned."""
+        H, D = self.layout.num_kv_heads, self.layout.head_dim
+        good = isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16 and x.dim() == 3 \
+            and (x.shape[1], x.shape[2]) == (H, D) and (rows is None or x.shape[0] == rows)
+        if not good:
+            lead = "T" if rows is None else rows
+            extra = " (64 rows per page)" if rows is not None else ""
+            raise ValueError(f"{name} must be a bfloat16 [{lead}, {H}, {D}] tensor{extra}; got "
+                             f"{getattr(x, 'dtype', None)} {tuple(getattr(x, 'shape', ()))}")
+        self._same_device(name, x)
+        token, head, channel = x.stride()
+        if (head, channel) != (D, 1):
+            raise ValueError(f"{name} must have a contiguous [num_kv_heads, head_dim] row per "
+                             f"token (strides (*, {D}, 1)); got {tuple(x.stride())}")
+        if x.data_ptr() % 16 != 0 or (token * x.element_size()) % 16 != 0:
+            raise ValueError(f"every token row of {name} must start 16-byte aligned")
+
     def append(self, k: torch.Tensor, v: torch.Tensor, slot_mapping: torch.Tensor, *,
                k_clip=None, v_clip=None) -> None:
         """Quantize and write tokens: k, v bfloat16 [T, HKV, D] (head dimension contiguous, free
@@ -295,26 +322,14 @@ class QuantKVCache:
         or past num_pages * 64 is skipped and sets a status bit (the reference traps)."""
         lay = self.layout
         self._refuse_channel_wise("append")
-        shape = (lay.num_kv_heads, lay.head_dim)
-        for name, x in (("k", k), ("v", v)):
-            if not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or x.dim() != 3 \
-                    or tuple(x.shape[1:]) != shape:
-                raise ValueError(f"{name} must be a bfloat16 [T, {shape[0]}, {shape[1]}] tensor; "
-                                 f"got {getattr(x, 'dtype', None)} "
-                                 f"{tuple(getattr(x, 'shape', ()))}")
-            if x.device != self.device:
-                raise ValueError(f"{name} is on {x.device}; the cache is on {self.device}")
-            if x.stride(2) != 1 or x.stride(1) != lay.head_dim:
-                raise ValueError(f"{name} must have a contiguous [num_kv_heads, head_dim] row "
-                                 f"per token (strides (*, {lay.head_dim}, 1)); got "
-                                 f"{tuple(x.stride())}")
-            if x.data_ptr() % 16 or (x.stride(0) * x.element_size()) % 16:
-                raise ValueError(f"every token row of {name} must start 16-byte aligned")
-        if k.shape[0] != v.shape[0]:
-            raise ValueError(f"k has {k.shape[0]} tokens and v has {v.shape[0]}")
-        if k.shape[0] > MAX_APPEND_TOKENS:
+        self._check_token_rows("k", k)
+        self._check_token_rows("v", v)
+        tokens = k.shape[0]
+        if v.shape[0] != tokens:
+            raise ValueError(f"k has {tokens} tokens and v has {v.shape[0]}")
+        if tokens > MAX_APPEND_TOKENS:
             raise ValueError(f"one append takes at most {MAX_APPEND_TOKENS} tokens; got "
-                             f"{k.shape[0]}: split it into several appends")
+                             f"{tokens}: split it into several appends")
         self._check_slots(slot_mapping, k.shape[0])
         kc, vc = clip_index(k_clip, lay.head_dim), clip_index(v_clip, lay.head_dim)
         if k.shape[0] == 0:
@@ -353,21 +368,8 @@ class QuantKVCache:
                 or valid_tokens.device != self.device):
             raise ValueError(f"valid_tokens must be a contiguous int32 [{groups}] tensor on "
                              f"{self.device}")
-        shape = (groups * PAGE_SIZE, lay.num_kv_heads, lay.head_dim)
-        for name, x in (("k", k), ("v", v)):
-            if not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 \
-                    or tuple(x.shape) != shape:
-                raise ValueError(f"{name} must be a bfloat16 {list(shape)} tensor (64 rows per "
-                                 f"page); got {getattr(x, 'dtype', None)} "
-                                 f"{tuple(getattr(x, 'shape', ()))}")
-            if x.device != self.device:
-                raise ValueError(f"{name} is on {x.device}; the cache is on {self.device}")
-            if x.stride(2) != 1 or x.stride(1) != lay.head_dim:
-                raise ValueError(f"{name} must have a contiguous [num_kv_heads, head_dim] row "
-                                 f"per token (strides (*, {lay.head_dim}, 1)); got "
-                                 f"{tuple(x.stride())}")
-            if x.data_ptr() % 16 or (x.stride(0) * x.element_size()) % 16:
-                raise ValueError(f"every token row of {name} must start 16-byte aligned")
+        self._check_token_rows("k", k, rows=groups * PAGE_SIZE)
+        self._check_token_rows("v", v, rows=groups * PAGE_SIZE)
         if groups == 0:
             return
         with _dev.on_device(self.device):
@@ -389,21 +391,23 @@ class QuantKVCache:
         T = k_codes.shape[0] if isinstance(k_codes, torch.Tensor) and k_codes.dim() else None
         groups = D // lay.k_quant[1]
         k_group = (T, H, groups) if groups > 1 else (T, H)
-        for name, x, dtype, shape in (("k_codes", k_codes, torch.uint8, (T, H, D)),
-                                      ("k_scale", k_scale, torch.float32, k_group),
-                                      ("k_zero", k_zero, torch.float32, k_group),
-                                      ("v_codes", v_codes, torch.uint8, (T, H, D)),
-                                      ("v_scale", v_scale, torch.float32, (T, H)),
-                                      ("v_zero", v_zero, torch.float32, (T, H))):
-            if not isinstance(x, torch.Tensor) or x.dtype != dtype or tuple(x.shape) != shape:
-                want = ["T" if e is None else e for e in shape]
-                raise ValueError(f"{name} must be a {dtype} {want} tensor; got "
+        wanted = {"k_codes": (k_codes, torch.uint8, (T, H, D)),
+                  "k_scale": (k_scale, torch.float32, k_group),
+                  "k_zero": (k_zero, torch.float32, k_group),
+                  "v_codes": (v_codes, torch.uint8, (T, H, D)),
+                  "v_scale": (v_scale, torch.float32, (T, H)),
+                  "v_zero": (v_zero, torch.float32, (T, H))}
+        for name, (x, dtype, shape) in wanted.items():
+            matches = isinstance(x, torch.Tensor) and x.dtype == dtype \
+                and tuple(x.shape) == shape
+            if not matches:
+                spelled = ["T" if extent is None else extent for extent in shape]
+                raise ValueError(f"{name} must be a {dtype} {spelled} tensor; got "
                                  f"{getattr(x, 'dtype', None)} {tuple(getattr(x, 'shape', ()))}")
             if not x.is_contiguous():
                 raise ValueError(f"{name} must be C-contiguous")
-            if x.device != self.device:
-                raise ValueError(f"{name} is on {x.device}; the cache is on {self.device}")
-            if dtype == torch.uint8 and x.data_ptr() % 16:
+            self._same_device(name, x)
+            if dtype == torch.uint8 and x.data_ptr() % 16 != 0:
                 raise ValueError(f"{name} must start 16-byte aligned")
         if T > MAX_APPEND_TOKENS:
             raise ValueError(f"one append takes at most {MAX_APPEND_TOKENS} tokens; got {T}: "
@@ -418,6 +422,23 @@ class QuantKVCache:
                 slot_mapping.data_ptr(), T, self.status.data_ptr(),
                 _dev.current_stream_ptr(self.device)), "append_quantized")
 
+    def _check_rows_out(self, name, x):
+        """A bf16 [N, HKV, D] destination whose token rows are whole, apart and 16-byte aligned."""
+        H, D = self.layout.num_kv_heads, self.layout.head_dim
+        typed = isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16 and x.dim() == 3
+        if not typed or (x.shape[1], x.shape[2]) != (H, D):
+            raise ValueError(f"{name} must be a bfloat16 [N, {H}, {D}] tensor; got "
+                             f"{getattr(x, 'dtype', None)} {tuple(getattr(x, 'shape', ()))}")
+        self._same_device(name, x)
+        token, head, channel = x.stride()
+        overlapping = x.shape[0] > 1 and token < H * D
+        if channel != 1 or head != D or overlapping:
+            raise ValueError(f"{name} must hold each token's [num_kv_heads, head_dim] row "
+                             f"contiguously, rows not overlapping (strides (>= {H * D}, {D}, 1)); "
+                             f"got {tuple(x.stride())}")
+        if x.data_ptr() % 16 != 0 or (token * x.element_size()) % 16 != 0:
+            raise ValueError(f"every token row of {name} must start 16-byte aligned")
+
     def dequantize(self, k_out, v_out, page_indptr, page_indices, seq_lens, out_indptr) -> None:
         """Read K and V of a batch back into bf16 rows: `k_out[out_indptr[b] + t] =
         bf16(fma(s_k, q, z_k))` for t < seq_lens[b], V likewise
@@ -430,34 +451,22 @@ class QuantKVCache:
                 f"K per channel over a page, which append_page_groups() writes); "
                 f"k_quant={lay.k_quant} v_quant={lay.v_quant} has a channel-wise tensor")
         H, D = lay.num_kv_heads, lay.head_dim
-        for name, x in (("k_out", k_out), ("v_out", v_out)):
-            if not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or x.dim() != 3 \
-                    or tuple(x.shape[1:]) != (H, D):
-                raise ValueError(f"{name} must be a bfloat16 [N, {H}, {D}] tensor; got "
-                                 f"{getattr(x, 'dtype', None)} "
-                                 f"{tuple(getattr(x, 'shape', ()))}")
-            if x.device != self.device:
-                raise ValueError(f"{name} is on {x.device}; the cache is on {self.device}")
-            if x.stride(2) != 1 or x.stride(1) != D or (x.shape[0] > 1 and x.stride(0) < H * D):
-                raise ValueError(f"{name} must hold each token's [num_kv_heads, head_dim] row "
-                                 f"contiguously, rows not overlapping (strides (>= {H * D}, "
-                                 f"{D}, 1)); got {tuple(x.stride())}")
-            if x.data_ptr() % 16 or (x.stride(0) * x.element_size()) % 16:
-                raise ValueError(f"every token row of {name} must start 16-byte aligned")
+        self._check_rows_out("k_out", k_out)
+        self._check_rows_out("v_out", v_out)
         if k_out.shape[0] != v_out.shape[0]:
             raise ValueError(f"k_out has {k_out.shape[0]} rows and v_out has {v_out.shape[0]}")
-        index = {"page_indptr": (page_indptr, (torch.int32,)),
-                 "page_indices": (page_indices, (torch.int32,)),
-                 "seq_lens": (seq_lens, (torch.int32,)),
-                 "out_indptr": (out_indptr, (torch.int32, torch.int64))}
-        for name, (x, dtypes) in index.items():
-            if not isinstance(x, torch.Tensor) or x.dtype not in dtypes or x.dim() != 1 \
-                    or not x.is_contiguous():
-                raise ValueError(f"{name} must be a contiguous one-dimensional "
-                                 f"{' or '.join(str(d) for d in dtypes)} tensor; got "
-                                 f"{getattr(x, 'dtype', None)} {tuple(getattr(x, 'shape', ()))}")
-            if x.device != self.device:
-                raise ValueError(f"{name} is on {x.device}; the cache is on {self.device}")
+        for name, x, allowed in (("page_indptr", page_indptr, (torch.int32,)),
+                                 ("page_indices", page_indices, (torch.int32,)),
+                                 ("seq_lens", seq_lens, (torch.int32,)),
+                                 ("out_indptr", out_indptr, (torch.int32, torch.int64))):
+            flat = (isinstance(x, torch.Tensor) and x.dtype in allowed and x.dim() == 1
+                    and x.is_contiguous())
+            if not flat:
+                kinds = " or ".join(str(t) for t in allowed)
+                raise ValueError(f"{name} must be a contiguous one-dimensional {kinds} tensor; "
+                                 f"got {getattr(x, 'dtype', None)} "
+                                 f"{tuple(getattr(x, 'shape', ()))}")
+            self._same_device(name, x)
         batch = seq_lens.shape[0]
         if page_indptr.shape[0] != batch + 1 or out_indptr.shape[0] != batch:
             raise ValueError(f"seq_lens has {batch} requests, so page_indptr must have "

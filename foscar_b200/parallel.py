@@ -151,7 +151,6 @@ class SequenceSplitExchange:
         self._handle = handle
         self._ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in handle.buffer_ptrs])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.step = 0
         # every rank's zeroed flags are in place before anyone posts a step
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
@@ -174,11 +173,12 @@ class SequenceSplitExchange:
         if tuple(out.shape) != (b, hq, d) or not out.is_contiguous():
             raise ValueError(f"out must be a contiguous [{b}, {hq}, {d}] tensor")
         code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[out.dtype]
-        self.step += 1
+        # step 0: the kernel counts the steps itself, so the call can be captured in a CUDA graph
+        # and replayed (every rank replays the same number of times)
         with _dev.on_device(self.device):
             _lib.check(_lib.load().fq_exchange_merge(
                 self._ptrs, self.rank, self.world, o_local.data_ptr(), lse_local.data_ptr(), b,
-                hq, d, self.step, out.data_ptr(), code,
+                hq, d, 0, out.data_ptr(), code,
                 None if lse is None else lse.data_ptr(), wait_budget_cycles,
                 self.status.data_ptr(), _dev.current_stream_ptr(self.device)), "exchange_merge")
         return out

@@ -210,7 +210,9 @@ int fq_merge_states(const float* o_shards, const float* lse_shards, int32_t num_
  * posts) and the gathered rows are merged locally as fq_merge_states merges them.
  * staging: host array of `world` device pointers, entry r being rank r's staging buffer of
  * fq_exchange_bytes bytes as mapped in this process (zeroed before the first step); step: 1, 2,
- * 3, ... the same on every rank. The reference has no counterpart (single-GPU library). */
+ * 3, ... the same on every rank, or 0 to count the steps on the device (every rank launching
+ * the same number of times), which makes the launch replayable from a CUDA graph. The reference
+ * has no counterpart (single-GPU library). */
 int64_t fq_exchange_bytes(int32_t world, int32_t batch, int32_t num_qo_heads, int32_t head_dim);
 int fq_exchange_merge(void* const* staging, int32_t rank, int32_t world, const float* o_local,
                       const float* lse_local, int32_t batch, int32_t num_qo_heads,

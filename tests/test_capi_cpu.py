@@ -120,6 +120,20 @@ def test_worklist_refuses_a_short_buffer():
                                 counts.ctypes.data, 2, 128) == _lib.ERR_TOO_LARGE
 
 
+@pytest.mark.parametrize("batch,hkv,length", [(1, 8, 100352), (4, 8, 100352), (16, 8, 100352),
+                                              (1, 1, 524288), (8, 2, 32768), (64, 8, 16384)])
+def test_uniform_planner_agrees_with_the_balanced_one(batch, hkv, length):
+    """On a uniform batch the closed-form planner (no host lengths) and the balanced piece list
+    cut a unit into similar numbers of pieces: both count a piece's overhead in the same tile
+    units."""
+    lib = _lib.load()
+    s = lib.fq_plan_splits(batch, hkv, 1, length, 2, 128, 148)
+    n, work, counts = _plan([length] * batch, hkv, 1, 148, bits=2)
+    most = int(counts.max())
+    assert s >= 1 and n > 0
+    assert most / 3 <= s <= max(most * 2.5, 2), (s, most)
+
+
 def test_uniform_planner_behaviour():
     lib = _lib.load()
     assert lib.fq_plan_splits(64, 8, 1, 16384, 2, 128, 148) == 1      # enough units: no split

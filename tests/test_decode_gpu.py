@@ -299,6 +299,17 @@ def test_pdl_flag_does_not_change_the_result():
     c = w.run(q, cache, enable_pdl=True)
     torch.cuda.synchronize()
     assert torch.equal(a, b) and torch.equal(a, c) and w.last_status() == 0
+    # a decode step: the writer rewrites the last tokens, the decode follows on the same stream;
+    # under a programmatic launch its set-up overlaps the writer's tail, its reads do not
+    tail = torch.from_numpy(slots[-3:]).cuda()
+    k2, v2 = make_kv(3, 8, 128, seed=22)
+    outs = []
+    for pdl in (True, False, True):
+        cache.append(k2, v2, tail)
+        outs.append(w.run(q, cache, enable_pdl=pdl))
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert not torch.equal(outs[0], a) and w.last_status() == 0 and cache.last_status() == 0
 
 
 def test_bad_page_id_sets_status_without_fault():
