@@ -21,6 +21,7 @@ def _written_cache(bits, d, hkv, seq, seed):
     k, v = make_kv(len(slots), hkv, d, seed=seed)
     layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device="cuda")
     cache = layout.allocate(npages + 1)          # the engine's pool tensors
+    cache.k_codes.zero_(); cache.v_codes.zero_(); cache.scales.zero_()
     writer = rb.compile_quant_append(layout)
     rb.launch_quant_append(writer, inputs=(k, v), slot_mapping=torch.from_numpy(slots).cuda(),
                            k_codes=cache.k_codes, v_codes=cache.v_codes, scales=cache.scales,
