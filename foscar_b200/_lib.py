@@ -55,7 +55,8 @@ class DecodeArgs(C.Structure):
                 ("q_descale_stride_h", C.c_int64), ("out", C.c_void_p), ("lse", C.c_void_p),
                 ("o_partial", C.c_void_p), ("l_partial", C.c_void_p), ("m_partial", C.c_void_p),
                 ("status", C.c_void_p), ("unit_counters", C.c_void_p),
-                ("split_counts", C.c_void_p), ("wait_budget_cycles", C.c_int64)]
+                ("split_counts", C.c_void_p), ("wait_budget_cycles", C.c_int64),
+                ("q_len", C.c_int32), ("reserved", C.c_int32)]
 
 
 _P = C.c_void_p

@@ -35,7 +35,7 @@ extern "C" int64_t fq_workspace_bytes(int32_t max_splits, int32_t batch, int32_t
 // output), as measured on B200 against the cost of streaming one tile (about 4.7 us against
 // 0.34 us per 128-token INT2 tile at head_dim 128).
 static long long piece_overhead(int bits, int head_dim) {
-  long long ovh = bits == 4 && head_dim != 64 ? 10 : 14;
+  long long ovh = bits == 4 && head_dim == 128 ? 10 : 14;
   if (const char* env = getenv("FOSCAR_B200_PIECE_OVERHEAD")) {   // tuning knob for experiments
     const int v = atoi(env);
     if (v >= 0 && v <= 256) ovh = v;

@@ -399,7 +399,9 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 #pragma unroll
       for (int u = 0; u < NT; ++u) {
         const int pos = tt * SP::TT + u * TILE + t;
-        const bool valid = (tt + 1) * SP::TT <= w.len || pos < w.len;
+        // with several query tokens a column stops short of the request's last positions
+        const bool whole = (tt + 1) * SP::TT <= w.len - (P.q_len - 1);
+        const bool valid = whole || pos < w.len;
         const float a_k = sk[u] * 512.f;
         wsc[u] = sv[u] * p2lp;
         if (!valid) { wsc[u] = 0.f; zv[u] = 0.f; }
@@ -412,11 +414,13 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
                            fmaf(head_k[8 + h], zk[u], head_k[16 + h] * zk1)));
           else
             xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[8 * u + h]), head_k[8 + h] * zk[u]);
-          x[u][h] = valid ? xv : -INFINITY;
+          x[u][h] = whole || pos < w.len - column_lag(P, w.ht * 8 + h) ? xv : -INFINITY;
           over = fmaxf(over, x[u][h] - m[h]);
         }
       }
-      if (named_barrier_or(1 + wg, 128, over > MAX_LAG)) {
+      // (a group's first tile of an item always takes the exact maximum: with several query
+      // tokens every score of that tile can be masked, which would leave m at -inf)
+      if (named_barrier_or(1 + wg, 128, over > MAX_LAG || m[0] == -INFINITY)) {
         const int buf = n & 1;
         float* wmax = red_max + ((wg * 2 + buf) * 4 + wq) * 8;
 #pragma unroll
@@ -428,8 +432,9 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         const float* gm = red_max + (wg * 2 + buf) * 4 * 8;
 #pragma unroll
         for (int h = 0; h < GP; ++h) {
-          const float tm =
-              fmaxf(m[h], fmaxf(fmaxf(gm[h], gm[8 + h]), fmaxf(gm[16 + h], gm[24 + h])));
+          // (floored so that a column with every score masked so far has a finite reference)
+          const float tm = fmaxf(
+              fmaxf(m[h], fmaxf(fmaxf(gm[h], gm[8 + h]), fmaxf(gm[16 + h], gm[24 + h]))), -1e30f);
           const float corr = m[h] == -INFINITY ? 0.f : fast_exp2(m[h] - tm);
           l[h] *= corr;
           c[h] *= corr;
@@ -598,10 +603,11 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
         const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
         if (w.slot < 0) {
+          const long long orow = caller_row(P, w.b, w.kvh, hl);
           const float val = L > 0.f ? O / L * P.a.o_scale : 0.f;
-          if (on) store_value(P.a.out, P.a.out_dtype, row * D + ch, val);
+          if (on) store_value(P.a.out, P.a.out_dtype, orow * D + ch, val);
           if (t == 0 && P.a.lse != nullptr)
-            P.a.lse[row] = L > 0.f ? (M + log2f(L)) * LN2 : -INFINITY;
+            P.a.lse[orow] = L > 0.f ? (M + log2f(L)) * LN2 : -INFINITY;
         } else {
           const long long prow =
               static_cast<long long>(w.slot) * P.a.batch * P.a.num_qo_heads + row;
@@ -754,15 +760,15 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           // yields each group's partial product in its own S column.
           constexpr bool SPLIT = SP::PAIR || KG == 2;
           const int hl = w.ht * 8 + (SPLIT ? (r & 7) : r);  // head inside the KV head's group
-          const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
           const bool live = (SPLIT || r < 8) && hl < P.heads_per_kv;
+          const long long qrow = live ? caller_row(P, w.b, w.kvh, hl) : 0;
           const bool mine = SPLIT ? ((r < 8) == (cc < 4)) : 16 * cc < D;
           const int src = SP::PAIR ? (cc & 3) : cc;
           float qsum = 0.f;
           if (live && mine) {
             const uint4 in = __ldg(reinterpret_cast<const uint4*>(
                 static_cast<const uint8_t*>(P.a.q) +
-                (static_cast<long long>(w.b) * P.a.num_qo_heads + head) * D + 16 * src));
+                qrow * D + 16 * src));
             const uint32_t words[4] = {in.x, in.y, in.z, in.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -792,8 +798,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
               if (live) {
                 scale = P.a.sm_scale * 1.4426950408889634f;
                 if (P.a.q_descale != nullptr)
-                  scale *= __ldg(P.a.q_descale + w.b * P.a.q_descale_stride_b +
-                                 head * P.a.q_descale_stride_h);
+                  scale *= caller_descale(P, qrow);
               }
               float* hc = reinterpret_cast<float*>(smem + SP::HEADC_OFF) + qb * 24;
               if (r < 8) {
@@ -1189,8 +1194,16 @@ extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void
   DecodeParams P{};
   P.p = *pools;
   P.a = a;
-  P.heads_per_kv = a.num_qo_heads / pools->num_kv_heads;
+  // several query tokens per request ride as further columns of their KV head's unit
+  P.q_len = a.q_len > 1 ? a.q_len : 1;
+  if (P.q_len > 64) return FQ_ERR_BAD_ARG;
+  P.gqa = a.num_qo_heads / pools->num_kv_heads;
+  P.heads_per_kv = P.gqa * P.q_len;
+  P.a.num_qo_heads = a.num_qo_heads * P.q_len;
   P.head_tiles = (P.heads_per_kv + 7) / 8;
+  // the separate merge launch writes rows in [B, HQ] order only
+  if (P.q_len > 1 && (a.worklist ? a.max_splits > 1 : a.kv_splits > 1) && !a.unit_counters)
+    return FQ_ERR_UNSUPPORTED;
   const long long units = static_cast<long long>(a.batch) * pools->num_kv_heads * P.head_tiles;
   if (a.worklist) {
     if (a.num_work <= 0 || a.max_splits < 1) return FQ_ERR_BAD_ARG;
@@ -1237,6 +1250,7 @@ extern "C" int fq_decode_split_static(const fq_pools* pools, const fq_decode_arg
   if (!pools || !args) return FQ_ERR_BAD_ARG;
   if (args->worklist != nullptr || args->kv_splits < 1) return FQ_ERR_BAD_ARG;
   if (args->batch <= 0 || args->num_qo_heads <= 0) return FQ_ERR_BAD_ARG;
+  if (args->q_len > 1) return FQ_ERR_UNSUPPORTED;   // fq_merge below writes [B, HQ] rows
   const long long rows = static_cast<long long>(args->kv_splits) * args->batch * args->num_qo_heads;
   const long long need = rows * (pools->head_dim + 2) * 4;
   if (need > static_cast<long long>(FQ_STATIC_SCRATCH_BYTES)) return FQ_ERR_SCRATCH_TOO_SMALL;

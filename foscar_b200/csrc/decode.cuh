@@ -22,9 +22,11 @@ constexpr int SMEM_LIMIT = 232448;   // 227 KiB opt-in limit per CTA on sm_100
 
 struct DecodeParams {
   fq_pools p;
-  fq_decode_args a;
-  int heads_per_kv;  // GQA ratio
-  int head_tiles;    // ceil(ratio / 8)
+  fq_decode_args a;  // num_qo_heads here counts a unit's columns: q_len x the caller's heads
+  int heads_per_kv;  // columns per KV head: q_len x the GQA ratio
+  int head_tiles;    // ceil(heads_per_kv / 8)
+  int q_len;         // query tokens per request (>= 1)
+  int gqa;           // the caller's query heads per KV head
   int num_items;     // implicit: B*HKV*head_tiles*kv_splits; explicit: row capacity
   int ring_stages;
   int tile_tokens;   // tile_tokens(bits, head_dim)
@@ -35,6 +37,28 @@ struct DecodeParams {
 struct WorkItem {
   int b, kvh, ht, t0, t1, slot, len, table_off;
 };
+
+// Column hl of KV head kvh (query token hl / gqa, head hl % gqa of the KV head's group) as a
+// row of the caller's q / out / lse tensors [B, q_len, HQ]; at one query token the identity.
+__device__ __forceinline__ long long caller_row(const DecodeParams& P, int b, int kvh, int hl) {
+  if (P.q_len == 1) return static_cast<long long>(b) * P.a.num_qo_heads + kvh * P.heads_per_kv + hl;
+  const int l = hl / P.gqa, h = hl - l * P.gqa;
+  const int hq = P.gqa * P.p.num_kv_heads;
+  return (static_cast<long long>(b) * P.q_len + l) * hq + kvh * P.gqa + h;
+}
+
+// How many of the request's last positions column hl does not see: query token l of q_len
+// attends to positions < len - (q_len - 1 - l).
+__device__ __forceinline__ int column_lag(const DecodeParams& P, int hl) {
+  return P.q_len == 1 ? 0 : max(P.q_len - 1 - hl / P.gqa, 0);
+}
+
+// q_descale of a caller row: element (row / HQ, row % HQ).
+__device__ __forceinline__ float caller_descale(const DecodeParams& P, long long row) {
+  const int hq = P.gqa * P.p.num_kv_heads;
+  return __ldg(P.a.q_descale + (row / hq) * P.a.q_descale_stride_b +
+               (row % hq) * P.a.q_descale_stride_h);
+}
 
 // Shared-memory plan for one (BITS, D) build. All offsets from a 1024-byte aligned base.
 template <int BITS, int D>
@@ -296,9 +320,10 @@ static __device__ __noinline__ void merge_unit_partials(const DecodeParams& P, i
       }
     }
     const bool live = den > 0.f;
-    store_value(P.a.out, P.a.out_dtype, row * d + ch, live ? acc / den * P.a.o_scale : 0.f);
+    const long long orow = caller_row(P, b, kvh, hl);
+    store_value(P.a.out, P.a.out_dtype, orow * d + ch, live ? acc / den * P.a.o_scale : 0.f);
     if (writes_lse && P.a.lse != nullptr)
-      P.a.lse[row] = live ? (M + log2f(den)) * LN2 : -INFINITY;
+      P.a.lse[orow] = live ? (M + log2f(den)) * LN2 : -INFINITY;
   }
 }
 

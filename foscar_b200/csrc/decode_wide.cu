@@ -459,7 +459,9 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         mbar_arrive(bars.ring_empty(rp1.s));
       }
       // positions past the request's length (its last tile only): score -inf, record neutral
-      const bool valid = tt * TILE + t < w.len;
+      // (with several query tokens a column stops short of the request's last positions)
+      const bool whole = (tt + 1) * TILE <= w.len - (P.q_len - 1);
+      const bool valid = whole || tt * TILE + t < w.len;
       const float ak = sk * 512.f;
       (void)ak; (void)zk;
       const float wsc = valid ? sv * p2lp : 0.f;
@@ -495,7 +497,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
                       ab[h] + nm);
           else
             dd = fmaf(head_k[h] * ak, __uint_as_float(raw[h]), fmaf(head_k[8 + h], zk, nm));
-          d[h] = valid ? dd : -INFINITY;
+          d[h] = whole || tt * TILE + t < w.len - column_lag(P, w.ht * 8 + h) ? dd : -INFINITY;
           over = fmaxf(over, d[h]);
         }
         if (fresh || named_barrier_or(1 + wg, 128, over > MAX_LAG)) {
@@ -516,7 +518,9 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
             l[h] *= corr[h];
             c[h] *= corr[h];
             m[h] = fresh ? shift : m[h] + shift;
-            d[h] -= shift;
+            // (a column whose every score of the group's first tile is masked: only the
+            // request's last tile, so the group has no further tile of this item)
+            d[h] = shift == -INFINITY ? -INFINITY : d[h] - shift;
           }
           if (pending) {
             // every earlier tile's O of this item is complete in tensor memory: per channel half
@@ -688,11 +692,12 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
         const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
         if (w.slot < 0) {
+          const long long orow = caller_row(P, w.b, w.kvh, hl);
           const float inv = L[h] > 0.f ? P.a.o_scale / L[h] : 0.f;
-          store_value(P.a.out, P.a.out_dtype, row * D + ch, v0 * inv);
-          store_value(P.a.out, P.a.out_dtype, row * D + 128 + ch, v1 * inv);
+          store_value(P.a.out, P.a.out_dtype, orow * D + ch, v0 * inv);
+          store_value(P.a.out, P.a.out_dtype, orow * D + 128 + ch, v1 * inv);
           if (t == 0 && P.a.lse != nullptr)
-            P.a.lse[row] = L[h] > 0.f ? (M[h] + log2f(L[h])) * LN2 : -INFINITY;
+            P.a.lse[orow] = L[h] > 0.f ? (M[h] + log2f(L[h])) * LN2 : -INFINITY;
         } else {
           const long long prow =
               static_cast<long long>(w.slot) * P.a.batch * P.a.num_qo_heads + row;
@@ -798,13 +803,13 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
           const int r = chunk >> 4, cc = chunk & 15;
           uint4 v = make_uint4(0, 0, 0, 0);
           const int hl = w.ht * 8 + r;
-          const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
           const bool live = r < 8 && hl < P.heads_per_kv;
+          const long long qrow = live ? caller_row(P, w.b, w.kvh, hl) : 0;
           float qsum = 0.f;   // the row's sum of q (K per channel: its max |q|)
           if (live) {
             const uint4 in = __ldg(reinterpret_cast<const uint4*>(
                 static_cast<const uint8_t*>(P.a.q) +
-                (static_cast<long long>(w.b) * P.a.num_qo_heads + head) * D + 16 * cc));
+                qrow * D + 16 * cc));
             const uint32_t words[4] = {in.x, in.y, in.z, in.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -844,8 +849,7 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
               if (live) {
                 scale = P.a.sm_scale * 1.4426950408889634f;
                 if (P.a.q_descale != nullptr)
-                  scale *= __ldg(P.a.q_descale + w.b * P.a.q_descale_stride_b +
-                                 head * P.a.q_descale_stride_h);
+                  scale *= caller_descale(P, qrow);
               }
               float* hc = reinterpret_cast<float*>(smem + SP::HEADC_OFF) + qb * 24;
               hc[r] = scale;

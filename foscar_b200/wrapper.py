@@ -164,7 +164,7 @@ class PagedDecodeWrapper:
         "_float_workspace_buffer", "_status", "_o_data_type", "_num_qo_heads", "_batch_size",
         "_kv_splits", "_seqlens", "_table_offsets", "_page_table", "_o_partial", "_l_partial",
         "_m_partial", "_max_splits", "_worklist", "_split_counts", "_unit_counters",
-        "_work_rows", "_plan_ctas", "_merge"))
+        "_work_rows", "_plan_ctas", "_merge", "_q_len"))
 
     def __setattr__(self, name, value):
         if name in self._PLAN_STATE:
@@ -187,6 +187,7 @@ class PagedDecodeWrapper:
         self._bits = None
         self._q_data_type = self._o_data_type = None
         self._num_qo_heads = self._num_kv_heads = self._head_dim = None
+        self._q_len, self._cols = 1, None
         self._sm_scale = None
         self._batch_size = None
         self._max_kv_len = None
@@ -264,9 +265,7 @@ class PagedDecodeWrapper:
             raise ValueError(f"the layout was resolved for {layout.arch} and this wrapper's "
                              f"device {self.device} is {arch}; create the layout for the device "
                              f"that decodes it")
-        if q_len_per_req != 1:
-            raise NotImplementedError(f"quantized decode is plain decode only; got "
-                                      f"q_len_per_req={q_len_per_req}")
+        q_len = self._check_q_len(q_len_per_req)
         _check_num_qo_heads(num_qo_heads, layout.num_kv_heads)
         if seq_lens.dtype not in (torch.int32, torch.int64):
             raise ValueError(f"seq_lens must be int32 or int64; got {seq_lens.dtype}")
@@ -281,12 +280,16 @@ class PagedDecodeWrapper:
             if reduction == "atomic":
                 raise NotImplementedError("quantized decode has no atomic-reduction arm")
             raise ValueError(f'quantized reduction must be "none" or "kernel"; got {reduction!r}')
-        self._set_common(layout, num_qo_heads, q_data_type, o_data_type, sm_scale, batch)
+        self._set_common(layout, num_qo_heads, q_data_type, o_data_type, sm_scale, batch, q_len)
 
         host_lens = None
         if kv_splits is None or kv_splits <= 0:
             if seq_lens.device.type == "cpu" or max_kv_len is None:
                 host_lens = seq_lens.detach().to("cpu", torch.int32).numpy()   # waits if on GPU
+        if host_lens is not None and q_len > 1 and int(host_lens.min()) < q_len:
+            raise ValueError(f"seq_lens counts the {q_len} query tokens of each request (they "
+                             f"are appended before the decode); got a length of "
+                             f"{int(host_lens.min())}")
         if max_kv_len is None:
             max_kv_len = int(host_lens.max()) if host_lens is not None else \
                 int(seq_lens.max().item())
@@ -306,7 +309,20 @@ class PagedDecodeWrapper:
             self._status_ptr()
         self._planned = True
 
-    def _set_common(self, layout, num_qo_heads, q_dtype, o_dtype, sm_scale, batch):
+    def _check_q_len(self, q_len_per_req):
+        """Query tokens per request. The reference refuses anything but 1
+        (src/foscar/wrapper.py:756-761); here the tokens of a request ride as further columns
+        of their KV head's unit, token l attending to positions < seq_len - (q_len - 1 - l)."""
+        if isinstance(q_len_per_req, bool) or not isinstance(q_len_per_req, int) \
+                or not 1 <= q_len_per_req <= 64:
+            raise ValueError(f"q_len_per_req must be an int in [1, 64]; got {q_len_per_req!r}")
+        if q_len_per_req > 1 and not self.fused_merge:
+            raise NotImplementedError("q_len_per_req > 1 needs the in-kernel merge of split "
+                                      "units (fused_merge=True): the separate merge launch "
+                                      "writes [batch, heads] rows only")
+        return q_len_per_req
+
+    def _set_common(self, layout, num_qo_heads, q_dtype, o_dtype, sm_scale, batch, q_len=1):
         if not layout.is_token_wise and not (layout.is_page_channel_k and layout.head_dim == 256):
             raise NotImplementedError(
                 f"this build decodes token-wise layouts, and K per channel over a page "
@@ -327,6 +343,9 @@ class PagedDecodeWrapper:
         self._bits = layout.bits
         self._q_data_type, self._o_data_type = q_dtype, o_dtype
         self._num_qo_heads, self._num_kv_heads = num_qo_heads, layout.num_kv_heads
+        self._q_len = q_len
+        # columns of the batch's units: a request's query tokens times its query heads
+        self._cols = num_qo_heads * q_len
         self._head_dim = layout.head_dim
         self._sm_scale = layout.head_dim ** -0.5 if sm_scale is None else sm_scale
         self._batch_size = batch
@@ -335,8 +354,7 @@ class PagedDecodeWrapper:
         lay = self._layout
         if kv_splits is None or kv_splits <= 0:
             kv_splits = _lib.load().fq_plan_splits(
-                self._batch_size, lay.num_kv_heads, _head_tiles(self._num_qo_heads,
-                                                                lay.num_kv_heads),
+                self._batch_size, lay.num_kv_heads, _head_tiles(self._cols, lay.num_kv_heads),
                 self._max_kv_len, lay.bits, lay.head_dim, _dev.sm_count(self.device))
             if kv_splits < 1:
                 _lib.check(kv_splits, "plan")
@@ -351,7 +369,7 @@ class PagedDecodeWrapper:
         if self._merge:
             self._o_partial, self._l_partial, self._m_partial = _carve_partials(
                 self._float_workspace_buffer, self._kv_splits, self._batch_size,
-                self._num_qo_heads, self._head_dim)
+                self._cols, self._head_dim)
             self._new_unit_counters()
 
     def _new_unit_counters(self):
@@ -360,7 +378,7 @@ class PagedDecodeWrapper:
         if not self.fused_merge:
             self._unit_counters = None
             return
-        units = self._batch_size * self._num_kv_heads * _head_tiles(self._num_qo_heads,
+        units = self._batch_size * self._num_kv_heads * _head_tiles(self._cols,
                                                                      self._num_kv_heads)
         if self._unit_counters is None or self._unit_counters.numel() != units:
             self._unit_counters = torch.zeros(units, dtype=torch.int32, device=self.device)
@@ -369,11 +387,11 @@ class PagedDecodeWrapper:
 
     def _plan_balanced(self, host_lens, non_blocking):
         lay, lib = self._layout, _lib.load()
-        ht = _head_tiles(self._num_qo_heads, lay.num_kv_heads)
+        ht = _head_tiles(self._cols, lay.num_kv_heads)
         ctas = _dev.sm_count(self.device)
         units = self._batch_size * lay.num_kv_heads * ht
         words = int(lib.fq_worklist_words(self._batch_size, lay.num_kv_heads, ht, ctas))
-        cap = _fit_splits(self._float_workspace_buffer, self._batch_size, self._num_qo_heads,
+        cap = _fit_splits(self._float_workspace_buffer, self._batch_size, self._cols,
                           self._head_dim)
         lens = np.ascontiguousarray(host_lens, dtype=np.int32)
         work = np.zeros(words, dtype=np.int32)
@@ -394,7 +412,7 @@ class PagedDecodeWrapper:
         self._max_splits = max(most, 1)
         if self._merge:
             self._o_partial, self._l_partial, self._m_partial = _carve_partials(
-                self._float_workspace_buffer, most, self._batch_size, self._num_qo_heads,
+                self._float_workspace_buffer, most, self._batch_size, self._cols,
                 self._head_dim)
             self._new_unit_counters()
         else:
@@ -413,7 +431,13 @@ class PagedDecodeWrapper:
         if x.device != self.device:
             raise ValueError(f"{name} is on {x.device}; this wrapper plans for {self.device}")
         b, hq, d = self._batch_size, self._num_qo_heads, self._head_dim
-        if tuple(x.shape) == (b, hq, d):
+        if self._q_len > 1:
+            three_d = False
+            if tuple(x.shape) != (b, self._q_len, hq, d):
+                raise ValueError(f"{name} has shape {tuple(x.shape)}; the plan is for "
+                                 f"[{b}, {self._q_len}, {hq}, {d}] (batch, query tokens, query "
+                                 f"heads, head dimension)")
+        elif tuple(x.shape) == (b, hq, d):
             three_d = True
         elif tuple(x.shape) == (b, 1, hq, d):
             three_d = False
@@ -453,20 +477,25 @@ class PagedDecodeWrapper:
                              f"{self.device}")
         three_d = self._check_tensor("q", q, self._q_data_type)
         b, hq, d = self._batch_size, self._num_qo_heads, self._head_dim
+        rows = (b, hq) if self._q_len == 1 else (b, self._q_len, hq)
         if lse is not None:
             if (lse.dtype != torch.float32 or lse.device != self.device
-                    or tuple(lse.shape) != (b, hq) or not lse.is_contiguous()
+                    or tuple(lse.shape) != rows or not lse.is_contiguous()
                     or lse.data_ptr() % 16):
-                raise ValueError(f"lse must be a C-contiguous, 16-byte aligned fp32 [{b}, {hq}] "
-                                 f"tensor on {self.device}; got {lse.dtype} {tuple(lse.shape)}")
+                raise ValueError(f"lse must be a C-contiguous, 16-byte aligned fp32 "
+                                 f"{list(rows)} tensor on {self.device}; got {lse.dtype} "
+                                 f"{tuple(lse.shape)}")
         if out is not None:
             self._check_tensor("out", out, self._o_data_type)
         if q_descale is not None:
             if (q_descale.dtype != torch.float32 or q_descale.device != self.device
-                    or tuple(q_descale.shape) != (b, hq)):
-                raise ValueError(f"q_descale must be an fp32 [{b}, {hq}] tensor on "
+                    or tuple(q_descale.shape) != rows):
+                raise ValueError(f"q_descale must be an fp32 {list(rows)} tensor on "
                                  f"{self.device}; got {q_descale.dtype} "
                                  f"{tuple(q_descale.shape)} on {q_descale.device}")
+            if self._q_len > 1 and q_descale.stride(0) != self._q_len * q_descale.stride(1):
+                raise ValueError(f"q_descale's batch stride must be {self._q_len} token "
+                                 f"strides; got strides {tuple(q_descale.stride())}")
         scale_s = self._sm_scale if sm_scale is None else sm_scale
         scale_o = 1.0 if o_scale is None else o_scale
         with _dev.on_device(self.device):
@@ -481,6 +510,7 @@ class PagedDecodeWrapper:
         """fq_decode's argument block with everything the plan fixes filled in."""
         args = _lib.DecodeArgs()
         args.batch, args.num_qo_heads = self._batch_size, self._num_qo_heads
+        args.q_len = self._q_len
         args.out_dtype = _OUT_CODE[self._o_data_type]
         args.kv_splits = 1 if self._worklist is not None else self._kv_splits
         args.max_splits = self._max_splits
@@ -510,8 +540,8 @@ class PagedDecodeWrapper:
                 enable_pdl=True):
         b, hq, d = self._batch_size, self._num_qo_heads, self._head_dim
         if out is None:
-            out = torch.empty((b, hq, d) if three_d else (b, 1, hq, d), dtype=self._o_data_type,
-                              device=self.device)
+            out = torch.empty((b, hq, d) if three_d else (b, self._q_len, hq, d),
+                              dtype=self._o_data_type, device=self.device)
         lib = _lib.load()
         stream = _dev.current_stream_ptr(self.device)
         args = self._plan_args
@@ -523,7 +553,8 @@ class PagedDecodeWrapper:
         args.q = q.data_ptr()
         if q_descale is not None:
             args.q_descale = q_descale.data_ptr()
-            args.q_descale_stride_b, args.q_descale_stride_h = q_descale.stride()
+            # with several query tokens the kernel's "batch" stride is the token stride
+            args.q_descale_stride_b, args.q_descale_stride_h = q_descale.stride()[-2:]
         else:
             args.q_descale = None
         args.out = out.data_ptr()
@@ -600,9 +631,7 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
                             "reduction= are eager mode's")
         if non_blocking is not True:
             raise TypeError("non_blocking= is eager mode's; graph mode copies nothing at plan()")
-        if q_len_per_req != 1:
-            raise NotImplementedError(f"quantized decode is plain decode only; got "
-                                      f"q_len_per_req={q_len_per_req}")
+        q_len = self._check_q_len(q_len_per_req)
         for name, flag in (("lse", lse), ("q_descale", q_descale)):
             if not isinstance(flag, bool):
                 raise TypeError(f"graph mode's {name}= declares whether every run() passes "
@@ -632,7 +661,8 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
                              f"got {max_kv_len!r}")
         q_data_type, o_data_type = _resolve_io_dtypes(layout, q_data_type, o_data_type)
         try:
-            self._set_common(layout, num_qo_heads, q_data_type, o_data_type, sm_scale, batch)
+            self._set_common(layout, num_qo_heads, q_data_type, o_data_type, sm_scale, batch,
+                             q_len)
             self._max_kv_len = max_kv_len
             with _dev.on_device(self.device):
                 self._graph = self._graph_setup(page_table, seq_lens, lse, q_descale)
@@ -645,7 +675,7 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
 
     def _graph_setup(self, page_table, seq_lens, lse, q_descale):
         lay, lib = self._layout, _lib.load()
-        b, hq, d = self._batch_size, self._num_qo_heads, self._head_dim
+        b, hq, d = self._batch_size, self._cols, self._head_dim
         ht = _head_tiles(hq, lay.num_kv_heads)
         ctas = _dev.sm_count(self.device)
         units = b * lay.num_kv_heads * ht

@@ -92,7 +92,8 @@ int fq_append_page_groups(const fq_pools* pools, const void* k, const void* v,
 
 /* Read K,V of a batch back into bf16 rows [N, HKV, D]: out[out_indptr[b]+t] =
  * bf16(fma(s, q, z)) for t < seq_lens[b]. Stands in for QuantKVCache.dequantize
- * (src/foscar/kv_cache.py:792-877). out_indptr is int32 or int64 (out_indptr_64). */
+ * (src/foscar/kv_cache.py:792-877). out_indptr is int32 or int64 (out_indptr_64). k_out and
+ * v_out are 16-byte aligned and the row strides (in elements) multiples of 8. */
 int fq_dequantize(const fq_pools* pools, void* k_out, void* v_out, int64_t k_row_stride,
                   int64_t v_row_stride, int64_t num_out_rows, const int32_t* page_indptr,
                   const int32_t* page_indices, int32_t num_entries, const int32_t* seq_lens,
@@ -157,6 +158,16 @@ typedef struct fq_decode_args {
    * CTA gives up, FQ_STATUS_TIMEOUT is set and the output is invalid; unit_counters may then be
    * left non-zero and must be cleared before the next launch. */
   int64_t wait_budget_cycles;
+  /* Query tokens per request (speculative / multi-token decode); 0 or 1 = one. With q_len = L > 1
+   * q and out are [B, L, HQ, D], lse is [B, L, HQ], q_descale element (b, l, h) sits at
+   * (b*L + l)*stride_b + h*stride_h, seq_lens counts the L new tokens (already appended), and
+   * query token l attends to positions < seq_lens[b] - (L - 1 - l). The L tokens of a KV head's
+   * query heads share that head's KV stream as L * HQ/HKV columns of one unit, so head_tiles =
+   * ceil(L * HQ/HKV / 8) for unit_counters, split_counts and the planners. Split units need
+   * unit_counters (the in-kernel merge); fq_merge does not know this row order. The reference
+   * refuses q_len_per_req != 1 (src/foscar/wrapper.py:756-761). */
+  int32_t q_len;
+  int32_t reserved;
 } fq_decode_args;
 
 int fq_decode(const fq_pools* pools, const fq_decode_args* args, void* stream);

@@ -311,7 +311,8 @@ def test_plan_refusals_are_transactional(recorder):
     w.plan(indptr, indices, seq, 32, lay)
     for bad, exc, match in [
         (dict(num_qo_heads=30), ValueError, "multiple of the layout's num_kv_heads"),
-        (dict(q_len_per_req=2), NotImplementedError, "plain decode"),
+        (dict(q_len_per_req=0), ValueError, "q_len_per_req must be an int"),
+        (dict(q_len_per_req=65), ValueError, "q_len_per_req must be an int"),
         (dict(q_data_type=torch.bfloat16), ValueError, "decode reads a"),
         (dict(o_data_type=torch.int8), ValueError, "decode writes a"),
         (dict(reduction="atomic"), NotImplementedError, "atomic"),
@@ -339,6 +340,40 @@ def test_plan_refusals_are_transactional(recorder):
     small = PagedDecodeWrapper(torch.zeros(64, dtype=torch.uint8))
     with pytest.raises(RuntimeError, match="byte workspace"):
         small.plan(indptr, indices, seq, 32, lay, kv_splits=2)
+
+
+def test_several_query_tokens_plan_as_columns(recorder):
+    """q_len_per_req = L: the unit's columns, partial buffers and counters grow L-fold, the
+    argument block carries q_len, and tensors take the [B, L, HQ, D] form."""
+    lay, cache = _cache(None)
+    w = PagedDecodeWrapper(torch.zeros(4 << 20, dtype=torch.uint8))
+    indptr, indices = _plan_args()
+    seq = torch.tensor([256, 200], dtype=torch.int32)
+    w.plan(indptr, indices, seq, 32, lay, kv_splits=2, q_len_per_req=3)
+    hkv = lay.num_kv_heads
+    assert w._o_partial.shape == (2, 2, 1, 96, 128)
+    assert w._unit_counters.numel() == 2 * hkv * ((32 // hkv * 3 + 7) // 8)
+    q = torch.zeros(2, 3, 32, 128).to(torch.float8_e4m3fn)
+    out = torch.zeros(2, 3, 32, 128, dtype=torch.bfloat16)
+    lse = torch.zeros(2, 3, 32)
+    recorder.calls.clear()
+    w.run(q, cache, out=out, lse=lse, q_descale=torch.ones(2, 3, 32))
+    args = ctypes.cast(recorder.calls[0][1][1], ctypes.POINTER(_lib.DecodeArgs)).contents
+    assert args.q_len == 3 and args.num_qo_heads == 32
+    assert (args.q_descale_stride_b, args.q_descale_stride_h) == (32, 1)
+    with pytest.raises(ValueError, match=r"\[2, 3, 32, 128\]"):
+        w.run(torch.zeros(2, 32, 128).to(torch.float8_e4m3fn), cache)
+    with pytest.raises(ValueError, match="lse must be"):
+        w.run(q, cache, out=out, lse=torch.zeros(2, 32))
+    with pytest.raises(ValueError, match="seq_lens counts the 3 query tokens"):
+        w.plan(indptr, indices, torch.tensor([256, 2], dtype=torch.int32), 32, lay,
+               q_len_per_req=3)
+    w.fused_merge = False
+    with pytest.raises(NotImplementedError, match="in-kernel merge"):
+        w.plan(indptr, indices, seq, 32, lay, q_len_per_req=2)
+    w.fused_merge = True
+    w.plan(indptr, indices, seq, 32, lay)
+    assert w._q_len == 1 and w._cols == 32
 
 
 def test_run_refusals(recorder):
