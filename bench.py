@@ -78,7 +78,8 @@ def algorithmic_bytes(cfg, seq):
 # DRAM bytes (read + write) of one decode launch of the named workload, from a separate ncu
 # capture of this command at its default arguments (not a figure of this run): reported as
 # `traffic` only when the run's arguments are those of the capture.
-CAPTURED_TRAFFIC = {"c2": 401_548_800, "c2-int4": 716_985_600}
+CAPTURED_TRAFFIC = {"c2": 402_309_888, "c2-int4": 717_094_656, "c5-int2": 2_161_422_448,
+                    "c4": 444_460_544}
 
 
 def measured_peak():
@@ -805,7 +806,8 @@ def main():
                          "traffic_from": "a separate ncu capture of this command's decode launch "
                                          "(dram__bytes_read.sum + dram__bytes_write.sum), not "
                                          "measured by this run" if default_args else None,
-                         "kernel": "decode_kernel", "kernel_us": decode_ms * 1e3,
+                         "kernel": "decode_wide_kernel" if cfg["d"] == 256 else "decode_kernel",
+                         "kernel_us": decode_ms * 1e3,
                          "algorithmic_bytes": abytes, "frac_of_8tbs_nominal": achieved / 8000.0},
             "e2e": {"value": world * b / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "us_per_step": e2e_ms * 1e3, "h2d_bytes_per_step": int(q_host.numel()),

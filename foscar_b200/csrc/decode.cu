@@ -151,7 +151,27 @@ struct TmemPlan {
 // unpack V into shared memory, fold the scales into the raw scores, softmax, write the P rows,
 // and (one of its own tiles later) add the tile's O to its accumulators. The group keeps its own
 // running (m, l, c, O); the four groups are merged once per work item.
-template <int BITS, int D, int GP, int KG>
+// The request's last tile with several query tokens per request: column h sees positions below
+// len - lag(h) only. Out of line, so that this rare path (and column_lag's division) costs the
+// tile loop nothing: the scores pass through local memory here and nowhere else. `pos0` is the
+// thread's first token position of the tile, `stride` the distance to its next one. Returns,
+// in `over`, the largest excess of a visible score over its column's reference.
+template <int NT, int GP>
+__device__ __noinline__ void mask_lagged_columns(const DecodeParams& P, int len, int ht, int pos0,
+                                                 int stride, float (&x)[NT][GP],
+                                                 const float (&m)[GP], float& over) {
+  float top = -INFINITY;
+  for (int h = 0; h < GP; ++h) {
+    const int lim = len - column_lag(P, ht * 8 + h);
+    for (int u = 0; u < NT; ++u) {
+      if (pos0 + u * stride >= lim) x[u][h] = -INFINITY;
+      top = fmaxf(top, x[u][h] - m[h]);
+    }
+  }
+  over = top;
+}
+
+template <int BITS, int D, int GP, int KG, bool MQ>
 __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem, uint32_t smem0,
                                             uint32_t tmem, const Bars& bars,
                                             volatile int* abort_flag, const ItemRange items,
@@ -208,7 +228,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 
   auto merge_unit = [&](int k, int b, int kvh, int ht, int h0, int hstep) {
     if (t < D)
-      merge_unit_partials(P, D, GP, channel_of_expanded_pos<BITS>(t), t == 0, k, b, kvh, ht, h0,
+      merge_unit_partials<MQ>(P, D, GP, channel_of_expanded_pos<BITS>(t), t == 0, k, b, kvh, ht, h0,
                           hstep);
   };
   // the split piece this CTA has written but not yet counted in (thread 0 of group 0 only)
@@ -396,11 +416,11 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       // shared memory.
       float x[NT][GP], wsc[NT];
       float over = -INFINITY;
+      // with several query tokens a column stops short of the request's last positions
+      const bool whole = (tt + 1) * SP::TT <= w.len - (MQ ? P.q_len - 1 : 0);
 #pragma unroll
       for (int u = 0; u < NT; ++u) {
         const int pos = tt * SP::TT + u * TILE + t;
-        // with several query tokens a column stops short of the request's last positions
-        const bool whole = (tt + 1) * SP::TT <= w.len - (P.q_len - 1);
         const bool valid = whole || pos < w.len;
         const float a_k = sk[u] * 512.f;
         wsc[u] = sv[u] * p2lp;
@@ -414,13 +434,16 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
                            fmaf(head_k[8 + h], zk[u], head_k[16 + h] * zk1)));
           else
             xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[8 * u + h]), head_k[8 + h] * zk[u]);
-          x[u][h] = whole || pos < w.len - column_lag(P, w.ht * 8 + h) ? xv : -INFINITY;
+          x[u][h] = valid ? xv : -INFINITY;
           over = fmaxf(over, x[u][h] - m[h]);
         }
       }
+      if constexpr (MQ) {
+        if (!whole) mask_lagged_columns<NT, GP>(P, w.len, w.ht, tt * SP::TT + t, TILE, x, m, over);
+      }
       // (a group's first tile of an item always takes the exact maximum: with several query
       // tokens every score of that tile can be masked, which would leave m at -inf)
-      if (named_barrier_or(1 + wg, 128, over > MAX_LAG || m[0] == -INFINITY)) {
+      if (named_barrier_or(1 + wg, 128, over > MAX_LAG || (MQ && m[0] == -INFINITY))) {
         const int buf = n & 1;
         float* wmax = red_max + ((wg * 2 + buf) * 4 + wq) * 8;
 #pragma unroll
@@ -433,8 +456,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 #pragma unroll
         for (int h = 0; h < GP; ++h) {
           // (floored so that a column with every score masked so far has a finite reference)
-          const float tm = fmaxf(
-              fmaxf(m[h], fmaxf(fmaxf(gm[h], gm[8 + h]), fmaxf(gm[16 + h], gm[24 + h]))), -1e30f);
+          float tm = fmaxf(m[h], fmaxf(fmaxf(gm[h], gm[8 + h]), fmaxf(gm[16 + h], gm[24 + h])));
+          if constexpr (MQ) tm = fmaxf(tm, -1e30f);
           const float corr = m[h] == -INFINITY ? 0.f : fast_exp2(m[h] - tm);
           l[h] *= corr;
           c[h] *= corr;
@@ -603,7 +626,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
         const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
         if (w.slot < 0) {
-          const long long orow = caller_row(P, w.b, w.kvh, hl);
+          const long long orow = caller_row<MQ>(P, w.b, w.kvh, hl);
           const float val = L > 0.f ? O / L * P.a.o_scale : 0.f;
           if (on) store_value(P.a.out, P.a.out_dtype, orow * D + ch, val);
           if (t == 0 && P.a.lse != nullptr)
@@ -650,7 +673,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 
 }  // namespace
 
-template <int BITS, int D, int GP, int KG>
+template <int BITS, int D, int GP, int KG, bool MQ>
 __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeParams P) {
   // KG: 1 whole-head K with f32 records, 3 the same with bf16 pairs, 2 two 64-channel K groups
   static_assert(KG == 1 || KG == 3 || (KG == 2 && D == 128),
@@ -761,7 +784,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
           constexpr bool SPLIT = SP::PAIR || KG == 2;
           const int hl = w.ht * 8 + (SPLIT ? (r & 7) : r);  // head inside the KV head's group
           const bool live = (SPLIT || r < 8) && hl < P.heads_per_kv;
-          const long long qrow = live ? caller_row(P, w.b, w.kvh, hl) : 0;
+          const long long qrow = live ? caller_row<MQ>(P, w.b, w.kvh, hl) : 0;
           const bool mine = SPLIT ? ((r < 8) == (cc < 4)) : 16 * cc < D;
           const int src = SP::PAIR ? (cc & 3) : cc;
           float qsum = 0.f;
@@ -798,7 +821,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
               if (live) {
                 scale = P.a.sm_scale * 1.4426950408889634f;
                 if (P.a.q_descale != nullptr)
-                  scale *= caller_descale(P, qrow);
+                  scale *= caller_descale<MQ>(P, w.b, w.kvh, hl);
               }
               float* hc = reinterpret_cast<float*>(smem + SP::HEADC_OFF) + qb * 24;
               if (r < 8) {
@@ -953,7 +976,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ workers
-    worker_role<BITS, D, GP, KG>(P, smem, smem0, tmem, bars, abort_flag, items, wprof);
+    worker_role<BITS, D, GP, KG, MQ>(P, smem, smem0, tmem, bars, abort_flag, items, wprof);
 #ifdef FQ_WAIT_PROFILE
     if (threadIdx.x == 0) wprof[21] = static_cast<int>(clock64() - kernel_t0);   // workers done
 #endif
@@ -1104,7 +1127,7 @@ static int device_sm_count() {
   return sms > 0 ? sms : 148;
 }
 
-template <int BITS, int D, int GP, int KG = 1>
+template <int BITS, int D, int GP, int KG = 1, bool MQ = false>
 static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   using SP = SmemPlan<BITS, D>;
   int stages = SP::max_ring_stages();
@@ -1129,7 +1152,7 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   P.item_slots = SP::ITEM_SLOTS + more;
   const int smem = SP::RING_OFF + stages * SP::STAGE + more * 32 + 1024;
   static bool configured[64] = {};  // per (BITS, D, GP) instantiation and device
-  auto kernel = decode_kernel<BITS, D, GP, KG>;
+  auto kernel = decode_kernel<BITS, D, GP, KG, MQ>;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -1198,6 +1221,9 @@ extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void
   P.q_len = a.q_len > 1 ? a.q_len : 1;
   if (P.q_len > 64) return FQ_ERR_BAD_ARG;
   P.gqa = a.num_qo_heads / pools->num_kv_heads;
+  P.gqa_inv = (65536 + P.gqa - 1) / P.gqa;
+  P.hq = a.num_qo_heads;
+  if (P.gqa * P.q_len > 512) return FQ_ERR_TOO_LARGE;   // (column_token's range)
   P.heads_per_kv = P.gqa * P.q_len;
   P.a.num_qo_heads = a.num_qo_heads * P.q_len;
   P.head_tiles = (P.heads_per_kv + 7) / 8;
@@ -1220,19 +1246,32 @@ extern "C" int fq_decode(const fq_pools* pools, const fq_decode_args* args, void
   const int gp = std::min(P.heads_per_kv, 8) <= 4 ? 4 : 8;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (pools->head_dim == 256) return launch_decode_wide(P, s);
-#define FQ_DISPATCH(DD, KK)                                                                   \
+#define FQ_DISPATCH(DD, KK, MM)                                                               \
   do {                                                                                        \
     if (pools->bits == 2)                                                                     \
-      return gp == 4 ? launch_decode<2, DD, 4, KK>(P, s) : launch_decode<2, DD, 8, KK>(P, s); \
-    return gp == 4 ? launch_decode<4, DD, 4, KK>(P, s) : launch_decode<4, DD, 8, KK>(P, s);   \
+      return gp == 4 ? launch_decode<2, DD, 4, KK, MM>(P, s)                                  \
+                     : launch_decode<2, DD, 8, KK, MM>(P, s);                                 \
+    return gp == 4 ? launch_decode<4, DD, 4, KK, MM>(P, s)                                    \
+                   : launch_decode<4, DD, 8, KK, MM>(P, s);                                   \
   } while (0)
-  if (pools->k_groups == 2) FQ_DISPATCH(128, 2);
-  if (pools->head_dim == 64) {
-    if (pools->scale_bf16) FQ_DISPATCH(64, 3);
-    FQ_DISPATCH(64, 1);
+  // several query tokens per request: builds of their own for whole-head K (f32 or bf16
+  // records), so that the one-token builds stay as they are
+  if (P.q_len > 1) {
+    if (pools->k_groups != 1) return FQ_ERR_UNSUPPORTED;
+    if (pools->head_dim == 64) {
+      if (pools->scale_bf16) FQ_DISPATCH(64, 3, true);
+      FQ_DISPATCH(64, 1, true);
+    }
+    if (pools->scale_bf16) FQ_DISPATCH(128, 3, true);
+    FQ_DISPATCH(128, 1, true);
   }
-  if (pools->scale_bf16) FQ_DISPATCH(128, 3);
-  FQ_DISPATCH(128, 1);
+  if (pools->k_groups == 2) FQ_DISPATCH(128, 2, false);
+  if (pools->head_dim == 64) {
+    if (pools->scale_bf16) FQ_DISPATCH(64, 3, false);
+    FQ_DISPATCH(64, 1, false);
+  }
+  if (pools->scale_bf16) FQ_DISPATCH(128, 3, false);
+  FQ_DISPATCH(128, 1, false);
 #undef FQ_DISPATCH
 }
 

@@ -27,6 +27,8 @@ struct DecodeParams {
   int head_tiles;    // ceil(heads_per_kv / 8)
   int q_len;         // query tokens per request (>= 1)
   int gqa;           // the caller's query heads per KV head
+  int gqa_inv;       // ceil(2^16 / gqa)
+  int hq;            // the caller's query heads
   int num_items;     // implicit: B*HKV*head_tiles*kv_splits; explicit: row capacity
   int ring_stages;
   int tile_tokens;   // tile_tokens(bits, head_dim)
@@ -38,26 +40,45 @@ struct WorkItem {
   int b, kvh, ht, t0, t1, slot, len, table_off;
 };
 
-// Column hl of KV head kvh (query token hl / gqa, head hl % gqa of the KV head's group) as a
-// row of the caller's q / out / lse tensors [B, q_len, HQ]; at one query token the identity.
+// Several query tokens per request (template flag MQ; the one-token builds carry none of it):
+// column hl of KV head kvh is query token hl / gqa, head hl % gqa of the KV head's group. The
+// quotient comes from a multiply and a shift (gqa_inv = ceil(2^16 / gqa), exact for hl < 512).
+__device__ __forceinline__ int column_token(const DecodeParams& P, int hl) {
+  return (hl * P.gqa_inv) >> 16;
+}
+
+// (token row, head) of column hl in the caller's q / out / lse / q_descale tensors
+// [B * q_len, HQ]; at one query token (b, kvh * heads_per_kv + hl).
+template <bool MQ>
+__device__ __forceinline__ int2 caller_col(const DecodeParams& P, int b, int kvh, int hl) {
+  if constexpr (!MQ) return make_int2(b, kvh * P.heads_per_kv + hl);
+  const int l = column_token(P, hl);
+  return make_int2(b * P.q_len + l, kvh * P.gqa + (hl - l * P.gqa));
+}
+template <bool MQ>
 __device__ __forceinline__ long long caller_row(const DecodeParams& P, int b, int kvh, int hl) {
-  if (P.q_len == 1) return static_cast<long long>(b) * P.a.num_qo_heads + kvh * P.heads_per_kv + hl;
-  const int l = hl / P.gqa, h = hl - l * P.gqa;
-  const int hq = P.gqa * P.p.num_kv_heads;
-  return (static_cast<long long>(b) * P.q_len + l) * hq + kvh * P.gqa + h;
+  if constexpr (!MQ)
+    return static_cast<long long>(b) * P.a.num_qo_heads +
+           (static_cast<long long>(kvh) * P.heads_per_kv + hl);
+  const int2 c = caller_col<true>(P, b, kvh, hl);
+  return static_cast<long long>(c.x) * P.hq + c.y;
 }
 
 // How many of the request's last positions column hl does not see: query token l of q_len
 // attends to positions < len - (q_len - 1 - l).
 __device__ __forceinline__ int column_lag(const DecodeParams& P, int hl) {
-  return P.q_len == 1 ? 0 : max(P.q_len - 1 - hl / P.gqa, 0);
+  return max(P.q_len - 1 - column_token(P, hl), 0);
 }
 
-// q_descale of a caller row: element (row / HQ, row % HQ).
-__device__ __forceinline__ float caller_descale(const DecodeParams& P, long long row) {
-  const int hq = P.gqa * P.p.num_kv_heads;
-  return __ldg(P.a.q_descale + (row / hq) * P.a.q_descale_stride_b +
-               (row % hq) * P.a.q_descale_stride_h);
+// q_descale of column hl: element (token row, head).
+template <bool MQ>
+__device__ __forceinline__ float caller_descale(const DecodeParams& P, int b, int kvh, int hl) {
+  if constexpr (!MQ) {
+    const long long head = static_cast<long long>(kvh) * P.heads_per_kv + hl;
+    return __ldg(P.a.q_descale + b * P.a.q_descale_stride_b + head * P.a.q_descale_stride_h);
+  }
+  const int2 c = caller_col<true>(P, b, kvh, hl);
+  return __ldg(P.a.q_descale + c.x * P.a.q_descale_stride_b + c.y * P.a.q_descale_stride_h);
 }
 
 // Shared-memory plan for one (BITS, D) build. All offsets from a 1024-byte aligned base.
@@ -273,6 +294,7 @@ __device__ __forceinline__ void store_value(void* out, int out_dtype, long long 
 // values eight at a time, so that a merge costs a few memory round trips whatever the piece
 // count (with the loads in sequence a 20-piece merge took longer than a short context's whole
 // decode). Kept out of line: it runs a few times per launch.
+template <bool MQ>
 static __device__ __noinline__ void merge_unit_partials(const DecodeParams& P, int d, int gp, int ch,
                                                  bool writes_lse, int k, int b, int kvh, int ht,
                                                  int h0, int hstep) {
@@ -320,7 +342,7 @@ static __device__ __noinline__ void merge_unit_partials(const DecodeParams& P, i
       }
     }
     const bool live = den > 0.f;
-    const long long orow = caller_row(P, b, kvh, hl);
+    const long long orow = caller_row<MQ>(P, b, kvh, hl);
     store_value(P.a.out, P.a.out_dtype, orow * d + ch, live ? acc / den * P.a.o_scale : 0.f);
     if (writes_lse && P.a.lse != nullptr)
       P.a.lse[orow] = live ? (M + log2f(den)) * LN2 : -INFINITY;

@@ -170,7 +170,7 @@ __device__ inline void expand_half(const uint32_t* w, uint32_t* out, bool v_oper
 // complete. Called by all 128 threads of the group that wrote the piece's partials, some time
 // after the stores: the barrier orders the group's stores before thread 0's release fence and
 // atomic. Thread t merges channels t and 128 + t.
-template <int BITS>
+template <int BITS, bool MQ>
 __device__ __noinline__ void count_in_piece(const DecodeParams& P, int gp, int wg, int t, int b,
                                             int kvh, int ht, volatile int* group_info) {
   named_barrier(1 + wg, 128);
@@ -186,12 +186,27 @@ __device__ __noinline__ void count_in_piece(const DecodeParams& P, int gp, int w
   const int k = group_info[wg];
   if (k > 0) {
     const int ch = channel_of_expanded_pos<BITS>(t);
-    merge_unit_partials(P, D, gp, ch, t == 0, k, b, kvh, ht, 0, 1);
-    merge_unit_partials(P, D, gp, 128 + ch, false, k, b, kvh, ht, 0, 1);
+    merge_unit_partials<MQ>(P, D, gp, ch, t == 0, k, b, kvh, ht, 0, 1);
+    merge_unit_partials<MQ>(P, D, gp, 128 + ch, false, k, b, kvh, ht, 0, 1);
   }
 }
 
-template <int BITS, int GP, bool KCH>
+// The request's last tile with several query tokens per request: column h sees positions below
+// len - lag(h) only. Out of line, so that this rare path (and column_lag's division) costs the
+// tile loop nothing. Returns, in `over`, the largest visible score (already relative to the
+// column's reference).
+template <int GP>
+__device__ __noinline__ void mask_lagged_columns(const DecodeParams& P, int len, int ht, int pos,
+                                                 float (&d)[GP], float& over) {
+  float top = -INFINITY;
+  for (int h = 0; h < GP; ++h) {
+    if (pos >= len - column_lag(P, ht * 8 + h)) d[h] = -INFINITY;
+    top = fmaxf(top, d[h]);
+  }
+  over = top;
+}
+
+template <int BITS, int GP, bool KCH, bool MQ>
 __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem, uint32_t smem0,
                                             uint32_t tmem, const Bars& bars,
                                             volatile int* abort_flag, const ItemRange items) {
@@ -460,7 +475,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       }
       // positions past the request's length (its last tile only): score -inf, record neutral
       // (with several query tokens a column stops short of the request's last positions)
-      const bool whole = (tt + 1) * TILE <= w.len - (P.q_len - 1);
+      const bool whole = (tt + 1) * TILE <= w.len - (MQ ? P.q_len - 1 : 0);
       const bool valid = whole || tt * TILE + t < w.len;
       const float ak = sk * 512.f;
       (void)ak; (void)zk;
@@ -497,8 +512,11 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
                       ab[h] + nm);
           else
             dd = fmaf(head_k[h] * ak, __uint_as_float(raw[h]), fmaf(head_k[8 + h], zk, nm));
-          d[h] = whole || tt * TILE + t < w.len - column_lag(P, w.ht * 8 + h) ? dd : -INFINITY;
+          d[h] = valid ? dd : -INFINITY;
           over = fmaxf(over, d[h]);
+        }
+        if constexpr (MQ) {
+          if (!whole) mask_lagged_columns<GP>(P, w.len, w.ht, tt * TILE + t, d, over);
         }
         if (fresh || named_barrier_or(1 + wg, 128, over > MAX_LAG)) {
           float* wmax = red_max + (wg * 4 + wq) * 8;
@@ -520,7 +538,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
             m[h] = fresh ? shift : m[h] + shift;
             // (a column whose every score of the group's first tile is masked: only the
             // request's last tile, so the group has no further tile of this item)
-            d[h] = shift == -INFINITY ? -INFINITY : d[h] - shift;
+            if constexpr (MQ) d[h] = shift == -INFINITY ? -INFINITY : d[h] - shift;
+            else d[h] -= shift;
           }
           if (pending) {
             // every earlier tile's O of this item is complete in tensor memory: per channel half
@@ -586,7 +605,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       pending = true;
       // a split piece finished before this tile is counted in now: its stores have drained
       if (piece_pending) {
-        count_in_piece<BITS>(P, GP, wg, t, piece_b, piece_kvh, piece_ht, group_info);
+        count_in_piece<BITS, MQ>(P, GP, wg, t, piece_b, piece_kvh, piece_ht, group_info);
         piece_pending = false;
       }
     }
@@ -626,7 +645,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     }
     // ---- this group holds the item's last tile: it finishes the item
     if (piece_pending) {   // (an item finished with no tile since the piece before it)
-      count_in_piece<BITS>(P, GP, wg, t, piece_b, piece_kvh, piece_ht, group_info);
+      count_in_piece<BITS, MQ>(P, GP, wg, t, piece_b, piece_kvh, piece_ht, group_info);
       piece_pending = false;
     }
     if (t == 0) {
@@ -692,7 +711,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         const long long head = static_cast<long long>(w.kvh) * P.heads_per_kv + hl;
         const long long row = static_cast<long long>(w.b) * P.a.num_qo_heads + head;
         if (w.slot < 0) {
-          const long long orow = caller_row(P, w.b, w.kvh, hl);
+          const long long orow = caller_row<MQ>(P, w.b, w.kvh, hl);
           const float inv = L[h] > 0.f ? P.a.o_scale / L[h] : 0.f;
           store_value(P.a.out, P.a.out_dtype, orow * D + ch, v0 * inv);
           store_value(P.a.out, P.a.out_dtype, orow * D + 128 + ch, v1 * inv);
@@ -713,10 +732,10 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     }
   }
   if (piece_pending)
-    count_in_piece<BITS>(P, GP, wg, t, piece_b, piece_kvh, piece_ht, group_info);
+    count_in_piece<BITS, MQ>(P, GP, wg, t, piece_b, piece_kvh, piece_ht, group_info);
 }
 
-template <int BITS, int GP, bool KCH>
+template <int BITS, int GP, bool KCH, bool MQ>
 __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const DecodeParams P) {
   using SP = Plan<BITS, KCH>;
   constexpr int G = SP::G;
@@ -804,7 +823,7 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
           uint4 v = make_uint4(0, 0, 0, 0);
           const int hl = w.ht * 8 + r;
           const bool live = r < 8 && hl < P.heads_per_kv;
-          const long long qrow = live ? caller_row(P, w.b, w.kvh, hl) : 0;
+          const long long qrow = live ? caller_row<MQ>(P, w.b, w.kvh, hl) : 0;
           float qsum = 0.f;   // the row's sum of q (K per channel: its max |q|)
           if (live) {
             const uint4 in = __ldg(reinterpret_cast<const uint4*>(
@@ -849,7 +868,7 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
               if (live) {
                 scale = P.a.sm_scale * 1.4426950408889634f;
                 if (P.a.q_descale != nullptr)
-                  scale *= caller_descale(P, qrow);
+                  scale *= caller_descale<MQ>(P, w.b, w.kvh, hl);
               }
               float* hc = reinterpret_cast<float*>(smem + SP::HEADC_OFF) + qb * 24;
               hc[r] = scale;
@@ -998,7 +1017,7 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
     }
     __syncwarp();
   } else {
-    worker_role<BITS, GP, KCH>(P, smem, smem0, tmem, bars, abort_flag, items);
+    worker_role<BITS, GP, KCH, MQ>(P, smem, smem0, tmem, bars, abort_flag, items);
   }
 
   tc_fence_before();
@@ -1016,7 +1035,7 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
 // ---------------------------------------------------------------------------------------------
 namespace wide {
 
-template <int BITS, int GP, bool KCH>
+template <int BITS, int GP, bool KCH, bool MQ>
 static int launch(DecodeParams& P, cudaStream_t stream) {
   using SP = Plan<BITS, KCH>;
   constexpr int G = SP::G;
@@ -1039,7 +1058,7 @@ static int launch(DecodeParams& P, cudaStream_t stream) {
   P.item_slots = SP::ITEM_SLOTS + more;
   const int smem = SP::RING_OFF + stages * SP::STAGE + more * 32 + 1024;
   static bool configured[64] = {};
-  auto kernel = decode_wide_kernel<BITS, GP, KCH>;
+  auto kernel = decode_wide_kernel<BITS, GP, KCH, MQ>;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -1077,16 +1096,26 @@ static int launch(DecodeParams& P, cudaStream_t stream) {
 }  // namespace wide
 
 // Launch of the head_dim 256 build (called by fq_decode once the arguments are checked).
-int launch_decode_wide(DecodeParams& P, cudaStream_t stream) {
+template <bool MQ>
+static int launch_wide(DecodeParams& P, cudaStream_t stream) {
   const int gp = (P.heads_per_kv < 8 ? P.heads_per_kv : 8) <= 4 ? 4 : 8;
   if (P.p.k_channel_group != 0) {
     if (P.p.bits == 2)
-      return gp == 4 ? wide::launch<2, 4, true>(P, stream) : wide::launch<2, 8, true>(P, stream);
-    return gp == 4 ? wide::launch<4, 4, true>(P, stream) : wide::launch<4, 8, true>(P, stream);
+      return gp == 4 ? wide::launch<2, 4, true, MQ>(P, stream)
+                     : wide::launch<2, 8, true, MQ>(P, stream);
+    return gp == 4 ? wide::launch<4, 4, true, MQ>(P, stream)
+                   : wide::launch<4, 8, true, MQ>(P, stream);
   }
   if (P.p.bits == 2)
-    return gp == 4 ? wide::launch<2, 4, false>(P, stream) : wide::launch<2, 8, false>(P, stream);
-  return gp == 4 ? wide::launch<4, 4, false>(P, stream) : wide::launch<4, 8, false>(P, stream);
+    return gp == 4 ? wide::launch<2, 4, false, MQ>(P, stream)
+                   : wide::launch<2, 8, false, MQ>(P, stream);
+  return gp == 4 ? wide::launch<4, 4, false, MQ>(P, stream)
+                 : wide::launch<4, 8, false, MQ>(P, stream);
+}
+
+int launch_decode_wide(DecodeParams& P, cudaStream_t stream) {
+  // (several query tokens per request: builds of their own, see decode.cuh)
+  return P.q_len > 1 ? launch_wide<true>(P, stream) : launch_wide<false>(P, stream);
 }
 
 }  // namespace fq
