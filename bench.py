@@ -152,7 +152,7 @@ class ClockSampler:
                           "nvidia-smi (100 ms period) has sampled it 4 times"}
 
 
-def build_gpu_case(cfg, device, seed):
+def build_gpu_case(cfg, device, seed, q_len=1):
     """The workload on the device, written through the library's own append."""
     from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
     seq = seq_lens_of(cfg, seed)
@@ -189,13 +189,15 @@ def build_gpu_case(cfg, device, seed):
                 t = torch.arange(a, a + m, device=device)
                 slots = pg_all.long()[t // PAGE] * PAGE + t % PAGE
                 cache.append(k.to(torch.bfloat16), v.to(torch.bfloat16), slots)
-    q = (torch.randn(cfg["batch"], cfg["hq"], cfg["d"], device=device, generator=g)
+    q_shape = (cfg["batch"], cfg["hq"], cfg["d"]) if q_len == 1 else \
+        (cfg["batch"], q_len, cfg["hq"], cfg["d"])
+    q = (torch.randn(*q_shape, device=device, generator=g)
          * cfg["q_scale"]).clamp(-448, 448).to(torch.float8_e4m3fn)
     ws = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     w = PagedDecodeWrapper(ws)
     w.plan(torch.from_numpy(indptr).to(device), torch.from_numpy(indices).to(device),
            torch.from_numpy(seq.astype(np.int32)), cfg["hq"], layout,
-           sm_scale=cfg["d"] ** -0.5 / cfg["q_scale"])
+           sm_scale=cfg["d"] ** -0.5 / cfg["q_scale"], q_len_per_req=q_len)
     torch.cuda.synchronize(device)
     if cache.last_status() != 0:
         raise RuntimeError(f"cache writer reported status {cache.last_status()}")
@@ -561,7 +563,10 @@ def workload_config(args, cfg, seq):
     return {"workload": f"{args.workload}: INT{cfg['bits']} paged GQA decode, batch {cfg['batch']}, "
                         f"{cfg['hq']}/{cfg['hkv']} heads, head_dim {cfg['d']}, page 64, seq_lens "
                         f"{cfg['seq'][0]}..{cfg['seq'][1]} ({int(seq.sum())} KV tokens per GPU), "
-                        f"random page table, token-wise asymmetric groups, q fp8 e4m3",
+                        f"random page table, "
+                        + ("K per channel over a page and V per token" if cfg.get("k_channel")
+                           else "token-wise asymmetric groups") + ", q fp8 e4m3"
+                        + (f", {args.q_len} query tokens per request" if args.q_len > 1 else ""),
             "l2": "inputs larger than L2 (packed cache streamed once per step)",
             "parallelism": f"dp{args.gpus} (independent batches per GPU, no collective)"}
 
@@ -600,14 +605,18 @@ def cache_op_figures(cfg, device, seed):
 GRID_SHAPES = {"hq32-hkv8-d128": (32, 8, 128), "hq8-hkv1-d128": (8, 1, 128),
                "hq16-hkv2-d64": (16, 2, 64)}
 # The reference's published B200 kernel times, us (benchmarks/decode_latency.csv of the
-# reference, quoted in its README.md:165-172, 192, 227): (INT2, INT4) per (shape, batch, context).
-GRID_PUBLISHED = {
-    ("hq32-hkv8-d128", 1, 32768): (15.3, 17.6), ("hq32-hkv8-d128", 1, 131072): (36.7, 44.2),
-    ("hq32-hkv8-d128", 1, 262144): (62.4, 74.8), ("hq32-hkv8-d128", 1, 524288): (114.3, 135.6),
-    ("hq32-hkv8-d128", 8, 32768): (62.5, 75.1), ("hq32-hkv8-d128", 8, 131072): (218.3, 251.9),
-    ("hq32-hkv8-d128", 8, 262144): (399.1, 456.2), ("hq32-hkv8-d128", 8, 524288): (758.1, 865.7),
-    ("hq8-hkv1-d128", 8, 524288): (114.8, 126.3), ("hq16-hkv2-d64", 8, 524288): (168.4, 206.1),
-}
+# reference, quoted in its README.md:165-172, 185-192, 220-227): (INT2, INT4) per (shape, batch,
+# context).
+GRID_PUBLISHED = {}
+for _shape, _batch, _int2, _int4 in (
+        ("hq32-hkv8-d128", 1, (15.3, 36.7, 62.4, 114.3), (17.6, 44.2, 74.8, 135.6)),
+        ("hq32-hkv8-d128", 8, (62.5, 218.3, 399.1, 758.1), (75.1, 251.9, 456.2, 865.7)),
+        ("hq8-hkv1-d128", 1, (12.9, 18.2, 22.4, 29.4), (12.2, 18.4, 22.6, 31.6)),
+        ("hq8-hkv1-d128", 8, (17.3, 37.5, 63.2, 114.8), (18.8, 44.2, 72.9, 126.3)),
+        ("hq16-hkv2-d64", 1, (12.0, 17.0, 22.1, 32.1), (11.8, 17.6, 23.4, 36.6)),
+        ("hq16-hkv2-d64", 8, (20.0, 51.0, 89.5, 168.4), (22.0, 59.6, 107.9, 206.1))):
+    for _ctx, _a, _b in zip((32768, 131072, 262144, 524288), _int2, _int4):
+        GRID_PUBLISHED[(_shape, _batch, _ctx)] = (_a, _b)
 
 
 def run_grid(args):
@@ -695,6 +704,8 @@ def main():
     ap.add_argument("--op", default="decode", choices=["decode", "append", "dequantize"],
                     help="decode: the headline step. append / dequantize: the cache writer or the "
                          "read-back kernel alone on a slice of the workload, as GB/s")
+    ap.add_argument("--q-len", type=int, default=1,
+                    help="query tokens per request (speculative step); tokens/s counts them all")
     ap.add_argument("--grid", action="store_true",
                     help="the reference's own benchmark grid with its cold-L2 protocol (one GPU)")
     args = ap.parse_args()
@@ -720,12 +731,12 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
 
-    case = build_gpu_case(cfg, device, args.seed + 17 * rank)
+    case = build_gpu_case(cfg, device, args.seed + 17 * rank, args.q_len)
     w, cache, q, seq = case["wrapper"], case["cache"], case["q"], case["seq"]
     b, hq, d = cfg["batch"], cfg["hq"], cfg["d"]
-    out = torch.empty(b, hq, d, dtype=torch.bfloat16, device=device)
+    out = torch.empty(q.shape, dtype=torch.bfloat16, device=device)
     q_host = q.cpu().view(torch.uint8).pin_memory()
-    out_host = torch.empty(b, hq, d, dtype=torch.bfloat16).pin_memory()
+    out_host = torch.empty(q.shape, dtype=torch.bfloat16).pin_memory()
     q_stage = torch.empty_like(q)
 
     def barrier():
@@ -786,14 +797,14 @@ def main():
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     step_ms, e2e_ms, decode_ms = (float(x) for x in stats.cpu())
     status = w.last_status()
-    default_args = args.seed == 0 and args.workload in CAPTURED_TRAFFIC
+    default_args = args.seed == 0 and args.workload in CAPTURED_TRAFFIC and args.q_len == 1
     line = None
     if rank == 0:
         peak, peak_kind = measured_peak()
         abytes = algorithmic_bytes(cfg, seq)
         achieved = abytes / (decode_ms * 1e-3) / 1e9
         line = {
-            "metric": "decode_tokens_per_s", "value": world * b / (step_ms * 1e-3),
+            "metric": "decode_tokens_per_s", "value": world * b * args.q_len / (step_ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": step_ms, "us_per_step": step_ms * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None,
@@ -809,7 +820,7 @@ def main():
                          "kernel": "decode_wide_kernel" if cfg["d"] == 256 else "decode_kernel",
                          "kernel_us": decode_ms * 1e3,
                          "algorithmic_bytes": abytes, "frac_of_8tbs_nominal": achieved / 8000.0},
-            "e2e": {"value": world * b / (e2e_ms * 1e-3), "unit": "tokens/s",
+            "e2e": {"value": world * b * args.q_len / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "us_per_step": e2e_ms * 1e3, "h2d_bytes_per_step": int(q_host.numel()),
                     "d2h_bytes_per_step": int(out_host.numel() * 2)},
             "gpu_launches": launches, "clocks": clocks.summary(), "device_status": status,
