@@ -9,11 +9,14 @@
 // Structure is this library's own. Two stream-ordered launches:
 //   1. page_start_kernel: every token at in-page position 0 begins a new use of its page: the
 //      page's scale records are zeroed and its maximum cell is cleared (count moved out).
-//   2. append_kernel: one warp per (token, KV head) quantizes, packs, stores the row, the
-//      record, and raises the page maximum with atomicMax, moving the count between bins.
+//   2. append_kernel: a half-warp per row (K and V of a (token, KV head) pair side by side in a
+//      warp, four pairs per pass) quantizes, packs, stores the row and the record, and raises
+//      the page maximum with atomicMax, moving the count between bins.
 // Zero-then-overwrite leaves exactly the bytes "clear every position no token of the launch
 // writes" leaves, and needs no scan of the slot map. HBM-bound: 2*D*2 bytes read per (token,
 // head), coalesced 16-byte-per-lane-group loads.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace fq {
@@ -115,8 +118,29 @@ __global__ void page_start_kernel(WriterArgs a) {
 // 2. rows
 // -------------------------------------------------------------------------------------------
 
+// A half-warp holds one row: lanes 0-15 a token's K row, lanes 16-31 its V row, D/16 channels a
+// lane. The two rows' reductions, scale divisions, packing and record hand-over then share their
+// instructions, and a warp takes ROWS_PER_WARP (token, head) pairs per pass with all their loads
+// issued before the first is used (at one warp per pair the kernel spent most of its time in the
+// per-pair fixed part and in waiting for two small loads).
+constexpr int ROWS_PER_WARP = 4;
+
+// Reduce over the `lanes` (16, 8 or 4) neighbouring lanes of a half-warp group; every lane of the
+// warp executes all four exchanges.
+__device__ __forceinline__ void group_min_max(float& mn, float& mx, int lanes) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) {
+    const float a = __shfl_xor_sync(0xFFFFFFFFu, mn, o), b = __shfl_xor_sync(0xFFFFFFFFu, mx, o);
+    if (o < lanes) {
+      mn = fminf(mn, a);
+      mx = fmaxf(mx, b);
+    }
+  }
+}
+
 // Per-row clip threshold: the element at `index` of the row's |x| sorted ascending, found by a
-// radix select over the 15 value bits of a bf16 magnitude (bits 30..16 of the f32 pattern).
+// radix select over the 15 value bits of a bf16 magnitude (bits 30..16 of the f32 pattern). The
+// row sits in the 16 lanes of a half-warp.
 template <int CH>
 __device__ inline float clip_threshold(const float (&x)[CH], int index) {
   uint32_t prefix = 0;
@@ -129,7 +153,7 @@ __device__ inline float clip_threshold(const float (&x)[CH], int index) {
       const uint32_t mag = __float_as_uint(x[i]) & 0x7FFFFFFFu;
       count += ((mag & decided) == prefix) ? 1 : 0;
     }
-    for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xFFFFFFFFu, count, o);
+    for (int o = 8; o > 0; o >>= 1) count += __shfl_xor_sync(0xFFFFFFFFu, count, o);
     if (rank >= count) {
       rank -= count;
       prefix |= 1u << bit;
@@ -138,13 +162,15 @@ __device__ inline float clip_threshold(const float (&x)[CH], int index) {
   return __uint_as_float(prefix);
 }
 
-// Quantize CH values held by this lane against the group's (s, z); returns them as a partial
-// 32-bit code word contribution (this lane's fields of word `c0 / W`).
-template <int BITS, int CH>
-__device__ inline uint32_t quantize_fields(const float (&x)[CH], float s, float z, int c0,
-                                           bool inside) {
+// Quantize the CH values of this lane against its group's (s, z) into the lane's part of the
+// row's code words: WPL whole words, or its fields of a word shared with neighbouring lanes.
+template <int BITS, int CH, int WPL>
+__device__ inline void quantize_fields(const float (&x)[CH], float s, float z, int c0, bool inside,
+                                       uint32_t (&word)[WPL]) {
   constexpr int QMAX = (1 << BITS) - 1;
-  uint32_t word = 0;
+  constexpr int W = 32 / BITS;
+#pragma unroll
+  for (int j = 0; j < WPL; ++j) word[j] = 0;
 #pragma unroll
   for (int i = 0; i < CH; ++i) {
     float xv = x[i];
@@ -152,13 +178,13 @@ __device__ inline uint32_t quantize_fields(const float (&x)[CH], float s, float 
     const float dividend = fmaxf(__fsub_rn(xv, z), DIVIDEND_FLOOR);
     int q = __float2int_rn(__fdiv_rn(dividend, s));
     q = min(q, QMAX);
-    word |= static_cast<uint32_t>(q) << (code_bit_offset<BITS>(c0 + i) & 31);
+    word[WPL == 1 ? 0 : i / W] |= static_cast<uint32_t>(q) << (code_bit_offset<BITS>(c0 + i) & 31);
   }
-  return word;
 }
 
 template <int BITS, int D, bool PREQ>
-__device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta);
+__device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta, long long first,
+                                            long long total);
 
 template <int BITS, int D, bool PREQ>
 __global__ void __launch_bounds__(256) append_kernel(WriterArgs a) {
@@ -170,7 +196,12 @@ __global__ void __launch_bounds__(256) append_kernel(WriterArgs a) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   for (int i = threadIdx.x; i < FQ_VMAX_BINS; i += blockDim.x) hist_delta[i] = 0;
   __syncthreads();
-  append_rows<BITS, D, PREQ>(a, hist_delta);
+  // resident CTAs, every warp striding over the (token, head) pairs ROWS_PER_WARP at a time
+  const long long total = static_cast<long long>(a.num_tokens) * a.p.num_kv_heads;
+  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const long long warp = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  for (long long first = warp * ROWS_PER_WARP; first < total; first += warps * ROWS_PER_WARP)
+    append_rows<BITS, D, PREQ>(a, hist_delta, first, total);
   __syncthreads();
   if (a.p.v_max_hist != nullptr)
     for (int i = threadIdx.x; i < FQ_VMAX_BINS; i += blockDim.x)
@@ -178,190 +209,198 @@ __global__ void __launch_bounds__(256) append_kernel(WriterArgs a) {
 }
 
 template <int BITS, int D, bool PREQ>
-__device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta) {
-  constexpr int CH = D / 32;        // channels per lane
-  constexpr int W = 32 / BITS;      // codes per word
-  constexpr int LPW = W / CH;       // lanes sharing one code word (>= 1)
-  constexpr int RB = D * BITS / 8;  // row bytes
+__device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta, long long first,
+                                            long long total) {
+  constexpr int R = ROWS_PER_WARP;
+  constexpr int CH = D / 16;                   // channels per lane: 4, 8 or 16
+  constexpr int W = 32 / BITS;                 // codes per word
+  constexpr int WPL = CH >= W ? CH / W : 1;    // whole words per lane ...
+  constexpr int LPW = CH >= W ? 1 : W / CH;    // ... or lanes sharing one word
+  constexpr int RB = D * BITS / 8;             // row bytes
   constexpr int QMAX = (1 << BITS) - 1;
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  constexpr int IN_WORDS = PREQ ? CH / 4 : CH / 2;   // 32-bit words of a lane's input
   const int lane = threadIdx.x & 31;
+  const int half = lane >> 4, hl = lane & 15;  // half 0: the K row, half 1: the V row
+  const int c0 = hl * CH;
   const int hkv = a.p.num_kv_heads;
-  if (warp >= a.num_tokens * hkv) return;
-  const int token = warp / hkv, head = warp % hkv;
   const int kg = a.p.k_groups;
   const bool kch = a.p.k_channel_group != 0;   // K goes by whole pages (append_k_channel_kernel)
-  const int c0 = lane * CH;
-  // The token's rows are requested before its slot is known: the slot, the rows and (below) the
-  // page's maximum cell are three global round trips, and only the last depends on another.
-  const __nv_bfloat16* kr = static_cast<const __nv_bfloat16*>(a.k) +
-                            token * a.k_stride + static_cast<long long>(head) * D + c0;
-  const __nv_bfloat16* vr = static_cast<const __nv_bfloat16*>(a.v) +
-                            token * a.v_stride + static_cast<long long>(head) * D + c0;
-  uint4 uk = make_uint4(0, 0, 0, 0), uv = make_uint4(0, 0, 0, 0);
-  if (!PREQ) {
-    if constexpr (CH == 8) {
-      if (!kch) uk = __ldg(reinterpret_cast<const uint4*>(kr));
-      uv = __ldg(reinterpret_cast<const uint4*>(vr));
-    } else if constexpr (CH == 4) {
-      const uint2 k2 = kch ? make_uint2(0, 0) : __ldg(reinterpret_cast<const uint2*>(kr));
-      const uint2 v2 = __ldg(reinterpret_cast<const uint2*>(vr));
-      uk.x = k2.x; uk.y = k2.y; uv.x = v2.x; uv.y = v2.y;
-    } else {
-      if (!kch) uk.x = __ldg(reinterpret_cast<const uint32_t*>(kr));
-      uv.x = __ldg(reinterpret_cast<const uint32_t*>(vr));
-    }
-  }
-  const long long slot = slot_of(a, token);
-  if (slot < 0) return;
-  const long long page = slot >> 6;
-  const int pos = static_cast<int>(slot & (PAGE - 1));
-  if (page >= a.p.num_pages) {
-    if (lane == 0 && a.status) atomicOr(a.status, FQ_STATUS_BAD_SLOT);
-    return;
-  }
-  // the page's current maximum, wanted only at the very end
-  uint32_t cell_seen = 0;
-  if (lane == 0 && a.p.v_page_max != nullptr)
-    cell_seen = *reinterpret_cast<volatile uint32_t*>(a.p.v_page_max + page * hkv + head);
-  float sk, zk, sv, zv;
-  uint32_t kw, vw;
+  const bool idle = kch && half == 0;
+  const int glanes = half == 0 ? 16 / kg : 16; // lanes of this lane's quantization group
 
-  if (!PREQ) {
-    float xk[CH], xv[CH];
-    if constexpr (CH == 8) {
-      const uint32_t wk[4] = {uk.x, uk.y, uk.z, uk.w}, wv[4] = {uv.x, uv.y, uv.z, uv.w};
+  // ---- every pair's slot and rows are requested before any is used
+  int token[R], head[R];
+  long long slot[R];
+  uint32_t in[R][IN_WORDS];
+  // (pairs are numbered token-major and a launch has fewer than 2^31 of them: one 32-bit
+  // division per pass, the pass's other pairs by stepping the head)
+  int tok = static_cast<int>(static_cast<uint32_t>(first) / static_cast<uint32_t>(hkv));
+  int hd = static_cast<int>(first) - tok * hkv;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        xk[2 * i] = __uint_as_float(wk[i] << 16);
-        xk[2 * i + 1] = __uint_as_float(wk[i] & 0xFFFF0000u);
-        xv[2 * i] = __uint_as_float(wv[i] << 16);
-        xv[2 * i + 1] = __uint_as_float(wv[i] & 0xFFFF0000u);
+  for (int r = 0; r < R; ++r) {
+    const bool live = first + r < total;
+    token[r] = live ? tok : 0;
+    head[r] = live ? hd : 0;
+    if (++hd == hkv) { hd = 0; ++tok; }
+    slot[r] = live ? slot_of(a, token[r]) : -1;
+#pragma unroll
+    for (int i = 0; i < IN_WORDS; ++i) in[r][i] = 0;
+    if (!live || idle) continue;
+    if (!PREQ) {
+      const __nv_bfloat16* row = static_cast<const __nv_bfloat16*>(half ? a.v : a.k) +
+                                 token[r] * (half ? a.v_stride : a.k_stride) +
+                                 static_cast<long long>(head[r]) * D + c0;
+      if constexpr (CH == 4) {
+        const uint2 t = __ldg(reinterpret_cast<const uint2*>(row));
+        in[r][0] = t.x; in[r][1] = t.y;
+      } else {
+#pragma unroll
+        for (int i = 0; i < CH / 8; ++i) {
+          const uint4 t = __ldg(reinterpret_cast<const uint4*>(row) + i);
+          in[r][4 * i] = t.x; in[r][4 * i + 1] = t.y; in[r][4 * i + 2] = t.z; in[r][4 * i + 3] = t.w;
+        }
       }
-    } else if constexpr (CH == 4) {
-      xk[0] = __uint_as_float(uk.x << 16); xk[1] = __uint_as_float(uk.x & 0xFFFF0000u);
-      xk[2] = __uint_as_float(uk.y << 16); xk[3] = __uint_as_float(uk.y & 0xFFFF0000u);
-      xv[0] = __uint_as_float(uv.x << 16); xv[1] = __uint_as_float(uv.x & 0xFFFF0000u);
-      xv[2] = __uint_as_float(uv.y << 16); xv[3] = __uint_as_float(uv.y & 0xFFFF0000u);
     } else {
-      xk[0] = __uint_as_float(uk.x << 16); xk[1] = __uint_as_float(uk.x & 0xFFFF0000u);
-      xv[0] = __uint_as_float(uv.x << 16); xv[1] = __uint_as_float(uv.x & 0xFFFF0000u);
-    }
-    if (a.k_clip >= 0) {
-      const float t = clip_threshold<CH>(xk, a.k_clip);
+      // engine-quantized: one code per byte
+      const uint8_t* row = static_cast<const uint8_t*>(half ? a.v : a.k) +
+                           (static_cast<long long>(token[r]) * hkv + head[r]) * D + c0;
 #pragma unroll
-      for (int i = 0; i < CH; ++i) xk[i] = fminf(fmaxf(xk[i], -t), t);
+      for (int i = 0; i < IN_WORDS; ++i) in[r][i] = __ldg(reinterpret_cast<const uint32_t*>(row) + i);
     }
-    if (a.v_clip >= 0) {
-      const float t = clip_threshold<CH>(xv, a.v_clip);
+  }
+  // the pages' current maxima, wanted only at the very end of each pair
+  uint32_t cell_seen[R];
 #pragma unroll
-      for (int i = 0; i < CH; ++i) xv[i] = fminf(fmaxf(xv[i], -t), t);
-    }
-    float kmn = xk[0], kmx = xk[0], vmn = xv[0], vmx = xv[0];
-#pragma unroll
-    for (int i = 1; i < CH; ++i) {
-      kmn = fminf(kmn, xk[i]); kmx = fmaxf(kmx, xk[i]);
-      vmn = fminf(vmn, xv[i]); vmx = fmaxf(vmx, xv[i]);
-    }
-    const int klanes = 32 / kg;  // lanes of one K group
-    kmn = warp_group_min(kmn, klanes); kmx = warp_group_max(kmx, klanes);
-    vmn = warp_group_min(vmn, 32); vmx = warp_group_max(vmx, 32);
-    const bool k_in = kmx <= ENVELOPE && kmn >= -ENVELOPE;
-    const bool v_in = vmx <= ENVELOPE && vmn >= -ENVELOPE;
-    zk = fminf(fmaxf(kmn, -ENVELOPE), ENVELOPE);
-    zv = fminf(fmaxf(vmn, -ENVELOPE), ENVELOPE);
-    const float ktop = fminf(fmaxf(kmx, -ENVELOPE), ENVELOPE);
-    const float vtop = fminf(fmaxf(vmx, -ENVELOPE), ENVELOPE);
-    sk = __fdiv_rn(fmaxf(__fsub_rn(ktop, zk), S_CLAMP), static_cast<float>(QMAX));
-    sv = __fdiv_rn(fmaxf(__fsub_rn(vtop, zv), S_CLAMP), static_cast<float>(QMAX));
-    kw = quantize_fields<BITS, CH>(xk, sk, zk, c0, k_in);
-    vw = quantize_fields<BITS, CH>(xv, sv, zv, c0, v_in);
-  } else {
-    // engine-quantized: one code per byte, masked to the stored width; records saturated
-    const uint8_t* kc = static_cast<const uint8_t*>(a.k) +
-                        (static_cast<long long>(token) * hkv + head) * D + c0;
-    const uint8_t* vc = static_cast<const uint8_t*>(a.v) +
-                        (static_cast<long long>(token) * hkv + head) * D + c0;
-    kw = vw = 0;
-#pragma unroll
-    for (int i = 0; i < CH; ++i) {
-      const int sh = code_bit_offset<BITS>(c0 + i) & 31;
-      kw |= static_cast<uint32_t>(__ldg(kc + i) & QMAX) << sh;
-      vw |= static_cast<uint32_t>(__ldg(vc + i) & QMAX) << sh;
-    }
-    const float s_lo = __fdiv_rn(S_CLAMP, static_cast<float>(QMAX));
-    const float s_hi = __fdiv_rn(2.0f * ENVELOPE, static_cast<float>(QMAX));
-    const long long row = static_cast<long long>(token) * hkv + head;
-    const int grp = lane / (32 / kg);
-    sk = fminf(fmaxf(__ldg(a.k_scale + row * kg + grp), s_lo), s_hi);
-    zk = fminf(fmaxf(__ldg(a.k_zero + row * kg + grp), -ENVELOPE), ENVELOPE);
-    sv = fminf(fmaxf(__ldg(a.v_scale + row), s_lo), s_hi);
-    zv = fminf(fmaxf(__ldg(a.v_zero + row), -ENVELOPE), ENVELOPE);
+  for (int r = 0; r < R; ++r) {
+    cell_seen[r] = 0;
+    const long long page = slot[r] >> 6;
+    if (lane == 0 && slot[r] >= 0 && page < a.p.num_pages && a.p.v_page_max != nullptr)
+      cell_seen[r] = *reinterpret_cast<volatile uint32_t*>(a.p.v_page_max + page * hkv + head[r]);
   }
 
-  // assemble code words across the lanes that share one, then one lane per word stores it
 #pragma unroll
-  for (int o = 1; o < LPW; o <<= 1) {
-    kw |= __shfl_xor_sync(0xFFFFFFFFu, kw, o);
-    vw |= __shfl_xor_sync(0xFFFFFFFFu, vw, o);
-  }
-  const long long row_index = (page * hkv + head) * PAGE + pos;
-  if (lane % LPW == 0) {
-    const int word = c0 / W;
-    if (!kch) reinterpret_cast<uint32_t*>(a.p.k_codes + row_index * RB)[word] = kw;
-    reinterpret_cast<uint32_t*>(a.p.v_codes + row_index * RB)[word] = vw;
-  }
+  for (int r = 0; r < R; ++r) {
+    if (slot[r] < 0) continue;                 // (warp-uniform)
+    const long long page = slot[r] >> 6;
+    const int pos = static_cast<int>(slot[r] & (PAGE - 1));
+    if (page >= a.p.num_pages) {
+      if (lane == 0 && a.status) atomicOr(a.status, FQ_STATUS_BAD_SLOT);
+      continue;
+    }
+    float s, z;               // this lane's group's record
+    uint32_t word[WPL];
+    if (!PREQ) {
+      float x[CH];
+#pragma unroll
+      for (int i = 0; i < CH / 2; ++i) {
+        x[2 * i] = __uint_as_float(in[r][i] << 16);
+        x[2 * i + 1] = __uint_as_float(in[r][i] & 0xFFFF0000u);
+      }
+      if (a.k_clip >= 0 || a.v_clip >= 0) {
+        const int index = half ? a.v_clip : a.k_clip;
+        const float t = clip_threshold<CH>(x, index < 0 ? 0 : index);
+        if (index >= 0) {
+#pragma unroll
+          for (int i = 0; i < CH; ++i) x[i] = fminf(fmaxf(x[i], -t), t);
+        }
+      }
+      float mn = x[0], mx = x[0];
+#pragma unroll
+      for (int i = 1; i < CH; ++i) {
+        mn = fminf(mn, x[i]);
+        mx = fmaxf(mx, x[i]);
+      }
+      group_min_max(mn, mx, glanes);
+      const bool inside = mx <= ENVELOPE && mn >= -ENVELOPE;
+      z = fminf(fmaxf(mn, -ENVELOPE), ENVELOPE);
+      const float top = fminf(fmaxf(mx, -ENVELOPE), ENVELOPE);
+      s = __fdiv_rn(fmaxf(__fsub_rn(top, z), S_CLAMP), static_cast<float>(QMAX));
+      quantize_fields<BITS, CH, WPL>(x, s, z, c0, inside, word);
+    } else {
+      // codes masked to the stored width; records saturated
+#pragma unroll
+      for (int j = 0; j < WPL; ++j) word[j] = 0;
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const uint32_t q = (in[r][i / 4] >> (8 * (i % 4))) & QMAX;
+        word[WPL == 1 ? 0 : i / W] |= q << (code_bit_offset<BITS>(c0 + i) & 31);
+      }
+      const float s_lo = __fdiv_rn(S_CLAMP, static_cast<float>(QMAX));
+      const float s_hi = __fdiv_rn(2.0f * ENVELOPE, static_cast<float>(QMAX));
+      const long long row = static_cast<long long>(token[r]) * hkv + head[r];
+      const long long rec = half ? row : row * kg + hl / (16 / kg);
+      s = fminf(fmaxf(__ldg((half ? a.v_scale : a.k_scale) + rec), s_lo), s_hi);
+      z = fminf(fmaxf(__ldg((half ? a.v_zero : a.k_zero) + rec), -ENVELOPE), ENVELOPE);
+    }
 
-  // scale records, rounded to the pool dtype; the K groups' (s, z) sit with their first lanes
-  const float sk1 = __shfl_sync(0xFFFFFFFFu, sk, (32 / kg) * 1 % 32);
-  const float zk1 = __shfl_sync(0xFFFFFFFFu, zk, (32 / kg) * 1 % 32);
-  const float sk2 = __shfl_sync(0xFFFFFFFFu, sk, (32 / kg) * 2 % 32);
-  const float zk2 = __shfl_sync(0xFFFFFFFFu, zk, (32 / kg) * 2 % 32);
-  const float sk3 = __shfl_sync(0xFFFFFFFFu, sk, (32 / kg) * 3 % 32);
-  const float zk3 = __shfl_sync(0xFFFFFFFFu, zk, (32 / kg) * 3 % 32);
-  if (lane == 0) {
-    char* block = static_cast<char*>(a.p.scales) + (page * hkv + head) * scale_block_bytes(a.p);
-    uint32_t sv_bits;
-    if (kch) {
-      // V ring at the front of the block: token t's (s_v, z_v) at element 2t
-      if (!a.p.scale_bf16) {
-        reinterpret_cast<float2*>(block)[pos] = make_float2(sv, zv);
+    // code words shared by neighbouring lanes are assembled, then one lane per word stores
+#pragma unroll
+    for (int o = 1; o < LPW; o <<= 1) word[0] |= __shfl_xor_sync(0xFFFFFFFFu, word[0], o);
+    const long long row_index = (page * hkv + head[r]) * PAGE + pos;
+    if (!idle && hl % LPW == 0) {
+      uint32_t* dst = reinterpret_cast<uint32_t*>((half ? a.p.v_codes : a.p.k_codes) +
+                                                  row_index * RB) + c0 / W;
+      if constexpr (WPL == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(word[0], word[1]);
+      else dst[0] = word[0];
+    }
+
+    // the records meet in lane 0: V's from lane 16, the K groups' from their first lanes
+    const float sv = __shfl_sync(0xFFFFFFFFu, s, 16), zv = __shfl_sync(0xFFFFFFFFu, z, 16);
+    const float sk = s, zk = z;
+    float sk1 = 0.f, zk1 = 0.f, sk2 = 0.f, zk2 = 0.f, sk3 = 0.f, zk3 = 0.f;
+    if (kg > 1) {   // (warp-uniform)
+      sk1 = __shfl_sync(0xFFFFFFFFu, s, (16 / kg) * 1 % 16);
+      zk1 = __shfl_sync(0xFFFFFFFFu, z, (16 / kg) * 1 % 16);
+      sk2 = __shfl_sync(0xFFFFFFFFu, s, (16 / kg) * 2 % 16);
+      zk2 = __shfl_sync(0xFFFFFFFFu, z, (16 / kg) * 2 % 16);
+      sk3 = __shfl_sync(0xFFFFFFFFu, s, (16 / kg) * 3 % 16);
+      zk3 = __shfl_sync(0xFFFFFFFFu, z, (16 / kg) * 3 % 16);
+    }
+    if (lane == 0) {
+      char* block = static_cast<char*>(a.p.scales) +
+                    (page * hkv + head[r]) * scale_block_bytes(a.p);
+      uint32_t sv_bits;
+      if (kch) {
+        // V ring at the front of the block: token t's (s_v, z_v) at element 2t
+        if (!a.p.scale_bf16) {
+          reinterpret_cast<float2*>(block)[pos] = make_float2(sv, zv);
+          sv_bits = __float_as_uint(sv);
+        } else {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(sv, zv);
+          const uint32_t vrec = *reinterpret_cast<const uint32_t*>(&h);
+          reinterpret_cast<uint32_t*>(block)[pos] = vrec;
+          sv_bits = vrec << 16;
+        }
+      } else if (!a.p.scale_bf16) {
+        // f32 pool: whole-head K only
+        reinterpret_cast<float4*>(block)[pos] = make_float4(sk, zk, sv, zv);
         sv_bits = __float_as_uint(sv);
       } else {
-        const __nv_bfloat162 h = __floats2bfloat162_rn(sv, zv);
-        const uint32_t vrec = *reinterpret_cast<const uint32_t*>(&h);
-        reinterpret_cast<uint32_t*>(block)[pos] = vrec;
+        auto pack = [](float s_, float z_) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(s_, z_);
+          return *reinterpret_cast<const uint32_t*>(&h);
+        };
+        const uint32_t vrec = pack(sv, zv);
         sv_bits = vrec << 16;
-      }
-    } else if (!a.p.scale_bf16) {
-      // f32 pool: whole-head K only
-      reinterpret_cast<float4*>(block)[pos] = make_float4(sk, zk, sv, zv);
-      sv_bits = __float_as_uint(sv);
-    } else {
-      auto pack = [](float s, float z) {
-        const __nv_bfloat162 h = __floats2bfloat162_rn(s, z);
-        return *reinterpret_cast<const uint32_t*>(&h);
-      };
-      const uint32_t vrec = pack(sv, zv);
-      sv_bits = vrec << 16;
-      if (kg == 1) {
-        reinterpret_cast<uint2*>(block)[pos] = make_uint2(pack(sk, zk), vrec);
-      } else {
-        uint32_t* kring = reinterpret_cast<uint32_t*>(block) + kg * pos;
-        kring[0] = pack(sk, zk);
-        kring[1] = pack(sk1, zk1);
-        if (kg == 4) {
-          kring[2] = pack(sk2, zk2);
-          kring[3] = pack(sk3, zk3);
+        if (kg == 1) {
+          reinterpret_cast<uint2*>(block)[pos] = make_uint2(pack(sk, zk), vrec);
+        } else {
+          uint32_t* kring = reinterpret_cast<uint32_t*>(block) + kg * pos;
+          kring[0] = pack(sk, zk);
+          kring[1] = pack(sk1, zk1);
+          if (kg == 4) {
+            kring[2] = pack(sk2, zk2);
+            kring[3] = pack(sk3, zk3);
+          }
+          reinterpret_cast<uint32_t*>(block + 2 * kg * PAGE * 2)[pos] = vrec;
         }
-        reinterpret_cast<uint32_t*>(block + 2 * kg * PAGE * 2)[pos] = vrec;
       }
-    }
-    if (a.p.v_page_max != nullptr) {
-      uint32_t* cell = a.p.v_page_max + page * hkv + head;
-      if (sv_bits > cell_seen) {   // a stale (smaller) reading only costs a redundant atomicMax
-        const uint32_t old = atomicMax(cell, sv_bits);
-        if (old < sv_bits) settle_count_local(hist_delta, old, sv_bits);
+      if (a.p.v_page_max != nullptr) {
+        uint32_t* cell = a.p.v_page_max + page * hkv + head[r];
+        if (sv_bits > cell_seen[r]) {   // a stale (smaller) reading only costs a redundant atomicMax
+          const uint32_t old = atomicMax(cell, sv_bits);
+          if (old < sv_bits) settle_count_local(hist_delta, old, sv_bits);
+        }
       }
     }
   }
@@ -465,16 +504,27 @@ __global__ void recount_kernel(uint32_t* cells, long long n, uint32_t* hist) {
 
 template <bool PREQ>
 static int launch_append(const WriterArgs& a, cudaStream_t stream) {
-  const long long warps = static_cast<long long>(a.num_tokens) * a.p.num_kv_heads;
-  if (warps == 0) return 0;
+  const long long pairs = static_cast<long long>(a.num_tokens) * a.p.num_kv_heads;
+  if (pairs == 0) return 0;
   const int threads = 256;
-  const long long blocks = (warps * 32 + threads - 1) / threads;
-  if (blocks > 0x7FFFFFFFLL) return FQ_ERR_TOO_LARGE;
-  page_start_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(a);
-#define FQ_LAUNCH(B, DD)                                                                  \
-  if (a.p.bits == B && a.p.head_dim == DD) {                                              \
-    append_kernel<B, DD, PREQ><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(a); \
-    return static_cast<int>(cudaGetLastError());                                          \
+  const long long start_blocks = (pairs * 32 + threads - 1) / threads;   // a warp per pair
+  if (start_blocks > 0x7FFFFFFFLL || pairs > 0x7FFFFFFFLL) return FQ_ERR_TOO_LARGE;
+  page_start_kernel<<<static_cast<unsigned>(start_blocks), threads, 0, stream>>>(a);
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+    sms = 148;
+  // the row pass: resident CTAs, a warp taking ROWS_PER_WARP pairs per pass
+  const long long want = (pairs + 8 * ROWS_PER_WARP - 1) / (8 * ROWS_PER_WARP);
+#define FQ_LAUNCH(B, DD)                                                                      \
+  if (a.p.bits == B && a.p.head_dim == DD) {                                                  \
+    int per_sm = 0;                                                                           \
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, append_kernel<B, DD, PREQ>,    \
+                                                      threads, 0) != cudaSuccess || per_sm < 1) \
+      per_sm = 2;                                                                             \
+    const long long grid = std::min<long long>(want, static_cast<long long>(sms) * per_sm);   \
+    append_kernel<B, DD, PREQ><<<static_cast<unsigned>(grid), threads, 0, stream>>>(a);       \
+    return static_cast<int>(cudaGetLastError());                                              \
   }
   FQ_LAUNCH(2, 64) FQ_LAUNCH(2, 128) FQ_LAUNCH(2, 256)
   FQ_LAUNCH(4, 64) FQ_LAUNCH(4, 128) FQ_LAUNCH(4, 256)
@@ -580,6 +630,9 @@ extern "C" int fq_append_quantized(const fq_pools* pools, const uint8_t* k_codes
   if (pools->k_channel_group != 0) return FQ_ERR_UNSUPPORTED;
   if (num_tokens < 0 || (num_tokens > 0 && (!k_codes || !v_codes || !k_scale || !k_zero ||
                                             !v_scale || !v_zero || !slot_mapping)))
+    return FQ_ERR_BAD_ARG;
+  // the code rows are read four bytes at a time
+  if ((reinterpret_cast<uintptr_t>(k_codes) | reinterpret_cast<uintptr_t>(v_codes)) & 3)
     return FQ_ERR_BAD_ARG;
   fq::WriterArgs a{};
   a.p = *pools;

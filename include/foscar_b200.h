@@ -70,8 +70,8 @@ int fq_append(const fq_pools* pools, const void* k, const void* v, int64_t k_tok
               int32_t k_clip, int32_t v_clip, int32_t* status, void* stream);
 
 /* Layout-only write of engine-quantized tokens: codes uint8 [T, HKV, D] one value per byte,
- * f32 scales/zeros [T, HKV(, k_groups)]. Stands in for QuantKVCache.append_quantized
- * (src/foscar/kv_cache.py:689-767). */
+ * f32 scales/zeros [T, HKV(, k_groups)]; the code pointers 4-byte aligned. Stands in for
+ * QuantKVCache.append_quantized (src/foscar/kv_cache.py:689-767). */
 int fq_append_quantized(const fq_pools* pools, const uint8_t* k_codes, const float* k_scale,
                         const float* k_zero, const uint8_t* v_codes, const float* v_scale,
                         const float* v_zero, const int64_t* slot_mapping, int32_t num_tokens,
