@@ -228,7 +228,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 
   auto merge_unit = [&](int k, int b, int kvh, int ht, int h0, int hstep) {
     if (t < D)
-      merge_unit_partials<MQ>(P, D, GP, channel_of_expanded_pos<BITS>(t), t == 0, k, b, kvh, ht, h0,
+      merge_unit_partials<MQ, 1>(P, D, GP, channel_of_expanded_pos<BITS>(t), t == 0, k, b, kvh, ht, h0,
                           hstep);
   };
   // the split piece this CTA has written but not yet counted in (thread 0 of group 0 only)

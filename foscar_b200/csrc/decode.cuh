@@ -288,13 +288,15 @@ __device__ __forceinline__ void store_value(void* out, int out_dtype, long long 
 }
 
 // Merge of a split unit's partials: the arithmetic and slot order of merge_kernel. Heads h0,
-// h0 + hstep, ... (< gp) of the unit's head tile; the calling thread takes channel `ch`. Called
+// h0 + hstep, ... (< gp) of the unit's head tile, HU of them at a time with their loads going
+// out together (the head_dim 256 kernel, where one group merges all eight heads of both channel
+// halves, takes two: 130 against 136 us on its token-wise workload; four cost more in registers
+// than they saved); the calling thread takes channel `ch`. Called
 // by whole warps whose threads all work on the same heads: the slots' (m, l) pairs are fetched
 // one per lane (the unit has at most 64 pieces) and handed round by shuffles, and the slots' o
 // values eight at a time, so that a merge costs a few memory round trips whatever the piece
-// count (with the loads in sequence a 20-piece merge took longer than a short context's whole
-// decode). Kept out of line: it runs a few times per launch.
-template <bool MQ>
+// count. Kept out of line: it runs a few times per launch.
+template <bool MQ, int HU>
 static __device__ __noinline__ void merge_unit_partials(const DecodeParams& P, int d, int gp, int ch,
                                                  bool writes_lse, int k, int b, int kvh, int ht,
                                                  int h0, int hstep) {
@@ -304,48 +306,74 @@ static __device__ __noinline__ void merge_unit_partials(const DecodeParams& P, i
   const int lane = threadIdx.x & 31;
   if (k > 64) k = 64;
 #pragma unroll 1
-  for (int h = h0; h < gp; h += hstep) {
-    const int hl = ht * 8 + h;
-    if (hl >= P.heads_per_kv) continue;
-    const long long head = static_cast<long long>(kvh) * P.heads_per_kv + hl;
-    const long long row = static_cast<long long>(b) * P.a.num_qo_heads + head;
-    // slot s: lane s % 32, word s / 32
-    float ms[2], ls[2];
+  for (int hb = h0; hb < gp; hb += hstep * HU) {
+    int hl[HU];
+    bool on[HU];
+    long long row[HU];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int s = lane + 32 * j;
-      ms[j] = s < k ? __ldcg(P.a.m_partial + s * rows + row) : -INFINITY;
-      ls[j] = s < k ? __ldcg(P.a.l_partial + s * rows + row) : 0.f;
+    for (int u = 0; u < HU; ++u) {
+      const int h = hb + u * hstep;
+      hl[u] = ht * 8 + h;
+      on[u] = h < gp && hl[u] < P.heads_per_kv;
+      row[u] = static_cast<long long>(b) * P.a.num_qo_heads +
+               (static_cast<long long>(kvh) * P.heads_per_kv + hl[u]);
     }
-    float M = fmaxf(ms[0], ms[1]);
+    // slot s: lane s % 32, word s / 32
+    float ms[HU][2], ls[HU][2];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
-    float wl[2];   // this lane's slots' weights (0 for a slot past k or without a maximum)
+    for (int u = 0; u < HU; ++u)
 #pragma unroll
-    for (int j = 0; j < 2; ++j) wl[j] = (M > -INFINITY && lane + 32 * j < k) ? exp2f(ms[j] - M) : 0.f;
-    float den = 0.f, acc = 0.f;
+      for (int j = 0; j < 2; ++j) {
+        const int s = lane + 32 * j;
+        const bool have = on[u] && s < k;
+        ms[u][j] = have ? __ldcg(P.a.m_partial + s * rows + row[u]) : -INFINITY;
+        ls[u][j] = have ? __ldcg(P.a.l_partial + s * rows + row[u]) : 0.f;
+      }
+    float M[HU], wl[HU][2], den[HU], acc[HU];
+#pragma unroll
+    for (int u = 0; u < HU; ++u) {
+      M[u] = fmaxf(ms[u][0], ms[u][1]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) M[u] = fmaxf(M[u], __shfl_xor_sync(0xFFFFFFFFu, M[u], o));
+      // this lane's slots' weights (0 for a slot past k or without a maximum)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        wl[u][j] = (M[u] > -INFINITY && lane + 32 * j < k) ? exp2f(ms[u][j] - M[u]) : 0.f;
+      den[u] = acc[u] = 0.f;
+    }
 #pragma unroll 1
     for (int s0 = 0; s0 < k; s0 += 8) {
-      float os[8];
+      float os[HU][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        os[i] = s0 + i < k ? __ldcg(P.a.o_partial + ((s0 + i) * rows + row) * d + ch) : 0.f;
+      for (int u = 0; u < HU; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          os[u][i] = on[u] && s0 + i < k
+                         ? __ldcg(P.a.o_partial + ((s0 + i) * rows + row[u]) * d + ch) : 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int s = s0 + i;                     // (warp-uniform)
-        const float wgt = __shfl_sync(0xFFFFFFFFu, s < 32 ? wl[0] : wl[1], s & 31);
-        const float lv = __shfl_sync(0xFFFFFFFFu, s < 32 ? ls[0] : ls[1], s & 31);
-        if (s < k) {
-          den += wgt * lv;
-          acc += wgt * os[i];
+#pragma unroll
+        for (int u = 0; u < HU; ++u) {
+          const float wgt = __shfl_sync(0xFFFFFFFFu, s < 32 ? wl[u][0] : wl[u][1], s & 31);
+          const float lv = __shfl_sync(0xFFFFFFFFu, s < 32 ? ls[u][0] : ls[u][1], s & 31);
+          if (s < k) {
+            den[u] += wgt * lv;
+            acc[u] += wgt * os[u][i];
+          }
         }
       }
     }
-    const bool live = den > 0.f;
-    const long long orow = caller_row<MQ>(P, b, kvh, hl);
-    store_value(P.a.out, P.a.out_dtype, orow * d + ch, live ? acc / den * P.a.o_scale : 0.f);
-    if (writes_lse && P.a.lse != nullptr)
-      P.a.lse[orow] = live ? (M + log2f(den)) * LN2 : -INFINITY;
+#pragma unroll
+    for (int u = 0; u < HU; ++u) {
+      if (!on[u]) continue;
+      const bool live = den[u] > 0.f;
+      const long long orow = caller_row<MQ>(P, b, kvh, hl[u]);
+      store_value(P.a.out, P.a.out_dtype, orow * d + ch,
+                  live ? acc[u] / den[u] * P.a.o_scale : 0.f);
+      if (writes_lse && P.a.lse != nullptr)
+        P.a.lse[orow] = live ? (M[u] + log2f(den[u])) * LN2 : -INFINITY;
+    }
   }
 }
 

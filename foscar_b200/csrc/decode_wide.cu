@@ -40,6 +40,17 @@
 namespace fq {
 namespace wide {
 
+#ifdef FQ_WAIT_PROFILE
+// Diagnostic builds only: (start, end, SM id) of every CTA, times on the global timer,
+// [gridDim.x][3].
+__device__ unsigned long long* g_cta_times = nullptr;
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#endif
+
 constexpr int D = 256;
 constexpr int SPT = 2;                     // ring stages (pages) per tile
 // worker groups: three; two when K is quantized per channel (the groups' own query stages and
@@ -186,8 +197,8 @@ __device__ __noinline__ void count_in_piece(const DecodeParams& P, int gp, int w
   const int k = group_info[wg];
   if (k > 0) {
     const int ch = channel_of_expanded_pos<BITS>(t);
-    merge_unit_partials<MQ>(P, D, gp, ch, t == 0, k, b, kvh, ht, 0, 1);
-    merge_unit_partials<MQ>(P, D, gp, 128 + ch, false, k, b, kvh, ht, 0, 1);
+    merge_unit_partials<MQ, 2>(P, D, gp, ch, t == 0, k, b, kvh, ht, 0, 1);
+    merge_unit_partials<MQ, 2>(P, D, gp, 128 + ch, false, k, b, kvh, ht, 0, 1);
   }
 }
 
@@ -750,6 +761,14 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SP::FLAG_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SP::FLAG_OFF + 24);
   int* status = P.a.status;
+#ifdef FQ_WAIT_PROFILE
+  if (threadIdx.x == 0 && g_cta_times != nullptr) {
+    uint32_t smid;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    g_cta_times[3 * blockIdx.x] = global_ns();
+    g_cta_times[3 * blockIdx.x + 2] = smid;
+  }
+#endif
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -1022,6 +1041,9 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
 
   tc_fence_before();
   __syncthreads();
+#ifdef FQ_WAIT_PROFILE
+  if (threadIdx.x == 0 && g_cta_times != nullptr) g_cta_times[3 * blockIdx.x + 1] = global_ns();
+#endif
   if (warp == W_S) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
@@ -1029,6 +1051,12 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
 }
 
 }  // namespace wide
+
+#ifdef FQ_WAIT_PROFILE
+extern "C" int fq_debug_set_cta_times(void* buffer) {
+  return static_cast<int>(cudaMemcpyToSymbol(fq::wide::g_cta_times, &buffer, sizeof(buffer)));
+}
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // host side
