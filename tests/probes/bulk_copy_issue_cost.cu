@@ -4,7 +4,8 @@
 // the two candidates for the decode kernel's ring. One CTA per SM fills 128 KB of shared memory
 // once (no stage is reused, so the issue loop never waits), then waits, bounded, for the bytes.
 // Prints, per chunk size and method, the cycles the issuing warp spent per chunk and the rate of
-// the whole grid. Every address and size is a multiple of 16 bytes; plain copies into this CTA's own shared memory, one GPU.
+// the whole grid. Every address and size is a multiple of 16 bytes; plain copies into this
+// CTA's own shared memory, one GPU.
 #include <cstdio>
 #include <cstdlib>
 

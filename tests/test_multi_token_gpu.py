@@ -86,3 +86,50 @@ def test_minimum_length_and_single_request():
     """seq_len == q_len: token 0 sees one position."""
     _case(2, 128, 32, 8, 4, [4], seed=2)
     _case(4, 128, 32, 8, 2, [2, 3], seed=3)
+
+
+def test_graph_mode_with_two_query_tokens():
+    """Graph mode: plan once with q_len_per_req=2, capture, then update lengths and replay."""
+    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout, graph_workspace_bytes
+    bits, hq, hkv, d, L = 2, 32, 8, 128, 2
+    batch, max_len = 3, 3000
+    max_pages = -(-max_len // 64)
+    layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device="cuda")
+    cache = layout.allocate(batch * max_pages)
+    table = torch.arange(batch * max_pages, dtype=torch.int32, device="cuda").view(batch, max_pages)
+    seq_dev = torch.full((batch,), L, dtype=torch.int32, device="cuda")
+    slots = np.concatenate([np.arange(max_len) + b * max_pages * 64 for b in range(batch)])
+    k, v = make_kv(len(slots), hkv, d, seed=4)
+    cache.append(k, v, torch.from_numpy(slots).cuda())
+    pools = cpu_twin(cache, k, v, slots)
+    # workspace for the columns of two query tokens: sized as for twice the heads
+    ws = torch.empty(graph_workspace_bytes(batch, hq * L, layout, max_kv_len=max_len),
+                     dtype=torch.uint8, device="cuda")
+    w = PagedDecodeWrapper(ws, use_cuda_graph=True)
+    w.plan(page_table=table, seq_lens=seq_dev, num_qo_heads=hq, layout=layout, max_kv_len=max_len,
+           q_len_per_req=L)
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(batch, L, hq, d, generator=g).to(torch.float8_e4m3fn).cuda()
+    out = torch.empty(batch, L, hq, d, dtype=torch.bfloat16, device="cuda")
+    w.run(q, cache, out=out)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        w.run(q, cache, out=out)
+    indptr = np.arange(batch + 1, dtype=np.int32) * max_pages
+    indices = np.arange(batch * max_pages, dtype=np.int32)
+    for lengths in ([2, 129, 3000], [2999, 257, 64]):
+        seq_dev.copy_(torch.tensor(lengths, dtype=torch.int32))
+        w.update(lengths)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert w.last_status() == 0
+        kv = ref_dequantize(pools, indptr, indices, lengths, rounded=False)
+        for r, n in enumerate(lengths):
+            for l in range(L):
+                sees = n - (L - 1 - l)
+                want, _ = ref_attention(q[r, l].cpu().float(), kv[r][0][:sees], kv[r][1][:sees],
+                                        d ** -0.5)
+                err = (out[r, l].float().cpu() - want).abs()
+                tol = 2e-3 + want.abs().mean().item() * 2.0 ** -9
+                assert err.max().item() <= MAX_ABS and err.mean().item() <= tol, (lengths, r, l)
