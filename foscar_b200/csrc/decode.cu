@@ -769,6 +769,24 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
     for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
       const WorkItem w = item_at(P, item_cache, item_more, SP::ITEM_SLOTS, ik, wi);
       if (w.t1 <= w.t0) continue;
+      constexpr int PPT = SP::PPT;   // pages per tile
+      const int npages = (w.len + PAGE - 1) / PAGE;
+      const int pend = min(PPT * w.t1, npages);
+      auto fetch = [&](int pg0) {
+        const int pg = pg0 + lane;
+        int id = -1;
+        if (pg < pend) {
+          const long long e = static_cast<long long>(w.table_off) + pg;
+          if (e >= 0 && e < P.a.table_len) id = __ldg(P.a.page_table + e);
+          if (id < 0 || id >= P.p.num_pages) {
+            id = -1;
+            if (status) atomicOr(status, FQ_STATUS_BAD_PAGE);
+          }
+        }
+        return id;
+      };
+      // (requested before the query rows are staged: the two global round trips overlap)
+      int cur = fetch(PPT * w.t0);
       if (pi == 0) {
         const int qb = qi & 1;
         mbar_wait(bars.q_empty(qb), ((qi >> 1) & 1) ^ 1, abort_flag, status, 7, wprof);
@@ -838,23 +856,6 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         if (lane == 0) mbar_arrive(bars.q_full(qb));
       }
       ++qi;
-      constexpr int PPT = SP::PPT;   // pages per tile
-      const int npages = (w.len + PAGE - 1) / PAGE;
-      const int pend = min(PPT * w.t1, npages);
-      auto fetch = [&](int pg0) {
-        const int pg = pg0 + lane;
-        int id = -1;
-        if (pg < pend) {
-          const long long e = static_cast<long long>(w.table_off) + pg;
-          if (e >= 0 && e < P.a.table_len) id = __ldg(P.a.page_table + e);
-          if (id < 0 || id >= P.p.num_pages) {
-            id = -1;
-            if (status) atomicOr(status, FQ_STATUS_BAD_PAGE);
-          }
-        }
-        return id;
-      };
-      int cur = fetch(PPT * w.t0);
       for (int base = PPT * w.t0; base < PPT * w.t1; base += 32) {
         const int nxt = base + 32 < PPT * w.t1 ? fetch(base + 32) : -1;
         for (int k = 0; k < 32 / PPT && base + PPT * k < PPT * w.t1; ++k, ++it) {

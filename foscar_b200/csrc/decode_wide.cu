@@ -42,13 +42,38 @@ namespace wide {
 
 #ifdef FQ_WAIT_PROFILE
 // Diagnostic builds only: (start, end, SM id) of every CTA, times on the global timer,
-// [gridDim.x][3].
+// [gridDim.x][3]; and the cycles lane 0 of each role spent in each of its waits,
+// [gridDim.x][6 roles][16 sites].
 __device__ unsigned long long* g_cta_times = nullptr;
+__device__ long long* g_wide_waits = nullptr;
+#define WT_BEGIN() long long wt_[16] = {}
+#define WT(site, ...)                          \
+  do {                                         \
+    const long long a_ = clock64();            \
+    __VA_ARGS__;                               \
+    wt_[site] += clock64() - a_;               \
+  } while (0)
+#define WT_MARK(var) const long long var = clock64()
+#define WT_SINCE(site, var) wt_[site] += clock64() - (var)
+#define WT_FLUSH(role)                                                           \
+  do {                                                                           \
+    if (g_wide_waits != nullptr)                                                 \
+      for (int i_ = 0; i_ < 16; ++i_)                                            \
+        g_wide_waits[(blockIdx.x * 6 + (role)) * 16 + i_] = wt_[i_];             \
+  } while (0)
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+#endif
+
+#ifndef FQ_WAIT_PROFILE
+#define WT_BEGIN() ((void)0)
+#define WT(site, ...) do { __VA_ARGS__; } while (0)
+#define WT_MARK(var) ((void)0)
+#define WT_SINCE(site, var) ((void)0)
+#define WT_FLUSH(role) ((void)0)
 #endif
 
 constexpr int D = 256;
@@ -267,6 +292,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   const float p2lp = exp2f(static_cast<float>(lp));
   const float o_mul = exp2f(static_cast<float>(9 - lp));
 
+  WT_BEGIN();
+  WT_MARK(role_t0);
   bool piece_pending = false;   // a split piece written but not yet counted in
   int piece_b = 0, piece_kvh = 0, piece_ht = 0;
 
@@ -310,7 +337,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
     // where a phase-parity wait would take an older phase for the one it needs.
     __syncwarp();
     if (lane == 0 && mytiles > 0) {
-      count_wait(q_staged, q_index + 1, abort_flag, status);
+      WT(0, count_wait(q_staged, q_index + 1, abort_flag, status));
       __threadfence_block();
     }
     __syncwarp();
@@ -337,8 +364,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       RingPos rp1 = rp;
       rp1.next(NS);
       const uint32_t stage = ring0 + (su ? rp1.s : rp.s) * SP::STAGE;
-      mbar_wait(bars.ring_full(rp.s), rp.ph, abort_flag, status);
-      mbar_wait(bars.ring_full(rp1.s), rp1.ph, abort_flag, status);
+      WT(1, mbar_wait(bars.ring_full(rp.s), rp.ph, abort_flag, status);
+         mbar_wait(bars.ring_full(rp1.s), rp1.ph, abort_flag, status));
       // ---- K per channel: the page's (s_d, z_d) fold into the query side. Per page and head
       //   score = 2^m * (sum_d Q'_d c_d) + sum_d z_d q_d,   Q'_d = s_d q_d 2^-m as three E4M3 planes
       // p0 + p1/16 + p2/256 (the reference's Q' and bias, src/foscar/_sm100/int_fold_asm.py:21-63,
@@ -439,7 +466,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       if (lane == 0) mbar_arrive(bars.k_ready(wg));
       // the group's previous PV MMA must be complete before its V stage and P rows are rewritten
       if (pending) {
-        mbar_wait(bars.pv_done(wg), (n - 1) & 1, abort_flag, status);
+        WT(2, mbar_wait(bars.pv_done(wg), (n - 1) & 1, abort_flag, status));
         tc_fence_after();
       }
       // ---- V row -> the group's shared-memory stage, one 128-byte-swizzled plane per channel half
@@ -496,7 +523,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       // tile of an item has no reference yet: it takes the scores themselves and always goes
       // through the exact maximum. Otherwise the reference may lag by MAX_LAG, and only a tile
       // that exceeds it takes the exact column maximum and rescales l, c and O.
-      mbar_wait(bars.s_done(wg), n & 1, abort_flag, status);
+      WT(3, mbar_wait(bars.s_done(wg), n & 1, abort_flag, status));
       float d[GP];
       const bool fresh = !pending;
       {
@@ -610,7 +637,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       if (lane == 0) {
         // The group's first PV MMA of the item starts its accumulator afresh: the item two
         // before this one, which used the same accumulator and state slot, must be finished.
-        if (!pending) count_wait(finished + par, ik >> 1, abort_flag, status);
+        if (!pending) WT(4, count_wait(finished + par, ik >> 1, abort_flag, status));
         mbar_arrive(bars.pv_ready(wg));
       }
       pending = true;
@@ -623,7 +650,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 
     // ---- the group's part of the item is done
     if (pending) {
-      mbar_wait(bars.pv_done(wg), (n - 1) & 1, abort_flag, status);
+      WT(5, mbar_wait(bars.pv_done(wg), (n - 1) & 1, abort_flag, status));
       tc_fence_after();
     }
     if (mytiles == 0) {   // an item without tiles: its state slot must be free as well
@@ -660,46 +687,75 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       piece_pending = false;
     }
     if (t == 0) {
-      count_wait(done_warps + par, 4 * (parts - 1), abort_flag, status);
+      WT(7, count_wait(done_warps + par, 4 * (parts - 1), abort_flag, status));
       __threadfence_block();
     }
+    WT_MARK(merge_t0);
     named_barrier(1 + wg, 128);
     tc_fence_after();
+    // The groups' states meet in two steps. One thread per head takes the groups' references and
+    // sums (in the fixed order of the groups' last tiles), fixes the item's reference and each
+    // group's weight 2^(m_g - M) and leaves them in this group's own state slot; after a group
+    // barrier every thread weighs the groups' accumulators of its two channels with them. (With
+    // every thread redoing the per-head part, the four warps of the finishing group spent
+    // 4.7 us per item here.)
+    const int g_first = (item_t0 + max(0, nt - G)) % G;
+    float* const fin = meta;   // this group's slot: [head][8] = weights of up to G groups, L, C, M
+    if (t < GP) {
+      const int h = t;
+      float mg[G], lg[G], cg[G];
+      float top = -INFINITY;
+#pragma unroll
+      for (int p = 0; p < G; ++p) {
+        int g = g_first + p;
+        if (g >= G) g -= G;
+        if (nt == 0) g = wg;
+        const float* gmeta =
+            reinterpret_cast<const float*>(smem + SP::STATE_OFF) + (par * G + g) * SP::META_WORDS;
+        const bool have = p < parts;
+        mg[p] = have ? gmeta[h] : -INFINITY;
+        lg[p] = have ? (gmeta[8 + h] + gmeta[24 + h]) + (gmeta[40 + h] + gmeta[56 + h]) : 0.f;
+        cg[p] = have ? (gmeta[16 + h] + gmeta[32 + h]) + (gmeta[48 + h] + gmeta[64 + h]) : 0.f;
+        top = fmaxf(top, mg[p]);
+      }
+      __syncwarp((1u << GP) - 1u);   // every head's thread has read this group's own slot
+      float ls = 0.f, cs = 0.f;
+#pragma unroll
+      for (int p = 0; p < G; ++p) {
+        const float wgt = mg[p] == -INFINITY ? 0.f : exp2f(mg[p] - top);
+        ls = fmaf(wgt, lg[p], ls);
+        cs = fmaf(wgt, cg[p], cs);
+        fin[8 * h + p] = wgt;
+      }
+      fin[8 * h + 4] = ls;
+      fin[8 * h + 5] = cs;
+      fin[8 * h + 6] = top;
+    }
+    named_barrier(1 + wg, 128);
     float M[GP], L[GP], C[GP], O0[GP], O1[GP];   // O0 / O1: channels t and 128 + t
 #pragma unroll
-    for (int h = 0; h < GP; ++h) { M[h] = -INFINITY; L[h] = C[h] = O0[h] = O1[h] = 0.f; }
-    const int g_first = (item_t0 + max(0, nt - G)) % G;
+    for (int h = 0; h < GP; ++h) {
+      O0[h] = O1[h] = 0.f;
+      L[h] = fin[8 * h + 4];
+      C[h] = fin[8 * h + 5];
+      M[h] = fin[8 * h + 6];
+    }
 #pragma unroll 1
     for (int p = 0; p < parts; ++p) {
       int g = g_first + p;
       if (g >= G) g -= G;
-      if (nt == 0) g = wg;
-      const float* gmeta =
-          reinterpret_cast<const float*>(smem + SP::STATE_OFF) + (par * G + g) * SP::META_WORDS;
+      if (nt == 0) break;   // an empty request: no accumulator was written
       uint32_t r0[16], r1[16];
-      if (nt > 0) {
-        tmem_ld16p(o_lane + (g * 2 + par) * SP::O_COLS, r0);
-        tmem_ld16p(o_lane + (g * 2 + par) * SP::O_COLS + 16, r1);
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) r0[i] = r1[i] = 0u;
-      }
+      tmem_ld16p(o_lane + (g * 2 + par) * SP::O_COLS, r0);
+      tmem_ld16p(o_lane + (g * 2 + par) * SP::O_COLS + 16, r1);
+      tmem_ld_wait();
 #pragma unroll
       for (int h = 0; h < GP; ++h) {
-        const float m1 = gmeta[h];
-        const float l1 = (gmeta[8 + h] + gmeta[24 + h]) + (gmeta[40 + h] + gmeta[56 + h]);
-        const float c1 = (gmeta[16 + h] + gmeta[32 + h]) + (gmeta[48 + h] + gmeta[64 + h]);
+        const float wgt = fin[8 * h + p];
         const float a0 = fmaf(__uint_as_float(r0[8 + h]), 0.0625f, __uint_as_float(r0[h]));
         const float a1 = fmaf(__uint_as_float(r1[8 + h]), 0.0625f, __uint_as_float(r1[h]));
-        const float Mn = fmaxf(M[h], m1);
-        const float f0 = M[h] == -INFINITY ? 0.f : exp2f(M[h] - Mn);
-        const float f1 = m1 == -INFINITY ? 0.f : exp2f(m1 - Mn);
-        L[h] = L[h] * f0 + l1 * f1;
-        C[h] = C[h] * f0 + c1 * f1;
-        O0[h] = O0[h] * f0 + a0 * f1;
-        O1[h] = O1[h] * f0 + a1 * f1;
-        M[h] = Mn;
+        O0[h] = fmaf(wgt, a0, O0[h]);
+        O1[h] = fmaf(wgt, a1, O1[h]);
       }
     }
     tc_fence_before();
@@ -741,9 +797,12 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         piece_b = w.b; piece_kvh = w.kvh; piece_ht = w.ht;
       }
     }
+    WT_SINCE(9, merge_t0);
   }
   if (piece_pending)
     count_in_piece<BITS, MQ>(P, GP, wg, t, piece_b, piece_kvh, piece_ht, group_info);
+  WT_SINCE(8, role_t0);
+  if (t == 0) WT_FLUSH(wg);
 }
 
 template <int BITS, int GP, bool KCH, bool MQ>
@@ -824,14 +883,34 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
     // producer also stages each item's query rows, in expansion order, as the S MMA's B operand.
     const int pi = warp == W_PRODUCER ? 0 : 1;
     const uint64_t stream_policy = l2_evict_first_policy();
+    WT_BEGIN();
+    WT_MARK(role_t0);
     int it = 0, qi = 0;
     RingPos rp;
     for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
       const WorkItem w = item_at(P, item_cache, item_more, SP::ITEM_SLOTS, ik, wi);
       if (w.t1 <= w.t0) continue;
+      const int npages = (w.len + PAGE - 1) / PAGE;
+      const int first_page = SPT * w.t0, end_page = SPT * w.t1;
+      const int pend = min(end_page, npages);
+      auto fetch = [&](int pg0) {
+        const int pg = pg0 + lane;
+        int id = -1;
+        if (pg < pend) {
+          const long long e = static_cast<long long>(w.table_off) + pg;
+          if (e >= 0 && e < P.a.table_len) id = __ldg(P.a.page_table + e);
+          if (id < 0 || id >= P.p.num_pages) {
+            id = -1;
+            if (status) atomicOr(status, FQ_STATUS_BAD_PAGE);
+          }
+        }
+        return id;
+      };
+      // (requested before the query rows are staged: the two global round trips overlap)
+      int cur = fetch(first_page);
       if (pi == 0) {
         const int qb = qi & 1;
-        mbar_wait(bars.q_empty(qb), ((qi >> 1) & 1) ^ 1, abort_flag, status);
+        WT(10, mbar_wait(bars.q_empty(qb), ((qi >> 1) & 1) ^ 1, abort_flag, status));
         // 16 rows of sixteen 16-byte chunks: a row's chunks sit in 16 neighbouring lanes
         // (K per channel: the 8 head rows only, unswizzled, for the workers to build the
         // operand from; the per-head constants are then the score scale and max |q|)
@@ -904,23 +983,6 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
         }
       }
       ++qi;
-      const int npages = (w.len + PAGE - 1) / PAGE;
-      const int first_page = SPT * w.t0, end_page = SPT * w.t1;
-      const int pend = min(end_page, npages);
-      auto fetch = [&](int pg0) {
-        const int pg = pg0 + lane;
-        int id = -1;
-        if (pg < pend) {
-          const long long e = static_cast<long long>(w.table_off) + pg;
-          if (e >= 0 && e < P.a.table_len) id = __ldg(P.a.page_table + e);
-          if (id < 0 || id >= P.p.num_pages) {
-            id = -1;
-            if (status) atomicOr(status, FQ_STATUS_BAD_PAGE);
-          }
-        }
-        return id;
-      };
-      int cur = fetch(first_page);
       for (int base = first_page; base < end_page; base += 32) {
         const int nxt = base + 32 < end_page ? fetch(base + 32) : -1;
         for (int k = 0; k < 32 && base + k < end_page; ++k, ++it) {
@@ -929,7 +991,7 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
           rp.next(NS);
           if ((it & 1) != pi) continue;
           const int id = __shfl_sync(0xFFFFFFFFu, cur, k);
-          mbar_wait(bars.ring_empty(s), eph, abort_flag, status);
+          WT(11, mbar_wait(bars.ring_empty(s), eph, abort_flag, status));
           const uint32_t full = bars.ring_full(s);
           if (id >= 0) {
             const long long blk = static_cast<long long>(id) * P.p.num_kv_heads + w.kvh;
@@ -959,6 +1021,8 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
         cur = nxt;
       }
     }
+    WT_SINCE(8, role_t0);
+    if (lane == 0 && pi == 0) WT_FLUSH(3);
     // drain: every copy this warp issued has landed once its stage reports full
     for (int back = 0; back < NS && back < it; ++back) {
       if (--rp.s < 0) { rp.s = NS - 1; rp.ph ^= 1u; }
@@ -972,14 +1036,16 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
       constexpr int ATOM16 = (KCH ? SP::QP_ATOM : SP::Q_ATOM) >> 4;
       int qi = 0, g = 0;
       uint32_t gph = 0;
+      WT_BEGIN();
+      WT_MARK(role_t0);
       for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
         const WorkItem w = item_at(P, item_cache, item_more, SP::ITEM_SLOTS, ik, wi);
         if (w.t1 <= w.t0) continue;
         const int qb = qi & 1;
-        mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status);
+        WT(13, mbar_wait(bars.q_full(qb), (qi >> 1) & 1, abort_flag, status));
         const uint32_t q_item = smem_desc_lo(smem0 + SP::Q_OFF + qb * SP::Q_BYTES, 16);
         for (int t = w.t0; t < w.t1; ++t) {
-          mbar_wait(bars.k_ready(g), gph, abort_flag, status);
+          WT(14, mbar_wait(bars.k_ready(g), gph, abort_flag, status));
           tc_fence_after();
           const uint32_t sd = tmem + SP::T_S + g * SP::S_COLS;
           const uint32_t ka = tmem + SP::T_KOP + g * SP::KOP_COLS;
@@ -999,6 +1065,8 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
         }
         ++qi;
       }
+      WT_SINCE(8, role_t0);
+      WT_FLUSH(4);
     }
     __syncwarp();
   } else if (warp == W_PV) {
@@ -1012,11 +1080,13 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
       const uint32_t p_lo0 = smem_desc_lo(smem0 + SP::P_OFF, 128);
       int g = 0;
       uint32_t gph = 0;
+      WT_BEGIN();
+      WT_MARK(role_t0);
       for (int wi = items.begin, ik = 0; wi < items.end; wi += items.step, ++ik) {
         const WorkItem w = item_at(P, item_cache, item_more, SP::ITEM_SLOTS, ik, wi);
         for (int t = w.t0; t < w.t1; ++t) {
           const uint32_t acc = t - w.t0 >= G ? 1u : 0u;
-          mbar_wait(bars.pv_ready(g), gph, abort_flag, status);
+          WT(15, mbar_wait(bars.pv_ready(g), gph, abort_flag, status));
           tc_fence_after();
           const uint32_t p_lo = p_lo0 + g * (SP::P_BYTES >> 4);
           const uint32_t od = tmem + SP::T_O + (g * 2 + (ik & 1)) * SP::O_COLS;
@@ -1033,6 +1103,8 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
           if (++g == G) { g = 0; gph ^= 1u; }
         }
       }
+      WT_SINCE(8, role_t0);
+      WT_FLUSH(5);
     }
     __syncwarp();
   } else {
@@ -1055,6 +1127,9 @@ __global__ void __launch_bounds__(threads_of(KCH), 1) decode_wide_kernel(const D
 #ifdef FQ_WAIT_PROFILE
 extern "C" int fq_debug_set_cta_times(void* buffer) {
   return static_cast<int>(cudaMemcpyToSymbol(fq::wide::g_cta_times, &buffer, sizeof(buffer)));
+}
+extern "C" int fq_debug_set_wide_waits(void* buffer) {
+  return static_cast<int>(cudaMemcpyToSymbol(fq::wide::g_wide_waits, &buffer, sizeof(buffer)));
 }
 #endif
 
