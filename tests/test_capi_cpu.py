@@ -167,3 +167,67 @@ def test_worklist_tiles_hold_256_tokens_at_head_dim_64():
     assert _lib.tile_tokens(4, 128) == 128
     assert _lib.tile_tokens(2, 128) in (128, 256)     # two tokens per lane in the INT2 build
     assert _lib.piece_overhead(2, 128) > 0
+
+
+def _fake_pools(**over):
+    """Pool descriptor with made-up, 16-byte aligned addresses: enough for the argument checks,
+    which run before any launch (nothing is dereferenced on the host)."""
+    p = _lib.Pools(bits=2, head_dim=128, num_kv_heads=8, k_groups=1, scale_bf16=0, num_pages=4,
+                   k_channel_group=0, k_codes=0x10000, v_codes=0x20000, scales=0x30000,
+                   v_page_max=0x40000, v_max_hist=0x50000)
+    for name, value in over.items():
+        setattr(p, name, value)
+    return p
+
+
+def test_entry_points_refuse_misaligned_or_senseless_arguments_before_any_launch():
+    import ctypes
+    lib = _lib.load()
+    ok, bad = 0x100000, 0x100002            # made-up device addresses
+    p = _fake_pools()
+    # writer: 16-byte rows and strides
+    assert lib.fq_append(ctypes.byref(p), bad, ok, 1024, 1024, ok, 4, -1, -1, None, None) \
+        == _lib.ERR_BAD_ARG
+    assert lib.fq_append(ctypes.byref(p), ok, ok, 1020, 1024, ok, 4, -1, -1, None, None) \
+        == _lib.ERR_BAD_ARG
+    assert lib.fq_append(ctypes.byref(p), ok, ok, 1024, 1024, ok, 4, 128, -1, None, None) \
+        == _lib.ERR_BAD_ARG                                  # clip index outside the row
+    assert lib.fq_append_quantized(ctypes.byref(p), bad, ok, ok, ok, ok, ok, ok, 4, None, None) \
+        == _lib.ERR_BAD_ARG
+    pz = _fake_pools(num_kv_heads=0)
+    assert lib.fq_append(ctypes.byref(pz), ok, ok, 1024, 1024, ok, 4, -1, -1, None, None) \
+        == _lib.ERR_BAD_ARG
+    p96 = _fake_pools(head_dim=96)
+    assert lib.fq_append(ctypes.byref(p96), ok, ok, 1024, 1024, ok, 4, -1, -1, None, None) \
+        == _lib.ERR_UNSUPPORTED
+    # read-back: 16-byte destinations, row strides in multiples of eight elements
+    assert lib.fq_dequantize(ctypes.byref(p), bad, ok, 1024, 1024, 64, ok, ok, 1, ok, ok, 0, 1,
+                             None, None) == _lib.ERR_BAD_ARG
+    assert lib.fq_dequantize(ctypes.byref(p), ok, ok, 1028, 1024, 64, ok, ok, 1, ok, ok, 0, 1,
+                             None, None) == _lib.ERR_BAD_ARG
+    # decode
+    def args(**over):
+        a = _lib.DecodeArgs()
+        a.batch, a.num_qo_heads, a.kv_splits, a.max_splits = 2, 32, 1, 1
+        a.seq_lens = a.page_table = a.table_offsets = ok
+        a.q, a.out, a.status = ok, ok, ok
+        for name, value in over.items():
+            setattr(a, name, value)
+        return a
+    def decode(pools, a):
+        return lib.fq_decode(ctypes.byref(pools), ctypes.byref(a), None)
+    assert decode(p, args(q=bad)) == _lib.ERR_BAD_ARG
+    assert decode(p, args(worklist=bad, num_work=4)) == _lib.ERR_BAD_ARG
+    assert decode(pz, args()) == _lib.ERR_BAD_ARG
+    assert decode(p, args(num_qo_heads=30)) == _lib.ERR_BAD_ARG
+    assert decode(p96, args()) == _lib.ERR_UNSUPPORTED
+    assert decode(p, args(kv_splits=2, max_splits=1, o_partial=ok, l_partial=ok, m_partial=ok)) \
+        == _lib.ERR_BAD_ARG
+    # several query tokens: at most 64, and split units only with the in-kernel merge
+    assert decode(p, args(q_len=65)) == _lib.ERR_BAD_ARG
+    assert decode(p, args(q_len=2, kv_splits=2, max_splits=2, o_partial=ok, l_partial=ok,
+                          m_partial=ok)) == _lib.ERR_UNSUPPORTED
+    assert lib.fq_decode_split_static(ctypes.byref(p), ctypes.byref(args(q_len=2)), None) \
+        == _lib.ERR_UNSUPPORTED
+    grouped = _fake_pools(k_groups=2, scale_bf16=1)
+    assert decode(grouped, args(q_len=2)) == _lib.ERR_UNSUPPORTED
