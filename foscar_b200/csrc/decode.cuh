@@ -329,6 +329,22 @@ static __device__ __noinline__ void merge_unit_partials(const DecodeParams& P, i
         ms[u][j] = have ? __ldcg(P.a.m_partial + s * rows + row[u]) : -INFINITY;
         ls[u][j] = have ? __ldcg(P.a.l_partial + s * rows + row[u]) : 0.f;
       }
+    // With several heads at a time (the head_dim 256 kernel) the first eight slots' o values are
+    // requested together with the (m, l) pairs: a unit of up to eight pieces then costs one
+    // memory round trip, not two in sequence. In the head_dim 64/128 kernel the same order
+    // measured 1 to 3 % slower on its many-item workload (register allocation of the kernel
+    // around this out-of-line function), so there the fetch stays inside the loop.
+    constexpr bool EARLY = HU > 1;
+    float os[HU][8];
+    auto fetch = [&](int s0) {
+#pragma unroll
+      for (int u = 0; u < HU; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          os[u][i] = on[u] && s0 + i < k
+                         ? __ldcg(P.a.o_partial + ((s0 + i) * rows + row[u]) * d + ch) : 0.f;
+    };
+    if constexpr (EARLY) fetch(0);
     float M[HU], wl[HU][2], den[HU], acc[HU];
 #pragma unroll
     for (int u = 0; u < HU; ++u) {
@@ -343,13 +359,7 @@ static __device__ __noinline__ void merge_unit_partials(const DecodeParams& P, i
     }
 #pragma unroll 1
     for (int s0 = 0; s0 < k; s0 += 8) {
-      float os[HU][8];
-#pragma unroll
-      for (int u = 0; u < HU; ++u)
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          os[u][i] = on[u] && s0 + i < k
-                         ? __ldcg(P.a.o_partial + ((s0 + i) * rows + row[u]) * d + ch) : 0.f;
+      if (!EARLY || s0 > 0) fetch(s0);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int s = s0 + i;                     // (warp-uniform)
