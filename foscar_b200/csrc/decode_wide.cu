@@ -412,7 +412,10 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         named_barrier(1 + wg, 128);
         const float* st0 = reinterpret_cast<const float*>(smem + SP::STATS_OFF) + (wg * 2 + su) * 2 * 12;
         const float smax = fmaxf(st0[0], st0[12]);
-        uint32_t pl[3][GP];   // this thread's four positions of the three planes of each head
+        // rows 24 * page + 8 * plane + h of the group's operand stage; atom = channel half
+        const uint32_t qp = smem0 + SP::Q_OFF + wg * SP::QP_BYTES + (pos0 >> 7) * SP::QP_ATOM +
+                            (pos0 & 15);
+        const int chunk = (pos0 & 127) >> 4;
 #pragma unroll
         for (int h = 0; h < GP; ++h) {
           // m = floor(log2(smax * qamax)) - 7, so that |s_d q_d| 2^-m < 256
@@ -425,35 +428,30 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           float y[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) y[i] = sd[i] * qf[h][i] * dn;
-          // y = p0 + p1 / 16 + p2 / 256, each plane the E4M3 rounding of what is left
-#pragma unroll
+          // y = p0 + p1 / 16 + p2 / 256, each plane the E4M3 rounding of what is left; this
+          // thread's four positions of a plane go straight to the stage (the plane loop is not
+          // unrolled: code size, see the K rows below)
+#pragma unroll 1
           for (int k = 0; k < 3; ++k) {
             const uint32_t a = f32x2_to_e4m3x2(y[0], y[1]), b = f32x2_to_e4m3x2(y[2], y[3]);
-            pl[k][h] = a | (b << 16);
+            const int r = 24 * su + 8 * k + h;
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(qp + r * 128 + ((chunk ^ (r & 7)) << 4)),
+                         "r"(a | (b << 16)) : "memory");
             const float2 fa = e4m3x2_to_f32x2(a), fb = e4m3x2_to_f32x2(b);
             y[0] = (y[0] - fa.x) * 16.f; y[1] = (y[1] - fa.y) * 16.f;
             y[2] = (y[2] - fb.x) * 16.f; y[3] = (y[3] - fb.y) * 16.f;
           }
         }
-        // rows 24 * page + 8 * plane + h; atom = channel half
-        const uint32_t qp = smem0 + SP::Q_OFF + wg * SP::QP_BYTES + (pos0 >> 7) * SP::QP_ATOM +
-                            (pos0 & 15);
-        const int chunk = (pos0 & 127) >> 4;
-#pragma unroll
-        for (int k = 0; k < 3; ++k)
-#pragma unroll
-          for (int h = 0; h < GP; ++h) {
-            const int r = 24 * su + 8 * k + h;
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(qp + r * 128 + ((chunk ^ (r & 7)) << 4)),
-                         "r"(pl[k][h]) : "memory");
-          }
         fence_proxy_async();
       }
       // ---- K row -> tensor memory, two 128-byte operand rows (the S MMA's A operand). The
       // columns are free: this group read the S of its previous tile, so that tile's MMA, their
       // last reader, is complete.
       tc_fence_after();
-#pragma unroll
+      // (the two halves of a row are NOT unrolled, here and for V below: the tile loop's code is
+      // large for the instruction cache with three or four warps a scheduler, and rolling these
+      // two loops took 4 to 5 % off the launch)
+#pragma unroll 1
       for (int r = 0; r < 2; ++r) {
         uint32_t wk[128 * BITS / 32], op[32];
         load_half_row<BITS>(stage + SP::K_OFF + srow * SP::RB, r, SP::row_swizzle(srow), wk);
@@ -470,7 +468,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         tc_fence_after();
       }
       // ---- V row -> the group's shared-memory stage, one 128-byte-swizzled plane per channel half
-#pragma unroll
+#pragma unroll 1
       for (int r = 0; r < 2; ++r) {
         uint32_t wv[128 * BITS / 32], op[32];
         load_half_row<BITS>(stage + SP::V_OFF + srow * SP::RB, r, SP::row_swizzle(srow), wv);
