@@ -167,21 +167,22 @@ struct RingPos {
   }
 };
 
-// Half a token row (16 * BITS bytes... D/2 channels) as packed words; chunk v of the row sits at
-// chunk v ^ swz.
+// A quarter of a token row (64 channels) as packed words; chunk v of the row sits at chunk
+// v ^ swz. (The row is taken a quarter at a time in loops that are not unrolled: see the tile
+// loop.)
 template <int BITS>
-__device__ inline void load_half_row(uint32_t row_addr, int half, int swz, uint32_t* w) {
-  constexpr int HC = D * BITS / 8 / 32;   // 16-byte chunks per half row
+__device__ inline void load_quarter_row(uint32_t row_addr, int quarter, int swz, uint32_t* w) {
+  constexpr int QC = D * BITS / 8 / 64;   // 16-byte chunks per quarter row: 1 or 2
 #pragma unroll
-  for (int v = 0; v < HC; ++v)
+  for (int v = 0; v < QC; ++v)
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(w[4 * v]), "=r"(w[4 * v + 1]), "=r"(w[4 * v + 2]), "=r"(w[4 * v + 3])
-                 : "r"(row_addr + (((half * HC + v) ^ swz) << 4)));
+                 : "r"(row_addr + (((quarter * QC + v) ^ swz) << 4)));
 }
-// packed words of 128 channels -> 32 words of exact E4M3 operand bytes (expansion order)
+// packed words of 64 channels -> 16 words of exact E4M3 operand bytes (expansion order)
 template <int BITS>
-__device__ inline void expand_half(const uint32_t* w, uint32_t* out, bool v_operand) {
-  constexpr int NW = 128 * BITS / 32;
+__device__ inline void expand_quarter(const uint32_t* w, uint32_t* out, bool v_operand) {
+  constexpr int NW = 64 * BITS / 32;
   if (BITS == 2 && v_operand) {
     // odd output words keep their codes two bits up (4 * code, still exact); see decode.cuh
 #pragma unroll
@@ -448,15 +449,15 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       // columns are free: this group read the S of its previous tile, so that tile's MMA, their
       // last reader, is complete.
       tc_fence_after();
-      // (the two halves of a row are NOT unrolled, here and for V below: the tile loop's code is
-      // large for the instruction cache with three or four warps a scheduler, and rolling these
-      // two loops took 4 to 5 % off the launch)
+      // (a row goes a quarter at a time in a loop that is NOT unrolled, here and for V below: the
+      // tile loop's code is large for the instruction cache with three or four warps a scheduler;
+      // rolling these loops took 4 to 5 % off the launch)
 #pragma unroll 1
-      for (int r = 0; r < 2; ++r) {
-        uint32_t wk[128 * BITS / 32], op[32];
-        load_half_row<BITS>(stage + SP::K_OFF + srow * SP::RB, r, SP::row_swizzle(srow), wk);
-        expand_half<BITS>(wk, op, false);
-        tmem_st32(k_dst + 32 * r, op);
+      for (int qd = 0; qd < 4; ++qd) {
+        uint32_t wk[64 * BITS / 32], op[16];
+        load_quarter_row<BITS>(stage + SP::K_OFF + srow * SP::RB, qd, SP::row_swizzle(srow), wk);
+        expand_quarter<BITS>(wk, op, false);
+        tmem_st16(k_dst + 16 * qd, op);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -469,14 +470,15 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       }
       // ---- V row -> the group's shared-memory stage, one 128-byte-swizzled plane per channel half
 #pragma unroll 1
-      for (int r = 0; r < 2; ++r) {
-        uint32_t wv[128 * BITS / 32], op[32];
-        load_half_row<BITS>(stage + SP::V_OFF + srow * SP::RB, r, SP::row_swizzle(srow), wv);
-        expand_half<BITS>(wv, op, true);
+      for (int qd = 0; qd < 4; ++qd) {
+        uint32_t wv[64 * BITS / 32], op[16];
+        load_quarter_row<BITS>(stage + SP::V_OFF + srow * SP::RB, qd, SP::row_swizzle(srow), wv);
+        expand_quarter<BITS>(wv, op, true);
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
+        for (int cc = 0; cc < 4; ++cc) {
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
-                           (v_row ^ static_cast<uint32_t>(cc << 4)) + r * SP::VOP_PLANE),
+                           (v_row ^ static_cast<uint32_t>((4 * (qd & 1) + cc) << 4)) +
+                           (qd >> 1) * SP::VOP_PLANE),
                        "r"(op[4 * cc]), "r"(op[4 * cc + 1]), "r"(op[4 * cc + 2]),
                        "r"(op[4 * cc + 3])
                        : "memory");
