@@ -303,24 +303,52 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       // complete. With two tokens per lane (head_dim 64) the second token's 64 bytes follow the
       // first's in the lane's 128-byte row.
       {
-        uint32_t op[NT * D / 4];
-#pragma unroll
-        for (int u = 0; u < NT; ++u) {
-          uint32_t wk[D * BITS / 32], part[D / 4];
+        if constexpr (SP::PAIR) {
+          // Two tokens per lane: one token's row (64 channels, 16 operand words) at a time, in a
+          // loop that is NOT unrolled. This build's tile loop is the largest, and with the loop
+          // rolled its code stays in the instruction cache better (INT4 838 -> 819 us on C5;
+          // the same rolling at head_dim 128 cost 2 to 9 %).
+          constexpr int QC = 64 * BITS / 128;   // 16-byte chunks of a token's row: 1 or 2
+          tc_fence_after();
+#pragma unroll 1
+          for (int u = 0; u < 2; ++u) {
+            uint32_t wk[64 * BITS / 32], op[16];
 #if FQ_STUB_ROLES & 2
 #pragma unroll
-          for (int i = 0; i < D / 4; ++i) part[i] = n;
+            for (int i = 0; i < 16; ++i) op[i] = n;
 #else
-          load_row<BITS, D>(stage + SP::K_OFF + (u * TILE + t) * SP::RB, wk, SP::row_swizzle(t));
-          expand_words<BITS, D>(wk, part);
+            const uint32_t row = stage + SP::K_OFF + (u * TILE + t) * SP::RB;
+#pragma unroll
+            for (int v = 0; v < QC; ++v)
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(wk[4 * v]), "=r"(wk[4 * v + 1]), "=r"(wk[4 * v + 2]),
+                             "=r"(wk[4 * v + 3])
+                           : "r"(row + ((v ^ SP::row_swizzle(t)) << 4)));
+            expand_words<BITS, 64>(wk, op);
+#endif
+            tmem_st16(k_dst + 16 * u, op);
+          }
+          FQ_STAMP(3);
+        } else {
+          uint32_t op[NT * D / 4];
+#pragma unroll
+          for (int u = 0; u < NT; ++u) {
+            uint32_t wk[D * BITS / 32], part[D / 4];
+#if FQ_STUB_ROLES & 2
+#pragma unroll
+            for (int i = 0; i < D / 4; ++i) part[i] = n;
+#else
+            load_row<BITS, D>(stage + SP::K_OFF + (u * TILE + t) * SP::RB, wk, SP::row_swizzle(t));
+            expand_words<BITS, D>(wk, part);
 #endif
 #pragma unroll
-          for (int i = 0; i < D / 4; ++i) op[u * (D / 4) + i] = part[i];
-        }
-        FQ_STAMP(3);
-        tc_fence_after();
+            for (int i = 0; i < D / 4; ++i) op[u * (D / 4) + i] = part[i];
+          }
+          FQ_STAMP(3);
+          tc_fence_after();
 #pragma unroll
-        for (int v = 0; v < NT * D / 32; ++v) tmem_st8(k_dst + 8 * v, op + 8 * v);
+          for (int v = 0; v < NT * D / 32; ++v) tmem_st8(k_dst + 8 * v, op + 8 * v);
+        }
         tmem_st_wait();
         FQ_STAMP(5);
         tc_fence_before();
@@ -332,7 +360,35 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       FQ_STAMP(18);
       // ---- V row(s) -> the group's 128-byte-swizzled shared-memory stage (the PV MMA's A
       // operand), laid out like the K row
-      {
+      if constexpr (SP::PAIR) {
+        constexpr int QC = 64 * BITS / 128;
+#pragma unroll 1
+        for (int u = 0; u < 2; ++u) {
+          uint32_t wv[64 * BITS / 32], op[16];
+#if FQ_STUB_ROLES & 4
+#pragma unroll
+          for (int i = 0; i < 16; ++i) op[i] = n;
+#else
+          const uint32_t row = stage + SP::V_OFF + (u * TILE + t) * SP::RB;
+#pragma unroll
+          for (int v = 0; v < QC; ++v)
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(wv[4 * v]), "=r"(wv[4 * v + 1]), "=r"(wv[4 * v + 2]),
+                           "=r"(wv[4 * v + 3])
+                         : "r"(row + ((v ^ SP::row_swizzle(t)) << 4)));
+          expand_words_v<BITS, 64>(wv, op);
+#endif
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
+                             v_row + (((4 * u + cc) ^ (t & 7)) << 4)),
+                         "r"(op[4 * cc]), "r"(op[4 * cc + 1]), "r"(op[4 * cc + 2]),
+                         "r"(op[4 * cc + 3])
+                         : "memory");
+          }
+        }
+        FQ_STAMP(6);
+      } else {
         uint32_t op[NT * D / 4];
 #pragma unroll
         for (int u = 0; u < NT; ++u) {
