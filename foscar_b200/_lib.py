@@ -68,6 +68,8 @@ _PROTOTYPES = {
     "fq_append_quantized": (C.c_int, [C.POINTER(Pools), _P, _P, _P, _P, _P, _P, _P, _I32, _P, _P]),
     "fq_append_page_groups": (C.c_int, [C.POINTER(Pools), _P, _P, _I64, _I64, _P, _P, _I32, _P,
                                         _P]),
+    "fq_append_quantized_page_groups": (C.c_int, [C.POINTER(Pools), _P, _P, _P, _P, _P, _P, _P, _P,
+                                                  _I32, _P, _P]),
     "fq_dequantize": (C.c_int, [C.POINTER(Pools), _P, _P, _I64, _I64, _I64, _P, _P, _I32, _P, _P,
                                 _I32, _I32, _P, _P]),
     "fq_recount_vmax": (C.c_int, [C.POINTER(Pools), _P]),

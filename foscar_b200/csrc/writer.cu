@@ -329,8 +329,10 @@ __device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta
       const float s_hi = __fdiv_rn(2.0f * ENVELOPE, static_cast<float>(QMAX));
       const long long row = static_cast<long long>(token[r]) * hkv + head[r];
       const long long rec = half ? row : row * kg + hl / (16 / kg);
-      s = fminf(fmaxf(__ldg((half ? a.v_scale : a.k_scale) + rec), s_lo), s_hi);
-      z = fminf(fmaxf(__ldg((half ? a.v_zero : a.k_zero) + rec), -ENVELOPE), ENVELOPE);
+      // (K by whole pages: the K half has neither codes nor a record of its own here)
+      s = idle ? s_lo : fminf(fmaxf(__ldg((half ? a.v_scale : a.k_scale) + rec), s_lo), s_hi);
+      z = idle ? 0.f
+               : fminf(fmaxf(__ldg((half ? a.v_zero : a.k_zero) + rec), -ENVELOPE), ENVELOPE);
     }
 
     // code words shared by neighbouring lanes are assembled, then one lane per word stores
@@ -406,6 +408,40 @@ __device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta
   }
 }
 
+// A channel's record after the block's V ring: row 0 s_d, row 1 z_d, in the pool's record type.
+template <int D>
+__device__ inline void store_channel_record(const fq_pools& p, long long blk, int d, float s,
+                                            float z) {
+  char* block = static_cast<char*>(p.scales) + blk * scale_block_bytes(p);
+  if (!p.scale_bf16) {
+    float* rec = reinterpret_cast<float*>(block) + 2 * PAGE;
+    rec[d] = s;
+    rec[D + d] = z;
+  } else {
+    __nv_bfloat16* rec = reinterpret_cast<__nv_bfloat16*>(block) + 2 * PAGE;
+    rec[d] = __float2bfloat16_rn(s);
+    rec[D + d] = __float2bfloat16_rn(z);
+  }
+}
+
+// A page's first n token rows from one code byte per (token, channel) in shared memory: field f
+// of word w holds channel W*w + f/2 + (W/2)*(f%2) (src/foscar/_sm100/code_layout.py:24-43).
+template <int BITS, int D>
+__device__ inline void store_packed_rows(const uint8_t* codes, int n, uint8_t* page_rows) {
+  constexpr int W = 32 / BITS;             // codes per word
+  constexpr int WORDS = D * BITS / 32;     // words per token row
+  uint32_t* rows = reinterpret_cast<uint32_t*>(page_rows);
+  for (int i = threadIdx.x; i < n * WORDS; i += blockDim.x) {
+    const int j = i / WORDS, w = i % WORDS;
+    const uint8_t* src = codes + j * D + W * w;
+    uint32_t word = 0;
+#pragma unroll
+    for (int f = 0; f < W; ++f)
+      word |= static_cast<uint32_t>(src[(f >> 1) + (W / 2) * (f & 1)]) << (BITS * f);
+    rows[j * WORDS + w] = word;
+  }
+}
+
 // -------------------------------------------------------------------------------------------
 // 3. K per channel over a page's tokens
 // -------------------------------------------------------------------------------------------
@@ -417,8 +453,6 @@ __device__ __forceinline__ void append_rows(const WriterArgs& a, int* hist_delta
 template <int BITS, int D>
 __global__ void __launch_bounds__(256) append_k_channel_kernel(WriterArgs a) {
   constexpr int QMAX = (1 << BITS) - 1;
-  constexpr int W = 32 / BITS;             // codes per word
-  constexpr int WORDS = D * BITS / 32;     // words per token row
   extern __shared__ __align__(16) uint8_t smem_k[];
   __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_k);   // [64][D]
   uint8_t* codes = smem_k + PAGE * D * 2;                            // [64][D]
@@ -458,30 +492,46 @@ __global__ void __launch_bounds__(256) append_k_channel_kernel(WriterArgs a) {
       const int q = min(__float2int_rn(__fdiv_rn(dividend, s)), QMAX);
       codes[j * D + d] = static_cast<uint8_t>(q);
     }
-    // the channel's record after the block's V ring: row 0 s_d, row 1 z_d
-    char* block = static_cast<char*>(a.p.scales) + blk * scale_block_bytes(a.p);
-    if (!a.p.scale_bf16) {
-      float* rec = reinterpret_cast<float*>(block) + 2 * PAGE;
-      rec[d] = s;
-      rec[D + d] = z;
-    } else {
-      __nv_bfloat16* rec = reinterpret_cast<__nv_bfloat16*>(block) + 2 * PAGE;
-      rec[d] = __float2bfloat16_rn(s);
-      rec[D + d] = __float2bfloat16_rn(z);
-    }
+    store_channel_record<D>(a.p, blk, d, s, z);
   }
   __syncthreads();
-  // packed rows: field f of word w holds channel W*w + f/2 + (W/2)*(f%2)
-  uint32_t* rows = reinterpret_cast<uint32_t*>(a.p.k_codes + blk * PAGE * (D * BITS / 8));
-  for (int i = threadIdx.x; i < n * WORDS; i += blockDim.x) {
-    const int j = i / WORDS, w = i % WORDS;
-    const uint8_t* src = codes + j * D + W * w;
-    uint32_t word = 0;
-#pragma unroll
-    for (int f = 0; f < W; ++f)
-      word |= static_cast<uint32_t>(src[(f >> 1) + (W / 2) * (f & 1)]) << (BITS * f);
-    rows[j * WORDS + w] = word;
+  store_packed_rows<BITS, D>(codes, n, a.p.k_codes + blk * PAGE * (D * BITS / 8));
+}
+
+// The same pages from an engine that quantized them itself: K codes one per byte
+// [P * 64, HKV, D] with f32 (s_d, z_d) [P, HKV, D] per page and channel. One CTA per (page
+// group, KV head) masks the codes to the stored width, packs the token rows and stores the
+// channel records, saturated like the token-wise records of fq_append_quantized.
+template <int BITS, int D>
+__global__ void __launch_bounds__(256) pack_k_channel_kernel(WriterArgs a) {
+  constexpr int QMAX = (1 << BITS) - 1;
+  __shared__ __align__(16) uint8_t codes[PAGE * D];
+  const int hkv = a.p.num_kv_heads;
+  const int group = blockIdx.x / hkv, head = blockIdx.x % hkv;
+  int n = a.valid != nullptr ? __ldg(a.valid + group) : PAGE;
+  if (n > PAGE) n = PAGE;
+  if (n <= 0) return;
+  const int page = __ldg(a.page_ids + group);
+  if (page < 0 || page >= a.p.num_pages) return;   // reported by the row pass
+  constexpr int WPR = D / 4;   // 32-bit words of a token's code bytes
+  for (int i = threadIdx.x; i < n * WPR; i += blockDim.x) {
+    const int j = i / WPR, c = i % WPR;
+    const uint8_t* src = static_cast<const uint8_t*>(a.k) +
+                         ((static_cast<long long>(group) * PAGE + j) * hkv + head) * D;
+    reinterpret_cast<uint32_t*>(codes + j * D)[c] =
+        __ldg(reinterpret_cast<const uint32_t*>(src) + c) & (0x01010101u * QMAX);
   }
+  const long long blk = static_cast<long long>(page) * hkv + head;
+  const float s_lo = __fdiv_rn(S_CLAMP, static_cast<float>(QMAX));
+  const float s_hi = __fdiv_rn(2.0f * ENVELOPE, static_cast<float>(QMAX));
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const long long rec = (static_cast<long long>(group) * hkv + head) * D + d;
+    const float s = fminf(fmaxf(__ldg(a.k_scale + rec), s_lo), s_hi);
+    const float z = fminf(fmaxf(__ldg(a.k_zero + rec), -ENVELOPE), ENVELOPE);
+    store_channel_record<D>(a.p, blk, d, s, z);
+  }
+  __syncthreads();
+  store_packed_rows<BITS, D>(codes, n, a.p.k_codes + blk * PAGE * (D * BITS / 8));
 }
 
 // -------------------------------------------------------------------------------------------
@@ -592,6 +642,47 @@ extern "C" int fq_append_page_groups(const fq_pools* pools, const void* k, const
   if (int e = fq::launch_append<false>(a, s)) return e;
 #define FQ_LAUNCH(B, DD) \
   if (pools->bits == B && pools->head_dim == DD) return fq::launch_k_channel<B, DD>(a, num_page_groups, s);
+  FQ_LAUNCH(2, 64) FQ_LAUNCH(2, 128) FQ_LAUNCH(2, 256)
+  FQ_LAUNCH(4, 64) FQ_LAUNCH(4, 128) FQ_LAUNCH(4, 256)
+#undef FQ_LAUNCH
+  return FQ_ERR_UNSUPPORTED;
+}
+
+extern "C" int fq_append_quantized_page_groups(const fq_pools* pools, const uint8_t* k_codes,
+                                               const float* k_scale, const float* k_zero,
+                                               const uint8_t* v_codes, const float* v_scale,
+                                               const float* v_zero, const int32_t* page_ids,
+                                               const int32_t* valid, int32_t num_page_groups,
+                                               int32_t* status, void* stream) {
+  if (int e = fq::check_pools(pools)) return e;
+  if (pools->k_channel_group != FQ_PAGE_SIZE) return FQ_ERR_UNSUPPORTED;
+  if (num_page_groups < 0 ||
+      (num_page_groups > 0 && (!k_codes || !v_codes || !k_scale || !k_zero || !v_scale ||
+                               !v_zero || !page_ids)))
+    return FQ_ERR_BAD_ARG;
+  if (num_page_groups == 0) return 0;
+  if (num_page_groups > (0x7FFFFFFF >> 6)) return FQ_ERR_TOO_LARGE;
+  // the code rows are read four bytes at a time
+  if ((reinterpret_cast<uintptr_t>(k_codes) | reinterpret_cast<uintptr_t>(v_codes)) & 3)
+    return FQ_ERR_BAD_ARG;
+  fq::WriterArgs a{};
+  a.p = *pools;
+  a.k = k_codes; a.v = v_codes;
+  a.k_scale = k_scale; a.k_zero = k_zero; a.v_scale = v_scale; a.v_zero = v_zero;
+  a.page_ids = page_ids;
+  a.valid = valid;
+  a.num_tokens = num_page_groups * FQ_PAGE_SIZE;
+  a.k_clip = a.v_clip = -1;
+  a.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // V rows, V records, page maxima: the layout-only row pass (it skips K for these pools)
+  if (int e = fq::launch_append<true>(a, s)) return e;
+#define FQ_LAUNCH(B, DD)                                                                   \
+  if (pools->bits == B && pools->head_dim == DD) {                                         \
+    fq::pack_k_channel_kernel<B, DD>                                                       \
+        <<<static_cast<unsigned>(num_page_groups) * pools->num_kv_heads, 256, 0, s>>>(a);  \
+    return static_cast<int>(cudaGetLastError());                                           \
+  }
   FQ_LAUNCH(2, 64) FQ_LAUNCH(2, 128) FQ_LAUNCH(2, 256)
   FQ_LAUNCH(4, 64) FQ_LAUNCH(4, 128) FQ_LAUNCH(4, 256)
 #undef FQ_LAUNCH

@@ -270,7 +270,8 @@ class QuantKVCache:
             raise NotImplementedError(
                 f"{method}() writes token-wise layouts only; k_quant={lay.k_quant} "
                 f"v_quant={lay.v_quant} has a channel-wise tensor"
-                + (" (write it by whole pages with append_page_groups())"
+                + (" (write it by whole pages with append_page_groups() or "
+                   "append_quantized_page_groups())"
                    if lay.is_page_channel_k else ""))
 
     def _check_slots(self, slot_mapping, num_tokens):
@@ -357,17 +358,7 @@ class QuantKVCache:
             raise NotImplementedError(
                 f"append_page_groups() writes k_quant=('channel', {PAGE_SIZE}) with token-wise V; "
                 f"this cache has k_quant={lay.k_quant} v_quant={lay.v_quant}")
-        if (not isinstance(page_indices, torch.Tensor) or page_indices.dtype != torch.int32
-                or page_indices.dim() != 1 or not page_indices.is_contiguous()
-                or page_indices.device != self.device):
-            raise ValueError(f"page_indices must be a contiguous int32 [P] tensor on {self.device}")
-        groups = page_indices.numel()
-        if valid_tokens is not None and (
-                not isinstance(valid_tokens, torch.Tensor) or valid_tokens.dtype != torch.int32
-                or tuple(valid_tokens.shape) != (groups,) or not valid_tokens.is_contiguous()
-                or valid_tokens.device != self.device):
-            raise ValueError(f"valid_tokens must be a contiguous int32 [{groups}] tensor on "
-                             f"{self.device}")
+        groups = self._check_page_groups(page_indices, valid_tokens)
         self._check_token_rows("k", k, rows=groups * PAGE_SIZE)
         self._check_token_rows("v", v, rows=groups * PAGE_SIZE)
         if groups == 0:
@@ -379,6 +370,69 @@ class QuantKVCache:
                 None if valid_tokens is None else valid_tokens.data_ptr(), groups,
                 self.status.data_ptr(), _dev.current_stream_ptr(self.device)),
                 "append_page_groups")
+
+    def _check_page_groups(self, page_indices, valid_tokens) -> int:
+        if (not isinstance(page_indices, torch.Tensor) or page_indices.dtype != torch.int32
+                or page_indices.dim() != 1 or not page_indices.is_contiguous()
+                or page_indices.device != self.device):
+            raise ValueError(f"page_indices must be a contiguous int32 [P] tensor on {self.device}")
+        groups = page_indices.numel()
+        if valid_tokens is not None and (
+                not isinstance(valid_tokens, torch.Tensor) or valid_tokens.dtype != torch.int32
+                or tuple(valid_tokens.shape) != (groups,) or not valid_tokens.is_contiguous()
+                or valid_tokens.device != self.device):
+            raise ValueError(f"valid_tokens must be a contiguous int32 [{groups}] tensor on "
+                             f"{self.device}")
+        return groups
+
+    def append_quantized_page_groups(self, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero,
+                                     page_indices: torch.Tensor,
+                                     valid_tokens: Optional[torch.Tensor] = None) -> None:
+        """Layout-only write of whole pages an engine quantized itself, for a cache whose K is
+        quantized per channel over the 64 tokens of a page: what `append_quantized` is to
+        `append`, for `append_page_groups` (the reference's `append_quantized` refuses these
+        layouts, src/foscar/kv_cache.py:769-774).
+
+        k_codes, v_codes: uint8 [P * 64, HKV, D], one value per byte, page i's tokens being rows
+        [64 i, 64 i + valid_tokens[i]); k_scale, k_zero: f32 [P, HKV, D] (per page and channel);
+        v_scale, v_zero: f32 [P * 64, HKV]. Codes are masked to the stored width and records
+        saturated to the quantizing writer's ranges."""
+        lay = self.layout
+        if not lay.is_page_channel_k:
+            raise NotImplementedError(
+                f"append_quantized_page_groups() writes k_quant=('channel', {PAGE_SIZE}) with "
+                f"token-wise V; this cache has k_quant={lay.k_quant} v_quant={lay.v_quant}")
+        groups = self._check_page_groups(page_indices, valid_tokens)
+        H, D, T = lay.num_kv_heads, lay.head_dim, groups * PAGE_SIZE
+        wanted = {"k_codes": (k_codes, torch.uint8, (T, H, D)),
+                  "k_scale": (k_scale, torch.float32, (groups, H, D)),
+                  "k_zero": (k_zero, torch.float32, (groups, H, D)),
+                  "v_codes": (v_codes, torch.uint8, (T, H, D)),
+                  "v_scale": (v_scale, torch.float32, (T, H)),
+                  "v_zero": (v_zero, torch.float32, (T, H))}
+        for name, (x, dtype, shape) in wanted.items():
+            if not (isinstance(x, torch.Tensor) and x.dtype == dtype
+                    and tuple(x.shape) == shape):
+                raise ValueError(f"{name} must be a {dtype} {list(shape)} tensor; got "
+                                 f"{getattr(x, 'dtype', None)} {tuple(getattr(x, 'shape', ()))}")
+            if not x.is_contiguous():
+                raise ValueError(f"{name} must be C-contiguous")
+            self._same_device(name, x)
+            if dtype == torch.uint8 and x.data_ptr() % 16 != 0:
+                raise ValueError(f"{name} must start 16-byte aligned")
+        if T > MAX_APPEND_TOKENS:
+            raise ValueError(f"one append takes at most {MAX_APPEND_TOKENS} tokens; got {T}: "
+                             f"split it into several appends")
+        if groups == 0:
+            return
+        with _dev.on_device(self.device):
+            _lib.check(_lib.load().fq_append_quantized_page_groups(
+                ctypes.byref(self._c_pools), k_codes.data_ptr(), k_scale.data_ptr(),
+                k_zero.data_ptr(), v_codes.data_ptr(), v_scale.data_ptr(), v_zero.data_ptr(),
+                page_indices.data_ptr(),
+                None if valid_tokens is None else valid_tokens.data_ptr(), groups,
+                self.status.data_ptr(), _dev.current_stream_ptr(self.device)),
+                "append_quantized_page_groups")
 
     def append_quantized(self, k_codes, k_scale, k_zero, v_codes, v_scale, v_zero,
                          slot_mapping) -> None:

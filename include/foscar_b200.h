@@ -90,6 +90,19 @@ int fq_append_page_groups(const fq_pools* pools, const void* k, const void* v,
                           const int32_t* page_ids, const int32_t* valid, int32_t num_page_groups,
                           int32_t* status, void* stream);
 
+/* The same page groups from an engine that quantized them itself (layout-only, the channel-wise
+ * counterpart of fq_append_quantized): k_codes, v_codes uint8 [P * 64, HKV, D] one value per
+ * byte, contiguous, 4-byte aligned; k_scale, k_zero f32 [P, HKV, D] (per page and channel);
+ * v_scale, v_zero f32 [P * 64, HKV]; page_ids, valid as above. Codes are masked to the stored
+ * width and records saturated like fq_append_quantized's. No reference counterpart
+ * (QuantKVCache.append_quantized refuses these layouts, src/foscar/kv_cache.py:769-774). */
+int fq_append_quantized_page_groups(const fq_pools* pools, const uint8_t* k_codes,
+                                    const float* k_scale, const float* k_zero,
+                                    const uint8_t* v_codes, const float* v_scale,
+                                    const float* v_zero, const int32_t* page_ids,
+                                    const int32_t* valid, int32_t num_page_groups,
+                                    int32_t* status, void* stream);
+
 /* Read K,V of a batch back into bf16 rows [N, HKV, D]: out[out_indptr[b]+t] =
  * bf16(fma(s, q, z)) for t < seq_lens[b]. Stands in for QuantKVCache.dequantize
  * (src/foscar/kv_cache.py:792-877). out_indptr is int32 or int64 (out_indptr_64). k_out and

@@ -18,5 +18,6 @@ from .ref_quant import (  # noqa: F401
     ref_vmax_bucket, ref_v_max_hist, ref_pscale_lp, emulate_fold_decode,
 )
 from .ref_channel import (  # noqa: F401
-    CpuChannelPools, ref_append_page_groups, ref_dequantize_channel,
+    CpuChannelPools, ref_append_page_groups, ref_append_quantized_page_groups,
+    ref_dequantize_channel,
 )

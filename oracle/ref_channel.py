@@ -23,7 +23,8 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from .ref_quant import (PAGE, _fma_f32, pack_rows, quantize_rows, ref_v_max_hist, unpack_rows)
+from .ref_quant import (PAGE, _fma_f32, pack_rows, quantize_rows, ref_v_max_hist, saturate_given,
+                        unpack_rows)
 
 
 class CpuChannelPools:
@@ -43,37 +44,63 @@ class CpuChannelPools:
         self.v_max_hist = np.zeros(256, dtype=np.uint32)
 
 
-def ref_append_page_groups(pools: CpuChannelPools, k, v, page_ids, valid=None):
-    """Write whole page groups: k, v bf16 [P * 64, HKV, D], page i's tokens being rows
-    [64 i, 64 i + valid[i]); page_ids [P]. K statistics run over the page's valid tokens only;
-    rows past them are not written, their V records are cleared (every page starts at 0)."""
-    page_ids = np.asarray(page_ids, dtype=np.int64)
-    n_pages = len(page_ids)
-    valid = np.full(n_pages, PAGE) if valid is None else np.asarray(valid, dtype=np.int64)
+def _write_page(pools: CpuChannelPools, p: int, n: int, kc, ks, kz, vc, vs, vz):
+    """Store one page's first n tokens: K codes [n, HKV, D] with channel records ks, kz
+    [HKV, D]; V codes [n, HKV, D] with token records vs, vz [n, HKV] (all records f32, rounded
+    to the pool dtype here). The page's V ring is rebuilt from 0 and its maximum recomputed."""
     d, sd = pools.d, pools.scale_dtype
+    pools.k_codes[p, :, :n] = pack_rows(kc, pools.bits).permute(1, 0, 2)
+    pools.scales[p, :, pools.k_ch:pools.k_ch + d] = ks.to(sd)
+    pools.scales[p, :, pools.k_ch + d:pools.k_ch + 2 * d] = kz.to(sd)
+    pools.v_codes[p, :, :n] = pack_rows(vc, pools.bits).permute(1, 0, 2)
+    ring = torch.zeros(pools.hkv, PAGE, 2, dtype=sd)
+    ring[:, :n, 0] = vs.to(sd).t()
+    ring[:, :n, 1] = vz.to(sd).t()
+    pools.scales[p, :, :2 * PAGE] = ring.reshape(pools.hkv, 2 * PAGE)
+    stored = vs.to(sd).float().contiguous().numpy().view(np.uint32)           # [n, HKV]
+    pools.v_page_max[p] = stored.max(axis=0)
+
+
+def _page_groups(pools: CpuChannelPools, page_ids, valid):
+    page_ids = np.asarray(page_ids, dtype=np.int64)
+    valid = np.full(len(page_ids), PAGE) if valid is None else np.asarray(valid, dtype=np.int64)
     for i, (p, n) in enumerate(zip(page_ids, valid)):
-        n = int(n)
+        n = min(int(n), PAGE)
         if n <= 0:
             continue
         if p < 0 or p >= pools.num_pages:
             raise IndexError("page outside the cache")
+        yield i, int(p), n
+
+
+def ref_append_page_groups(pools: CpuChannelPools, k, v, page_ids, valid=None):
+    """Write whole page groups: k, v bf16 [P * 64, HKV, D], page i's tokens being rows
+    [64 i, 64 i + valid[i]); page_ids [P]. K statistics run over the page's valid tokens only;
+    rows past them are not written, their V records are cleared (every page starts at 0)."""
+    for i, p, n in _page_groups(pools, page_ids, valid):
         rows = slice(PAGE * i, PAGE * i + n)
         # K: per (head, channel) over the n tokens
         x = k[rows].float().permute(1, 2, 0).contiguous()            # [HKV, D, n]
         codes, s, z = quantize_rows(x, pools.bits)                   # [HKV, D, n], [HKV, D, 1]
-        pools.k_codes[p, :, :n] = pack_rows(codes.permute(2, 0, 1).contiguous(),
-                                            pools.bits).permute(1, 0, 2)
-        pools.scales[p, :, pools.k_ch:pools.k_ch + d] = s[..., 0].to(sd)
-        pools.scales[p, :, pools.k_ch + d:pools.k_ch + 2 * d] = z[..., 0].to(sd)
         # V: per token over the head
         vc, vs, vz = quantize_rows(v[rows], pools.bits)              # [n, HKV, D], [n, HKV, 1]
-        pools.v_codes[p, :, :n] = pack_rows(vc, pools.bits).permute(1, 0, 2)
-        ring = torch.zeros(pools.hkv, PAGE, 2, dtype=sd)
-        ring[:, :n, 0] = vs[..., 0].to(sd).t()
-        ring[:, :n, 1] = vz[..., 0].to(sd).t()
-        pools.scales[p, :, :2 * PAGE] = ring.reshape(pools.hkv, 2 * PAGE)
-        stored = vs[..., 0].to(sd).float().contiguous().numpy().view(np.uint32)   # [n, HKV]
-        pools.v_page_max[p] = stored.max(axis=0)
+        _write_page(pools, p, n, codes.permute(2, 0, 1).contiguous(), s[..., 0], z[..., 0],
+                    vc, vs[..., 0], vz[..., 0])
+    pools.v_max_hist[:] = ref_v_max_hist(pools.v_page_max)
+
+
+def ref_append_quantized_page_groups(pools: CpuChannelPools, k_codes, k_scale, k_zero, v_codes,
+                                     v_scale, v_zero, page_ids, valid=None):
+    """The layout-only form: k_codes, v_codes uint8 [P * 64, HKV, D] one value per byte; k_scale,
+    k_zero f32 [P, HKV, D]; v_scale, v_zero f32 [P * 64, HKV]. Codes masked to the stored width
+    and records saturated as the token-wise layout-only write does
+    (src/foscar/kv_cache.py:689-767, src/foscar/_append_core.py:709-717)."""
+    mask = (1 << pools.bits) - 1
+    for i, p, n in _page_groups(pools, page_ids, valid):
+        rows = slice(PAGE * i, PAGE * i + n)
+        ks, kz = saturate_given(k_scale[i].float(), k_zero[i].float(), pools.bits)
+        vs, vz = saturate_given(v_scale[rows].float(), v_zero[rows].float(), pools.bits)
+        _write_page(pools, p, n, k_codes[rows] & mask, ks, kz, v_codes[rows] & mask, vs, vz)
     pools.v_max_hist[:] = ref_v_max_hist(pools.v_page_max)
 
 

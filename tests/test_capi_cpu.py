@@ -194,6 +194,18 @@ def test_entry_points_refuse_misaligned_or_senseless_arguments_before_any_launch
         == _lib.ERR_BAD_ARG                                  # clip index outside the row
     assert lib.fq_append_quantized(ctypes.byref(p), bad, ok, ok, ok, ok, ok, ok, 4, None, None) \
         == _lib.ERR_BAD_ARG
+    # the layout-only page-group write: channel-wise K pools only, code rows 4-byte aligned
+    pch = _fake_pools(head_dim=256, k_channel_group=64)
+    assert lib.fq_append_quantized_page_groups(ctypes.byref(p), ok, ok, ok, ok, ok, ok, ok, None,
+                                               1, None, None) == _lib.ERR_UNSUPPORTED
+    assert lib.fq_append_quantized_page_groups(ctypes.byref(pch), ok, ok, ok, bad, ok, ok, ok,
+                                               None, 1, None, None) == _lib.ERR_BAD_ARG
+    assert lib.fq_append_quantized_page_groups(ctypes.byref(pch), ok, None, ok, ok, ok, ok, ok,
+                                               None, 1, None, None) == _lib.ERR_BAD_ARG
+    assert lib.fq_append_quantized_page_groups(ctypes.byref(pch), ok, ok, ok, ok, ok, ok, ok,
+                                               None, 0, None, None) == 0
+    assert lib.fq_append_quantized_page_groups(ctypes.byref(pch), ok, ok, ok, ok, ok, ok, ok,
+                                               None, 1 << 26, None, None) == _lib.ERR_TOO_LARGE
     pz = _fake_pools(num_kv_heads=0)
     assert lib.fq_append(ctypes.byref(pz), ok, ok, 1024, 1024, ok, 4, -1, -1, None, None) \
         == _lib.ERR_BAD_ARG

@@ -11,8 +11,8 @@ import pytest
 import torch
 
 from helpers import PAGE, make_q
-from oracle import (CpuChannelPools, ref_append_page_groups, ref_attention,
-                    ref_dequantize_channel)
+from oracle import (CpuChannelPools, quantize_rows, ref_append_page_groups,
+                    ref_append_quantized_page_groups, ref_attention, ref_dequantize_channel)
 
 pytestmark = pytest.mark.gpu
 
@@ -76,6 +76,104 @@ def test_page_group_writer_bytes(bits, d, scale_dtype):
     assert np.array_equal(vpm[np.sort(indices)], pools.v_page_max[np.sort(indices)])
     hist = cache.v_max_hist.view(torch.int32).cpu().numpy().view(np.uint32)
     assert np.array_equal(hist, pools.v_max_hist)
+
+
+def _engine_quantized(k, v, bits, valid):
+    """What an engine that quantizes by itself would hand over for the page rows k, v: codes one
+    per byte, K records per (page, head, channel) over each page's valid tokens, V records per
+    token. Codes carry junk in their high bits and rows past a page's valid tokens are random:
+    the write has to mask the first and skip the second."""
+    pages, (hkv, d) = len(valid), k.shape[1:]
+    g = torch.Generator().manual_seed(5)
+    kc = torch.randint(0, 256, (pages * PAGE, hkv, d), generator=g, dtype=torch.uint8)
+    vc = torch.randint(0, 256, (pages * PAGE, hkv, d), generator=g, dtype=torch.uint8)
+    ks, kz = torch.randn(pages, hkv, d, generator=g), torch.randn(pages, hkv, d, generator=g)
+    vs, vz = torch.rand(pages * PAGE, hkv, generator=g), torch.randn(pages * PAGE, hkv, generator=g)
+    junk = 256 - (1 << bits)
+    for i, n in enumerate(valid):
+        rows = slice(PAGE * i, PAGE * i + int(n))
+        c, s, z = quantize_rows(k[rows].float().permute(1, 2, 0).contiguous(), bits)
+        kc[rows] = c.permute(2, 0, 1).to(torch.uint8) | (kc[rows] & junk)
+        ks[i], kz[i] = s[..., 0], z[..., 0]
+        c, s, z = quantize_rows(v[rows], bits)
+        vc[rows] = c.to(torch.uint8) | (vc[rows] & junk)
+        vs[rows], vz[rows] = s[..., 0], z[..., 0]
+    return kc, ks, kz, vc, vs, vz
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+@pytest.mark.parametrize("d", [64, 128, 256])
+@pytest.mark.parametrize("scale_dtype", [None, torch.bfloat16])
+def test_layout_only_page_group_write(bits, d, scale_dtype):
+    """Pages an engine quantized itself: the bytes equal the CPU statement of the layout-only
+    write, and, the engine having used the writer's own arithmetic, the bytes the quantizing
+    page-group writer leaves for the same rows."""
+    from foscar_b200 import QuantKVLayout
+    seq, hkv = [1, 64, 65, 200, 1000], 2
+    indptr, indices, valid, total = _page_batch(seq, 21)
+    k, v = _page_rows(seq, hkv, d, 21, outliers=True)
+    given = _engine_quantized(k, v, bits, valid)
+    layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device="cuda",
+                                  k_quant=("channel", 64), scale_dtype=scale_dtype)
+    ids, val = torch.from_numpy(indices).cuda(), torch.from_numpy(valid).cuda()
+    cache = layout.allocate(total + 1)
+    cache.append_quantized_page_groups(*(x.cuda() for x in given), ids, val)
+    twin = layout.allocate(total + 1)
+    twin.append_page_groups(k.cuda(), v.cuda(), ids, val)
+    torch.cuda.synchronize()
+    assert cache.last_status() == 0 and twin.last_status() == 0
+    pools = CpuChannelPools(total + 1, hkv, d, bits, scale_dtype=layout.scale_dtype)
+    ref_append_quantized_page_groups(pools, *given, indices, valid)
+    sel = torch.as_tensor(np.sort(indices).astype(np.int64))
+    kc, vc, tk, tv = (x.cpu() for x in (cache.k_codes, cache.v_codes, twin.k_codes, twin.v_codes))
+    for e, (p, n) in enumerate(zip(indices, valid)):
+        assert torch.equal(kc[p, :, :n], pools.k_codes[p, :, :n]), f"K codes of page entry {e}"
+        assert torch.equal(vc[p, :, :n], pools.v_codes[p, :, :n]), f"V codes of page entry {e}"
+        assert torch.equal(kc[p, :, :n], tk[p, :, :n]) and torch.equal(vc[p, :, :n], tv[p, :, :n])
+    got = cache.scales.cpu()[sel].contiguous().view(torch.uint8)
+    assert torch.equal(got, pools.scales[sel].contiguous().view(torch.uint8)), "scale blocks"
+    assert torch.equal(got, twin.scales.cpu()[sel].contiguous().view(torch.uint8))
+    vpm = cache.v_page_max.view(torch.int32).cpu().numpy().view(np.uint32)
+    assert np.array_equal(vpm[np.sort(indices)], pools.v_page_max[np.sort(indices)])
+    hist = cache.v_max_hist.view(torch.int32).cpu().numpy().view(np.uint32)
+    assert np.array_equal(hist, pools.v_max_hist)
+
+
+def test_layout_only_page_group_write_saturates_records():
+    """Records outside the quantizing writer's ranges (and NaN) are saturated, as the token-wise
+    layout-only write does; a page written again replaces its maximum."""
+    from foscar_b200 import QuantKVLayout
+    bits, d, hkv = 4, 256, 2
+    layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device="cuda",
+                                  k_quant=("channel", 64))
+    cache = layout.allocate(3)
+    pools = CpuChannelPools(3, hkv, d, bits, scale_dtype=layout.scale_dtype)
+    g = torch.Generator().manual_seed(9)
+    ids = np.array([2, 0], dtype=np.int32)
+    for step in range(2):
+        kc = torch.randint(0, 16, (2 * PAGE, hkv, d), generator=g, dtype=torch.uint8)
+        vc = torch.randint(0, 16, (2 * PAGE, hkv, d), generator=g, dtype=torch.uint8)
+        ks = torch.randn(2, hkv, d, generator=g)
+        kz = torch.randn(2, hkv, d, generator=g)
+        vs = torch.rand(2 * PAGE, hkv, generator=g) * (0.1 if step else 1.0)
+        vz = torch.randn(2 * PAGE, hkv, generator=g)
+        ks[0, 0, :4] = torch.tensor([0.0, -1.0, float("nan"), float("inf")])
+        kz[1, 1, :3] = torch.tensor([float("inf"), -float("inf"), float("nan")])
+        vs[3, 0], vs[4, 1], vz[5, 0] = 0.0, float("inf"), float("nan")
+        given = (kc, ks, kz, vc, vs, vz)
+        cache.append_quantized_page_groups(*(x.cuda() for x in given),
+                                           torch.from_numpy(ids).cuda())
+        ref_append_quantized_page_groups(pools, *given, ids)
+        torch.cuda.synchronize()
+        assert cache.last_status() == 0
+        sel = torch.tensor([0, 2])
+        assert torch.equal(cache.scales.cpu()[sel].contiguous().view(torch.uint8),
+                           pools.scales[sel].contiguous().view(torch.uint8))
+        assert torch.equal(cache.k_codes.cpu()[sel], pools.k_codes[sel])
+        vpm = cache.v_page_max.view(torch.int32).cpu().numpy().view(np.uint32)
+        assert np.array_equal(vpm[[0, 2]], pools.v_page_max[[0, 2]])
+        hist = cache.v_max_hist.view(torch.int32).cpu().numpy().view(np.uint32)
+        assert np.array_equal(hist, pools.v_max_hist)
 
 
 @pytest.mark.parametrize("bits,d", [(4, 256), (2, 128)])

@@ -209,6 +209,17 @@ def test_append_argument_refusals(fake_b200):
         cache2.append_page_groups(k, k, torch.zeros(1, dtype=torch.int32))
     with pytest.raises(NotImplementedError, match="append_page_groups\\(\\) writes k_quant"):
         cache.append_page_groups(k, k, torch.zeros(1, dtype=torch.int32))
+    c = torch.zeros(64, 8, 128, dtype=torch.uint8)
+    rec, per_token, page = torch.zeros(1, 8, 128), torch.zeros(64, 8), torch.zeros(1, dtype=torch.int32)
+    with pytest.raises(NotImplementedError, match="append_quantized_page_groups\\(\\) writes k_quant"):
+        cache.append_quantized_page_groups(c, rec, rec, c, per_token, per_token, page)
+    with pytest.raises(ValueError, match="k_scale must be a torch.float32 \\[1, 8, 128\\]"):
+        cache2.append_quantized_page_groups(c, per_token, rec, c, per_token, per_token, page)
+    with pytest.raises(ValueError, match="v_codes must be a torch.uint8 \\[64, 8, 128\\]"):
+        cache2.append_quantized_page_groups(c, rec, rec, c[:32], per_token, per_token, page)
+    with pytest.raises(ValueError, match="valid_tokens must be a contiguous int32"):
+        cache2.append_quantized_page_groups(c, rec, rec, c, per_token, per_token, page,
+                                            torch.zeros(2, dtype=torch.int32))
     lay3, cache3 = _cache(fake_b200, k_quant=("channel", 64), v_quant=("channel", 64))
     with pytest.raises(NotImplementedError, match="token-wise layouts only"):
         cache3.dequantize(k, k, slots.int(), slots.int(), slots.int(), slots.int())
