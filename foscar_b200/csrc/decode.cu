@@ -74,7 +74,9 @@
 
 // Diagnostic builds only: a bit mask of roles whose arithmetic is skipped while every barrier
 // arrival stays (1 softmax, 2 K unpack, 4 V unpack, 8 producers' copies; 16 / 32: one S / PV MMA
-// per tile instead of four). The output is
+// per tile instead of four; 64 / 128: the INT2 K / V unpack at the instruction count of a 4-bit
+// operand feed, i.e. two masks and a shift per packed word and half the operand words stored,
+// at head_dim 128). The output is
 // then meaningless; the launch time and instruction count show what each role costs.
 #ifndef FQ_STUB_ROLES
 #define FQ_STUB_ROLES 0
@@ -194,6 +196,15 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   const uint32_t o_src = tmem + lane_base + TP::O + wg * TP::O_COLS + (SP::PAIR && wq >= 2 ? 16 : 0);
   const uint32_t v_row = smem0 + SP::VOP_OFF + wg * SP::VOP_STAGE + t * SP::ROW;
   const uint32_t p_row = smem0 + SP::P_OFF + wg * SP::P_BYTES + t * 16;
+#if FQ_STUB_ROLES & (64 | 128)
+  {   // the operand words the short stubs never write: zero once
+    uint32_t zero[8] = {};
+    for (int v = 0; v < TP::KOP_COLS / 8; ++v) tmem_st8(k_dst + 8 * v, zero);
+    tmem_st_wait();
+    for (int cc = 0; cc < 8; ++cc)
+      asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(v_row + (cc << 4)), "r"(0) : "memory");
+  }
+#endif
   float* red_max = reinterpret_cast<float*>(smem + SP::RED_OFF);              // [wg][buf][warp][8]
   float* red_sum = reinterpret_cast<float*>(smem + SP::RED_OFF + 256 * G);    // [wg][warp][16]
   // this warp's copy of the item's per-head constants: sm_scale*log2e*q_descale, and that times
@@ -339,6 +350,15 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
             for (int i = 0; i < D / 4; ++i) part[i] = n;
 #else
             load_row<BITS, D>(stage + SP::K_OFF + (u * TILE + t) * SP::RB, wk, SP::row_swizzle(t));
+#if FQ_STUB_ROLES & 64
+            if constexpr (BITS == 2) {
+#pragma unroll
+              for (int i = 0; i < D / 16; ++i) {
+                part[2 * i] = wk[i] & 0x33333333u;
+                part[2 * i + 1] = (wk[i] >> 2) & 0x33333333u;
+              }
+            } else
+#endif
             expand_words<BITS, D>(wk, part);
 #endif
 #pragma unroll
@@ -347,7 +367,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           FQ_STAMP(3);
           tc_fence_after();
 #pragma unroll
-          for (int v = 0; v < NT * D / 32; ++v) tmem_st8(k_dst + 8 * v, op + 8 * v);
+          for (int v = 0; v < NT * D / (((FQ_STUB_ROLES & 64) && BITS == 2) ? 64 : 32); ++v)
+            tmem_st8(k_dst + 8 * v, op + 8 * v);
         }
         tmem_st_wait();
         FQ_STAMP(5);
@@ -398,6 +419,15 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           for (int i = 0; i < D / 4; ++i) part[i] = n;
 #else
           load_row<BITS, D>(stage + SP::V_OFF + (u * TILE + t) * SP::RB, wv, SP::row_swizzle(t));
+#if FQ_STUB_ROLES & 128
+          if constexpr (BITS == 2) {
+#pragma unroll
+            for (int i = 0; i < D / 16; ++i) {
+              part[2 * i] = wv[i] & 0x33333333u;
+              part[2 * i + 1] = (wv[i] >> 2) & 0x33333333u;
+            }
+          } else
+#endif
           expand_words_v<BITS, D>(wv, part);
 #endif
 #pragma unroll
@@ -405,7 +435,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         }
         FQ_STAMP(6);
 #pragma unroll
-        for (int cc = 0; cc < NT * D / 16; ++cc) {
+        for (int cc = 0; cc < NT * D / (((FQ_STUB_ROLES & 128) && BITS == 2) ? 32 : 16); ++cc) {
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(v_row + ((cc ^ (t & 7)) << 4)),
                        "r"(op[4 * cc]), "r"(op[4 * cc + 1]), "r"(op[4 * cc + 2]),
                        "r"(op[4 * cc + 3])
