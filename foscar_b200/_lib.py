@@ -85,6 +85,7 @@ _PROTOTYPES = {
     "fq_plan_worklist": (C.c_int, [_P, _I32, _I32, _I32, _I32, _I32, _P, _I32, _P, _I32, _I32]),
     "fq_workspace_bytes": (_I64, [_I32, _I32, _I32, _I32]),
     "fq_worklist_words": (_I64, [_I32, _I32, _I32, _I32]),
+    "fq_worklist_attach_requests": (C.c_int, [_P, _I64, _P, _P, _I32]),
     "fq_umma_selftest": (C.c_int, [_I32, _P, _P, _P, _P, _P, _P, _P, _P]),
     "fq_tile_tokens": (C.c_int, [_I32, _I32]),
     "fq_piece_overhead": (C.c_int, [_I32, _I32]),

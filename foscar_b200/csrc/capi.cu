@@ -171,6 +171,25 @@ extern "C" int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t 
   return pieces_total;
 }
 
+extern "C" int fq_worklist_attach_requests(int32_t* worklist, int64_t words,
+                                           const int32_t* seq_lens,
+                                           const int32_t* table_offsets, int32_t batch) {
+  if (!worklist || !seq_lens || !table_offsets || batch < 1 || words < WORK_WORDS)
+    return FQ_ERR_BAD_ARG;
+  const long long pieces = worklist[0], rows_off = worklist[3];
+  if (pieces < 0 || rows_off < WORK_WORDS || rows_off + pieces * WORK_WORDS > words)
+    return FQ_ERR_BAD_ARG;
+  int32_t* rows = worklist + rows_off;
+  for (long long i = 0; i < pieces; ++i) {
+    int32_t* row = rows + i * WORK_WORDS;
+    if (row[0] < 0 || row[0] >= batch) return FQ_ERR_BAD_ARG;
+    row[6] = seq_lens[row[0]];
+    row[7] = table_offsets[row[0]];
+  }
+  worklist[4] = 1;
+  return 0;
+}
+
 extern "C" int64_t fq_worklist_words(int32_t batch, int32_t num_kv_heads, int32_t head_tiles,
                                      int32_t num_ctas) {
   if (batch < 1 || num_kv_heads < 1 || head_tiles < 1 || num_ctas < 1) return FQ_ERR_BAD_ARG;

@@ -142,14 +142,19 @@ struct SmemPlan {
 static __device__ __noinline__ WorkItem decode_item(const DecodeParams& P, int i) {
   WorkItem w;
   const fq_decode_args& a = P.a;
+  int len = 0, table_off = 0;
+  bool carried = false;   // the list's rows carry the request's length and table offset
   if (a.worklist != nullptr) {
-    const int* rows = a.worklist + __ldg(a.worklist + 3);  // header word 3: rows' word offset
+    const int rows_off = __ldg(a.worklist + 3);   // header word 3: rows' word offset
+    carried = __ldg(a.worklist + 4) != 0;         // header word 4: fq_worklist_attach_requests
+    const int* rows = a.worklist + rows_off;
     const int4 r0 = __ldg(reinterpret_cast<const int4*>(rows) + 2 * i);
     const int4 r1 = __ldg(reinterpret_cast<const int4*>(rows) + 2 * i + 1);
     w.b = r0.x; w.kvh = r0.y; w.ht = r0.z; w.t0 = r0.w; w.t1 = r1.x; w.slot = r1.y;
+    len = r1.z; table_off = r1.w;
     const bool ok = w.b >= 0 && w.b < a.batch && w.kvh >= 0 && w.kvh < P.p.num_kv_heads &&
                     w.ht >= 0 && w.ht < P.head_tiles && w.slot < a.max_splits;
-    if (!ok) { w.b = 0; w.kvh = 0; w.ht = 0; w.t0 = w.t1 = 0; w.slot = -2; }
+    if (!ok) { w.b = 0; w.kvh = 0; w.ht = 0; w.t0 = w.t1 = 0; w.slot = -2; carried = false; }
   } else {
     const int S = a.kv_splits;
     w.slot = S > 1 ? i % S : -1;
@@ -159,7 +164,12 @@ static __device__ __noinline__ WorkItem decode_item(const DecodeParams& P, int i
     w.b = rest / P.p.num_kv_heads;
     w.t0 = 0; w.t1 = 0x7FFFFFFF;
   }
-  int len = __ldg(a.seq_lens + w.b);
+  // Otherwise two more loads that depend on the row: with a cold L2 a further round trip
+  // before the CTA's first page id can be requested.
+  if (!carried) {
+    len = __ldg(a.seq_lens + w.b);
+    table_off = __ldg(a.table_offsets + w.b);
+  }
   if (len < 0) len = 0;
   w.len = len;
   const int tiles = (len + P.tile_tokens - 1) / P.tile_tokens;
@@ -173,7 +183,7 @@ static __device__ __noinline__ WorkItem decode_item(const DecodeParams& P, int i
     w.t0 = max(0, min(w.t0, tiles));
     w.t1 = max(w.t0, min(w.t1, tiles));
   }
-  w.table_off = __ldg(a.table_offsets + w.b);
+  w.table_off = table_off;
   return w;
 }
 

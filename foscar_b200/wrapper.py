@@ -303,7 +303,8 @@ class PagedDecodeWrapper:
 
         with _dev.on_device(self.device):
             if host_lens is not None and reduction != "none":
-                self._plan_balanced(host_lens, non_blocking)
+                host_offsets = indptr.detach().to("cpu", torch.int32)[:batch].contiguous().numpy()
+                self._plan_balanced(host_lens, host_offsets, non_blocking)
             else:
                 self._plan_uniform(kv_splits, reduction)
             self._status_ptr()
@@ -385,7 +386,11 @@ class PagedDecodeWrapper:
         else:
             self._unit_counters.zero_()
 
-    def _plan_balanced(self, host_lens, non_blocking):
+    # Rows of a planned piece list carry their request's length and table offset, so the kernel
+    # need not fetch them after the row (a dependent round trip less before a CTA's first tile).
+    carry_requests = True
+
+    def _plan_balanced(self, host_lens, host_offsets, non_blocking):
         lay, lib = self._layout, _lib.load()
         ht = _head_tiles(self._cols, lay.num_kv_heads)
         ctas = _dev.sm_count(self.device)
@@ -405,6 +410,10 @@ class PagedDecodeWrapper:
             return
         if pieces < 0:
             _lib.check(pieces, "plan")
+        if self.carry_requests:
+            _lib.check(lib.fq_worklist_attach_requests(work.ctypes.data, words, lens.ctypes.data,
+                                                       host_offsets.ctypes.data,
+                                                       self._batch_size), "plan")
         most = int(counts.max())
         self._kv_splits = most
         self._reduction = "kernel" if most > 1 else "none"
@@ -697,6 +706,7 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
                                * page_table.shape[1])
         total = words + units
         g = dict(words=words, units=units, ctas=ctas, ht=ht, cap=cap, lse=lse,
+                 offsets=np.arange(b, dtype=np.int32) * int(page_table.shape[1]),
                  q_descale=q_descale, stream=None, next_host=0,
                  host=[torch.empty(total, dtype=torch.int32).pin_memory()
                        for _ in range(_GRAPH_HOST_BUFFERS)],
@@ -721,6 +731,11 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
                                       buf[words:].ctypes.data, lay.bits, lay.head_dim)
         if pieces < 0:
             _lib.check(pieces, "update")
+        if self.carry_requests:
+            _lib.check(lib.fq_worklist_attach_requests(buf.ctypes.data, words,
+                                                       lengths.ctypes.data,
+                                                       g["offsets"].ctypes.data,
+                                                       self._batch_size), "update")
 
     def update(self, lengths) -> None:
         """Once per step, outside the graph and before its replay: plan the step from host

@@ -122,9 +122,11 @@ int fq_recount_vmax(const fq_pools* pools, void* stream);
  * A work item is (request, KV head, head tile, chunk of 128-token tiles). With worklist ==
  * NULL the items are implicit: every request is cut into `kv_splits` contiguous chunks by the
  * kernel from seq_lens. Otherwise worklist is the int32 list fq_plan_worklist writes: a header
- * {pieces, units, ctas, rows' word offset, 0...}, cta_start[ctas + 1] (padded to 8 words), then
- * one row per piece
+ * {pieces, units, ctas, rows' word offset, rows carry their request (0/1), 0...},
+ * cta_start[ctas + 1] (padded to 8 words), then one row per piece
  *   {request, kv_head, head_tile, tile_begin, tile_end, partial_slot, 0, 0}
+ * (the last two words: the request's length and table offset once
+ * fq_worklist_attach_requests has filled them in)
  * with partial_slot -1 = write the final output. CTA c runs rows [cta_start[c], cta_start[c+1]).
  * The header is read on the device, so a captured launch follows a list rewritten between
  * replays; launch with max_ctas = the plan's ctas.
@@ -262,6 +264,14 @@ int fq_plan_worklist(const int32_t* seq_lens, int32_t batch, int32_t num_kv_head
                      int32_t bits, int32_t head_dim);
 int64_t fq_worklist_words(int32_t batch, int32_t num_kv_heads, int32_t head_tiles,
                           int32_t num_ctas);
+/* Host-only, optional: write every row's request length and page-table offset into the row's
+ * two spare words (from host copies of seq_lens and table_offsets, [batch] each) and set header
+ * word 4, so that the kernel takes them from the row instead of from fq_decode_args.seq_lens /
+ * table_offsets: one dependent global round trip less before a CTA's first tile (about a
+ * microsecond of a launch that starts with a cold L2). The lengths given here then count, not
+ * the device array's; a list without the mark is read as before. No reference counterpart. */
+int fq_worklist_attach_requests(int32_t* worklist, int64_t words, const int32_t* seq_lens,
+                                const int32_t* table_offsets, int32_t batch);
 int fq_tile_tokens(int32_t bits, int32_t head_dim);
 int fq_piece_overhead(int32_t bits, int32_t head_dim);
 int64_t fq_workspace_bytes(int32_t max_splits, int32_t batch, int32_t num_qo_heads,

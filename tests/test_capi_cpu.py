@@ -111,6 +111,30 @@ def test_worklist_never_exceeds_the_split_cap(lens, hkv, ht, cap):
             assert a1 == b0
 
 
+def test_rows_take_their_requests_length_and_table_offset():
+    """fq_worklist_attach_requests fills every row's two spare words from host arrays and marks
+    the header; a list that is not passed through it keeps them 0."""
+    lib = _lib.load()
+    lens = [5000, 1, 70000]
+    n, work, counts = _plan(lens, 2, 1, 148)
+    rows = work[work[3]:work[3] + 8 * n].reshape(n, 8)
+    assert work[4] == 0 and not rows[:, 6:].any()
+    lens32 = np.asarray(lens, dtype=np.int32)
+    offsets = np.asarray([0, 79, 80], dtype=np.int32)
+    assert lib.fq_worklist_attach_requests(work.ctypes.data, len(work), lens32.ctypes.data,
+                                           offsets.ctypes.data, 3) == 0
+    assert work[4] == 1
+    assert np.array_equal(rows[:, 6], lens32[rows[:, 0]])
+    assert np.array_equal(rows[:, 7], offsets[rows[:, 0]])
+    # a batch smaller than the rows' requests, a buffer shorter than the list, missing arrays
+    assert lib.fq_worklist_attach_requests(work.ctypes.data, len(work), lens32.ctypes.data,
+                                           offsets.ctypes.data, 2) == _lib.ERR_BAD_ARG
+    assert lib.fq_worklist_attach_requests(work.ctypes.data, int(work[3]) + 8, lens32.ctypes.data,
+                                           offsets.ctypes.data, 3) == _lib.ERR_BAD_ARG
+    assert lib.fq_worklist_attach_requests(work.ctypes.data, len(work), None,
+                                           offsets.ctypes.data, 3) == _lib.ERR_BAD_ARG
+
+
 def test_worklist_refuses_a_short_buffer():
     lib = _lib.load()
     lens = np.array([100], dtype=np.int32)

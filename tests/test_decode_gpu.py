@@ -134,6 +134,37 @@ def test_outlier_keys_fp8_query_scale():
     _run_case(2, 128, 32, 8, [3000, 5000], outliers=True, q_scale=8.0, seed=5)
 
 
+@pytest.mark.parametrize("bits,d,hq,hkv", [(2, 128, 32, 8), (4, 64, 16, 2), (4, 256, 16, 2)])
+def test_rows_that_carry_their_request_change_nothing(bits, d, hq, hkv):
+    """A planned list whose rows carry the request's length and table offset (what plan() makes)
+    and one whose rows leave them to the device arrays (a C caller's list that was not passed
+    through fq_worklist_attach_requests) give the same bits."""
+    from foscar_b200 import PagedDecodeWrapper, QuantKVLayout
+    seq = [9000, 1, 333, 4097]
+    indptr, indices, slots, npages = paged_batch(seq, seed=13)
+    k, v = make_kv(len(slots), hkv, d, seed=13)
+    layout = QuantKVLayout.create(bits=bits, head_dim=d, num_kv_heads=hkv, device="cuda")
+    cache = layout.allocate(npages)
+    cache.append(k, v, torch.from_numpy(slots).cuda())
+    q = make_q(len(seq), hq, d)
+    outs, lses = [], []
+    for carry in (True, False):
+        w = PagedDecodeWrapper(torch.empty(64 << 20, dtype=torch.uint8, device="cuda"))
+        w.carry_requests = carry
+        w.plan(torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda(),
+               torch.tensor(seq, dtype=torch.int32), hq, layout)
+        header = w._worklist[:8].cpu()
+        assert int(header[4]) == int(carry)
+        out = torch.empty(len(seq), hq, d, dtype=torch.bfloat16, device="cuda")
+        lse = torch.empty(len(seq), hq, device="cuda")
+        w.run(q, cache, out=out, lse=lse)
+        torch.cuda.synchronize()
+        assert w.last_status() == 0
+        outs.append(out)
+        lses.append(lse)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(lses[0], lses[1])
+
+
 @pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
 def test_output_dtypes_and_descale(out_dtype):
     _run_case(4, 128, 16, 4, [300, 900], out_dtype=out_dtype, q_descale=True)

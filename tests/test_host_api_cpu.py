@@ -252,6 +252,7 @@ class _Recorder:
 
     def __getattr__(self, name):
         if name in ("fq_plan_splits", "fq_plan_worklist", "fq_worklist_words",
+                    "fq_worklist_attach_requests",
                     "fq_workspace_bytes", "fq_error_string", "fq_version"):
             return getattr(self.real, name)
 
