@@ -36,6 +36,7 @@ extern "C" int64_t fq_workspace_bytes(int32_t max_splits, int32_t batch, int32_t
 // 0.34 us per 128-token INT2 tile at head_dim 128).
 static long long piece_overhead(int bits, int head_dim) {
   long long ovh = bits == 4 && head_dim == 128 ? 10 : 14;
+  if (two_token_build(bits, head_dim)) ovh = 7;   // the same time in 256-token tiles
   if (const char* env = getenv("FOSCAR_B200_PIECE_OVERHEAD")) {   // tuning knob for experiments
     const int v = atoi(env);
     if (v >= 0 && v <= 256) ovh = v;

@@ -92,10 +92,10 @@ __device__ int* g_wait_profile = nullptr;
 namespace {
 
 // barrier words: the ring's 2*ns first, then the fixed ones
+template <int G>
 struct Bars {
   uint32_t base;
   int ns;
-  static constexpr int G = WORKER_GROUPS;
   __device__ uint32_t at(int i) const { return base + 8u * i; }
   __device__ uint32_t ring_full(int s) const { return at(s); }
   __device__ uint32_t ring_empty(int s) const { return at(ns + s); }
@@ -135,15 +135,18 @@ struct RingPos {
 // Tensor-memory column plan (f32 columns): per worker group one K operand stage (a 128-byte row
 // per lane at head_dim 64, where a lane holds two tokens), one S buffer of 16 columns and one O
 // buffer of 16 columns per token of a lane.
-template <int D>
+template <int BITS, int D>
 struct TmemPlan {
+  static constexpr int G = worker_groups(BITS, D);
   static constexpr bool PAIR = D == 64;
-  static constexpr int KOP_COLS = PAIR ? 32 : D / 4;
+  static constexpr bool TWO = two_token_build(BITS, D);   // two 128-byte rows, two S buffers
+  static constexpr int KOP_COLS = PAIR ? 32 : (TWO ? 2 : 1) * D / 4;
+  static constexpr int S_COLS = TWO ? 32 : 16;
   static constexpr int O_COLS = PAIR ? 32 : 16;
   static constexpr int KOP = 0;
-  static constexpr int S = WORKER_GROUPS * KOP_COLS;
-  static constexpr int O = S + WORKER_GROUPS * 16;
-  static constexpr int USED = O + WORKER_GROUPS * O_COLS;
+  static constexpr int S = G * KOP_COLS;
+  static constexpr int O = S + G * S_COLS;
+  static constexpr int USED = O + G * O_COLS;
   static constexpr int ALLOC = USED <= 128 ? 128 : (USED <= 256 ? 256 : 512);
   static_assert(USED <= 512, "tensor memory plan exceeds 512 columns");
 };
@@ -175,12 +178,12 @@ __device__ __noinline__ void mask_lagged_columns(const DecodeParams& P, int len,
 
 template <int BITS, int D, int GP, int KG, bool MQ>
 __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem, uint32_t smem0,
-                                            uint32_t tmem, const Bars& bars,
+                                            uint32_t tmem, const Bars<SmemPlan<BITS, D>::G>& bars,
                                             volatile int* abort_flag, const ItemRange items,
                                             int* wprof) {
   using SP = SmemPlan<BITS, D>;
-  using TP = TmemPlan<D>;
-  constexpr int G = WORKER_GROUPS;
+  using TP = TmemPlan<BITS, D>;
+  constexpr int G = SP::G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wg = warp >> 2, wq = warp & 3;
   const int t = threadIdx.x & 127;  // token row while unpacking and in softmax, channel in O
@@ -189,8 +192,8 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
   const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
   const uint32_t ring0 = smem0 + SP::RING_OFF;
   const uint32_t k_dst = tmem + lane_base + TP::KOP + wg * TP::KOP_COLS;
-  const uint32_t s_src = tmem + lane_base + TP::S + wg * 16;
-  constexpr int NT = SP::PAIR ? 2 : 1;   // tokens per lane
+  const uint32_t s_src = tmem + lane_base + TP::S + wg * TP::S_COLS;
+  constexpr int NT = SP::TT / TILE;   // tokens per lane
   // a lane's O columns: at two tokens per lane, rows 0-63 (warps 0, 1) hold the first token
   // set's channels and take its P columns, rows 64-127 the second's
   const uint32_t o_src = tmem + lane_base + TP::O + wg * TP::O_COLS + (SP::PAIR && wq >= 2 ? 16 : 0);
@@ -435,17 +438,22 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         }
         FQ_STAMP(6);
 #pragma unroll
-        for (int cc = 0; cc < NT * D / (((FQ_STUB_ROLES & 128) && BITS == 2) ? 32 : 16); ++cc) {
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(v_row + ((cc ^ (t & 7)) << 4)),
-                       "r"(op[4 * cc]), "r"(op[4 * cc + 1]), "r"(op[4 * cc + 2]),
-                       "r"(op[4 * cc + 3])
-                       : "memory");
+        for (int u = 0; u < NT; ++u) {   // token 128 u + t is row 128 u + t of the stage
+#pragma unroll
+          for (int cc = 0; cc < D / (((FQ_STUB_ROLES & 128) && BITS == 2) ? 32 : 16); ++cc) {
+            const int oc = u * (D / 16) + cc;
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
+                             v_row + u * TILE * SP::ROW + ((cc ^ (t & 7)) << 4)),
+                         "r"(op[4 * oc]), "r"(op[4 * oc + 1]), "r"(op[4 * oc + 2]),
+                         "r"(op[4 * oc + 3])
+                         : "memory");
+          }
         }
       }
       FQ_STAMP(9);
       // the tokens' records; then the ring stage goes back to the producers
       float sk[NT], zk[NT], sv[NT], zv[NT];
-      float sk1 = 0.f, zk1 = 0.f;   // the second K group's pair (KG == 2)
+      float sk1[NT] = {}, zk1[NT] = {};   // the second K group's pair (KG == 2)
 #pragma unroll
       for (int u = 0; u < NT; ++u) {
         const int row = u * TILE + t;
@@ -456,7 +464,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
                        : "r"(slot + (row & 63) * 8));
           asm volatile("ld.shared.u32 %0, [%1];" : "=r"(vr) : "r"(slot + 8 * PAGE + (row & 63) * 4));
           sk[u] = __uint_as_float(k0 << 16); zk[u] = __uint_as_float(k0 & 0xFFFF0000u);
-          sk1 = __uint_as_float(k1 << 16); zk1 = __uint_as_float(k1 & 0xFFFF0000u);
+          sk1[u] = __uint_as_float(k1 << 16); zk1[u] = __uint_as_float(k1 & 0xFFFF0000u);
           sv[u] = __uint_as_float(vr << 16); zv[u] = __uint_as_float(vr & 0xFFFF0000u);
         } else if constexpr (KG != 3) {   // KG == 1: f32 records; KG == 3: bf16 pairs
           asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
@@ -477,8 +485,18 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
       // ---- raw scores: columns [0, GP) for the lane's first token, [8, 8 + GP) for its second
       mbar_wait(bars.s_done(wg), n & 1, abort_flag, status, 12, wprof);
       tc_fence_after();
-      uint32_t raw[(NT == 2 || KG == 2) ? 16 : GP];
-      if constexpr (NT == 2 || KG == 2) tmem_ld16(s_src, raw);
+      // (two tokens with a 128-byte row each: a 16-column S buffer per token, RS apart in raw)
+      constexpr int RS = SP::TWO ? (KG == 2 ? 16 : 8) : 8;
+      uint32_t raw[SP::TWO ? 2 * RS : ((NT == 2 || KG == 2) ? 16 : GP)];
+      if constexpr (SP::TWO) {
+        if constexpr (KG == 2) {
+          tmem_ld16p(s_src, raw);
+          tmem_ld16p(s_src + 16, raw + 16);
+        } else {
+          tmem_ld8p(s_src, raw);
+          tmem_ld8p(s_src + 16, raw + 8);
+        }
+      } else if constexpr (NT == 2 || KG == 2) tmem_ld16(s_src, raw);
       else if constexpr (GP == 4) tmem_ld4(s_src, raw);
       else tmem_ld8(s_src, raw);
       tmem_ld_wait();
@@ -515,11 +533,11 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         for (int h = 0; h < GP; ++h) {
           float xv;
           if constexpr (KG == 2)
-            xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[h]),
-                      fmaf(head_k[h] * (sk1 * 512.f), __uint_as_float(raw[8 + h]),
-                           fmaf(head_k[8 + h], zk[u], head_k[16 + h] * zk1)));
+            xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[RS * u + h]),
+                      fmaf(head_k[h] * (sk1[u] * 512.f), __uint_as_float(raw[RS * u + 8 + h]),
+                           fmaf(head_k[8 + h], zk[u], head_k[16 + h] * zk1[u])));
           else
-            xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[8 * u + h]), head_k[8 + h] * zk[u]);
+            xv = fmaf(head_k[h] * a_k, __uint_as_float(raw[RS * u + h]), head_k[8 + h] * zk[u]);
           x[u][h] = valid ? xv : -INFINITY;
           over = fmaxf(over, x[u][h] - m[h]);
         }
@@ -760,23 +778,23 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 }  // namespace
 
 template <int BITS, int D, int GP, int KG, bool MQ>
-__global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeParams P) {
+__global__ void __launch_bounds__(decode_threads(BITS, D), 1) decode_kernel(const DecodeParams P) {
   // KG: 1 whole-head K with f32 records, 3 the same with bf16 pairs, 2 two 64-channel K groups
   static_assert(KG == 1 || KG == 3 || (KG == 2 && D == 128),
                 "K groups of 64 channels at head_dim 128");
   static_assert(D == 64 || D == 128, "this build tiles head_dim 64 and 128");
   using SP = SmemPlan<BITS, D>;
-  using TP = TmemPlan<D>;
-  constexpr int G = WORKER_GROUPS;
+  using TP = TmemPlan<BITS, D>;
+  constexpr int G = SP::G;
   constexpr int W_PRODUCER = 4 * G, W_S = W_PRODUCER + 1, W_PV = W_PRODUCER + 2,
                 W_PRODUCER2 = W_PRODUCER + 3;
-  static_assert(DECODE_THREADS == 32 * (W_PRODUCER2 + 1), "warp roles and block size disagree");
+  static_assert(decode_threads(BITS, D) == 32 * (W_PRODUCER2 + 1), "warp roles and block size disagree");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* const smem = smem_raw + (smem0 - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int NS = P.ring_stages;
-  Bars bars{smem0 + SP::BAR_OFF, NS};
+  Bars<G> bars{smem0 + SP::BAR_OFF, NS};
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SP::BAR_OFF + 1024);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SP::BAR_OFF + 1016);
   int* status = P.a.status;
@@ -1014,12 +1032,16 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
         for (int t = w.t0; t < w.t1; ++t) {
           mbar_wait(bars.k_ready(g), gph, abort_flag, status, 2, wprof);
           tc_fence_after();
-          const uint32_t sd = tmem + TP::S + g * 16;
-          const uint32_t ka = tmem + TP::KOP + g * TP::KOP_COLS;
-          umma_ts_c<Q_HI, IDESC_S, false>(sd, ka, q_lo);
+          // (with a 128-byte row per token, a chain and a 16-column S buffer per token)
 #pragma unroll
-          for (int k = 1; k < ((FQ_STUB_ROLES & 16) ? 1 : (SP::PAIR ? 2 : 1) * D / 32); ++k)
-            umma_ts_c<Q_HI, IDESC_S, true>(sd, ka + 8 * k, q_lo + 2 * k);
+          for (int u = 0; u < (SP::TWO ? 2 : 1); ++u) {
+            const uint32_t sd = tmem + TP::S + g * TP::S_COLS + 16 * u;
+            const uint32_t ka = tmem + TP::KOP + g * TP::KOP_COLS + (D / 4) * u;
+            umma_ts_c<Q_HI, IDESC_S, false>(sd, ka, q_lo);
+#pragma unroll
+            for (int k = 1; k < ((FQ_STUB_ROLES & 16) ? 1 : (SP::PAIR ? 2 : 1) * D / 32); ++k)
+              umma_ts_c<Q_HI, IDESC_S, true>(sd, ka + 8 * k, q_lo + 2 * k);
+          }
           tc_commit(bars.s_done(g));
           if (t == w.t1 - 1) tc_commit(bars.q_empty(qb));
           if (++g == G) { g = 0; gph ^= 1u; }
@@ -1051,7 +1073,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) decode_kernel(const DecodeP
             const uint32_t pu = p_lo + u * (TILE * 16 >> 4);
             umma_ss_c<V_HI, P_HI, IDESC_PV, false>(od + 16 * u, v_lo, pu);
 #pragma unroll
-            for (int k = 1; k < ((FQ_STUB_ROLES & 32) ? 1 : TILE / 32); ++k)
+            for (int k = 1; k < ((FQ_STUB_ROLES & 32) ? 1 : (SP::TWO ? 2 : 1) * TILE / 32); ++k)
               umma_ss_c<V_HI, P_HI, IDESC_PV, true>(od + 16 * u, v_lo + k * (32 * SP::ROW >> 4),
                                                     pu + k * (32 * 16 >> 4));
           }
@@ -1217,25 +1239,26 @@ static int device_sm_count() {
 template <int BITS, int D, int GP, int KG = 1, bool MQ = false>
 static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   using SP = SmemPlan<BITS, D>;
+  constexpr int THREADS = decode_threads(BITS, D);
   int stages = SP::max_ring_stages();
   if (stages > 20) stages = 20;
   if (const char* env = getenv("FOSCAR_B200_RING_STAGES")) {   // tuning knob for experiments
     const int want = atoi(env);
-    if (want >= WORKER_GROUPS && want < stages) stages = want;
+    if (want >= SP::G && want < stages) stages = want;
   }
   // An even ring: the two producers take alternate tiles, so with an even stage count a stage
   // always belongs to the same producer, which then sees every release of it. With an odd count
   // a producer meets a stage every second lap only and waits on a phase parity that an older,
   // still outstanding release also satisfies (a 5-stage ring hung on exactly that).
   stages &= ~1;
-  if (stages < WORKER_GROUPS) return FQ_ERR_UNSUPPORTED;  // a group steps the ring by one lap at most
+  if (stages < SP::G) return FQ_ERR_UNSUPPORTED;  // a group steps the ring by one lap at most
   P.ring_stages = stages;
   P.tile_tokens = SP::TT;
   P.wait_budget = P.a.wait_budget_cycles > 0 ? P.a.wait_budget_cycles : WAIT_BUDGET_CYCLES;
   // Shared memory the ring leaves over holds more decoded work items (32 bytes each), up to
   // one per thread of the CTA's start-up pass.
   const int spare = SMEM_LIMIT - 1024 - SP::RING_OFF - stages * SP::STAGE;
-  const int more = std::max(0, std::min(spare / 32, DECODE_THREADS - SP::ITEM_SLOTS));
+  const int more = std::max(0, std::min(spare / 32, THREADS - SP::ITEM_SLOTS));
   P.item_slots = SP::ITEM_SLOTS + more;
   const int smem = SP::RING_OFF + stages * SP::STAGE + more * 32 + 1024;
   static bool configured[64] = {};  // per (BITS, D, GP) instantiation and device
@@ -1254,7 +1277,7 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   if (P.a.flags & 1) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(DECODE_THREADS);
+    cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -1264,7 +1287,7 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
     cfg.numAttrs = 1;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, P));
   }
-  kernel<<<grid, DECODE_THREADS, smem, stream>>>(P);
+  kernel<<<grid, THREADS, smem, stream>>>(P);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -9,15 +9,33 @@ constexpr int TILE = 128;            // MMA rows: tensor-memory lanes, threads o
 // Tokens per sequence tile. head_dim 128: one token per lane (two pages). head_dim 64: two tokens
 // per lane, t and 128 + t of the tile (four pages): their 64-byte operand rows sit side by side
 // in one 128-byte row, so a tile of 256 tokens costs what a 128-token tile of head_dim 128 costs.
-__host__ __device__ constexpr int tile_tokens(int /*bits*/, int head_dim) {
-  return head_dim == 64 ? 256 : 128;
+// INT2 at head_dim 128 can be built the same way (-DFQ_INT2_TWO_TOKENS=1): two tokens per lane,
+// each with a 128-byte operand row and a score chain of its own, in three worker groups instead
+// of four (the V operand stage of 256 tokens is 32 KB a group), so that the per-tile waits,
+// barriers, tensor-memory round trips and the O accumulation are paid once per 256 tokens. It
+// passes the same tests and was measured no faster (long contexts +1 %, mixed batches +5 to
+// +14 %), so the build with one token per lane is the default.
+#ifndef FQ_INT2_TWO_TOKENS
+#define FQ_INT2_TWO_TOKENS 0
+#endif
+__host__ __device__ constexpr bool two_token_build(int bits, int head_dim) {
+  return FQ_INT2_TWO_TOKENS != 0 && bits == 2 && head_dim == 128;
+}
+__host__ __device__ constexpr int tile_tokens(int bits, int head_dim) {
+  return head_dim == 64 || two_token_build(bits, head_dim) ? 256 : 128;
 }
 constexpr int WORK_WORDS = 8;        // int32 words per explicit work-list row
 #ifndef FQ_WORKER_GROUPS
 #define FQ_WORKER_GROUPS 4
 #endif
 constexpr int WORKER_GROUPS = FQ_WORKER_GROUPS;  // 128-thread groups, tile i -> group i % G
-constexpr int DECODE_THREADS = 32 * (4 * WORKER_GROUPS + 4);  // + 2 producers + 2 MMA issuers
+__host__ __device__ constexpr int worker_groups(int bits, int head_dim) {
+  return two_token_build(bits, head_dim) ? 3 : WORKER_GROUPS;
+}
+// + 2 producers + 2 MMA issuers
+__host__ __device__ constexpr int decode_threads(int bits, int head_dim) {
+  return 32 * (4 * worker_groups(bits, head_dim) + 4);
+}
 constexpr int SMEM_LIMIT = 232448;   // 227 KiB opt-in limit per CTA on sm_100
 
 struct DecodeParams {
@@ -96,7 +114,9 @@ struct SmemPlan {
     return CHUNKS == 4 ? (row >> 1) & 3 : (CHUNKS == 2 ? (row >> 2) & 1 : 0);
   }
   static constexpr int TT = tile_tokens(BITS, D);      // tokens per tile
-  static constexpr bool PAIR = TT == 2 * TILE;         // two tokens per lane
+  static constexpr int G = worker_groups(BITS, D);     // worker groups of this build
+  static constexpr bool PAIR = D == 64;                // two tokens per lane, rows side by side
+  static constexpr bool TWO = TT == 2 * TILE && !PAIR; // two tokens per lane, a row each
   static constexpr int PPT = TT / PAGE;                // pages per tile
   static constexpr int K_OFF = 0;                      // a ring stage: K pages, V pages, records
   static constexpr int V_OFF = PPT * CODE_PAGE;
@@ -105,12 +125,12 @@ struct SmemPlan {
   // Operand rows keep a 128-byte pitch (the swizzle atom) whatever D <= 128: head_dim 64 uses
   // the first half of each row.
   static constexpr int ROW = 128;
-  static constexpr int VOP_STAGE = TILE * ROW;         // expanded V operand, one tile
+  static constexpr int VOP_STAGE = (TWO ? 2 : 1) * TILE * ROW;   // expanded V operand, one tile
   static constexpr int Q_BYTES = 16 * ROW;             // 16 MMA rows
   static constexpr int P_BYTES = TT * 16;              // 16 bytes (8 hi + 8 lo) per token, a
                                                        // plane of 128 rows per token of a lane
   static constexpr int VOP_OFF = 0;
-  static constexpr int Q_OFF = VOP_OFF + WORKER_GROUPS * VOP_STAGE;
+  static constexpr int Q_OFF = VOP_OFF + G * VOP_STAGE;
   static constexpr int P_OFF = Q_OFF + 2 * Q_BYTES;
   // A group's state at the end of a work item (accumulators + (m,l,c), 4224 bytes) goes into the
   // group's own V operand stage: its last PV MMA is complete by then, every group has read the
@@ -119,12 +139,12 @@ struct SmemPlan {
   static constexpr int XCHG_OFF = VOP_OFF;
   static constexpr int XCHG_STRIDE = VOP_STAGE;
   static_assert(XCHG_BYTES <= VOP_STAGE, "a group's state must fit its V stage");
-  static constexpr int RED_OFF = P_OFF + WORKER_GROUPS * P_BYTES;  // reductions
+  static constexpr int RED_OFF = P_OFF + G * P_BYTES;  // reductions
   // column maxima 256 B and sums 256 B per group; then 96 B of per-head constants per worker
   // warp (score scale, and score scale times the query sum of each K group); two 16-byte merge
   // notices; two items' per-head constants as the producer leaves them (2 x 96 B)
-  static constexpr int HEADK_OFF = RED_OFF + 512 * WORKER_GROUPS;
-  static constexpr int INFO_OFF = HEADK_OFF + 96 * 4 * WORKER_GROUPS;
+  static constexpr int HEADK_OFF = RED_OFF + 512 * G;
+  static constexpr int INFO_OFF = HEADK_OFF + 96 * 4 * G;
   static constexpr int HEADC_OFF = INFO_OFF + 32;
   static constexpr int RED_BYTES = (HEADC_OFF + 192 - RED_OFF + 1023) / 1024 * 1024;
   static constexpr int BAR_OFF = RED_OFF + RED_BYTES;
