@@ -76,7 +76,8 @@
 // arrival stays (1 softmax, 2 K unpack, 4 V unpack, 8 producers' copies; 16 / 32: one S / PV MMA
 // per tile instead of four; 64 / 128: the INT2 K / V unpack at the instruction count of a 4-bit
 // operand feed, i.e. two masks and a shift per packed word and half the operand words stored,
-// at head_dim 128). The output is
+// at head_dim 128; 256 / 512: one of a row's eight V operand stores / four K operand stores
+// only). The output is
 // then meaningless; the launch time and instruction count show what each role costs.
 #ifndef FQ_STUB_ROLES
 #define FQ_STUB_ROLES 0
@@ -371,7 +372,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
           tc_fence_after();
 #pragma unroll
           for (int v = 0; v < NT * D / (((FQ_STUB_ROLES & 64) && BITS == 2) ? 64 : 32); ++v)
-            tmem_st8(k_dst + 8 * v, op + 8 * v);
+            if (!(FQ_STUB_ROLES & 512) || v == 0) tmem_st8(k_dst + 8 * v, op + 8 * v);
         }
         tmem_st_wait();
         FQ_STAMP(5);
@@ -441,6 +442,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
         for (int u = 0; u < NT; ++u) {   // token 128 u + t is row 128 u + t of the stage
 #pragma unroll
           for (int cc = 0; cc < D / (((FQ_STUB_ROLES & 128) && BITS == 2) ? 32 : 16); ++cc) {
+            if ((FQ_STUB_ROLES & 256) && cc > 0) continue;
             const int oc = u * (D / 16) + cc;
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
                              v_row + u * TILE * SP::ROW + ((cc ^ (t & 7)) << 4)),
