@@ -28,6 +28,14 @@ def tile_tokens(bits: int, head_dim: int) -> int:
     return int(n)
 
 
+def ctas_per_sm(bits: int, head_dim: int) -> int:
+    """CTAs of the decode kernel's build for (bits, head_dim) that share an SM (1 or 2)."""
+    n = load().fq_ctas_per_sm(bits, head_dim)
+    if n < 0:
+        check(n, "ctas_per_sm")
+    return int(n)
+
+
 def piece_overhead(bits: int, head_dim: int) -> int:
     """Fixed cost of a work piece in tile units, as the balanced planner counts it."""
     n = load().fq_piece_overhead(bits, head_dim)
@@ -87,6 +95,7 @@ _PROTOTYPES = {
     "fq_worklist_words": (_I64, [_I32, _I32, _I32, _I32]),
     "fq_worklist_attach_requests": (C.c_int, [_P, _I64, _P, _P, _I32]),
     "fq_umma_selftest": (C.c_int, [_I32, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "fq_ctas_per_sm": (C.c_int, [_I32, _I32]),
     "fq_tile_tokens": (C.c_int, [_I32, _I32]),
     "fq_piece_overhead": (C.c_int, [_I32, _I32]),
     "fq_wait_selftest": (C.c_int, [_I64, _P, _P, _P]),

@@ -780,7 +780,7 @@ __device__ __forceinline__ void worker_role(const DecodeParams& P, uint8_t* smem
 }  // namespace
 
 template <int BITS, int D, int GP, int KG, bool MQ>
-__global__ void __launch_bounds__(decode_threads(BITS, D), 1) decode_kernel(const DecodeParams P) {
+__global__ void __launch_bounds__(decode_threads(BITS, D), ctas_per_sm(BITS, D)) decode_kernel(const DecodeParams P) {
   // KG: 1 whole-head K with f32 records, 3 the same with bf16 pairs, 2 two 64-channel K groups
   static_assert(KG == 1 || KG == 3 || (KG == 2 && D == 128),
                 "K groups of 64 channels at head_dim 128");
@@ -1259,7 +1259,8 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   P.wait_budget = P.a.wait_budget_cycles > 0 ? P.a.wait_budget_cycles : WAIT_BUDGET_CYCLES;
   // Shared memory the ring leaves over holds more decoded work items (32 bytes each), up to
   // one per thread of the CTA's start-up pass.
-  const int spare = SMEM_LIMIT - 1024 - SP::RING_OFF - stages * SP::STAGE;
+  constexpr int LIMIT = smem_limit(BITS, D);
+  const int spare = LIMIT - 1024 - SP::RING_OFF - stages * SP::STAGE;
   const int more = std::max(0, std::min(spare / 32, THREADS - SP::ITEM_SLOTS));
   P.item_slots = SP::ITEM_SLOTS + more;
   const int smem = SP::RING_OFF + stages * SP::STAGE + more * 32 + 1024;
@@ -1269,11 +1270,11 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SMEM_LIMIT);
+                                         LIMIT);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  int ctas = P.a.max_ctas > 0 ? P.a.max_ctas : device_sm_count();
+  int ctas = P.a.max_ctas > 0 ? P.a.max_ctas : device_sm_count() * ctas_per_sm(BITS, D);
   int grid = P.a.worklist ? ctas : std::min(ctas, P.num_items);
   if (grid < 1) grid = 1;
   if (P.a.flags & 1) {
@@ -1297,6 +1298,12 @@ static int launch_decode(DecodeParams& P, cudaStream_t stream) {
 
 
 using namespace fq;
+
+extern "C" int fq_ctas_per_sm(int32_t bits, int32_t head_dim) {
+  if ((bits != 2 && bits != 4) || (head_dim != 64 && head_dim != 128 && head_dim != 256))
+    return FQ_ERR_UNSUPPORTED;
+  return head_dim == 256 ? 1 : ctas_per_sm(bits, head_dim);
+}
 
 extern "C" int fq_tile_tokens(int32_t bits, int32_t head_dim) {
   if ((bits != 2 && bits != 4) || (head_dim != 64 && head_dim != 128 && head_dim != 256))

@@ -29,14 +29,29 @@ constexpr int WORK_WORDS = 8;        // int32 words per explicit work-list row
 #define FQ_WORKER_GROUPS 4
 #endif
 constexpr int WORKER_GROUPS = FQ_WORKER_GROUPS;  // 128-thread groups, tile i -> group i % G
+// Two CTAs of two worker groups each per SM instead of one CTA of four (-DFQ_INT2_TWO_CTAS=1,
+// the INT2 builds): the CTAs' item epilogues and prologues overlap each other's tiles; each gets
+// half the shared memory (the INT4 rings would be too shallow). Measured 16 to 31 % slower than
+// one CTA of four groups on every workload tried, so it is off.
+#ifndef FQ_INT2_TWO_CTAS
+#define FQ_INT2_TWO_CTAS 0
+#endif
+__host__ __device__ constexpr int ctas_per_sm(int bits, int head_dim) {
+  return FQ_INT2_TWO_CTAS != 0 && bits == 2 && head_dim <= 128 && !two_token_build(bits, head_dim)
+             ? 2 : 1;
+}
 __host__ __device__ constexpr int worker_groups(int bits, int head_dim) {
-  return two_token_build(bits, head_dim) ? 3 : WORKER_GROUPS;
+  return two_token_build(bits, head_dim) ? 3 : (ctas_per_sm(bits, head_dim) == 2 ? 2 : WORKER_GROUPS);
 }
 // + 2 producers + 2 MMA issuers
 __host__ __device__ constexpr int decode_threads(int bits, int head_dim) {
   return 32 * (4 * worker_groups(bits, head_dim) + 4);
 }
 constexpr int SMEM_LIMIT = 232448;   // 227 KiB opt-in limit per CTA on sm_100
+// (two CTAs per SM: half of the SM's 228 KiB less the KiB the system keeps per CTA)
+__host__ __device__ constexpr int smem_limit(int bits, int head_dim) {
+  return ctas_per_sm(bits, head_dim) == 2 ? 115712 : SMEM_LIMIT;
+}
 
 struct DecodeParams {
   fq_pools p;
@@ -154,7 +169,7 @@ struct SmemPlan {
   static constexpr int ITEM_SLOTS = (BAR_BYTES - 1280) / 32;
   static constexpr int RING_OFF = (BAR_OFF + BAR_BYTES + 1023) / 1024 * 1024;
   static constexpr int max_ring_stages() {
-    return (SMEM_LIMIT - 1024 /*alignment slack*/ - RING_OFF) / STAGE;
+    return (smem_limit(BITS, D) - 1024 /*alignment slack*/ - RING_OFF) / STAGE;
   }
 };
 

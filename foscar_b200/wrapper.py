@@ -116,7 +116,7 @@ def graph_workspace_bytes(max_batch: int, num_qo_heads: int, layout: QuantKVLayo
     if layout.arch != arch:
         raise ValueError(f"the layout was resolved for {layout.arch} and {dev} is {arch}")
     _check_num_qo_heads(num_qo_heads, layout.num_kv_heads)
-    sms = _dev.sm_count(dev)
+    sms = _dev.sm_count(dev) * _lib.ctas_per_sm(layout.bits, layout.head_dim)
     tiles = -(-int(max_kv_len) // _lib.tile_tokens(layout.bits, layout.head_dim))
     ovh = _lib.piece_overhead(layout.bits, layout.head_dim)
     words = 0
@@ -356,7 +356,8 @@ class PagedDecodeWrapper:
         if kv_splits is None or kv_splits <= 0:
             kv_splits = _lib.load().fq_plan_splits(
                 self._batch_size, lay.num_kv_heads, _head_tiles(self._cols, lay.num_kv_heads),
-                self._max_kv_len, lay.bits, lay.head_dim, _dev.sm_count(self.device))
+                self._max_kv_len, lay.bits, lay.head_dim,
+                _dev.sm_count(self.device) * _lib.ctas_per_sm(lay.bits, lay.head_dim))
             if kv_splits < 1:
                 _lib.check(kv_splits, "plan")
             if reduction == "none":
@@ -393,7 +394,7 @@ class PagedDecodeWrapper:
     def _plan_balanced(self, host_lens, host_offsets, non_blocking):
         lay, lib = self._layout, _lib.load()
         ht = _head_tiles(self._cols, lay.num_kv_heads)
-        ctas = _dev.sm_count(self.device)
+        ctas = _dev.sm_count(self.device) * _lib.ctas_per_sm(lay.bits, lay.head_dim)
         units = self._batch_size * lay.num_kv_heads * ht
         words = int(lib.fq_worklist_words(self._batch_size, lay.num_kv_heads, ht, ctas))
         cap = _fit_splits(self._float_workspace_buffer, self._batch_size, self._cols,
@@ -686,7 +687,7 @@ class _GraphDecodeWrapper(PagedDecodeWrapper):
         lay, lib = self._layout, _lib.load()
         b, hq, d = self._batch_size, self._cols, self._head_dim
         ht = _head_tiles(hq, lay.num_kv_heads)
-        ctas = _dev.sm_count(self.device)
+        ctas = _dev.sm_count(self.device) * _lib.ctas_per_sm(lay.bits, lay.head_dim)
         units = b * lay.num_kv_heads * ht
         words = int(lib.fq_worklist_words(b, lay.num_kv_heads, ht, ctas))
         tiles = -(-self._max_kv_len // _lib.tile_tokens(lay.bits, d))

@@ -273,6 +273,9 @@ int64_t fq_worklist_words(int32_t batch, int32_t num_kv_heads, int32_t head_tile
 int fq_worklist_attach_requests(int32_t* worklist, int64_t words, const int32_t* seq_lens,
                                 const int32_t* table_offsets, int32_t batch);
 int fq_tile_tokens(int32_t bits, int32_t head_dim);
+/* CTAs of the decode kernel that share an SM in this build of the library (1 or 2): a planner
+ * gives fq_plan_worklist / fq_plan_splits that many times the device's SM count. */
+int fq_ctas_per_sm(int32_t bits, int32_t head_dim);
 int fq_piece_overhead(int32_t bits, int32_t head_dim);
 int64_t fq_workspace_bytes(int32_t max_splits, int32_t batch, int32_t num_qo_heads,
                            int32_t head_dim);

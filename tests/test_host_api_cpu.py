@@ -252,7 +252,8 @@ class _Recorder:
 
     def __getattr__(self, name):
         if name in ("fq_plan_splits", "fq_plan_worklist", "fq_worklist_words",
-                    "fq_worklist_attach_requests",
+                    "fq_worklist_attach_requests", "fq_ctas_per_sm", "fq_tile_tokens",
+                    "fq_piece_overhead",
                     "fq_workspace_bytes", "fq_error_string", "fq_version"):
             return getattr(self.real, name)
 
